@@ -1,0 +1,147 @@
+/*
+ * kernl_b200 — C ABI of the B200 (sm_100a) fused transformer-inference kernels.
+ *
+ * Every entry point is asynchronous on the CUDA stream it is given, allocates nothing,
+ * never synchronises the device (except kb_device_status_read) and returns a KB_* status.
+ * Pointers are device pointers unless stated otherwise. Strides are in ELEMENTS.
+ * `stream` is a cudaStream_t passed as void* so that this header needs no CUDA include.
+ *
+ * Each function cites the interface of the reference project (ELS-RD/kernl) that it
+ * replaces, as <file>:<line> relative to that project's root.
+ */
+#ifndef KERNL_B200_H
+#define KERNL_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes -------------------------------------------------------------------- */
+#define KB_OK               0
+#define KB_ERR_BAD_ARG     (-1)  /* null pointer, negative size, bad enum                   */
+#define KB_ERR_UNSUPPORTED (-2)  /* shape/stride/dtype outside what the kernels implement   */
+#define KB_ERR_LAUNCH      (-3)  /* CUDA runtime/driver reported an error at launch         */
+#define KB_ERR_TIMEOUT     (-4)  /* a bounded device-side wait expired (see status word)    */
+#define KB_ERR_NO_DEVICE   (-5)  /* no CUDA device / not an sm_100 device                   */
+#define KB_ERR_TOO_LARGE   (-6)  /* size beyond a documented fixed maximum                  */
+
+/* ---- element types ------------------------------------------------------------------- */
+#define KB_F16  0
+#define KB_BF16 1
+#define KB_F32  2   /* accepted for attention masks only */
+
+/* ---- activations fused in the linear epilogue.
+ * Reference: src/kernl/implementations/activation_func.py:28-49 (tanh, relu, fast_gelu, gelu);
+ * SILU has no counterpart there (needed by the Llama-shaped decoder). ---------------------- */
+#define KB_ACT_NONE      0
+#define KB_ACT_TANH      1
+#define KB_ACT_GELU      2   /* exact erf form  */
+#define KB_ACT_FAST_GELU 3   /* tanh approximation */
+#define KB_ACT_RELU      4
+#define KB_ACT_SILU      5
+
+/* ---------------------------------------------------------------------------------------
+ * LayerNorm / RMSNorm forward.
+ * Replaces: src/kernl/implementations/layer_norm.py:279-335 (LayerNorm.forward launching
+ * _layer_norm_fwd_fused_single_pass, :114-205).
+ *   y[r,c] = (x[r,c]-mean_r) * rstd_r * gamma[c] + beta[c]         (is_rms == 0)
+ *   y[r,c] =  x[r,c] * rsqrt(mean(x_r^2)+eps) * gamma[c]           (is_rms != 0, beta unused)
+ * Statistics are computed in fp32 with the biased variance. The fp16 eps clamp
+ * (eps = max(eps, 1.6e-5), layer_norm.py:295-296) is the CALLER's job: eps is used as given.
+ * mean / rstd are optional fp32 [rows] side outputs (NULL to skip).
+ * ------------------------------------------------------------------------------------- */
+typedef struct {
+    const void* x;          /* [rows, cols], strides x_row_stride / x_col_stride          */
+    void*       y;          /* [rows, cols], strides y_row_stride / y_col_stride          */
+    const void* gamma;      /* [cols] contiguous                                          */
+    const void* beta;       /* [cols] contiguous or NULL                                  */
+    float*      mean;       /* [rows] or NULL                                             */
+    float*      rstd;       /* [rows] or NULL                                             */
+    int64_t     rows, cols;
+    int64_t     x_row_stride, x_col_stride;
+    int64_t     y_row_stride, y_col_stride;
+    float       eps;
+    int32_t     is_rms;
+    int32_t     dtype;      /* KB_F16 / KB_BF16 (x, y, gamma, beta share it)              */
+} kb_norm_params;
+
+int kb_norm_fwd(const kb_norm_params* p, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Fused linear: y = act(x · Wᵀ + bias), fp32 accumulation on tcgen05 tensor cores.
+ * Replaces: src/kernl/implementations/linear_layer.py:213-282 (LinearLayer.forward launching
+ * kernel_fma, :91-210). W is [N,K] contiguous (linear_layer.py:244); x is [M,K] with unit K
+ * stride and a row stride that is a multiple of 8 elements; K must be a multiple of 8.
+ * act_inputs (optional, [M,N], row stride = y_row_stride) receives the pre-activation values
+ * (linear_layer.py:193-195).
+ * ------------------------------------------------------------------------------------- */
+typedef struct {
+    const void* x;          /* [M,K]                                                       */
+    const void* w;          /* [N,K] contiguous                                            */
+    const void* bias;       /* [N] or NULL                                                 */
+    void*       y;          /* [M,N]                                                       */
+    void*       act_inputs; /* [M,N] or NULL                                               */
+    int64_t     M, N, K;
+    int64_t     x_row_stride;
+    int64_t     y_row_stride;
+    int32_t     activation; /* KB_ACT_*                                                    */
+    int32_t     dtype;      /* KB_F16 / KB_BF16                                            */
+} kb_linear_params;
+
+int kb_linear_fwd(const kb_linear_params* p, void* stream);
+
+/* Gated linear unit for SwiGLU feed-forward blocks: y[m,n] = silu(g[m,n]) * u[m,n], where
+ * gu = [M, 2*N] holds g in columns [0,N) and u in columns [N,2N). No counterpart in the
+ * reference's dispatched path; semantics follow experimental/llama-v2/kernel/fused_kernel_ff.py:10-114. */
+int kb_silu_mul(const void* gu, void* y, int64_t M, int64_t N, int32_t dtype, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Fused attention forward: O = softmax(sm_scale · Q·Kᵀ + mask [causal]) · V, online softmax.
+ * Replaces: src/kernl/implementations/attention.py:438-529 (Attention.forward launching
+ * _fwd_kernel, :122-435).
+ *   q [B,H,M,D], k/v [B,H,N,D], o [B,H,M,D]; D in {64,128}; unit D stride required for q,k,v,o;
+ *   the other q/k/v strides must be multiples of 8 elements.
+ *   mask: additive, logical shape [B|1, H|1, M|1, N]; a broadcast dimension is passed with
+ *   stride 0. -inf entries are clamped to the lowest finite value of mask_dtype
+ *   (attention.py:380,516). is_causal keeps col <= row, top-left aligned (attention.py:347).
+ * ------------------------------------------------------------------------------------- */
+typedef struct {
+    const void* q; const void* k; const void* v; void* o;
+    const void* mask;        /* or NULL                                                    */
+    int64_t B, H, M, N, D;
+    int64_t q_strides[4];    /* batch, head, row, dim                                      */
+    int64_t k_strides[4];
+    int64_t v_strides[4];
+    int64_t o_strides[4];
+    int64_t mask_strides[4]; /* batch, head, row, col ; 0 = broadcast                       */
+    float   sm_scale;
+    int32_t is_causal;
+    int32_t dtype;           /* KB_F16 / KB_BF16 for q,k,v,o                               */
+    int32_t mask_dtype;      /* KB_F16 / KB_BF16 / KB_F32                                  */
+} kb_attn_params;
+
+int kb_attention_fwd(const kb_attn_params* p, void* stream);
+
+/* Decode-shape ("skinny") attention: few query rows, many keys; the keys are split into
+ * chunks handled by different CTAs and merged with the online-softmax recurrence.
+ * Replaces: src/kernl/implementations/attention_skinny.py:369-536 (SkinnyAttention.forward
+ * launching _fwd_part_1 :58-272 and _fwd_part_2 :275-366). Same tensor conventions as
+ * kb_attention_fwd but arbitrary strides. `scratch` must hold kb_attention_decode_scratch_bytes()
+ * bytes; it needs no initialisation. */
+int64_t kb_attention_decode_scratch_bytes(int64_t B, int64_t H, int64_t M, int64_t N, int64_t D);
+int kb_attention_decode_fwd(const kb_attn_params* p, void* scratch, int64_t scratch_bytes, void* stream);
+
+/* ---- device status word ---------------------------------------------------------------
+ * Kernels with bounded waits record a non-zero code here instead of trapping or hanging.
+ * kb_device_status_read synchronises the current device, returns the word and clears it. */
+int kb_device_status_read(int32_t* status_out);
+
+const char* kb_status_str(int status);
+int kb_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KERNL_B200_H */

@@ -1,0 +1,132 @@
+"""ctypes binding of libkernl_b200.so (the C ABI declared in include/kernl_b200.h).
+
+There is no fallback: if the library is missing or a kernel reports an error, the caller gets an
+exception. The library itself loads without a GPU (it links the CUDA runtime statically), which
+lets CPU-only checks verify the exported symbols.
+"""
+import ctypes
+import os
+from ctypes import POINTER, Structure, c_float, c_int32, c_int64, c_void_p
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libkernl_b200.so")
+
+KB_OK = 0
+KB_F16, KB_BF16, KB_F32 = 0, 1, 2
+ACTIVATIONS = {"": 0, None: 0, "tanh": 1, "gelu": 2, "fast_gelu": 3, "relu": 4, "silu": 5}
+
+EXPORTED_SYMBOLS = [
+    "kb_norm_fwd",
+    "kb_linear_fwd",
+    "kb_silu_mul",
+    "kb_attention_fwd",
+    "kb_attention_decode_scratch_bytes",
+    "kb_attention_decode_fwd",
+    "kb_device_status_read",
+    "kb_status_str",
+    "kb_version",
+]
+
+
+class NormParams(Structure):
+    _fields_ = [
+        ("x", c_void_p), ("y", c_void_p), ("gamma", c_void_p), ("beta", c_void_p),
+        ("mean", c_void_p), ("rstd", c_void_p),
+        ("rows", c_int64), ("cols", c_int64),
+        ("x_row_stride", c_int64), ("x_col_stride", c_int64),
+        ("y_row_stride", c_int64), ("y_col_stride", c_int64),
+        ("eps", c_float), ("is_rms", c_int32), ("dtype", c_int32),
+    ]
+
+
+class LinearParams(Structure):
+    _fields_ = [
+        ("x", c_void_p), ("w", c_void_p), ("bias", c_void_p), ("y", c_void_p), ("act_inputs", c_void_p),
+        ("M", c_int64), ("N", c_int64), ("K", c_int64),
+        ("x_row_stride", c_int64), ("y_row_stride", c_int64),
+        ("activation", c_int32), ("dtype", c_int32),
+    ]
+
+
+class AttnParams(Structure):
+    _fields_ = [
+        ("q", c_void_p), ("k", c_void_p), ("v", c_void_p), ("o", c_void_p), ("mask", c_void_p),
+        ("B", c_int64), ("H", c_int64), ("M", c_int64), ("N", c_int64), ("D", c_int64),
+        ("q_strides", c_int64 * 4), ("k_strides", c_int64 * 4), ("v_strides", c_int64 * 4),
+        ("o_strides", c_int64 * 4), ("mask_strides", c_int64 * 4),
+        ("sm_scale", c_float), ("is_causal", c_int32), ("dtype", c_int32), ("mask_dtype", c_int32),
+    ]
+
+
+_lib = None
+
+
+def load() -> ctypes.CDLL:
+    """Load the CUDA library once; raise if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python -m kernl_b200.build` (needs nvcc). "
+            "kernl_b200 has no CPU or PyTorch fallback."
+        )
+    lib = ctypes.CDLL(LIB_PATH)
+    lib.kb_norm_fwd.argtypes = [POINTER(NormParams), c_void_p]
+    lib.kb_norm_fwd.restype = ctypes.c_int
+    lib.kb_linear_fwd.argtypes = [POINTER(LinearParams), c_void_p]
+    lib.kb_linear_fwd.restype = ctypes.c_int
+    lib.kb_silu_mul.argtypes = [c_void_p, c_void_p, c_int64, c_int64, c_int32, c_void_p]
+    lib.kb_silu_mul.restype = ctypes.c_int
+    lib.kb_attention_fwd.argtypes = [POINTER(AttnParams), c_void_p]
+    lib.kb_attention_fwd.restype = ctypes.c_int
+    lib.kb_attention_decode_scratch_bytes.argtypes = [c_int64] * 5
+    lib.kb_attention_decode_scratch_bytes.restype = c_int64
+    lib.kb_attention_decode_fwd.argtypes = [POINTER(AttnParams), c_void_p, c_int64, c_void_p]
+    lib.kb_attention_decode_fwd.restype = ctypes.c_int
+    lib.kb_device_status_read.argtypes = [POINTER(c_int32)]
+    lib.kb_device_status_read.restype = ctypes.c_int
+    lib.kb_status_str.argtypes = [ctypes.c_int]
+    lib.kb_status_str.restype = ctypes.c_char_p
+    lib.kb_version.restype = ctypes.c_int
+    if hasattr(lib, "kb_debug_force_bn"):
+        lib.kb_debug_force_bn.argtypes = [ctypes.c_int]
+        lib.kb_debug_force_bn.restype = None
+    _lib = lib
+    return lib
+
+
+def status_str(status: int) -> str:
+    return load().kb_status_str(status).decode()
+
+
+def check(status: int, what: str) -> None:
+    if status != KB_OK:
+        raise RuntimeError(f"kernl_b200: {what} failed: {status_str(status)} (status {status})")
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    if dtype == torch.float16:
+        return KB_F16
+    if dtype == torch.bfloat16:
+        return KB_BF16
+    if dtype == torch.float32:
+        return KB_F32
+    raise AssertionError(f"unsupported dtype {dtype}")
+
+
+def current_stream(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def device_status() -> list:
+    """Synchronise the device and return (and clear) the kernels' status word; raises when a
+    bounded device-side wait expired."""
+    out = (c_int32 * 4)()
+    st = load().kb_device_status_read(out)
+    vals = list(out)
+    if st != KB_OK:
+        raise RuntimeError(f"kernl_b200 device status: {status_str(st)}; word = {vals}")
+    return vals

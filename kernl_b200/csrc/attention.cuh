@@ -1,0 +1,468 @@
+// Fused attention forward for sm_100a: O = softmax(sm_scale·Q·Kᵀ + mask [causal]) · V.
+//
+// One CTA owns TWO query tiles of 128 rows of one (batch, head) and streams the keys/values in
+// blocks of 128. Roles (384 threads = 3 warpgroups):
+//   warps 0..3    softmax group of tile 0 (one query row per thread)
+//   warps 4..7    softmax group of tile 1
+//   warp 8        TMA producer: both Q tiles once, then the K and V blocks through two small rings
+//   warp 9        tcgen05 issuer (one elected thread):  S_t = Q_t·K_jᵀ  (operands in shared memory)
+//                 and  O_t += P_t·V_j  (P read from TMEM, V from shared memory, N-major)
+//   warps 10..11  idle (they only give their registers away)
+// The third warpgroup shrinks its register allowance (setmaxnreg) so that the softmax threads can
+// hold a whole 128-wide score row in registers.
+// While one group runs its exponentials, the tensor core works on the other tile (ping-pong).
+// TMEM columns: S_0 [0,128)  S_1 [128,256)  O_0 [256,256+D)  O_1 [384,384+D); P_t (16-bit, two
+// per column) overwrites the first 64 columns of S_t once the thread has its row in registers.
+//
+// Online softmax in the log2 domain with LAZY rescaling: the running reference maximum of a row
+// only moves (and O is only rescaled in TMEM) when the true maximum has grown by more than 2^8,
+// so P stays below 256 — exactly representable range for fp16/bf16 — and most iterations skip
+// the O round trip. The final O is divided by the fp32 row sum.
+//
+// Semantics follow src/kernl/implementations/attention.py:122-435 of the reference: scale before
+// mask (:345), additive mask with -inf clamped to the lowest finite value of the mask's dtype
+// (:380,:516), causal = keep col <= row, top-left aligned (:347), P rounded to the input dtype
+// before P·V (:424), fp32 statistics and accumulation (:290-295).
+#pragma once
+#include "common.cuh"
+
+namespace kb {
+
+constexpr int kAttnThreads = 384;
+constexpr int kAttnBlock = 128;  // rows per query tile and keys per block
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLazyThreshold = 8.0f;
+
+struct AttnDev {
+    void* o;
+    const void* mask;
+    int64_t o_strides[4];
+    int64_t mask_strides[4];
+    int B, H, M, N;
+    float scale_log2;  // sm_scale * log2(e)
+    int is_causal;
+    int mask_dtype;
+    int num_pairs;  // ceil(ceil(M/128)/2)
+};
+
+template <int D>
+struct AttnCfg {
+    static constexpr int kKvStages = D == 64 ? 3 : 2;
+    static constexpr int kTileBytes = kAttnBlock * D * 2;  // one Q tile / one K block / one V block
+    static constexpr int kSmemBytes = (2 + 2 * kKvStages) * kTileBytes + 512 + 1024;
+};
+
+__device__ __forceinline__ float mask_lowest(int mask_dtype) {
+    if (mask_dtype == KB_F16) return -65504.0f;
+    if (mask_dtype == KB_BF16) return -3.3895313892515355e38f;
+    return -3.4028234663852886e38f;
+}
+
+__device__ __forceinline__ float mask_load(const void* base, int64_t off, int mask_dtype) {
+    if (mask_dtype == KB_F16) return __half2float(reinterpret_cast<const __half*>(base)[off]);
+    if (mask_dtype == KB_BF16) return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(base)[off]);
+    return reinterpret_cast<const float*>(base)[off];
+}
+
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+template <typename T, int D>
+__global__ void __launch_bounds__(kAttnThreads, 1)
+attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                    const __grid_constant__ CUtensorMap tmap_v, const AttnDev p) {
+    using Cfg = AttnCfg<D>;
+    constexpr int KVS = Cfg::kKvStages;
+    constexpr int TILE = Cfg::kTileBytes;
+    constexpr int CHUNK = kAttnBlock * 64 * 2;  // one 64-column (128-byte swizzled) slab of a tile
+    constexpr uint32_t kTmemCols = 512;
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    const uint32_t q_smem = smem_u32(smem);
+    const uint32_t k_smem = q_smem + 2 * TILE;
+    const uint32_t v_smem = k_smem + KVS * TILE;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (2 + 2 * KVS) * TILE);
+    const uint32_t bar_base = smem_u32(bars);
+    // barrier slots
+    auto q_full = [&](int t) { return bar_base + 8u * t; };
+    auto k_full = [&](int s) { return bar_base + 8u * (2 + s); };
+    auto k_empty = [&](int s) { return bar_base + 8u * (2 + KVS + s); };
+    auto v_full = [&](int s) { return bar_base + 8u * (2 + 2 * KVS + s); };
+    auto v_empty = [&](int s) { return bar_base + 8u * (2 + 3 * KVS + s); };
+    auto s_full = [&](int t) { return bar_base + 8u * (2 + 4 * KVS + t); };
+    auto p_full = [&](int t) { return bar_base + 8u * (4 + 4 * KVS + t); };
+    auto o_final = [&](int t) { return bar_base + 8u * (6 + 4 * KVS + t); };
+    constexpr int kNumBars = 8 + 4 * KVS;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBars);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    // Work assignment: heavy (late) query tiles first so that causal work is balanced.
+    const int BH = p.B * p.H;
+    const int pair = p.num_pairs - 1 - (int)(blockIdx.x / BH);
+    const int bh = (int)(blockIdx.x % BH);
+    const int b = bh / p.H, h = bh % p.H;
+    const int num_m_tiles = (p.M + kAttnBlock - 1) / kAttnBlock;
+    const int num_n_blocks = (p.N + kAttnBlock - 1) / kAttnBlock;
+    int mt[2], nblk[2];
+    int ntl = 0;  // live tiles in this CTA (1 or 2)
+    for (int t = 0; t < 2; ++t) {
+        mt[t] = pair * 2 + t;
+        if (mt[t] < num_m_tiles) {
+            ntl = t + 1;
+            nblk[t] = p.is_causal ? min(num_n_blocks, mt[t] + 1) : num_n_blocks;
+        } else {
+            nblk[t] = 0;
+        }
+    }
+    const int max_blk = max(nblk[0], nblk[1]);
+
+    if (threadIdx.x == 0) {
+        for (int t = 0; t < 2; ++t) {
+            mbar_init(q_full(t), 1);
+            mbar_init(s_full(t), 1);
+            mbar_init(p_full(t), 4);
+            mbar_init(o_final(t), 1);
+        }
+        for (int s = 0; s < KVS; ++s) {
+            mbar_init(k_full(s), 1);
+            mbar_init(k_empty(s), 1);
+            mbar_init(v_full(s), 1);
+            mbar_init(v_empty(s), 1);
+        }
+        *abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == 9) {
+        tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+        tmem_relinquish();
+    }
+    if (warp == 8 && lane == 0) {
+        tma_prefetch_desc(&tmap_q);
+        tma_prefetch_desc(&tmap_k);
+        tma_prefetch_desc(&tmap_v);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp >= 8) {
+      asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+      if (warp == 8) {
+        // ------------------------------------------------------------------ TMA producer
+        if (elect_one()) {
+            bool ok = true;
+            for (int t = 0; t < ntl; ++t) {
+                mbar_arrive_expect_tx(q_full(t), TILE);
+                for (int c = 0; c < D / 64; ++c)
+                    tma_load_4d(q_smem + t * TILE + c * CHUNK, &tmap_q, q_full(t), c * 64,
+                                mt[t] * kAttnBlock, h, b);
+            }
+            for (int j = 0; j < max_blk && ok; ++j) {
+                const int s = j % KVS;
+                const uint32_t ph = (uint32_t)((j / KVS) & 1);
+                if (!mbar_wait(k_empty(s), ph ^ 1, abort_flag, 100)) { ok = false; break; }
+                mbar_arrive_expect_tx(k_full(s), TILE);
+                for (int c = 0; c < D / 64; ++c)
+                    tma_load_4d(k_smem + s * TILE + c * CHUNK, &tmap_k, k_full(s), c * 64,
+                                j * kAttnBlock, h, b);
+                if (!mbar_wait(v_empty(s), ph ^ 1, abort_flag, 101)) { ok = false; break; }
+                mbar_arrive_expect_tx(v_full(s), TILE);
+                for (int c = 0; c < D / 64; ++c)
+                    tma_load_4d(v_smem + s * TILE + c * CHUNK, &tmap_v, v_full(s), c * 64,
+                                j * kAttnBlock, h, b);
+            }
+            if (!ok) {
+                for (int i = 0; i < 64; ++i) __nanosleep(2000);
+            }
+        }
+    } else if (warp == 9) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (elect_one()) {
+            constexpr uint32_t idesc_qk = make_idesc_f16(Elem<T>::kIsBf16, 128, 128, 0, 0);
+            constexpr uint32_t idesc_pv = make_idesc_f16(Elem<T>::kIsBf16, 128, D, 0, 1);
+            bool ok = true;
+            auto issue_qk = [&](int t, int s) {
+                const uint32_t a_base = q_smem + t * TILE;
+                const uint32_t b_base = k_smem + s * TILE;
+#pragma unroll
+                for (int ks = 0; ks < D / 16; ++ks) {
+                    const uint32_t off = (uint32_t)((ks / 4) * CHUNK + (ks % 4) * 32);
+                    tc_mma_ss(tmem_base + (uint32_t)(t * 128), make_smem_desc_sw128(a_base + off, 16, 1024),
+                              make_smem_desc_sw128(b_base + off, 16, 1024), idesc_qk, ks > 0 ? 1u : 0u);
+                }
+            };
+            auto issue_pv = [&](int t, int s, bool accumulate) {
+                const uint32_t b_base = v_smem + s * TILE;
+#pragma unroll
+                for (int ks = 0; ks < kAttnBlock / 16; ++ks) {
+                    // 16 keys = 16 rows of 128 bytes; the second 64-wide slab of D is CHUNK bytes away
+                    tc_mma_ts(tmem_base + (uint32_t)(256 + t * 128), tmem_base + (uint32_t)(t * 128 + ks * 8),
+                              make_smem_desc_sw128(b_base + ks * 2048, CHUNK, 1024), idesc_pv,
+                              (accumulate || ks > 0) ? 1u : 0u);
+                }
+            };
+            for (int t = 0; t < ntl && ok; ++t)
+                if (!mbar_wait(q_full(t), 0, abort_flag, 200)) ok = false;
+            if (ok && max_blk > 0) {
+                if (!mbar_wait(k_full(0), 0, abort_flag, 201)) ok = false;
+                if (ok) {
+                    tc_fence_after();
+                    for (int t = 0; t < ntl; ++t) {
+                        if (nblk[t] > 0) {
+                            issue_qk(t, 0);
+                            tc_commit(s_full(t));
+                        }
+                    }
+                    tc_commit(k_empty(0));
+                }
+            }
+            for (int j = 0; j < max_blk && ok; ++j) {
+                const int s = j % KVS;
+                const uint32_t ph = (uint32_t)((j / KVS) & 1);
+                const int s1 = (j + 1) % KVS;
+                const uint32_t ph1 = (uint32_t)(((j + 1) / KVS) & 1);
+                if (!mbar_wait(v_full(s), ph, abort_flag, 202)) { ok = false; break; }
+                if (j + 1 < max_blk) {
+                    if (!mbar_wait(k_full(s1), ph1, abort_flag, 203)) { ok = false; break; }
+                }
+                for (int t = 0; t < ntl; ++t) {
+                    if (j >= nblk[t]) continue;
+                    if (!mbar_wait(p_full(t), (uint32_t)(j & 1), abort_flag, 204)) { ok = false; break; }
+                    tc_fence_after();
+                    issue_pv(t, s, j > 0);
+                    if (j + 1 < nblk[t]) {
+                        issue_qk(t, s1);
+                        tc_commit(s_full(t));
+                    } else {
+                        tc_commit(o_final(t));
+                    }
+                }
+                if (!ok) break;
+                tc_commit(v_empty(s));
+                if (j + 1 < max_blk) tc_commit(k_empty(s1));
+            }
+        }
+      }
+    } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+        // ------------------------------------------------------------------ softmax groups
+        const int t = warp >> 2;        // tile handled by this group
+        const int q = warp & 3;         // TMEM lane quadrant of this warp
+        if (t < ntl && nblk[t] > 0) {
+            const int row = mt[t] * kAttnBlock + q * 32 + lane;
+            const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
+            const uint32_t s_addr = lane_addr + (uint32_t)(t * 128);
+            const uint32_t o_addr = lane_addr + (uint32_t)(256 + t * 128);
+            const float c = p.scale_log2;
+            const bool has_mask = p.mask != nullptr;
+            const bool plain = !has_mask && c > 0.f;
+            const float mlow = mask_lowest(p.mask_dtype);
+            const int64_t mask_row_off =
+                has_mask ? (int64_t)b * p.mask_strides[0] + (int64_t)h * p.mask_strides[1] +
+                               (int64_t)min(row, p.M - 1) * p.mask_strides[2]
+                         : 0;
+            float m_ref = -INFINITY;  // reference maximum used for the exponentials (log2 domain; raw S
+                                      // units when `plain`)
+            float l = 0.f;
+            bool ok = true;
+            for (int j = 0; j < nblk[t]; ++j) {
+                if (!mbar_wait(s_full(t), (uint32_t)(j & 1), abort_flag, 300 + t)) { ok = false; break; }
+                tc_fence_after();
+                uint32_t sr[4][32];
+#pragma unroll
+                for (int cch = 0; cch < 4; ++cch) tmem_ld_32x32(s_addr + cch * 32, sr[cch]);
+                tmem_ld_wait();
+
+                const int col0 = j * kAttnBlock;
+                const bool bound = (col0 + kAttnBlock > p.N) || (p.is_causal && col0 + kAttnBlock - 1 > mt[t] * kAttnBlock);
+                // ---- transform to the domain in which the maximum is taken
+                if (!plain) {
+#pragma unroll
+                    for (int cch = 0; cch < 4; ++cch) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            float v = __uint_as_float(sr[cch][i]) * c;
+                            if (has_mask) {
+                                const int col = col0 + cch * 32 + i;
+                                float mv = 0.f;
+                                if (col < p.N)
+                                    mv = mask_load(p.mask, mask_row_off + (int64_t)col * p.mask_strides[3], p.mask_dtype);
+                                mv = fmaxf(mv, mlow);
+                                v = fmaf(mv, kLog2e, v);
+                            }
+                            sr[cch][i] = __float_as_uint(v);
+                        }
+                    }
+                }
+                if (bound) {
+#pragma unroll
+                    for (int cch = 0; cch < 4; ++cch) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            const int col = col0 + cch * 32 + i;
+                            if (col >= p.N || (p.is_causal && col > row)) sr[cch][i] = __float_as_uint(-INFINITY);
+                        }
+                    }
+                }
+                float mx = -INFINITY;
+#pragma unroll
+                for (int cch = 0; cch < 4; ++cch) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(sr[cch][i]));
+                }
+                // ---- lazy rescale. In `plain` mode m_ref and mx are raw scores; exponent = (s - m_ref)*c.
+                const float unit = plain ? c : 1.0f;
+                float m_new = fmaxf(m_ref, mx);
+                if (m_new == -INFINITY) m_new = 0.f;  // row with nothing visible yet
+                const bool grow = (m_new - m_ref) * unit > kLazyThreshold;  // also true on the first block
+                float alpha = 1.0f;
+                if (grow) {
+                    alpha = (m_ref == -INFINITY) ? 0.f : fast_exp2((m_ref - m_new) * unit);
+                    m_ref = m_new;
+                    l *= alpha;
+                }
+                if (j > 0 && __any_sync(0xffffffffu, grow)) {
+                    // S_j complete implies P·V of block j-1 complete (issued earlier, same thread), so O is quiescent.
+#pragma unroll
+                    for (int dch = 0; dch < D / 32; ++dch) {
+                        uint32_t orr[32];
+                        tmem_ld_32x32(o_addr + dch * 32, orr);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) orr[i] = __float_as_uint(__uint_as_float(orr[i]) * alpha);
+                        tmem_st_32x32(o_addr + dch * 32, orr);
+                    }
+                }
+                // ---- exponentials, row sum, pack to 16 bit, write P over the first 64 columns of S
+                const float neg_ref = -m_ref * unit;
+#pragma unroll
+                for (int cch = 0; cch < 4; ++cch) {
+                    uint32_t pk[16];
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const float e0 = fast_exp2(fmaf(__uint_as_float(sr[cch][2 * i]), unit, neg_ref));
+                        const float e1 = fast_exp2(fmaf(__uint_as_float(sr[cch][2 * i + 1]), unit, neg_ref));
+                        l += e0 + e1;
+                        pk[i] = Elem<T>::pack2(e0, e1);
+                    }
+                    tmem_st_32x16(s_addr + cch * 16, pk);
+                }
+                tmem_st_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(p_full(t));
+            }
+            // ---- epilogue: O / l -> global
+            if (ok && mbar_wait(o_final(t), 0, abort_flag, 310 + t)) {
+                tc_fence_after();
+                const float inv_l = 1.0f / l;
+                T* o_row = reinterpret_cast<T*>(p.o) + (int64_t)b * p.o_strides[0] + (int64_t)h * p.o_strides[1] +
+                           (int64_t)row * p.o_strides[2];
+                const bool vec = p.o_strides[3] == 1 && ((((uintptr_t)o_row) & 15) == 0);
+#pragma unroll
+                for (int dch = 0; dch < D / 32; ++dch) {
+                    uint32_t orr[32];
+                    tmem_ld_32x32(o_addr + dch * 32, orr);
+                    tmem_ld_wait();
+                    if (row < p.M) {
+                        if (vec) {
+#pragma unroll
+                            for (int v = 0; v < 4; ++v) {
+                                uint4 w;
+                                w.x = Elem<T>::pack2(__uint_as_float(orr[v * 8 + 0]) * inv_l, __uint_as_float(orr[v * 8 + 1]) * inv_l);
+                                w.y = Elem<T>::pack2(__uint_as_float(orr[v * 8 + 2]) * inv_l, __uint_as_float(orr[v * 8 + 3]) * inv_l);
+                                w.z = Elem<T>::pack2(__uint_as_float(orr[v * 8 + 4]) * inv_l, __uint_as_float(orr[v * 8 + 5]) * inv_l);
+                                w.w = Elem<T>::pack2(__uint_as_float(orr[v * 8 + 6]) * inv_l, __uint_as_float(orr[v * 8 + 7]) * inv_l);
+                                reinterpret_cast<uint4*>(o_row + dch * 32)[v] = w;
+                            }
+                        } else {
+                            for (int i = 0; i < 32; ++i)
+                                o_row[(int64_t)(dch * 32 + i) * p.o_strides[3]] =
+                                    Elem<T>::from_f32(__uint_as_float(orr[i]) * inv_l);
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 9) {
+        __syncwarp();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+template <typename T, int D>
+static int launch_attention_td(const kb_attn_params& p, cudaStream_t stream) {
+    using Cfg = AttnCfg<D>;
+    CUtensorMap tq, tk, tv;
+    auto enc = [&](CUtensorMap* out, const void* ptr, int64_t rows, const int64_t* st) -> int {
+        if (st[3] != 1) return KB_ERR_UNSUPPORTED;
+        const uint64_t dims[4] = {(uint64_t)D, (uint64_t)rows, (uint64_t)p.H, (uint64_t)p.B};
+        // A dimension of extent 1 may carry any stride in the caller's tensor; TMA still wants a
+        // multiple of 16 bytes, and the value is never used, so substitute a harmless one.
+        auto fix = [](int64_t extent, int64_t stride) -> uint64_t {
+            return (extent == 1) ? 16u : (uint64_t)stride * 2u;
+        };
+        const uint64_t strides[4] = {0, fix(rows, st[2]), fix(p.H, st[1]), fix(p.B, st[0])};
+        const uint32_t box[4] = {64, (uint32_t)kAttnBlock, 1, 1};
+        return encode_tmap_16bit(out, ptr, 4, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B,
+                                 CU_TENSOR_MAP_L2_PROMOTION_L2_128B);
+    };
+    int st = enc(&tq, p.q, p.M, p.q_strides);
+    if (st != KB_OK) return st;
+    st = enc(&tk, p.k, p.N, p.k_strides);
+    if (st != KB_OK) return st;
+    st = enc(&tv, p.v, p.N, p.v_strides);
+    if (st != KB_OK) return st;
+
+    AttnDev d;
+    d.o = p.o;
+    d.mask = p.mask;
+    for (int i = 0; i < 4; ++i) {
+        d.o_strides[i] = p.o_strides[i];
+        d.mask_strides[i] = p.mask ? p.mask_strides[i] : 0;
+    }
+    d.B = (int)p.B; d.H = (int)p.H; d.M = (int)p.M; d.N = (int)p.N;
+    d.scale_log2 = p.sm_scale * kLog2e;
+    d.is_causal = p.is_causal ? 1 : 0;
+    d.mask_dtype = p.mask ? p.mask_dtype : KB_F32;
+    const int num_m_tiles = (int)((p.M + kAttnBlock - 1) / kAttnBlock);
+    d.num_pairs = (num_m_tiles + 1) / 2;
+
+    static bool attr_set = false;
+    if (!attr_set) {
+        if (cudaFuncSetAttribute(attention_tc_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 Cfg::kSmemBytes) != cudaSuccess)
+            return KB_ERR_LAUNCH;
+        attr_set = true;
+    }
+    const int64_t grid = (int64_t)d.num_pairs * p.B * p.H;
+    if (grid > 0x7fffffff) return KB_ERR_UNSUPPORTED;
+    attention_tc_kernel<T, D><<<(unsigned)grid, kAttnThreads, Cfg::kSmemBytes, stream>>>(tq, tk, tv, d);
+    return cudaGetLastError() == cudaSuccess ? KB_OK : KB_ERR_LAUNCH;
+}
+
+static int launch_attention(const kb_attn_params& p, cudaStream_t stream) {
+    if (p.N <= 0) return KB_ERR_UNSUPPORTED;
+    if (p.M > 0x7fffffff || p.N > 0x7fffffff || p.B * p.H > 0x7fffffff) return KB_ERR_UNSUPPORTED;
+    if (p.dtype == KB_F16) {
+        if (p.D == 64) return launch_attention_td<__half, 64>(p, stream);
+        if (p.D == 128) return launch_attention_td<__half, 128>(p, stream);
+    } else if (p.dtype == KB_BF16) {
+        if (p.D == 64) return launch_attention_td<__nv_bfloat16, 64>(p, stream);
+        if (p.D == 128) return launch_attention_td<__nv_bfloat16, 128>(p, stream);
+    }
+    return KB_ERR_UNSUPPORTED;
+}
+
+}  // namespace kb

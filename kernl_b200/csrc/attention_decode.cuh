@@ -1,0 +1,203 @@
+// Decode-shape ("skinny") attention for sm_100a: few query rows against many keys.
+// With one query row the tensor cores are pointless (M=1) and the op is bound by streaming K and V
+// from HBM once, so this is a CUDA-core split-KV kernel:
+//   part 1  grid (splits, M, B*H): each CTA scores a chunk of keys for one query row (one key per
+//           thread, 128-bit loads), runs the online softmax over the chunk in blocks of 128 keys and
+//           accumulates exp(S-m)·V; it writes (m, l, acc[D]) fp32 to scratch
+//   part 2  grid (M, B*H): merges the chunks with the online-softmax recurrence and writes O
+// Same maths as src/kernl/implementations/attention_skinny.py:58-366 of the reference (which keeps
+// its partial outputs in fp16; fp32 here). Additive masks and the causal flag are honoured in-kernel.
+#pragma once
+#include "common.cuh"
+#include "attention.cuh"
+
+namespace kb {
+
+constexpr int kDecThreads = 128;
+constexpr int kDecMaxSplits = 256;
+constexpr int kDecMaxD = 256;
+
+struct DecDev {
+    const void* q; const void* k; const void* v; void* o; const void* mask;
+    int64_t q_strides[4], k_strides[4], v_strides[4], o_strides[4], mask_strides[4];
+    int B, H, M, N, D;
+    float scale_log2;
+    int is_causal, mask_dtype;
+    int num_splits, chunk;  // chunk = keys per split, multiple of 128
+    float* scratch;         // [B*H, M, num_splits, D+2]
+};
+
+static void decode_split(int64_t N, int* num_splits, int* chunk) {
+    int64_t c = 128;
+    while ((N + c - 1) / c > kDecMaxSplits) c *= 2;
+    *chunk = (int)c;
+    *num_splits = (int)((N + c - 1) / c);
+    if (*num_splits < 1) *num_splits = 1;
+}
+
+static int64_t decode_scratch_bytes(int64_t B, int64_t H, int64_t M, int64_t N, int64_t D) {
+    if (B < 0 || H < 0 || M < 0 || N < 0 || D <= 0) return -1;
+    int splits, chunk;
+    decode_split(N, &splits, &chunk);
+    return B * H * M * (int64_t)splits * (D + 2) * (int64_t)sizeof(float);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kDecThreads)
+attn_decode_part1_kernel(const DecDev p) {
+    __shared__ float q_s[kDecMaxD];
+    __shared__ float sc_s[kDecThreads];
+    __shared__ float red_s[kDecThreads / 32];
+    const int split = blockIdx.x, row = blockIdx.y, bh = blockIdx.z;
+    const int b = bh / p.H, h = bh % p.H;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int D = p.D;
+
+    const T* qp = reinterpret_cast<const T*>(p.q) + (int64_t)b * p.q_strides[0] + (int64_t)h * p.q_strides[1] +
+                  (int64_t)row * p.q_strides[2];
+    for (int d = tid; d < D; d += kDecThreads) q_s[d] = Elem<T>::to_f32(qp[(int64_t)d * p.q_strides[3]]) * p.scale_log2;
+    __syncthreads();
+
+    const T* kbase = reinterpret_cast<const T*>(p.k) + (int64_t)b * p.k_strides[0] + (int64_t)h * p.k_strides[1];
+    const T* vbase = reinterpret_cast<const T*>(p.v) + (int64_t)b * p.v_strides[0] + (int64_t)h * p.v_strides[1];
+    const bool k_vec = p.k_strides[3] == 1 && (p.k_strides[2] % 8) == 0 && (((uintptr_t)kbase) & 15) == 0 && (D % 8) == 0;
+    const float mlow = mask_lowest(p.mask_dtype);
+    const int64_t mask_off = p.mask ? (int64_t)b * p.mask_strides[0] + (int64_t)h * p.mask_strides[1] +
+                                          (int64_t)row * p.mask_strides[2]
+                                    : 0;
+
+    float m_run = -INFINITY, l_run = 0.f;
+    float acc[kDecMaxD / kDecThreads];
+#pragma unroll
+    for (int i = 0; i < kDecMaxD / kDecThreads; ++i) acc[i] = 0.f;
+
+    const int key_begin = split * p.chunk;
+    const int key_end = min(p.N, key_begin + p.chunk);
+    for (int k0 = key_begin; k0 < key_end; k0 += kDecThreads) {
+        // ---- one key per thread: score in the log2 domain
+        const int key = k0 + tid;
+        float s = -INFINITY;
+        if (key < key_end && !(p.is_causal && key > row)) {
+            const T* kr = kbase + (int64_t)key * p.k_strides[2];
+            float dot = 0.f;
+            if (k_vec) {
+                for (int d = 0; d < D; d += 8) {
+                    const uint4 w = __ldg(reinterpret_cast<const uint4*>(kr + d));
+                    const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float2 f = Elem<T>::unpack2(ww[i]);
+                        dot = fmaf(f.x, q_s[d + 2 * i], dot);
+                        dot = fmaf(f.y, q_s[d + 2 * i + 1], dot);
+                    }
+                }
+            } else {
+                for (int d = 0; d < D; ++d) dot = fmaf(Elem<T>::to_f32(kr[(int64_t)d * p.k_strides[3]]), q_s[d], dot);
+            }
+            s = dot;
+            if (p.mask) {
+                float mv = mask_load(p.mask, mask_off + (int64_t)key * p.mask_strides[3], p.mask_dtype);
+                s = fmaf(fmaxf(mv, mlow), kLog2e, s);
+            }
+        }
+        // ---- block maximum
+        float mx = s;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        if (lane == 0) red_s[warp] = mx;
+        __syncthreads();
+        mx = fmaxf(fmaxf(red_s[0], red_s[1]), fmaxf(red_s[2], red_s[3]));
+        __syncthreads();
+        float m_new = fmaxf(m_run, mx);
+        if (m_new == -INFINITY) m_new = 0.f;
+        const float alpha = (m_run == -INFINITY) ? 0.f : fast_exp2(m_run - m_new);
+        const float pe = fast_exp2(s - m_new);
+        // P is rounded to the input dtype before P·V, as the reference does (attention_skinny.py:262).
+        sc_s[tid] = Elem<T>::to_f32(Elem<T>::from_f32(pe));
+        float ps = pe;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, o);
+        if (lane == 0) red_s[warp] = ps;
+        __syncthreads();
+        l_run = l_run * alpha + (red_s[0] + red_s[1] + red_s[2] + red_s[3]);
+        m_run = m_new;
+        // ---- P·V: thread d accumulates output dimension d over the block's keys
+        const int nk = min(kDecThreads, key_end - k0);
+#pragma unroll
+        for (int i = 0; i < kDecMaxD / kDecThreads; ++i) {
+            const int d = tid + i * kDecThreads;
+            if (d < D) {
+                float a = acc[i] * alpha;
+                const T* vp = vbase + (int64_t)k0 * p.v_strides[2] + (int64_t)d * p.v_strides[3];
+                for (int kk = 0; kk < nk; ++kk) a = fmaf(sc_s[kk], Elem<T>::to_f32(vp[(int64_t)kk * p.v_strides[2]]), a);
+                acc[i] = a;
+            }
+        }
+        __syncthreads();
+    }
+    float* out = p.scratch + (((int64_t)bh * p.M + row) * p.num_splits + split) * (D + 2);
+    if (tid == 0) { out[0] = m_run; out[1] = l_run; }
+#pragma unroll
+    for (int i = 0; i < kDecMaxD / kDecThreads; ++i) {
+        const int d = tid + i * kDecThreads;
+        if (d < D) out[2 + d] = acc[i];
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kDecThreads)
+attn_decode_part2_kernel(const DecDev p) {
+    const int row = blockIdx.x, bh = blockIdx.y;
+    const int b = bh / p.H, h = bh % p.H;
+    const int D = p.D;
+    const float* in = p.scratch + ((int64_t)bh * p.M + row) * p.num_splits * (D + 2);
+    float m_tot = -INFINITY;
+    for (int s = 0; s < p.num_splits; ++s) m_tot = fmaxf(m_tot, in[(int64_t)s * (D + 2)]);
+    float l_tot = 0.f;
+    for (int s = 0; s < p.num_splits; ++s) {
+        const float ms = in[(int64_t)s * (D + 2)];
+        if (ms != -INFINITY) l_tot += in[(int64_t)s * (D + 2) + 1] * fast_exp2(ms - m_tot);
+    }
+    T* op = reinterpret_cast<T*>(p.o) + (int64_t)b * p.o_strides[0] + (int64_t)h * p.o_strides[1] +
+            (int64_t)row * p.o_strides[2];
+    for (int d = threadIdx.x; d < D; d += kDecThreads) {
+        float a = 0.f;
+        for (int s = 0; s < p.num_splits; ++s) {
+            const float ms = in[(int64_t)s * (D + 2)];
+            if (ms != -INFINITY) a += in[(int64_t)s * (D + 2) + 2 + d] * fast_exp2(ms - m_tot);
+        }
+        op[(int64_t)d * p.o_strides[3]] = Elem<T>::from_f32(a / l_tot);
+    }
+}
+
+static int launch_attention_decode(const kb_attn_params& p, void* scratch, int64_t scratch_bytes, cudaStream_t stream) {
+    if (p.N <= 0 || p.D > kDecMaxD) return KB_ERR_UNSUPPORTED;
+    if (p.M > 65535 || p.B * p.H > 65535) return KB_ERR_UNSUPPORTED;
+    if (scratch == nullptr) return KB_ERR_BAD_ARG;
+    const int64_t need = decode_scratch_bytes(p.B, p.H, p.M, p.N, p.D);
+    if (scratch_bytes < need) return KB_ERR_BAD_ARG;
+    DecDev d;
+    d.q = p.q; d.k = p.k; d.v = p.v; d.o = p.o; d.mask = p.mask;
+    for (int i = 0; i < 4; ++i) {
+        d.q_strides[i] = p.q_strides[i]; d.k_strides[i] = p.k_strides[i]; d.v_strides[i] = p.v_strides[i];
+        d.o_strides[i] = p.o_strides[i]; d.mask_strides[i] = p.mask ? p.mask_strides[i] : 0;
+    }
+    d.B = (int)p.B; d.H = (int)p.H; d.M = (int)p.M; d.N = (int)p.N; d.D = (int)p.D;
+    d.scale_log2 = p.sm_scale * kLog2e;
+    d.is_causal = p.is_causal ? 1 : 0;
+    d.mask_dtype = p.mask ? p.mask_dtype : KB_F32;
+    decode_split(p.N, &d.num_splits, &d.chunk);
+    d.scratch = reinterpret_cast<float*>(scratch);
+    const dim3 g1((unsigned)d.num_splits, (unsigned)p.M, (unsigned)(p.B * p.H));
+    const dim3 g2((unsigned)p.M, (unsigned)(p.B * p.H));
+    if (p.dtype == KB_F16) {
+        attn_decode_part1_kernel<__half><<<g1, kDecThreads, 0, stream>>>(d);
+        attn_decode_part2_kernel<__half><<<g2, kDecThreads, 0, stream>>>(d);
+    } else {
+        attn_decode_part1_kernel<__nv_bfloat16><<<g1, kDecThreads, 0, stream>>>(d);
+        attn_decode_part2_kernel<__nv_bfloat16><<<g2, kDecThreads, 0, stream>>>(d);
+    }
+    return cudaGetLastError() == cudaSuccess ? KB_OK : KB_ERR_LAUNCH;
+}
+
+}  // namespace kb

@@ -1,0 +1,202 @@
+// C ABI of the kernl_b200 kernels (declared in include/kernl_b200.h) and the host helpers they
+// share. All kernels live in this single translation unit so that they share one device status word.
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "common.cuh"
+#include "norm.cuh"
+#include "linear.cuh"
+#include "attention.cuh"
+#include "attention_decode.cuh"
+
+namespace kb {
+
+typedef CUresult (*PFN_encodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                    CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                    CUtensorMapFloatOOBfill);
+
+static PFN_encodeTiled get_encode_fn() {
+    static PFN_encodeTiled fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<PFN_encodeTiled>(p);
+    });
+    return fn;
+}
+
+int encode_tmap_16bit(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
+                      const uint64_t* strides_bytes, const uint32_t* box, CUtensorMapSwizzle swz,
+                      CUtensorMapL2promotion l2) {
+    PFN_encodeTiled fn = get_encode_fn();
+    if (fn == nullptr) return KB_ERR_NO_DEVICE;
+    if (((uintptr_t)base & 15) != 0) return KB_ERR_UNSUPPORTED;
+    cuuint64_t gdims[5];
+    cuuint64_t gstrides[4];
+    cuuint32_t gbox[5], estr[5];
+    for (int i = 0; i < rank; ++i) {
+        gdims[i] = dims[i];
+        gbox[i] = box[i];
+        estr[i] = 1;
+        if (i > 0) {
+            if (strides_bytes[i] % 16 != 0) return KB_ERR_UNSUPPORTED;
+            gstrides[i - 1] = strides_bytes[i];
+        }
+    }
+    // CU_TENSOR_MAP_DATA_TYPE_FLOAT16 and BFLOAT16 move bytes identically; zero fill for OOB.
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, (cuuint32_t)rank, const_cast<void*>(base), gdims,
+                    gstrides, gbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz, l2,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? KB_OK : KB_ERR_UNSUPPORTED;
+}
+
+int sm_count() {
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+        int v = 0;
+        if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) return 148;
+        n = v;
+    }
+    return n;
+}
+
+static int check_device() {
+    static int state = 0;  // 0 unknown, 1 ok, -1 bad
+    if (state == 0) {
+        int dev = 0, major = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) {
+            cudaGetLastError();
+            return KB_ERR_NO_DEVICE;
+        }
+        state = (major == 10) ? 1 : -1;
+    }
+    return state == 1 ? KB_OK : KB_ERR_NO_DEVICE;
+}
+
+static int g_forced_bn = 0;
+
+}  // namespace kb
+
+using namespace kb;
+
+extern "C" {
+
+int kb_version(void) { return 100; }
+
+const char* kb_status_str(int status) {
+    switch (status) {
+        case KB_OK: return "ok";
+        case KB_ERR_BAD_ARG: return "bad argument";
+        case KB_ERR_UNSUPPORTED: return "unsupported shape, stride, alignment or dtype";
+        case KB_ERR_LAUNCH: return "CUDA launch error";
+        case KB_ERR_TIMEOUT: return "a bounded device-side wait expired";
+        case KB_ERR_NO_DEVICE: return "no sm_100 CUDA device";
+        case KB_ERR_TOO_LARGE: return "size beyond the fixed maximum of this entry point";
+        default: return "unknown status";
+    }
+}
+
+int kb_device_status_read(int32_t* status_out) {
+    if (status_out == nullptr) return KB_ERR_BAD_ARG;
+    int st = check_device();
+    if (st != KB_OK) return st;
+    int h[4] = {0, 0, 0, 0};
+    if (cudaDeviceSynchronize() != cudaSuccess) return KB_ERR_LAUNCH;
+    if (cudaMemcpyFromSymbol(h, g_device_status, sizeof(h)) != cudaSuccess) return KB_ERR_LAUNCH;
+    for (int i = 0; i < 4; ++i) status_out[i] = h[i];
+    if (h[0] != 0) {
+        int z[4] = {0, 0, 0, 0};
+        if (cudaMemcpyToSymbol(g_device_status, z, sizeof(z)) != cudaSuccess) return KB_ERR_LAUNCH;
+        return KB_ERR_TIMEOUT;
+    }
+    return KB_OK;
+}
+
+int kb_norm_fwd(const kb_norm_params* p, void* stream) {
+    if (p == nullptr || p->x == nullptr || p->y == nullptr || p->gamma == nullptr) return KB_ERR_BAD_ARG;
+    if (p->rows < 0 || p->cols <= 0) return KB_ERR_BAD_ARG;
+    if (p->rows == 0) return KB_OK;
+    int st = check_device();
+    if (st != KB_OK) return st;
+    st = launch_norm(*p, (cudaStream_t)stream);
+    if (st != KB_OK) return st;
+    return cudaGetLastError() == cudaSuccess ? KB_OK : KB_ERR_LAUNCH;
+}
+
+// Test hook: force the GEMM column-tile width (0 = heuristic). Not part of the stable ABI.
+void kb_debug_force_bn(int bn) { g_forced_bn = bn; }
+
+int kb_linear_fwd(const kb_linear_params* p, void* stream) {
+    if (p == nullptr || p->x == nullptr || p->w == nullptr || p->y == nullptr) return KB_ERR_BAD_ARG;
+    if (p->M < 0 || p->N <= 0 || p->K <= 0) return KB_ERR_BAD_ARG;
+    if (p->activation < KB_ACT_NONE || p->activation > KB_ACT_SILU) return KB_ERR_BAD_ARG;
+    if (p->M == 0) return KB_OK;
+    if (p->K % 8 != 0 || p->x_row_stride % 8 != 0) return KB_ERR_UNSUPPORTED;
+    if (((uintptr_t)p->x & 15) || ((uintptr_t)p->w & 15)) return KB_ERR_UNSUPPORTED;
+    if (p->M > 0x7fffffff || p->N > 0x7fffffff || p->K > 0x7fffffff) return KB_ERR_UNSUPPORTED;
+    int st = check_device();
+    if (st != KB_OK) return st;
+    return launch_linear(*p, (cudaStream_t)stream, g_forced_bn);
+}
+
+int kb_silu_mul(const void* gu, void* y, int64_t M, int64_t N, int32_t dtype, void* stream) {
+    if (gu == nullptr || y == nullptr || M < 0 || N <= 0) return KB_ERR_BAD_ARG;
+    if (M == 0) return KB_OK;
+    if (N % 8 != 0 || ((uintptr_t)gu & 15) || ((uintptr_t)y & 15)) return KB_ERR_UNSUPPORTED;
+    int st = check_device();
+    if (st != KB_OK) return st;
+    const int64_t total = M * (N / 8);
+    const int threads = 256;
+    int64_t blocks = (total + threads - 1) / threads;
+    if (blocks > (int64_t)sm_count() * 16) blocks = (int64_t)sm_count() * 16;
+    if (dtype == KB_F16)
+        silu_mul_kernel<__half><<<(unsigned)blocks, threads, 0, (cudaStream_t)stream>>>((const __half*)gu, (__half*)y, M, N);
+    else if (dtype == KB_BF16)
+        silu_mul_kernel<__nv_bfloat16><<<(unsigned)blocks, threads, 0, (cudaStream_t)stream>>>(
+            (const __nv_bfloat16*)gu, (__nv_bfloat16*)y, M, N);
+    else
+        return KB_ERR_UNSUPPORTED;
+    return cudaGetLastError() == cudaSuccess ? KB_OK : KB_ERR_LAUNCH;
+}
+
+static int check_attn(const kb_attn_params* p) {
+    if (p == nullptr || p->q == nullptr || p->k == nullptr || p->v == nullptr || p->o == nullptr)
+        return KB_ERR_BAD_ARG;
+    if (p->B < 0 || p->H < 0 || p->M < 0 || p->N < 0 || p->D <= 0) return KB_ERR_BAD_ARG;
+    if (p->dtype != KB_F16 && p->dtype != KB_BF16) return KB_ERR_UNSUPPORTED;
+    if (p->mask != nullptr && p->mask_dtype != KB_F16 && p->mask_dtype != KB_BF16 && p->mask_dtype != KB_F32)
+        return KB_ERR_UNSUPPORTED;
+    return KB_OK;
+}
+
+int kb_attention_fwd(const kb_attn_params* p, void* stream) {
+    int st = check_attn(p);
+    if (st != KB_OK) return st;
+    if (p->B == 0 || p->H == 0 || p->M == 0) return KB_OK;
+    st = check_device();
+    if (st != KB_OK) return st;
+    return launch_attention(*p, (cudaStream_t)stream);
+}
+
+int64_t kb_attention_decode_scratch_bytes(int64_t B, int64_t H, int64_t M, int64_t N, int64_t D) {
+    return decode_scratch_bytes(B, H, M, N, D);
+}
+
+int kb_attention_decode_fwd(const kb_attn_params* p, void* scratch, int64_t scratch_bytes, void* stream) {
+    int st = check_attn(p);
+    if (st != KB_OK) return st;
+    if (p->B == 0 || p->H == 0 || p->M == 0) return KB_OK;
+    st = check_device();
+    if (st != KB_OK) return st;
+    return launch_attention_decode(*p, scratch, scratch_bytes, (cudaStream_t)stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,354 @@
+// Fused linear layer y = act(x · Wᵀ + bias) for sm_100a.
+//
+// Persistent, warp-specialised tcgen05 GEMM:
+//   warp 0      TMA producer: x tile [128 x 64] and W tile [BN x 64] per stage, 128-byte swizzle
+//   warp 1      MMA issuer: one elected thread issues tcgen05.mma (M=128, N=BN, K=16) x 4 per stage,
+//               accumulators in TMEM, double-buffered (2 x BN columns) so that the epilogue of tile
+//               i overlaps the main loop of tile i+1
+//   warps 2..5  epilogue: tcgen05.ld of the accumulator (one row per thread), + bias, activation
+//               in fp32, convert, store
+// Both operands are K-major (x is [M,K], W is [N,K]) which is exactly what tcgen05 wants, so
+// no transposes are needed. Ragged M / N / K edges rely on TMA zero fill for loads and on
+// predicated stores.
+#pragma once
+#include "common.cuh"
+
+namespace kb {
+
+constexpr int kGemmBM = 128;
+constexpr int kGemmBK = 64;
+constexpr int kGemmThreads = 192;
+
+template <int BN>
+struct GemmCfg {
+    static constexpr int kStages = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
+    static constexpr int kABytes = kGemmBM * kGemmBK * 2;
+    static constexpr int kBBytes = BN * kGemmBK * 2;
+    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
+    // tiles + barriers/flags + slack for the 1024-byte alignment of the tiles
+    static constexpr int kSmemBytes = kStages * kStageBytes + 256 + 1024;
+};
+
+__device__ __forceinline__ float act_apply(float z, int activation) {
+    switch (activation) {
+        case KB_ACT_TANH: return tanhf(z);
+        case KB_ACT_GELU: return z * 0.5f * (1.0f + erff(z * 0.70710678118654752440f));
+        case KB_ACT_FAST_GELU:
+            return 0.5f * z * (1.0f + tanhf(0.79788456080286535588f * (z + 0.044715f * z * z * z)));
+        case KB_ACT_RELU: return fmaxf(z, 0.0f);
+        case KB_ACT_SILU: return z / (1.0f + __expf(-z));
+        default: return z;
+    }
+}
+
+__device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& m_idx, int& n_idx) {
+    // Grouped rasterisation: 8 row-tiles share each sweep over the column tiles so that the
+    // CTAs running at the same time reuse W and x tiles out of L2.
+    constexpr int kGroupM = 8;
+    const int group_size = kGroupM * num_n;
+    const int group_id = t / group_size;
+    const int first_m = group_id * kGroupM;
+    const int gsz = min(num_m - first_m, kGroupM);
+    const int r = t % group_size;
+    m_idx = first_m + r % gsz;
+    n_idx = r / gsz;
+}
+
+template <typename T, int BN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
+                 const T* __restrict__ bias, T* __restrict__ y, T* __restrict__ act_inputs, int M,
+                 int N, int K, int64_t y_row_stride, int activation) {
+    using Cfg = GemmCfg<BN>;
+    constexpr int STAGES = Cfg::kStages;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::kStageBytes);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const uint32_t smem_base = smem_u32(smem);
+    const uint32_t bar_base = smem_u32(bars);
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+    auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
+    auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(tfull_bar(a), 1);
+            mbar_init(tempty_bar(a), 4);
+        }
+        *abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(tmem_slot), Cfg::kTmemCols);
+        tmem_relinquish();
+    }
+    if (warp == 0 && lane == 0) {
+        tma_prefetch_desc(&tmap_x);
+        tma_prefetch_desc(&tmap_w);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int num_m = (M + kGemmBM - 1) / kGemmBM;
+    const int num_n = (N + BN - 1) / BN;
+    const int num_tiles = num_m * num_n;
+    const int num_k = (K + kGemmBK - 1) / kGemmBK;
+
+    if (warp == 0) {
+        if (elect_one()) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+                int m_idx, n_idx;
+                tile_coords(t, num_m, num_n, m_idx, n_idx);
+                for (int kb = 0; kb < num_k; ++kb) {
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1, abort_flag, 100)) { ok = false; break; }
+                    mbar_arrive_expect_tx(full_bar(stage), Cfg::kStageBytes);
+                    const uint32_t a_dst = smem_base + stage * Cfg::kStageBytes;
+                    tma_load_2d(a_dst, &tmap_x, full_bar(stage), kb * kGemmBK, m_idx * kGemmBM);
+                    tma_load_2d(a_dst + Cfg::kABytes, &tmap_w, full_bar(stage), kb * kGemmBK,
+                                n_idx * BN);
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+            if (!ok) {
+                // Give copies that are still in flight a bounded chance to land before the CTA's
+                // shared memory is released.
+                for (int i = 0; i < 64; ++i) __nanosleep(2000);
+            }
+        }
+    } else if (warp == 1) {
+        if (elect_one()) {
+            constexpr uint32_t idesc = make_idesc_f16(Elem<T>::kIsBf16, kGemmBM, BN, 0, 0);
+            int stage = 0;
+            uint32_t phase = 0;
+            int acc = 0;
+            uint32_t acc_phase = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+                if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1, abort_flag, 200)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+                for (int kb = 0; kb < num_k; ++kb) {
+                    if (!mbar_wait(full_bar(stage), phase, abort_flag, 201)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_base + stage * Cfg::kStageBytes;
+                    const uint64_t a_desc = make_smem_desc_sw128(a_addr, 16, 1024);
+                    const uint64_t b_desc = make_smem_desc_sw128(a_addr + Cfg::kABytes, 16, 1024);
+#pragma unroll
+                    for (int k = 0; k < kGemmBK / 16; ++k) {
+                        // +32 bytes along K inside the 128-byte swizzle row = +2 in the address field
+                        tc_mma_ss(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc,
+                                  (kb > 0 || k > 0) ? 1u : 0u);
+                    }
+                    tc_commit(empty_bar(stage));
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+                if (!ok) break;
+                tc_commit(tfull_bar(acc));
+                acc ^= 1;
+                if (acc == 0) acc_phase ^= 1;
+            }
+        }
+    } else {
+        const int q = warp & 3;  // TMEM lane quadrant this warp may access
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+            int m_idx, n_idx;
+            tile_coords(t, num_m, num_n, m_idx, n_idx);
+            if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, 300)) { ok = false; break; }
+            tc_fence_after();
+            const int row = m_idx * kGemmBM + q * 32 + lane;
+            const int n0 = n_idx * BN;
+            T* y_row = y + (int64_t)row * y_row_stride;
+            T* a_row = act_inputs ? act_inputs + (int64_t)row * y_row_stride : nullptr;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                if (n0 + c0 >= N) break;
+                uint32_t r[32];
+                tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + c0), r);
+                tmem_ld_wait();
+                const int col0 = n0 + c0;
+                const bool full_chunk = (col0 + 32 <= N);
+                float z[32];
+                if (bias != nullptr) {
+                    if (full_chunk && (((uintptr_t)(bias + col0)) & 15) == 0) {
+#pragma unroll
+                        for (int v = 0; v < 4; ++v) {
+                            const uint4 bw = __ldg(reinterpret_cast<const uint4*>(bias + col0) + v);
+                            const uint32_t w[4] = {bw.x, bw.y, bw.z, bw.w};
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const float2 bf = Elem<T>::unpack2(w[i]);
+                                z[v * 8 + 2 * i] = __uint_as_float(r[v * 8 + 2 * i]) + bf.x;
+                                z[v * 8 + 2 * i + 1] = __uint_as_float(r[v * 8 + 2 * i + 1]) + bf.y;
+                            }
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            const float b = (col0 + j < N) ? Elem<T>::to_f32(bias[col0 + j]) : 0.f;
+                            z[j] = __uint_as_float(r[j]) + b;
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) z[j] = __uint_as_float(r[j]);
+                }
+                if (row < M) {
+                    const bool vec = full_chunk && ((((uintptr_t)(y_row + col0)) & 15) == 0) &&
+                                     (a_row == nullptr || (((uintptr_t)(a_row + col0)) & 15) == 0);
+                    if (a_row != nullptr) {
+                        if (vec) {
+#pragma unroll
+                            for (int v = 0; v < 4; ++v) {
+                                uint4 o;
+                                o.x = Elem<T>::pack2(z[v * 8 + 0], z[v * 8 + 1]);
+                                o.y = Elem<T>::pack2(z[v * 8 + 2], z[v * 8 + 3]);
+                                o.z = Elem<T>::pack2(z[v * 8 + 4], z[v * 8 + 5]);
+                                o.w = Elem<T>::pack2(z[v * 8 + 6], z[v * 8 + 7]);
+                                reinterpret_cast<uint4*>(a_row + col0)[v] = o;
+                            }
+                        } else {
+                            for (int j = 0; j < 32; ++j)
+                                if (col0 + j < N) a_row[col0 + j] = Elem<T>::from_f32(z[j]);
+                        }
+                    }
+                    if (activation != KB_ACT_NONE) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) z[j] = act_apply(z[j], activation);
+                    }
+                    if (vec) {
+#pragma unroll
+                        for (int v = 0; v < 4; ++v) {
+                            uint4 o;
+                            o.x = Elem<T>::pack2(z[v * 8 + 0], z[v * 8 + 1]);
+                            o.y = Elem<T>::pack2(z[v * 8 + 2], z[v * 8 + 3]);
+                            o.z = Elem<T>::pack2(z[v * 8 + 4], z[v * 8 + 5]);
+                            o.w = Elem<T>::pack2(z[v * 8 + 6], z[v * 8 + 7]);
+                            reinterpret_cast<uint4*>(y_row + col0)[v] = o;
+                        }
+                    } else {
+                        for (int j = 0; j < 32; ++j)
+                            if (col0 + j < N) y_row[col0 + j] = Elem<T>::from_f32(z[j]);
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty_bar(acc));
+            acc ^= 1;
+            if (acc == 0) acc_phase ^= 1;
+        }
+    }
+
+    // Teardown: every role falls through to here, also after an abandoned wait.
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tmem_dealloc(tmem_base, Cfg::kTmemCols);
+    }
+}
+
+template <typename T, int BN>
+static int launch_linear_bn(const kb_linear_params& p, cudaStream_t stream) {
+    using Cfg = GemmCfg<BN>;
+    CUtensorMap tmap_x, tmap_w;
+    {
+        const uint64_t dims[2] = {(uint64_t)p.K, (uint64_t)p.M};
+        const uint64_t strides[2] = {0, (uint64_t)p.x_row_stride * 2};
+        const uint32_t box[2] = {kGemmBK, kGemmBM};
+        int st = encode_tmap_16bit(&tmap_x, p.x, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B,
+                                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B);
+        if (st != KB_OK) return st;
+    }
+    {
+        const uint64_t dims[2] = {(uint64_t)p.K, (uint64_t)p.N};
+        const uint64_t strides[2] = {0, (uint64_t)p.K * 2};
+        const uint32_t box[2] = {kGemmBK, BN};
+        int st = encode_tmap_16bit(&tmap_w, p.w, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B,
+                                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
+        if (st != KB_OK) return st;
+    }
+    static bool attr_set = false;  // per instantiation
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(linear_tc_kernel<T, BN>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+        if (e != cudaSuccess) return KB_ERR_LAUNCH;
+        attr_set = true;
+    }
+    const int num_tiles = (int)(((p.M + kGemmBM - 1) / kGemmBM) * ((p.N + BN - 1) / BN));
+    const int grid = num_tiles < sm_count() ? num_tiles : sm_count();
+    linear_tc_kernel<T, BN><<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(
+        tmap_x, tmap_w, (const T*)p.bias, (T*)p.y, (T*)p.act_inputs, (int)p.M, (int)p.N, (int)p.K,
+        p.y_row_stride, p.activation);
+    return cudaGetLastError() == cudaSuccess ? KB_OK : KB_ERR_LAUNCH;
+}
+
+// Column-tile width: the widest tile that still yields at least one tile per SM; narrow tiles for
+// problems with few rows so that the (bandwidth-bound) weight stream is spread over many SMs.
+static int pick_bn(int64_t M, int64_t N, int forced_bn) {
+    if (forced_bn == 256 || forced_bn == 128 || forced_bn == 64 || forced_bn == 32) return forced_bn;
+    const int64_t num_m = (M + kGemmBM - 1) / kGemmBM;
+    const int sms = sm_count();
+    for (int bn : {256, 128, 64}) {
+        if (num_m * ((N + bn - 1) / bn) >= sms) return bn;
+    }
+    return 32;
+}
+
+template <typename T>
+static int launch_linear_t(const kb_linear_params& p, cudaStream_t stream, int forced_bn) {
+    switch (pick_bn(p.M, p.N, forced_bn)) {
+        case 256: return launch_linear_bn<T, 256>(p, stream);
+        case 128: return launch_linear_bn<T, 128>(p, stream);
+        case 64: return launch_linear_bn<T, 64>(p, stream);
+        default: return launch_linear_bn<T, 32>(p, stream);
+    }
+}
+
+static int launch_linear(const kb_linear_params& p, cudaStream_t stream, int forced_bn) {
+    if (p.dtype == KB_F16) return launch_linear_t<__half>(p, stream, forced_bn);
+    if (p.dtype == KB_BF16) return launch_linear_t<__nv_bfloat16>(p, stream, forced_bn);
+    return KB_ERR_UNSUPPORTED;
+}
+
+// y = silu(g) * u with gu = [g | u] along columns.
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ y, int64_t M, int64_t N) {
+    const int64_t nvec = N / 8;
+    const int64_t total = M * nvec;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t m = i / nvec, c = (i % nvec) * 8;
+        const uint4 g = *reinterpret_cast<const uint4*>(gu + m * 2 * N + c);
+        const uint4 u = *reinterpret_cast<const uint4*>(gu + m * 2 * N + N + c);
+        const uint32_t gw[4] = {g.x, g.y, g.z, g.w}, uw[4] = {u.x, u.y, u.z, u.w};
+        uint32_t ow[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float2 gf = Elem<T>::unpack2(gw[k]), uf = Elem<T>::unpack2(uw[k]);
+            ow[k] = Elem<T>::pack2(gf.x / (1.f + __expf(-gf.x)) * uf.x, gf.y / (1.f + __expf(-gf.y)) * uf.y);
+        }
+        *reinterpret_cast<uint4*>(y + m * N + c) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+    }
+}
+
+}  // namespace kb

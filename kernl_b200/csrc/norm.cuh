@@ -1,0 +1,203 @@
+// LayerNorm / RMSNorm forward for sm_100a. HBM-bound: x is read once and y written once.
+//
+// Fast path: one warp per row, the whole row held in registers as 128-bit vectors (8 elements of
+// a 16-bit type per load), statistics by warp shuffles in fp32, two-pass variance taken from the
+// registers (no second trip to memory). Algorithmic traffic per row is 2*cols*2 bytes.
+// Generic path: arbitrary strides / column counts, one warp per row, re-reads the row (served by
+// L1/L2) — correctness path for the strided cases the reference accepts
+// (src/kernl/implementations/layer_norm.py:321-324).
+#pragma once
+#include "common.cuh"
+
+namespace kb {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ uint4 ld_stream_16B(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+__device__ __forceinline__ void st_stream_16B(void* p, uint4 v) {
+    asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z),
+                 "r"(v.w)
+                 : "memory");
+}
+
+// CHUNKS = ceil(cols / 256): each lane owns CHUNKS vectors of 8 elements; vector c of lane l covers
+// columns (c*32 + l)*8 .. +8. cols must be a multiple of 8.
+template <typename T, int CHUNKS, bool RMS>
+__global__ void __launch_bounds__(128)
+norm_fwd_rowwarp_kernel(const T* __restrict__ x, T* __restrict__ y, const T* __restrict__ gamma,
+                        const T* __restrict__ beta, float* __restrict__ mean_out,
+                        float* __restrict__ rstd_out, int64_t rows, int cols, int64_t x_row_stride,
+                        int64_t y_row_stride, float eps) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + warp;
+    if (row >= rows) return;
+    const T* xr = x + row * x_row_stride;
+    T* yr = y + row * y_row_stride;
+
+    uint4 v[CHUNKS];
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+        const int col = (c * 32 + lane) * 8;
+        if (col < cols) v[c] = ld_stream_16B(xr + col);
+        else v[c] = make_uint4(0, 0, 0, 0);
+    }
+
+    const float inv_n = 1.0f / (float)cols;
+    float mean = 0.f, rstd;
+    if (!RMS) {
+        float s = 0.f;
+#pragma unroll
+        for (int c = 0; c < CHUNKS; ++c) {
+            const uint32_t w[4] = {v[c].x, v[c].y, v[c].z, v[c].w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                float2 f = Elem<T>::unpack2(w[i]);
+                s += f.x + f.y;
+            }
+        }
+        mean = warp_sum(s) * inv_n;
+    }
+    {
+        float s = 0.f;
+#pragma unroll
+        for (int c = 0; c < CHUNKS; ++c) {
+            const int col = (c * 32 + lane) * 8;
+            if (col < cols) {
+                const uint32_t w[4] = {v[c].x, v[c].y, v[c].z, v[c].w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    float2 f = Elem<T>::unpack2(w[i]);
+                    const float a = f.x - mean, b = f.y - mean;
+                    s += a * a + b * b;
+                }
+            }
+        }
+        rstd = rsqrtf(warp_sum(s) * inv_n + eps);
+    }
+    if (lane == 0) {
+        if (mean_out) mean_out[row] = mean;
+        if (rstd_out) rstd_out[row] = rstd;
+    }
+
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+        const int col = (c * 32 + lane) * 8;
+        if (col < cols) {
+            const uint4 g = *reinterpret_cast<const uint4*>(gamma + col);
+            uint4 b = make_uint4(0, 0, 0, 0);
+            if (!RMS && beta != nullptr) b = *reinterpret_cast<const uint4*>(beta + col);
+            const uint32_t xw[4] = {v[c].x, v[c].y, v[c].z, v[c].w};
+            const uint32_t gw[4] = {g.x, g.y, g.z, g.w};
+            const uint32_t bw[4] = {b.x, b.y, b.z, b.w};
+            uint32_t ow[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 xf = Elem<T>::unpack2(xw[i]);
+                const float2 gf = Elem<T>::unpack2(gw[i]);
+                const float2 bf = Elem<T>::unpack2(bw[i]);
+                const float o0 = (xf.x - mean) * rstd * gf.x + bf.x;
+                const float o1 = (xf.y - mean) * rstd * gf.y + bf.y;
+                ow[i] = Elem<T>::pack2(o0, o1);
+            }
+            st_stream_16B(yr + col, make_uint4(ow[0], ow[1], ow[2], ow[3]));
+        }
+    }
+}
+
+// Generic strided path: one warp per row, three sweeps over the row.
+template <typename T, bool RMS>
+__global__ void __launch_bounds__(128)
+norm_fwd_generic_kernel(const T* __restrict__ x, T* __restrict__ y, const T* __restrict__ gamma,
+                        const T* __restrict__ beta, float* __restrict__ mean_out,
+                        float* __restrict__ rstd_out, int64_t rows, int64_t cols,
+                        int64_t x_row_stride, int64_t x_col_stride, int64_t y_row_stride,
+                        int64_t y_col_stride, float eps) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + warp;
+    if (row >= rows) return;
+    const T* xr = x + row * x_row_stride;
+    T* yr = y + row * y_row_stride;
+    const float inv_n = 1.0f / (float)cols;
+    float mean = 0.f;
+    if (!RMS) {
+        float s = 0.f;
+        for (int64_t c = lane; c < cols; c += 32) s += Elem<T>::to_f32(xr[c * x_col_stride]);
+        mean = warp_sum(s) * inv_n;
+    }
+    float s2 = 0.f;
+    for (int64_t c = lane; c < cols; c += 32) {
+        const float d = Elem<T>::to_f32(xr[c * x_col_stride]) - mean;
+        s2 += d * d;
+    }
+    const float rstd = rsqrtf(warp_sum(s2) * inv_n + eps);
+    if (lane == 0) {
+        if (mean_out) mean_out[row] = mean;
+        if (rstd_out) rstd_out[row] = rstd;
+    }
+    for (int64_t c = lane; c < cols; c += 32) {
+        const float xv = Elem<T>::to_f32(xr[c * x_col_stride]);
+        const float g = Elem<T>::to_f32(gamma[c]);
+        const float b = (!RMS && beta != nullptr) ? Elem<T>::to_f32(beta[c]) : 0.f;
+        yr[c * y_col_stride] = Elem<T>::from_f32((xv - mean) * rstd * g + b);
+    }
+}
+
+template <typename T, bool RMS>
+static int launch_norm_t(const kb_norm_params& p, cudaStream_t stream) {
+    const T* x = (const T*)p.x;
+    T* y = (T*)p.y;
+    const T* g = (const T*)p.gamma;
+    const T* b = (const T*)p.beta;
+    constexpr int kWarps = 4;
+    const unsigned grid = (unsigned)((p.rows + kWarps - 1) / kWarps);
+    const bool vec_ok = p.x_col_stride == 1 && p.y_col_stride == 1 && (p.cols % 8) == 0 &&
+                        (p.x_row_stride % 8) == 0 && (p.y_row_stride % 8) == 0 &&
+                        ((uintptr_t)p.x % 16) == 0 && ((uintptr_t)p.y % 16) == 0 &&
+                        ((uintptr_t)p.gamma % 16) == 0 &&
+                        (p.beta == nullptr || ((uintptr_t)p.beta % 16) == 0) && p.cols <= 6144;
+    if (vec_ok) {
+        const int chunks = (int)((p.cols + 255) / 256);
+#define KB_NORM_CASE(C)                                                                          \
+    if (chunks <= C) {                                                                           \
+        norm_fwd_rowwarp_kernel<T, C, RMS><<<grid, kWarps * 32, 0, stream>>>(                    \
+            x, y, g, b, p.mean, p.rstd, p.rows, (int)p.cols, p.x_row_stride, p.y_row_stride,     \
+            p.eps);                                                                              \
+        return KB_OK;                                                                            \
+    }
+        KB_NORM_CASE(1)
+        KB_NORM_CASE(2)
+        KB_NORM_CASE(3)
+        KB_NORM_CASE(4)
+        KB_NORM_CASE(6)
+        KB_NORM_CASE(8)
+        KB_NORM_CASE(12)
+        KB_NORM_CASE(16)
+        KB_NORM_CASE(24)
+#undef KB_NORM_CASE
+    }
+    norm_fwd_generic_kernel<T, RMS><<<grid, kWarps * 32, 0, stream>>>(
+        x, y, g, b, p.mean, p.rstd, p.rows, p.cols, p.x_row_stride, p.x_col_stride, p.y_row_stride,
+        p.y_col_stride, p.eps);
+    return KB_OK;
+}
+
+static int launch_norm(const kb_norm_params& p, cudaStream_t stream) {
+    if (p.dtype == KB_F16)
+        return p.is_rms ? launch_norm_t<__half, true>(p, stream) : launch_norm_t<__half, false>(p, stream);
+    if (p.dtype == KB_BF16)
+        return p.is_rms ? launch_norm_t<__nv_bfloat16, true>(p, stream)
+                        : launch_norm_t<__nv_bfloat16, false>(p, stream);
+    return KB_ERR_UNSUPPORTED;
+}
+
+}  // namespace kb

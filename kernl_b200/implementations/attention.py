@@ -1,0 +1,119 @@
+"""Fused attention front-end (reference: src/kernl/implementations/attention.py)."""
+import math
+from typing import List, Optional, Union
+
+import torch
+
+from kernl_b200 import _lib
+from kernl_b200.implementations._autocast import cast_if_autocast
+
+
+def attention_reference(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    output: torch.Tensor,
+    sm_scale: float,
+    is_causal: bool,
+    attention_mask: Union[torch.Tensor, None],
+) -> torch.Tensor:
+    """Eager attention, the ground truth of the reference's tests (attention.py:29-61):
+    softmax(q·kᵀ·sm_scale + mask, causal → -inf above the top-left-aligned diagonal)·v, written
+    into `output`. The reference builds its causal mask on "cuda" (:57); here it follows q.device
+    so that the same function also runs on CPU.
+    """
+    p = torch.matmul(q, k.transpose(2, 3)) * sm_scale
+    if attention_mask is not None:
+        p += attention_mask
+    if is_causal:
+        m_size, n_size = q.size(2), k.size(2)
+        keep = torch.tril(torch.ones((m_size, n_size), device=q.device))
+        p = torch.where(keep == 0, float("-inf"), p)
+    p = torch.nn.functional.softmax(p, dim=-1)
+    return torch.matmul(p.to(v.dtype), v, out=output)
+
+
+def closest_power_of_2(n: int, min_range: int = 16, max_range: int = 128) -> List[int]:
+    """Powers of two around n clamped to [min_range, max_range] (reference: attention.py:64-70)."""
+    n = max(min(n, max_range), min_range)
+    lo = math.floor(math.log2(n - 1))
+    hi = math.ceil(math.log2(n + 1))
+    return [2**i for i in range(lo, hi + 1)]
+
+
+def _tma_ready(t: torch.Tensor) -> torch.Tensor:
+    """q/k/v feed TMA: unit stride on the head dimension, other strides multiples of 8 elements,
+    16-byte aligned base. Tensors laid out differently (e.g. column-major q) are copied once."""
+    ok = t.stride(3) == 1 and t.data_ptr() % 16 == 0
+    for d in range(3):
+        if t.size(d) > 1 and t.stride(d) % 8 != 0:
+            ok = False
+    return t if ok else t.contiguous()
+
+
+def _check_mask(attention_mask, batch, heads, m_size, n_size):
+    assert attention_mask.size(0) == batch or attention_mask.size(0) == 1, "Incompatible broadcast batch dimension"
+    assert attention_mask.size(1) == heads or attention_mask.size(1) == 1, "Incompatible broadcast heads dimension"
+    assert attention_mask.size(2) == m_size or attention_mask.size(2) == 1, "Incompatible broadcast m_size dimension"
+    assert attention_mask.size(3) == n_size, "Last size of mask must broadcast on QK^t"
+
+
+def make_params(q, k, v, output, sm_scale, is_causal, attention_mask) -> "_lib.AttnParams":
+    batch, heads, m_size, dhead = q.size()
+    n_size = k.size(2)
+    p = _lib.AttnParams()
+    p.q, p.k, p.v, p.o = q.data_ptr(), k.data_ptr(), v.data_ptr(), output.data_ptr()
+    p.B, p.H, p.M, p.N, p.D = batch, heads, m_size, n_size, dhead
+    for i in range(4):
+        p.q_strides[i], p.k_strides[i] = q.stride(i), k.stride(i)
+        p.v_strides[i], p.o_strides[i] = v.stride(i), output.stride(i)
+    if attention_mask is not None:
+        p.mask = attention_mask.data_ptr()
+        for i in range(4):
+            # a broadcast (size-1) dimension never advances
+            p.mask_strides[i] = attention_mask.stride(i) if attention_mask.size(i) > 1 else 0
+        p.mask_dtype = _lib.dtype_code(attention_mask.dtype)
+    else:
+        p.mask = None
+        p.mask_dtype = _lib.KB_F32
+    p.sm_scale = float(sm_scale)
+    p.is_causal = 1 if is_causal else 0
+    p.dtype = _lib.dtype_code(q.dtype)
+    return p
+
+
+def attention_forward(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    output: torch.Tensor,
+    sm_scale: float,
+    is_causal: bool = False,
+    attention_mask: Optional[torch.Tensor] = None,
+):
+    """Flash attention on the tcgen05 kernel, written into `output` (which is returned).
+
+    Same contract as the reference's `attention_forward` (attention.py:532-541 →
+    Attention.forward :438-529): q [B,H,M,D], k/v [B,H,N,D], all fp16 or all bf16;
+    attention_mask additive, broadcastable over batch / heads / rows with last size N; -inf mask
+    entries behave as the lowest finite value of the mask dtype; `is_causal` keeps col <= row.
+    Head dimension 64 or 128.
+    """
+    q, k, v, output, attention_mask = cast_if_autocast(q, k, v, output, attention_mask)
+    assert q.shape[-1] == k.shape[-1]
+    assert (
+        q.dtype == k.dtype == v.dtype == output.dtype
+    ), f"All tensors must have the same dtype: {q.dtype}, {k.dtype}, {v.dtype}, {output.dtype}"
+    assert q.dtype in [torch.float16, torch.bfloat16], f"Only float16 and bfloat16 are supported, got {q.dtype}"
+    assert q.is_cuda, "kernl_b200 ops run on a CUDA (sm_100a) device only"
+    batch, heads, m_size, dhead = q.size()
+    n_size = k.size(2)
+    assert dhead in (64, 128), f"head dimension must be 64 or 128 on the tcgen05 kernel, got {dhead}"
+    if attention_mask is not None:
+        _check_mask(attention_mask, batch, heads, m_size, n_size)
+        assert attention_mask.dtype in (torch.float16, torch.bfloat16, torch.float32)
+    qc, kc, vc = _tma_ready(q), _tma_ready(k), _tma_ready(v)
+    p = make_params(qc, kc, vc, output, sm_scale, is_causal, attention_mask)
+    with torch.cuda.device(q.device):
+        _lib.check(_lib.load().kb_attention_fwd(p, _lib.current_stream(q.device)), "attention_forward")
+    return output

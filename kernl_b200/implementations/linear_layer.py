@@ -1,0 +1,79 @@
+"""Fused linear front-end (reference: src/kernl/implementations/linear_layer.py)."""
+from typing import Optional
+
+import torch
+
+from kernl_b200 import _lib
+from kernl_b200.implementations._autocast import cast_if_autocast
+
+
+def linear_layer(
+    x: torch.Tensor,
+    weight: torch.Tensor,
+    bias: Optional[torch.Tensor],
+    activation="",
+    act_inputs: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """activation(x @ weight.T + bias) on the tcgen05 GEMM kernel.
+
+    Same contract as the reference's `linear_layer` (linear_layer.py:285-292 →
+    LinearLayer.forward :213-282): x is 2-D or 3-D (flattened over its first two dims), weight is
+    [N, K] contiguous, bias [N] contiguous or None, activation in {"", "tanh", "gelu",
+    "fast_gelu", "relu"} (plus "silu"); `act_inputs`, if given, receives the pre-activation
+    values. Returns [M, N], or [x.shape[0], -1, N] for 3-D x. fp32 inputs (tf32 in the
+    reference) are not supported: fp16/bf16 only.
+    """
+    x, weight, bias = cast_if_autocast(x, weight, bias)
+    x_ = x if x.ndim == 2 else x.flatten(0, 1)
+    assert x.dtype == weight.dtype, f"Input and weight must have the same dtype, got {x.dtype} and {weight.dtype}"
+    if bias is not None:
+        assert x.dtype == bias.dtype, f"Input and bias must have the same dtype, got {x.dtype} and {bias.dtype}"
+    assert x.dtype in (torch.float16, torch.bfloat16), f"Only float16 and bfloat16 are supported, got {x.dtype}"
+    assert x_.shape[1] == weight.shape[1], f"Incompatible dimensions: {x_.shape} - {weight.shape}"
+    assert bias is None or bias.is_contiguous()
+    assert bias is None or bias.shape[0] == weight.shape[0], "Incompatible dimensions in between weight and bias"
+    assert weight.is_contiguous()
+    assert activation in _lib.ACTIVATIONS, f"Unknown activation: {activation}"
+    assert x.is_cuda, "kernl_b200 ops run on a CUDA (sm_100a) device only"
+
+    M, K = x_.shape
+    N = weight.shape[0]
+    # The TMA path wants unit K stride and 16-byte aligned rows; anything else is copied once.
+    if x_.stride(1) != 1 or x_.stride(0) % 8 != 0 or x_.data_ptr() % 16 != 0:
+        x_ = x_.contiguous()
+    if K % 8 != 0:
+        # K is padded with zeros to the next multiple of 8 (16-byte rows for TMA); zeros add nothing.
+        pad = 8 - K % 8
+        x_ = torch.nn.functional.pad(x_, (0, pad))
+        weight = torch.nn.functional.pad(weight, (0, pad))
+        K += pad
+    outputs = torch.empty((M, N), device=x.device, dtype=x.dtype)
+    if act_inputs is not None:
+        assert act_inputs.shape == (M, N) and act_inputs.dtype == x.dtype and act_inputs.is_contiguous()
+    if M > 0:
+        p = _lib.LinearParams(
+            x=x_.data_ptr(), w=weight.data_ptr(), bias=bias.data_ptr() if bias is not None else None,
+            y=outputs.data_ptr(), act_inputs=act_inputs.data_ptr() if act_inputs is not None else None,
+            M=M, N=N, K=K, x_row_stride=x_.stride(0), y_row_stride=outputs.stride(0),
+            activation=_lib.ACTIVATIONS[activation], dtype=_lib.dtype_code(x.dtype),
+        )
+        with torch.cuda.device(x.device):
+            _lib.check(_lib.load().kb_linear_fwd(p, _lib.current_stream(x.device)), "linear_layer")
+    return outputs if x.ndim == 2 else outputs.reshape(x.shape[0], -1, N)
+
+
+def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
+    """silu(gate) * up for gate_up = [..., 2*N] laid out as [gate | up] (SwiGLU feed-forward)."""
+    assert gate_up.dtype in (torch.float16, torch.bfloat16) and gate_up.is_contiguous()
+    n2 = gate_up.shape[-1]
+    assert n2 % 16 == 0
+    n = n2 // 2
+    m = gate_up.numel() // n2
+    out = torch.empty(gate_up.shape[:-1] + (n,), dtype=gate_up.dtype, device=gate_up.device)
+    with torch.cuda.device(gate_up.device):
+        _lib.check(
+            _lib.load().kb_silu_mul(gate_up.data_ptr(), out.data_ptr(), m, n, _lib.dtype_code(gate_up.dtype),
+                                    _lib.current_stream(gate_up.device)),
+            "silu_mul",
+        )
+    return out

@@ -1,0 +1,356 @@
+#!/usr/bin/env python
+"""Benchmark of the fused transformer-inference hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Headline workload (N=1): the isolated fused-attention op of the baseline's second config —
+fp16 Q/K/V [8, 12, 512, 64] ~ N(0,1), non-causal, per-sequence random padding mask (valid length
+uniform in [64, 512]), sm_scale = 1/8. One "step" = one attention forward over that batch.
+Metric: fused attention TFLOP/s with the algorithmic flop count 4·B·H·M·N·D (padding is additive
+data and is not discounted).
+
+Timing: every step's kernel is bracketed by its own CUDA events on the launching stream; a 256 MB
+buffer is zeroed before each step (outside the events) so Q/K/V are cold in the 126 MB L2 and the
+host launch latency is hidden behind the flush. ms_per_step is the mean of the K event durations;
+with N GPUs each rank runs the same per-GPU batch (independent replicas, no collective in the data
+path), the ranks are bracketed by barrier + synchronize, and the slowest rank's time is used.
+
+Extra objects on the JSON line: `roofline` (tensor-pipe bound of the attention kernel, against the
+measured cuBLAS bf16 peak), `cpu_baseline` (the CPU oracle — a restatement of the reference's eager
+attention — timed on this box's host cores), `e2e` (the same op through the public Python API with
+pinned host buffers: H2D of q/k/v/mask + kernel + D2H of the output inside the timed region),
+`ops` (fused linear and norm kernels against their own rooflines) and `clocks`.
+
+`--impl reference` times the reference's CPU implementation of the same op (its eager
+`attention_reference`, restated by the oracle) on the host cores with all threads.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOAD = {"B": 8, "H": 12, "S": 512, "D": 64}
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            p = json.load(open(path))
+            return {k: float(p[k]) for k in FALLBACK_PEAKS}, "measured"
+        except Exception:
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+def make_inputs(seed=0):
+    """Seeded CPU fp32 inputs of the headline workload, so the CPU baseline and the GPU see the
+    same values."""
+    import torch
+
+    B, H, S, D = (WORKLOAD[k] for k in "BHSD")
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randn((B, H, S, D), generator=g)
+    k = torch.randn((B, H, S, D), generator=g)
+    v = torch.randn((B, H, S, D), generator=g)
+    valid = torch.randint(64, S + 1, (B,), generator=g)
+    mask = torch.where(valid[:, None] > torch.arange(S)[None, :], 0.0, float("-inf")).reshape(B, 1, 1, S)
+    return q, k, v, mask
+
+
+def attention_flops():
+    B, H, S, D = (WORKLOAD[k] for k in "BHSD")
+    return 4.0 * B * H * S * S * D
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu_index = gpu_index
+        self.samples = []
+        self.proc = None
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.samples.append((time.time(), line.strip()))
+
+    def stop(self, t0, t1):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        rows = [s for (t, s) in self.samples if t0 - 0.05 <= t <= t1 + 0.15] or [s for (_, s) in self.samples]
+        mhz, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in rows:
+            parts = [x.strip() for x in r.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                mhz.append(float(parts[0]))
+                mx = float(parts[1])
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(mhz) if mhz else None, "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(mhz)}
+
+
+def time_cpu_attention(steps, warmup):
+    """The reference's eager attention (restated by the oracle) on the host cores, fp32."""
+    import torch
+    from oracle import kernl_oracle as O
+
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    q, k, v, mask = make_inputs()
+    for _ in range(warmup):
+        O.attention(q, k, v, 0.125, False, mask)
+    ts = []
+    for _ in range(steps):
+        t0 = time.perf_counter()
+        O.attention(q, k, v, 0.125, False, mask)
+        ts.append(time.perf_counter() - t0)
+    return statistics.mean(ts), cores
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps, warmup = args.steps, max(args.warmup, 1)
+    sec, cores = time_cpu_attention(steps, warmup)
+    tflops = attention_flops() / sec / 1e12
+    line = {
+        "impl": "reference",
+        "metric": "fused attention TFLOP/s", "value": tflops, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "ms_per_step": sec * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "attention fwd [8,12,512,64], padding mask, non-causal (baseline config 2)",
+                   "note": "reference's eager attention_reference restated in fp32 PyTorch on the host CPU; "
+                           "its Triton path needs an Ampere+ GPU and Triton 2.0 and cannot run here"},
+        "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                         "sample": f"{steps} full steps of the workload"},
+        "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def event_time(fn, steps, warmup, flush):
+    """Per-step CUDA-event durations (ms) with an L2 flush before each step, outside the events."""
+    import torch
+
+    for _ in range(warmup):
+        flush.zero_()
+        fn()
+    torch.cuda.synchronize()
+    pairs = []
+    for _ in range(steps):
+        flush.zero_()
+        s = torch.cuda.Event(enable_timing=True)
+        e = torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        pairs.append((s, e))
+    torch.cuda.synchronize()
+    return [s.elapsed_time(e) for s, e in pairs]
+
+
+def run_ours(args):
+    import torch
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (sm_100a); there is no CPU fallback")
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    from kernl_b200 import _lib, build
+    from kernl_b200.implementations.attention import attention_forward
+    from kernl_b200.implementations.layer_norm import layer_norm
+    from kernl_b200.implementations.linear_layer import linear_layer
+
+    build.build()
+    _lib.load()
+    peaks, peak_kind = load_peaks()
+    steps, warmup = args.steps, max(args.warmup, 3)
+    dev = torch.device("cuda", local_rank)
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.int8, device=dev)
+
+    q32, k32, v32, mask32 = make_inputs()
+    q, k, v, mask = (t.half().to(dev) for t in (q32, k32, v32, mask32))
+    out = torch.empty_like(q)
+    step = lambda: attention_forward(q, k, v, out, 0.125, False, mask)
+
+    # ---------------- timed region: K steps, device-timed, bracketed by barrier + synchronize
+    step()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    t_wall0 = time.time()
+    durs = event_time(step, steps, warmup, flush)
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    t_wall1 = time.time()
+    clocks = sampler.stop(t_wall0, t_wall1)
+    _lib.device_status()
+    ms_local = statistics.mean(durs)
+    ms = ms_local
+    if dist is not None:
+        t = torch.tensor([ms_local], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    flops = attention_flops()
+    value = world * flops / (ms * 1e-3) / 1e12
+
+    # ---------------- end to end through the public API with host buffers
+    hq, hk, hv, hm = (t.half().pin_memory() for t in (q32, k32, v32, mask32))
+    hout = torch.empty(q.shape, dtype=torch.float16).pin_memory()
+    dq, dk, dv, dm, do = (torch.empty_like(t, device=dev) for t in (hq, hk, hv, hm, hq))
+
+    def e2e_step():
+        dq.copy_(hq, non_blocking=True)
+        dk.copy_(hk, non_blocking=True)
+        dv.copy_(hv, non_blocking=True)
+        dm.copy_(hm, non_blocking=True)
+        attention_forward(dq, dk, dv, do, 0.125, False, dm)
+        hout.copy_(do, non_blocking=True)
+
+    for _ in range(3):
+        e2e_step()
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    e2e_t0 = time.perf_counter()
+    for _ in range(steps):
+        e2e_step()
+    torch.cuda.synchronize()
+    e2e_ms_local = (time.perf_counter() - e2e_t0) * 1e3 / steps
+    e2e_ms = e2e_ms_local
+    if dist is not None:
+        t = torch.tensor([e2e_ms_local], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    h2d = sum(t.numel() * t.element_size() for t in (hq, hk, hv, hm))
+    d2h = hout.numel() * hout.element_size()
+
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    # ---------------- rank 0 only: other hot-path kernels against their rooflines, CPU baseline
+    ops = {}
+    g = torch.Generator().manual_seed(0)
+    M, K, N = 8192, 4096, 11008
+    x = torch.randn((M, K), generator=g).half().to(dev)
+    w = (torch.randn((N, K), generator=g) * 0.02).half().to(dev)
+    b = (torch.randn((N,), generator=g) * 0.02).half().to(dev)
+    for act in ("", "gelu"):
+        d = event_time(lambda: linear_layer(x, w, b, act), 10, 3, flush)
+        tf = 2.0 * M * N * K / (statistics.mean(d) * 1e-3) / 1e12
+        ops[f"linear_M8192_K4096_N11008_{act or 'none'}"] = {
+            "tflops": round(tf, 1), "frac_of_tensor_peak": round(tf / peaks["bf16_tflops"], 3), "ms": round(statistics.mean(d), 4)}
+    del x, w, b
+    for cols in (768, 4096):
+        xn = torch.randn((16384, cols), generator=g).half().to(dev)
+        gm = (torch.rand((cols,), generator=g) + 0.5).half().to(dev)
+        bt = (torch.randn((cols,), generator=g) * 0.1).half().to(dev)
+        for rms in (False, True):
+            d = event_time(lambda: layer_norm(xn, gm, None if rms else bt, 1e-5, use_rms_norm=rms), 20, 3, flush)
+            gbs = (4.0 * 16384 * cols + 4 * cols) / (statistics.mean(d) * 1e-3) / 1e9
+            ops[f"{'rmsnorm' if rms else 'layernorm'}_16384x{cols}"] = {
+                "gbs": round(gbs, 1), "frac_of_hbm_peak": round(gbs / peaks["hbm_gbs"], 3), "ms": round(statistics.mean(d), 4)}
+    _lib.device_status()
+
+    cpu_sec, cores = time_cpu_attention(5, 2)
+    cpu_tflops = flops / cpu_sec / 1e12
+
+    per_launch_tflops = flops / (ms_local * 1e-3) / 1e12
+    line = {
+        "metric": "fused attention TFLOP/s", "value": value, "unit": "TFLOP/s",
+        "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {
+            "workload": "attention fwd fp16 [batch 8, heads 12, seq 512, head_dim 64], per-sequence padding mask, "
+                        "non-causal, sm_scale 1/8 (baseline config 2)",
+            "per_gpu_batch": WORKLOAD["B"], "parallelism": f"replicas x{world} (batch-sharded, no collective)",
+            "timing": "CUDA events per step on the launching stream; 256 MB L2 flush before each step, outside the events",
+            "flops_per_step": flops,
+        },
+        "roofline": {
+            "bound": "tensor", "achieved": per_launch_tflops, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+            "frac": per_launch_tflops / peaks["bf16_tflops"], "traffic": None,
+            "peak_source": f"{peak_kind} cuBLAS bf16 burst (MEASURED_PEAKS.json)" if peak_kind == "measured" else "fallback 1590 TFLOP/s",
+            "kernel": "attention_tc_kernel<half,64>",
+        },
+        "cpu_baseline": {"value": cpu_tflops, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                         "sample": "5 full steps of the workload in fp32 (oracle restatement of the reference's eager attention)"},
+        "e2e": {"value": world * flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
+        "gpu_launches": steps,
+        "clocks": clocks,
+        "ops": ops,
+    }
+    print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

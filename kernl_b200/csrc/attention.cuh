@@ -102,6 +102,15 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
+    // A wait that expired in an earlier CTA or launch leaves the status word set: do no work until
+    // the host has read (and cleared) it, so that one failure cannot cost a second per CTA.
+    {
+        __shared__ int s_skip;
+        if (threadIdx.x == 0) s_skip = *reinterpret_cast<volatile int*>(&g_device_status[0]);
+        __syncthreads();
+        if (s_skip != 0) return;
+    }
+
     // Work assignment: heavy (late) query tiles first so that causal work is balanced.
     const int BH = p.B * p.H;
     const int pair = p.num_pairs - 1 - (int)(blockIdx.x / BH);

@@ -30,17 +30,36 @@ struct GemmCfg {
     static constexpr int kSmemBytes = kStages * kStageBytes + 256 + 1024;
 };
 
-__device__ __forceinline__ float act_apply(float z, int activation) {
-    switch (activation) {
-        case KB_ACT_TANH: return tanhf(z);
-        case KB_ACT_GELU: return z * 0.5f * (1.0f + erff(z * 0.70710678118654752440f));
-        case KB_ACT_FAST_GELU:
-            return 0.5f * z * (1.0f + tanhf(0.79788456080286535588f * (z + 0.044715f * z * z * z)));
-        case KB_ACT_RELU: return fmaxf(z, 0.0f);
-        case KB_ACT_SILU: return z / (1.0f + __expf(-z));
-        default: return z;
-    }
+// Activations of the epilogue, evaluated on the fp32 accumulator (+bias).
+// tanh uses the hardware tanh.approx (relative error about 2^-11, far below the rounding of the
+// 16-bit output). erf uses the rational approximation 7.1.26 of Abramowitz & Stegun,
+// erf(x) = 1 - (a1 t + ... + a5 t^5) exp(-x^2) with t = 1/(1 + p x), absolute error <= 1.5e-7 in
+// exact arithmetic (about 1e-6 in fp32): the libdevice erff costs several times more instructions
+// than the GEMM main loop leaves room for in the epilogue warps.
+__device__ __forceinline__ float act_tanh(float z) {
+    float y;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(z));
+    return y;
 }
+__device__ __forceinline__ float act_erf(float x) {
+    const float ax = fabsf(x);
+    const float t = __fdividef(1.0f, fmaf(0.3275911f, ax, 1.0f));
+    float poly = fmaf(1.061405429f, t, -1.453152027f);
+    poly = fmaf(poly, t, 1.421413741f);
+    poly = fmaf(poly, t, -0.284496736f);
+    poly = fmaf(poly, t, 0.254829592f);
+    poly *= t;
+    const float e = __expf(-ax * ax);
+    const float r = fmaf(-poly, e, 1.0f);
+    return copysignf(r, x);
+}
+__device__ __forceinline__ float act_gelu(float z) {
+    return z * 0.5f * (1.0f + act_erf(z * 0.70710678118654752440f));
+}
+__device__ __forceinline__ float act_fast_gelu(float z) {
+    return 0.5f * z * (1.0f + act_tanh(0.79788456080286535588f * (z + 0.044715f * z * z * z)));
+}
+__device__ __forceinline__ float act_silu(float z) { return __fdividef(z, 1.0f + __expf(-z)); }
 
 __device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& m_idx, int& n_idx) {
     // Grouped rasterisation: 8 row-tiles share each sweep over the column tiles so that the
@@ -76,6 +95,15 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
     auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    // A wait that expired in an earlier CTA or launch leaves the status word set: do no work until
+    // the host has read (and cleared) it, so that one failure cannot cost a second per CTA.
+    {
+        __shared__ int s_skip;
+        if (threadIdx.x == 0) s_skip = *reinterpret_cast<volatile int*>(&g_device_status[0]);
+        __syncthreads();
+        if (s_skip != 0) return;
+    }
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -230,9 +258,30 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                                 if (col0 + j < N) a_row[col0 + j] = Elem<T>::from_f32(z[j]);
                         }
                     }
-                    if (activation != KB_ACT_NONE) {
+                    // The switch sits outside the element loop so that each case unrolls over
+                    // registers.
+                    switch (activation) {
+                        case KB_ACT_TANH:
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) z[j] = act_apply(z[j], activation);
+                            for (int j = 0; j < 32; ++j) z[j] = act_tanh(z[j]);
+                            break;
+                        case KB_ACT_GELU:
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) z[j] = act_gelu(z[j]);
+                            break;
+                        case KB_ACT_FAST_GELU:
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) z[j] = act_fast_gelu(z[j]);
+                            break;
+                        case KB_ACT_RELU:
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) z[j] = fmaxf(z[j], 0.0f);
+                            break;
+                        case KB_ACT_SILU:
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) z[j] = act_silu(z[j]);
+                            break;
+                        default: break;
                     }
                     if (vec) {
 #pragma unroll

@@ -1,0 +1,75 @@
+"""Generates tests/golden/*.npz from the reference's own eager functions.
+
+Run in a container that has the reference tree (default /root/reference, override with
+KERNL_REFERENCE_ROOT): it imports `attention_reference`, `pytorch_naive_layernorm` and
+`pytorch_naive_rmsnorm` from the reference's sources, evaluates them on seeded CPU inputs and
+stores inputs and outputs. The fixtures are small (a few hundred KB in total) and committed; the
+tests only read the .npz files, never the reference tree.
+
+Not covered (and why): the causal branch of `attention_reference` builds its mask on "cuda"
+(src/kernl/implementations/attention.py:57) and cannot run on a CPU-only box; the reference's
+`linear_layer` module does not import under the installed Triton (`triton.ops` is gone), and its
+tests use plain `F.linear` + activation as ground truth anyway.
+"""
+import os
+import sys
+
+import numpy as np
+import torch
+
+REF_ROOT = os.environ.get("KERNL_REFERENCE_ROOT", "/root/reference")
+sys.path.insert(0, os.path.join(REF_ROOT, "src"))
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def main():
+    from kernl.implementations.attention import attention_reference
+    from kernl.implementations.layer_norm import pytorch_naive_layernorm, pytorch_naive_rmsnorm
+
+    # ---- attention, non-causal: no mask / broadcast padding mask / full bias mask / row-broadcast
+    cases = {}
+    g = torch.Generator().manual_seed(0)
+    for name, (B, H, M, N, D, kind, scale) in {
+        "nomask": (2, 3, 33, 33, 64, None, 0.3),
+        "pad": (2, 2, 40, 40, 64, "pad", 0.125),
+        "bias": (1, 2, 24, 50, 64, "bias", 0.3),
+        "cross": (1, 8, 1, 24, 64, "rowvec", 1.0),
+        "d128": (1, 2, 17, 29, 128, "bias", 0.0883883),
+    }.items():
+        q = torch.randn(B, H, M, D, generator=g)
+        k = torch.randn(B, H, N, D, generator=g)
+        v = torch.randn(B, H, N, D, generator=g)
+        mask = None
+        if kind == "pad":
+            valid = torch.randint(1, N, (B,), generator=g)
+            mask = torch.where(valid[:, None] > torch.arange(N)[None, :], 0.0, float("-inf")).reshape(B, 1, 1, N)
+        elif kind == "bias":
+            mask = torch.rand(B, H, M, N, generator=g)
+        elif kind == "rowvec":
+            mask = torch.rand(B, H, 1, N, generator=g)
+        out = attention_reference(q, k, v, torch.empty_like(q), scale, False, mask)
+        cases[f"{name}_q"], cases[f"{name}_k"], cases[f"{name}_v"] = q.numpy(), k.numpy(), v.numpy()
+        if mask is not None:
+            cases[f"{name}_mask"] = mask.numpy()
+        cases[f"{name}_scale"] = np.float32(scale)
+        cases[f"{name}_out"] = out.numpy()
+    np.savez_compressed(os.path.join(HERE, "attention_reference.npz"), **cases)
+
+    # ---- norms: x = -20 + 0.5*randn as in the reference's test (test/test_layer_norm.py:58)
+    cases = {}
+    for n in (128, 250, 768):
+        x = -20 + 0.5 * torch.randn(16, n, generator=g)
+        w = torch.rand(n, generator=g) + 0.5
+        b = torch.randn(n, generator=g) * 0.1
+        cases[f"n{n}_x"], cases[f"n{n}_w"], cases[f"n{n}_b"] = x.numpy(), w.numpy(), b.numpy()
+        # pytorch_naive_layernorm uses the unbiased variance (torch.var default); stored as is,
+        # next to F.layer_norm which the reference's tests use as ground truth.
+        cases[f"n{n}_naive_ln"] = pytorch_naive_layernorm(x.clone(), w, b, 1e-5).numpy()
+        cases[f"n{n}_f_ln"] = torch.nn.functional.layer_norm(x, (n,), w, b, 1e-5).numpy()
+        cases[f"n{n}_rms"] = pytorch_naive_rmsnorm(x.clone(), w, 1e-6).numpy()
+    np.savez_compressed(os.path.join(HERE, "norm_reference.npz"), **cases)
+    print("wrote", os.listdir(HERE))
+
+
+if __name__ == "__main__":
+    main()

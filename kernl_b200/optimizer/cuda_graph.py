@@ -1,0 +1,126 @@
+"""CUDA-graph capture wrapper (reference: src/kernl/optimizer/cuda_graph.py).
+
+Same semantics as the reference: the callable is captured once for the shapes of its example
+inputs; every call copies the new inputs into a static arena (first-fit-decreasing bin packing
+over a global list of pools) and replays the graph; the outputs are static tensors that the next
+call overwrites, returned as a list (callers index [0]). The reference goes through
+`torch._inductor.compile_fx.cudagraphify_impl`; this implementation captures with
+`torch.cuda.CUDAGraph` directly: warm-up on a side stream, capture, replay.
+"""
+import math
+from typing import Callable, Iterable, Optional, Union
+
+import torch
+from torch._subclasses import FakeTensor
+
+from kernl_b200.optimizer.pool_cuda_graphs import CudaGraphPool, get_aligned_size
+
+static_inputs_pool = []
+
+
+def get_pool_size(inputs: list, existing_pools: list) -> int:
+    """Size of a new pool: at least the sum of the aligned inputs and at least the largest
+    existing pool; below 1 GiB rounded up to a power of two so that small pools stay reusable
+    (reference: cuda_graph.py:29-44)."""
+    size = sum(get_aligned_size(p) for p in inputs)
+    size = max([size] + [p.size for p in existing_pools])
+    if size < 1024 * 1024 * 1024:
+        size = 2 ** math.ceil(math.log2(size))
+    return max(size, 8)
+
+
+def argsort(iterable: Iterable, key: Callable) -> list:
+    """Indices that sort `iterable` by `key` (stable) (reference: cuda_graph.py:47-54)."""
+    return [i for i, _ in sorted(enumerate(iterable), key=lambda pair: key(pair[1]))]
+
+
+def prepare_inputs(inputs: list, pools: list) -> list:
+    """Copy `inputs` into the pools and return the copies, in input order.
+
+    Deterministic, so that the same shapes always land on the same addresses: pools are reset and
+    sorted by size ascending, inputs are visited by storage size ascending, each goes into the
+    first pool with room; the leftovers share one new pool (reference: cuda_graph.py:57-100).
+    """
+    for p in pools:
+        p.reset()
+    pools.sort(key=lambda p: p.size)
+    order = argsort(inputs, key=lambda t: t.untyped_storage().size())
+    copies: list = [None] * len(inputs)
+    leftovers = []
+    for idx in order:
+        t = inputs[idx]
+        for pool in pools:
+            if pool.can_store(t):
+                copies[idx] = pool.copy_to_pool(t)
+                break
+        else:
+            leftovers.append(idx)
+    if leftovers:
+        new_pool = CudaGraphPool(
+            get_pool_size([inputs[i] for i in leftovers], existing_pools=pools), device=inputs[0].device
+        )
+        pools.append(new_pool)
+        for idx in leftovers:
+            assert new_pool.can_store(inputs[idx])
+            copies[idx] = new_pool.copy_to_pool(inputs[idx])
+    return copies
+
+
+def _capture(model: Callable, static_inputs: list) -> Callable:
+    """Warm up on a side stream, capture one graph, return a replay function."""
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        model(*static_inputs)
+    side.synchronize()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        static_outputs = model(*static_inputs)
+    if not isinstance(static_outputs, (list, tuple)):
+        static_outputs = (static_outputs,)
+    static_outputs = list(static_outputs)
+
+    def replay():
+        graph.replay()
+        return static_outputs
+
+    return replay
+
+
+def cuda_graphs_wrapper(model: Callable, inputs: Union[list, tuple]) -> Callable:
+    """Run `model` through a CUDA graph (reference: cuda_graph.py:103-138).
+
+    With real example inputs the graph is captured now (after one extra eager call, because
+    kernels may mutate their inputs during warm-up); with FakeTensor inputs everything is deferred
+    to the first real call, with the RNG state preserved around warm-up and capture.
+    """
+    assert isinstance(inputs, (list, tuple))
+    if not any(isinstance(inp, FakeTensor) for inp in inputs):
+        static_inputs = prepare_inputs(inputs=list(inputs), pools=static_inputs_pool)
+        model(*static_inputs)
+        replay = _capture(model, static_inputs)
+
+        def run_now(*args):
+            prepare_inputs(inputs=list(args), pools=static_inputs_pool)
+            return replay()
+
+        return run_now
+
+    replay: Optional[Callable] = None
+
+    def run(*new_inputs):
+        nonlocal replay
+        static_inputs = prepare_inputs(inputs=list(new_inputs), pools=static_inputs_pool)
+        if replay is None:
+            cpu_state = torch.get_rng_state()
+            cuda_state = torch.cuda.get_rng_state()
+            model(*static_inputs)
+            replay = _capture(model, static_inputs)
+            torch.set_rng_state(cpu_state)
+            torch.cuda.set_rng_state(cuda_state)
+        return replay()
+
+    return run

@@ -1,0 +1,146 @@
+"""Pool and bin-packing logic of the CUDA-graph wrapper on CPU tensors (as the reference tests it,
+test/test_cuda_graph.py:7-62), plus capture/replay on the GPU."""
+import pytest
+import torch
+
+from kernl_b200.optimizer.cuda_graph import argsort, get_pool_size, prepare_inputs
+from kernl_b200.optimizer.pool_cuda_graphs import CudaGraphPool, get_aligned_size
+
+
+def test_argsort():
+    assert argsort(iterable=[1, 5, 3, 4, 5], key=lambda x: x) == [0, 2, 3, 1, 4]
+
+
+def test_aligned_size():
+    t = torch.ones((33,))
+    assert get_aligned_size(t, alignment=16) == 144
+    assert get_aligned_size(t, alignment=32) == 160
+    assert get_aligned_size(torch.ones((1,)), alignment=8) == 8
+
+
+def test_pool_size_rule():
+    small = [torch.ones(3, dtype=torch.float32)]  # 12 bytes -> 16 aligned -> 16
+    assert get_pool_size(small, []) == 16
+    assert get_pool_size(small, [CudaGraphPool(48, device="cpu")]) == 64
+    big = [torch.empty(0, dtype=torch.int8).new_empty(1)]
+    assert get_pool_size(big, []) == 8
+
+
+def test_cuda_graph_pool_e2e():
+    all_inputs = [
+        torch.tensor([1, 2, 3]),
+        torch.tensor([4, 5, 6, 7], dtype=torch.bfloat16),
+        torch.tensor([8]),
+        torch.tensor([9, 10, 11, 12], dtype=torch.double),
+        torch.tensor([13, 14], dtype=torch.int8),
+        torch.tensor([15], dtype=torch.float32),
+        torch.tensor([16], dtype=torch.int64),
+    ]
+    all_pools = [CudaGraphPool(32, device="cpu"), CudaGraphPool(48, device="cpu")]
+    new_tensors = prepare_inputs(inputs=all_inputs, pools=all_pools)
+    assert len(new_tensors) == len(all_inputs)
+    assert len(all_pools) == 3
+    for original, copy in zip(all_inputs, new_tensors):
+        assert original.shape == copy.shape
+        assert original.stride() == copy.stride()
+        assert original.dtype == copy.dtype
+        assert original.device == copy.device
+        assert torch.all(original == copy)
+        assert original.data_ptr() != copy.data_ptr()
+    # deterministic: the same inputs land on the same addresses again
+    again = prepare_inputs(inputs=all_inputs, pools=all_pools)
+    assert [t.data_ptr() for t in again] == [t.data_ptr() for t in new_tensors]
+    assert len(all_pools) == 3
+
+
+def test_cuda_graph_pool_cpu():
+    c = CudaGraphPool(8, device="cpu")
+    assert not c.can_store(torch.ones((16,), dtype=torch.int64))
+    t = torch.ones((1,), dtype=torch.int8)
+    assert c.can_store(t)
+    assert c.offset == 0
+    c.copy_to_pool(t)
+    assert c.offset == 8
+    c.reset()
+    assert c.offset == 0
+
+
+def test_zero_stride_inputs_are_materialised():
+    pool = CudaGraphPool(64, device="cpu")
+    t = torch.tensor([1.0, 2.0]).reshape(1, 2).expand(1, 2)[:, :1].expand(1, 4)  # stride (2, 0)
+    copy = pool.copy_to_pool(t)
+    assert copy.stride() == (2, 1)
+    assert torch.equal(copy, t)
+
+
+@pytest.mark.gpu
+def test_pool_rejects_other_device_and_exact_fit():
+    c = CudaGraphPool(8, device="cpu")
+    assert not c.can_store(torch.ones((1,), dtype=torch.int8).cuda())
+    pool = CudaGraphPool(16)
+    tensor = torch.tensor([1, 1, 1, 1], dtype=torch.float32, device="cuda")
+    assert len(tensor.untyped_storage()) == 16
+    pool.copy_to_pool(tensor)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("fake", [False, True], ids=["real_inputs", "deferred"])
+def test_cuda_graphs_wrapper_replays_kernels(lib, fake):
+    """Capture a linear + layer-norm chain; replay with new inputs; outputs are static tensors
+    overwritten by the next call (reference semantics, test/test_linear_layer.py:91-95)."""
+    from torch._subclasses import FakeTensorMode
+
+    from kernl_b200.implementations.layer_norm import layer_norm
+    from kernl_b200.implementations.linear_layer import linear_layer
+    from kernl_b200.optimizer import cuda_graph
+    from oracle import kernl_oracle as O
+
+    cuda_graph.static_inputs_pool.clear()
+    g = torch.Generator().manual_seed(0)
+    w = (torch.randn((256, 128), generator=g) * 0.05).half()
+    b = torch.randn((256,), generator=g).half()
+    gamma, beta = torch.rand((256,), generator=g).half(), torch.randn((256,), generator=g).half()
+    wc, bc, gc, btc = w.cuda(), b.cuda(), gamma.cuda(), beta.cuda()
+
+    def model(x):
+        return (layer_norm(linear_layer(x, wc, bc, "gelu"), gc, btc, 1e-5),)
+
+    x0 = torch.randn((64, 128), generator=g).half()
+    if fake:
+        with FakeTensorMode() as mode:
+            example = [mode.from_tensor(x0)]
+        run = cuda_graph.cuda_graphs_wrapper(model, example)
+    else:
+        run = cuda_graph.cuda_graphs_wrapper(model, [x0.cuda()])
+    ptrs = set()
+    for seed in range(3):
+        x = torch.randn((64, 128), generator=torch.Generator().manual_seed(seed)).half()
+        out = run(x.cuda())[0]
+        ptrs.add(out.data_ptr())
+        expected = O.layer_norm(O.linear(x, w, b, "gelu").half(), gamma, beta, 1.6e-5)
+        O.assert_parity(out, expected, max_abs=2e-2)
+    assert len(ptrs) == 1
+    cuda_graph.static_inputs_pool.clear()
+
+
+@pytest.mark.gpu
+def test_attention_under_cuda_graph(lib):
+    """Decode-shape attention under the wrapper (test/test_attention.py:176-208)."""
+    from kernl_b200.implementations.attention import attention_forward
+    from kernl_b200.implementations.attention_skinny import skinny_attention_forward
+    from kernl_b200.optimizer import cuda_graph
+    from oracle import kernl_oracle as O
+
+    cuda_graph.static_inputs_pool.clear()
+    g = torch.Generator().manual_seed(0)
+    q = torch.randn((5, 6, 1, 64), generator=g).half()
+    k, v = torch.randn((5, 6, 1500, 64), generator=g).half(), torch.randn((5, 6, 1500, 64), generator=g).half()
+    expected = O.attention(q, k, v, 0.3)
+    for fn in (skinny_attention_forward, attention_forward):
+        def model(q_, k_, v_):
+            return (fn(q_, k_, v_, torch.empty_like(q_), 0.3),)
+
+        run = cuda_graph.cuda_graphs_wrapper(model, [q.cuda(), k.cuda(), v.cuda()])
+        out = run(q.cuda(), k.cuda(), v.cuda())[0]
+        O.assert_parity(out, expected, what=fn.__name__)
+    cuda_graph.static_inputs_pool.clear()

@@ -339,13 +339,103 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_sweep(args):
+    """Per-shape kernel timings of the op configs (attention sweep, linear shapes, norms, decode),
+    one JSON line per case: device time per launch with a cold L2, achieved TFLOP/s or GB/s and
+    the fraction of the measured peak that bounds the case. Not part of the default run."""
+    import torch
+
+    from kernl_b200 import _lib, build
+    from kernl_b200.implementations.attention import attention_forward
+    from kernl_b200.implementations.attention_skinny import skinny_attention_forward
+    from kernl_b200.implementations.layer_norm import layer_norm
+    from kernl_b200.implementations.linear_layer import linear_layer
+
+    build.build()
+    peaks, _ = load_peaks()
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.int8, device=dev)
+    g = torch.Generator().manual_seed(0)
+    iters, warm = args.steps, max(args.warmup, 3)
+    want = lambda name: (args.sweep in ("all", name.split(":")[0])) and (args.case is None or args.case in name)
+
+    def emit(name, ms_list, flops=None, nbytes=None):
+        ms = statistics.mean(ms_list)
+        rec = {"case": name, "ms": round(ms, 5), "ms_min": round(min(ms_list), 5)}
+        if flops is not None:
+            rec["tflops"] = round(flops / ms / 1e9, 1)
+            rec["frac_tensor_peak"] = round(flops / ms / 1e9 / peaks["bf16_tflops"], 4)
+        if nbytes is not None:
+            rec["gbs"] = round(nbytes / ms / 1e6, 1)
+            rec["frac_hbm_peak"] = round(nbytes / ms / 1e6 / peaks["hbm_gbs"], 4)
+        print(json.dumps(rec), flush=True)
+
+    for S in (128, 256, 512, 1024, 2048, 4096):
+        for kind in ("full", "causal", "pad"):
+            for (D, H, dt, tag) in ((64, 12, torch.float16, "f16"), (128, 32, torch.bfloat16, "bf16")):
+                tokens = 4096 if D == 64 else 16384
+                name = f"attention:{tag}_d{D}_s{S}_{kind}"
+                if not want(name):
+                    continue
+                B = tokens // S
+                q, k, v = (torch.randn((B, H, S, D), generator=g).to(dt).to(dev) for _ in range(3))
+                mask = None
+                if kind == "pad":
+                    valid = torch.randint(min(64, S), S + 1, (B,), generator=g)
+                    mask = torch.where(valid[:, None] > torch.arange(S)[None, :], 0.0, float("-inf")).reshape(B, 1, 1, S).to(dt).to(dev)
+                o = torch.empty_like(q)
+                causal = kind == "causal"
+                d = event_time(lambda: attention_forward(q, k, v, o, D ** -0.5, causal, mask), iters, warm, flush)
+                fl = 4.0 * B * H * D * (S * (S + 1) / 2 if causal else S * S)
+                emit(name, d, flops=fl)
+    for M in (16, 128, 1024, 8192):
+        for (K, N) in ((768, 768), (768, 3072), (3072, 768), (4096, 11008), (11008, 4096)):
+            for act in ("", "gelu", "relu"):
+                name = f"linear:M{M}_K{K}_N{N}_{act or 'none'}"
+                if not want(name):
+                    continue
+                x = torch.randn((M, K), generator=g).half().to(dev)
+                w = (torch.randn((N, K), generator=g) * 0.02).half().to(dev)
+                b = (torch.randn((N,), generator=g) * 0.02).half().to(dev)
+                d = event_time(lambda: linear_layer(x, w, b, act), iters, warm, flush)
+                emit(name, d, flops=2.0 * M * N * K, nbytes=2.0 * (M * K + N * K + M * N) + 2 * N)
+    for cols in (768, 4096):
+        for rms in (False, True):
+            name = f"norm:{'rms' if rms else 'ln'}_16384x{cols}"
+            if not want(name):
+                continue
+            x = torch.randn((16384, cols), generator=g).half().to(dev)
+            gm = (torch.rand((cols,), generator=g) + 0.5).half().to(dev)
+            bt = (torch.randn((cols,), generator=g) * 0.1).half().to(dev)
+            d = event_time(lambda: layer_norm(x, gm, None if rms else bt, 1e-5, use_rms_norm=rms), iters, warm, flush)
+            emit(name, d, nbytes=4.0 * 16384 * cols + 4 * cols)
+    for (B, H, N, D, dt, tag) in ((1, 12, 512, 64, torch.float16, "t5_cross"), (8, 32, 2048, 128, torch.bfloat16, "llama_decode"),
+                                  (64, 32, 2048, 128, torch.bfloat16, "llama_decode_b64")):
+        name = f"decode:{tag}"
+        if not want(name):
+            continue
+        q = torch.randn((B, H, 1, D), generator=g).to(dt).to(dev)
+        k, v = (torch.randn((B, H, N, D), generator=g).to(dt).to(dev) for _ in range(2))
+        o = torch.empty_like(q)
+        d = event_time(lambda: skinny_attention_forward(q, k, v, o, D ** -0.5), iters, warm, flush)
+        emit(name, d, nbytes=2.0 * 2 * B * H * N * D)
+    _lib.device_status()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--sweep", choices=["all", "attention", "linear", "norm", "decode"], default=None,
+                    help="per-shape kernel timings instead of the headline line")
+    ap.add_argument("--case", default=None, help="with --sweep: only cases whose name contains this")
     args = ap.parse_args()
+    if args.sweep is not None:
+        run_sweep(args)
+        return
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -42,6 +42,7 @@ struct AttnDev {
     float scale_log2;  // sm_scale * log2(e)
     int is_causal;
     int mask_dtype;
+    int mask_vec;   // mask rows can be read with aligned 128-bit loads
     int num_pairs;  // ceil(ceil(M/128)/2)
 };
 
@@ -162,7 +163,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp >= 8) {
-      asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+      asm volatile("setmaxnreg.dec.sync.aligned.u32 48;");
       if (warp == 8) {
         // ------------------------------------------------------------------ TMA producer
         if (elect_one()) {
@@ -197,23 +198,31 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             constexpr uint32_t idesc_qk = make_idesc_f16(Elem<T>::kIsBf16, 128, 128, 0, 0);
             constexpr uint32_t idesc_pv = make_idesc_f16(Elem<T>::kIsBf16, 128, D, 0, 1);
             bool ok = true;
+            // Descriptor halves that never change: high word = stride offset 1024 B, version 1, 128-byte
+            // swizzle; low word = address >> 4 (+ the leading offset for the N-major V operand).
+            constexpr uint32_t desc_hi = (1024u >> 4) | (1u << 14) | (2u << 29);
+            const uint32_t q_lo = (q_smem & 0x3FFFF) >> 4;
+            const uint32_t k_lo = (k_smem & 0x3FFFF) >> 4;
+            const uint32_t v_lo = ((v_smem & 0x3FFFF) >> 4) | ((uint32_t)(CHUNK >> 4) << 16);
+            auto desc = [&](uint32_t lo) { return ((uint64_t)desc_hi << 32) | (uint64_t)lo; };
             auto issue_qk = [&](int t, int s) {
-                const uint32_t a_base = q_smem + t * TILE;
-                const uint32_t b_base = k_smem + s * TILE;
+                const uint32_t a_lo = q_lo + (uint32_t)(t * (TILE >> 4));
+                const uint32_t b_lo = k_lo + (uint32_t)(s * (TILE >> 4));
+                const uint32_t d_tmem = tmem_base + (uint32_t)(t * 128);
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks) {
-                    const uint32_t off = (uint32_t)((ks / 4) * CHUNK + (ks % 4) * 32);
-                    tc_mma_ss(tmem_base + (uint32_t)(t * 128), make_smem_desc_sw128(a_base + off, 16, 1024),
-                              make_smem_desc_sw128(b_base + off, 16, 1024), idesc_qk, ks > 0 ? 1u : 0u);
+                    const uint32_t off = (uint32_t)(((ks / 4) * CHUNK + (ks % 4) * 32) >> 4);
+                    tc_mma_ss(d_tmem, desc(a_lo + off), desc(b_lo + off), idesc_qk, ks > 0 ? 1u : 0u);
                 }
             };
             auto issue_pv = [&](int t, int s, bool accumulate) {
-                const uint32_t b_base = v_smem + s * TILE;
+                const uint32_t b_lo = v_lo + (uint32_t)(s * (TILE >> 4));
+                const uint32_t d_tmem = tmem_base + (uint32_t)(256 + t * 128);
+                const uint32_t a_tmem = tmem_base + (uint32_t)(t * 128);
 #pragma unroll
                 for (int ks = 0; ks < kAttnBlock / 16; ++ks) {
-                    // 16 keys = 16 rows of 128 bytes; the second 64-wide slab of D is CHUNK bytes away
-                    tc_mma_ts(tmem_base + (uint32_t)(256 + t * 128), tmem_base + (uint32_t)(t * 128 + ks * 8),
-                              make_smem_desc_sw128(b_base + ks * 2048, CHUNK, 1024), idesc_pv,
+                    // 16 keys = 16 rows of 128 bytes = 2048 B; the second 64-wide slab of D is CHUNK bytes away
+                    tc_mma_ts(d_tmem, a_tmem + (uint32_t)(ks * 8), desc(b_lo + (uint32_t)(ks * (2048 >> 4))), idesc_pv,
                               (accumulate || ks > 0) ? 1u : 0u);
                 }
             };
@@ -293,20 +302,53 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                 const bool bound = (col0 + kAttnBlock > p.N) || (p.is_causal && col0 + kAttnBlock - 1 > mt[t] * kAttnBlock);
                 // ---- transform to the domain in which the maximum is taken
                 if (!plain) {
+                    if (!has_mask) {
 #pragma unroll
-                    for (int cch = 0; cch < 4; ++cch) {
+                        for (int cch = 0; cch < 4; ++cch) {
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) {
-                            float v = __uint_as_float(sr[cch][i]) * c;
-                            if (has_mask) {
-                                const int col = col0 + cch * 32 + i;
-                                float mv = 0.f;
-                                if (col < p.N)
-                                    mv = mask_load(p.mask, mask_row_off + (int64_t)col * p.mask_strides[3], p.mask_dtype);
-                                mv = fmaxf(mv, mlow);
-                                v = fmaf(mv, kLog2e, v);
+                            for (int i = 0; i < 32; ++i) sr[cch][i] = __float_as_uint(__uint_as_float(sr[cch][i]) * c);
+                        }
+                    } else {
+#pragma unroll
+                        for (int hc = 0; hc < 8; ++hc) {
+                            const int colc = col0 + hc * 16;
+                            float mvals[16];
+                            if (p.mask_vec && colc + 16 <= p.N) {
+                                // 16 consecutive mask values of this row as 128-bit loads (a row-broadcast
+                                // mask makes every lane read the same address: one transaction per warp)
+                                if (p.mask_dtype == KB_F32) {
+                                    const float4* mp = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.mask) + mask_row_off + colc);
+#pragma unroll
+                                    for (int v4 = 0; v4 < 4; ++v4) {
+                                        const float4 f = __ldg(mp + v4);
+                                        mvals[v4 * 4 + 0] = f.x; mvals[v4 * 4 + 1] = f.y; mvals[v4 * 4 + 2] = f.z; mvals[v4 * 4 + 3] = f.w;
+                                    }
+                                } else {
+                                    const uint4* mp = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.mask) + mask_row_off + colc);
+#pragma unroll
+                                    for (int v4 = 0; v4 < 2; ++v4) {
+                                        const uint4 w = __ldg(mp + v4);
+                                        const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+                                        for (int i = 0; i < 4; ++i) {
+                                            const float2 f = (p.mask_dtype == KB_F16) ? Elem<__half>::unpack2(ww[i]) : Elem<__nv_bfloat16>::unpack2(ww[i]);
+                                            mvals[v4 * 8 + 2 * i] = f.x;
+                                            mvals[v4 * 8 + 2 * i + 1] = f.y;
+                                        }
+                                    }
+                                }
+                            } else {
+#pragma unroll
+                                for (int i = 0; i < 16; ++i) {
+                                    const int col = colc + i;
+                                    mvals[i] = (col < p.N) ? mask_load(p.mask, mask_row_off + (int64_t)col * p.mask_strides[3], p.mask_dtype) : 0.f;
+                                }
                             }
-                            sr[cch][i] = __float_as_uint(v);
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) {
+                                uint32_t& sv = sr[hc >> 1][(hc & 1) * 16 + i];
+                                sv = __float_as_uint(fmaf(fmaxf(mvals[i], mlow), kLog2e, __uint_as_float(sv) * c));
+                            }
                         }
                     }
                 }
@@ -340,13 +382,13 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                 if (j > 0 && __any_sync(0xffffffffu, grow)) {
                     // S_j complete implies P·V of block j-1 complete (issued earlier, same thread), so O is quiescent.
 #pragma unroll
-                    for (int dch = 0; dch < D / 32; ++dch) {
-                        uint32_t orr[32];
-                        tmem_ld_32x32(o_addr + dch * 32, orr);
+                    for (int dch = 0; dch < D / 16; ++dch) {
+                        uint32_t orr[16];
+                        tmem_ld_32x16(o_addr + dch * 16, orr);
                         tmem_ld_wait();
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) orr[i] = __float_as_uint(__uint_as_float(orr[i]) * alpha);
-                        tmem_st_32x32(o_addr + dch * 32, orr);
+                        for (int i = 0; i < 16; ++i) orr[i] = __float_as_uint(__uint_as_float(orr[i]) * alpha);
+                        tmem_st_32x16(o_addr + dch * 16, orr);
                     }
                 }
                 // ---- exponentials, row sum, pack to 16 bit, write P over the first 64 columns of S
@@ -445,6 +487,11 @@ static int launch_attention_td(const kb_attn_params& p, cudaStream_t stream) {
     d.scale_log2 = p.sm_scale * kLog2e;
     d.is_causal = p.is_causal ? 1 : 0;
     d.mask_dtype = p.mask ? p.mask_dtype : KB_F32;
+    d.mask_vec = 0;
+    if (p.mask != nullptr && p.mask_strides[3] == 1 && (((uintptr_t)p.mask) & 15) == 0) {
+        const int64_t per16 = (p.mask_dtype == KB_F32) ? 4 : 8;  // elements per 16 bytes
+        d.mask_vec = (p.mask_strides[0] % per16 == 0 && p.mask_strides[1] % per16 == 0 && p.mask_strides[2] % per16 == 0) ? 1 : 0;
+    }
     const int num_m_tiles = (int)((p.M + kAttnBlock - 1) / kAttnBlock);
     d.num_pairs = (num_m_tiles + 1) / 2;
 

@@ -1,0 +1,133 @@
+"""Attention graph rewrites (reference: src/kernl/optimizer/attention.py).
+
+`attention_wrapper` is the call site of the fused kernels: the rewrites replace eager attention
+sub-graphs by a call to it. Patterns 1-3 are the reference's (BERT-style `/ 8.0`, T5-style fp32
+softmax, bmm-style 3-D tensors); two further rewrites cover what current `transformers` emits:
+a direct `scaled_dot_product_attention` call and the `* scaling` form.
+"""
+from typing import Optional
+
+import torch
+
+from kernl_b200.implementations.attention import attention_forward
+from kernl_b200.implementations.attention_skinny import skinny_attention_forward
+from kernl_b200.utils.extended_matcher import replace_pattern
+
+
+def attention_wrapper(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    output: torch.Tensor,
+    sm_scale: float,
+    is_causal: bool,
+    attention_mask: Optional[torch.Tensor],
+) -> torch.Tensor:
+    """Dispatch between the fused and the decode-shape kernel (reference: optimizer/attention.py:24-55).
+
+    3-D (bmm-style) inputs get a unit head dimension. One query row against more than 50 keys goes
+    to the split-KV kernel; the reference sends the masked / causal variant of that shape to eager
+    PyTorch (:48-49), here the same kernel handles masks, so nothing leaves the CUDA library.
+    """
+    extend_head = q.dim() == 3
+    if extend_head:
+        q, k, v, output = q.unsqueeze(1), k.unsqueeze(1), v.unsqueeze(1), output.unsqueeze(1)
+    if attention_mask is not None and attention_mask.dtype == torch.bool:
+        # boolean keep-masks (scaled_dot_product_attention convention) become additive 0 / -inf
+        attention_mask = torch.zeros_like(attention_mask, dtype=q.dtype).masked_fill_(~attention_mask, float("-inf"))
+    if q.size(-2) == 1 and k.size(-2) > 50:
+        skinny_attention_forward(q, k, v, output, sm_scale, is_causal=is_causal, attention_mask=attention_mask)
+    else:
+        attention_forward(q, k, v, output, sm_scale, is_causal=is_causal, attention_mask=attention_mask)
+    if extend_head:
+        output = output.squeeze(1)
+    return output
+
+
+torch.fx.wrap("attention_wrapper")
+
+
+def fuse_attention_pattern_1(gm: torch.fx.GraphModule, is_causal: bool):
+    """softmax(q·kᵀ / 8.0 + mask)·v (reference: optimizer/attention.py:61-76)."""
+
+    def pattern(q, k, attention_mask, v):
+        scores = torch.matmul(q, k.transpose(-1, -2))
+        scores = scores / 8.0
+        scores = scores + attention_mask
+        probs = torch.nn.functional.softmax(scores, dim=-1)
+        return torch.matmul(probs, v)
+
+    def replace(q, k, attention_mask, v):
+        output = torch.empty_like(q)
+        output = attention_wrapper(q, k, v, output, 1 / 8.0, is_causal, attention_mask)
+        return output
+
+    replace_pattern(gm, pattern, replace)
+
+
+def fuse_attention_pattern_2(gm: torch.fx.GraphModule, is_causal: bool):
+    """T5 form: unscaled scores + position bias, softmax in fp32, cast back (reference: :79-95)."""
+
+    def pattern(q, k, encoder_decoder_position_bias, v):
+        scores = torch.matmul(q, k.transpose(3, 2))
+        scores = torch.add(scores, encoder_decoder_position_bias)
+        probs = torch.nn.functional.softmax(scores.float(), dim=-1)
+        probs = probs.type_as(scores)
+        return torch.matmul(probs, v)
+
+    def replace(q, k, encoder_decoder_position_bias, v):
+        output = torch.empty_like(q)
+        output = attention_wrapper(q, k, v, output, 1.0, is_causal, encoder_decoder_position_bias)
+        return output
+
+    replace_pattern(gm, pattern, replace)
+
+
+def fuse_attention_pattern_3(gm: torch.fx.GraphModule, is_causal: bool):
+    """bmm form on [batch*heads, seq, dim] tensors, no mask, no scale (reference: :98-112)."""
+
+    def pattern(q, k, v):
+        scores = torch.bmm(q, k.transpose(1, 2))
+        probs = torch.nn.functional.softmax(scores, dim=-1)
+        return torch.bmm(probs, v)
+
+    def replace(q, k, v):
+        output = torch.empty_like(q)
+        output = attention_wrapper(q, k, v, output, 1.0, is_causal, None)
+        return output
+
+    replace_pattern(gm, pattern, replace)
+
+
+def fuse_attention_sdpa(gm: torch.fx.GraphModule, is_causal: bool):
+    """`F.scaled_dot_product_attention(q, k, v, attn_mask=…, scale=…, is_causal=…)` calls, which is
+    what current `transformers` models emit by default. Has no counterpart in the reference (its
+    target stack predates the op); literals (scale, is_causal) are read from the node."""
+    targets = (torch.nn.functional.scaled_dot_product_attention, torch._C._nn.scaled_dot_product_attention)
+    changed = False
+    for node in list(gm.graph.nodes):
+        if node.op != "call_function" or node.target not in targets:
+            continue
+        args = list(node.args)
+        kwargs = dict(node.kwargs)
+        q, k, v = args[0], args[1], args[2]
+        mask = args[3] if len(args) > 3 else kwargs.get("attn_mask")
+        dropout_p = args[4] if len(args) > 4 else kwargs.get("dropout_p", 0.0)
+        causal = args[5] if len(args) > 5 else kwargs.get("is_causal", False)
+        scale = kwargs.get("scale")
+        if dropout_p not in (0, 0.0) or kwargs.get("enable_gqa", False) or isinstance(causal, torch.fx.Node):
+            continue
+        if isinstance(scale, torch.fx.Node):
+            continue
+        with gm.graph.inserting_before(node):
+            out = gm.graph.call_function(torch.empty_like, (q,))
+            if scale is None:
+                head_dim = gm.graph.call_method("size", (q, -1))
+                scale = gm.graph.call_function(pow, (head_dim, -0.5))
+            fused = gm.graph.call_function(attention_wrapper, (q, k, v, out, scale, bool(causal) or is_causal, mask))
+        node.replace_all_uses_with(fused)
+        gm.graph.erase_node(node)
+        changed = True
+    if changed:
+        gm.graph.lint()
+        gm.recompile()

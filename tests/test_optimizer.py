@@ -1,0 +1,211 @@
+"""Graph rewrites: matcher semantics on CPU, rewrite coverage on TorchDynamo graphs of randomly
+initialised BERT / T5 encoders (CPU, structure only), and the end-to-end model configs on the GPU
+against fp32 eager on the CPU (the tolerance of this build: max-abs <= 1e-2, cosine >= 0.9995)."""
+import collections
+
+import pytest
+import torch
+
+from kernl_b200.utils.extended_matcher import replace_pattern
+from kernl_b200.utils.fx import static_args_are_equal
+
+
+def marker(v, module, tag=""):
+    return v
+
+
+torch.fx.wrap("marker")
+
+
+class TwoLayer(torch.nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.fc = torch.nn.Linear(4, 4)
+        self.act = torch.nn.ReLU()
+        self.fc2 = torch.nn.Linear(4, 4)
+        self.norm = torch.nn.LayerNorm(4)
+
+    def forward(self, x):
+        return self.norm(self.fc2(self.act(self.fc(x))) / 8.0)
+
+
+def _pattern_pair(activation_module):
+    class Pattern(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.linear = torch.nn.Linear(1, 1)
+            self.activation = activation_module
+
+        def forward(self, v):
+            return self.activation(self.linear(v))
+
+    class Replacement(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.linear = torch.nn.Linear(1, 1)
+            self.activation = activation_module
+
+        def forward(self, v):
+            return marker(v, self.linear, tag="fused")
+
+    return Pattern(), Replacement()
+
+
+def test_module_type_matching_and_remapping():
+    gm = torch.fx.symbolic_trace(TwoLayer())
+    assert len(replace_pattern(gm, *_pattern_pair(torch.nn.Tanh()))) == 0  # wrong activation type
+    matches = replace_pattern(gm, *_pattern_pair(torch.nn.ReLU()))
+    assert len(matches) == 1
+    fused = [n for n in gm.graph.nodes if n.op == "call_function" and n.target is marker]
+    assert len(fused) == 1 and fused[0].kwargs == {"tag": "fused"}
+    # the replacement's dummy module now points at the matched layer
+    assert fused[0].args[1].op == "get_attr" and fused[0].args[1].target == "fc"
+    assert [n.target for n in gm.graph.nodes if n.op == "call_module"] == ["fc2", "norm"]
+
+
+def test_literals_must_be_equal():
+    gm = torch.fx.symbolic_trace(TwoLayer())
+    assert len(replace_pattern(gm, lambda a: a / 4.0, lambda a: a * 0.25)) == 0
+    assert len(replace_pattern(gm, lambda a: a / 8, lambda a: a * 0.125)) == 0  # int 8 is not float 8.0
+    x = torch.randn(3, 4)
+    expected = gm(x)
+    assert len(replace_pattern(gm, lambda a: a / 8.0, lambda a: a * 0.125)) == 1
+    assert torch.allclose(gm(x), expected)
+
+
+def test_interior_value_used_outside_blocks_the_match():
+    def fn(x, w):
+        h = torch.matmul(x, w)
+        return torch.relu(h) + h  # h escapes the relu(matmul) pattern
+
+    gm = torch.fx.symbolic_trace(fn)
+    assert len(replace_pattern(gm, lambda a, b: torch.relu(torch.matmul(a, b)), lambda a, b: torch.matmul(a, b))) == 0
+
+
+def test_multiple_non_overlapping_matches():
+    def fn(x):
+        return torch.relu(torch.relu(torch.relu(x) + 1.0) + 1.0)
+
+    gm = torch.fx.symbolic_trace(fn)
+    matches = replace_pattern(gm, lambda a: torch.relu(a) + 1.0, lambda a: torch.sigmoid(a))
+    assert len(matches) == 2
+    x = torch.randn(5)
+    assert torch.allclose(gm(x), torch.relu(torch.sigmoid(torch.sigmoid(x))))
+
+
+def test_static_args_helper():
+    gm = torch.fx.symbolic_trace(lambda a: a.transpose(1, 2))
+    gm2 = torch.fx.symbolic_trace(lambda a: a.transpose(2, 1))
+    n1 = [n for n in gm.graph.nodes if n.op == "call_method"][0]
+    n2 = [n for n in gm2.graph.nodes if n.op == "call_method"][0]
+    assert static_args_are_equal(n1, n1) and not static_args_are_equal(n1, n2)
+
+
+def _rewritten_ops(model, **inputs):
+    import torch._dynamo
+
+    from kernl_b200.optimizer.dynamo_backend import dynamo_backend_ofi
+
+    torch._dynamo.reset()
+    torch._dynamo.config.inline_inbuilt_nn_modules = False
+    counts = collections.Counter()
+
+    class Stop(Exception):
+        pass
+
+    def backend(gm, example_inputs):
+        dynamo_backend_ofi(gm)
+        for n in gm.graph.nodes:
+            if n.op == "call_function":
+                counts[getattr(n.target, "__name__", str(n.target))] += 1
+            elif n.op == "call_module":
+                counts["module:" + type(gm.get_submodule(n.target)).__name__] += 1
+
+        def stop(*a):
+            raise Stop()
+
+        return stop
+
+    try:
+        torch._dynamo.optimize(backend)(model.forward)(**inputs)
+    except Stop:
+        pass
+    torch._dynamo.reset()
+    return counts
+
+
+def test_bert_graph_is_fully_rewritten():
+    from transformers import BertConfig, BertModel
+
+    model = BertModel(BertConfig(num_hidden_layers=2)).eval()
+    c = _rewritten_ops(model, input_ids=torch.randint(0, 1000, (1, 16)), attention_mask=torch.ones(1, 16, dtype=torch.long))
+    assert c["attention_wrapper"] == 2
+    assert c["linear_wrapper"] == 2 * 6 + 1  # q, k, v, o, ffn up (+GELU), ffn down per layer; pooler (+tanh)
+    assert c["layer_norm_wrapper"] == 1 + 2 * 2
+    assert c["module:Linear"] == 0 and c["module:LayerNorm"] == 0 and c["module:Dropout"] == 0
+    assert c["scaled_dot_product_attention"] == 0 and c["gelu"] == 0
+
+
+def test_t5_encoder_graph_is_fully_rewritten():
+    from transformers import T5Config, T5EncoderModel
+
+    cfg = T5Config(d_model=768, d_ff=3072, num_layers=2, num_heads=12, d_kv=64, vocab_size=32128, feed_forward_proj="relu")
+    model = T5EncoderModel(cfg).eval()
+    c = _rewritten_ops(model, input_ids=torch.randint(0, 1000, (1, 16)))
+    assert c["attention_wrapper"] == 2
+    assert c["linear_wrapper"] == 2 * 6
+    assert c["layer_norm_rms_wrapper"] == 2 * 2 + 1
+    assert c["softmax"] == 0 and c["matmul"] == 0 and c["module:Linear"] == 0 and c["rsqrt"] == 0
+
+
+@pytest.mark.gpu
+def test_bert_base_end_to_end(lib):
+    """Config 1: BERT-base, random init (seed 0), batch 1 x seq 128, fp16 on the GPU through
+    optimize_model vs fp32 eager on the CPU."""
+    import torch._dynamo
+    from transformers import BertConfig, BertModel
+
+    from kernl_b200.model_optimization import optimize_model
+    from oracle import kernl_oracle as O
+
+    torch._dynamo.reset()
+    torch.manual_seed(0)
+    model = BertModel(BertConfig()).eval()
+    g = torch.Generator().manual_seed(0)
+    ids = torch.randint(0, 30522, (1, 128), generator=g)
+    mask = torch.ones((1, 128), dtype=torch.long)
+    with torch.inference_mode():
+        expected = model(input_ids=ids, attention_mask=mask).last_hidden_state
+    gpu_model = model.half().cuda()
+    optimize_model(gpu_model)
+    with torch.inference_mode():
+        for _ in range(3):  # first call traces and captures, the next ones replay the graph
+            out = gpu_model(input_ids=ids.cuda(), attention_mask=mask.cuda())
+    O.assert_parity(out.last_hidden_state, expected, what="BERT-base last_hidden_state")
+    torch._dynamo.reset()
+
+
+@pytest.mark.gpu
+def test_t5_encoder_end_to_end(lib):
+    """T5-base-shaped encoder (config 4's encoder half), random init, batch 1 x 512 tokens."""
+    import torch._dynamo
+    from transformers import T5Config, T5EncoderModel
+
+    from kernl_b200.model_optimization import optimize_model
+    from oracle import kernl_oracle as O
+
+    torch._dynamo.reset()
+    torch.manual_seed(0)
+    cfg = T5Config(d_model=768, d_ff=3072, num_layers=12, num_heads=12, d_kv=64, vocab_size=32128,
+                   feed_forward_proj="relu", relative_attention_num_buckets=32)
+    model = T5EncoderModel(cfg).eval()
+    ids = torch.randint(0, 32128, (1, 512), generator=torch.Generator().manual_seed(0))
+    with torch.inference_mode():
+        expected = model(input_ids=ids).last_hidden_state
+    gpu_model = model.half().cuda()
+    optimize_model(gpu_model)
+    with torch.inference_mode():
+        for _ in range(3):
+            out = gpu_model(input_ids=ids.cuda())
+    O.assert_parity(out.last_hidden_state, expected, what="T5 encoder last_hidden_state")
+    torch._dynamo.reset()

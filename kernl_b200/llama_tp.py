@@ -1,0 +1,253 @@
+"""Llama-2-shaped decoder on the kernl_b200 ops, with Megatron-style tensor parallelism.
+
+This is the host side of the baseline's fifth config (32 layers, hidden 4096, 32 heads of 128,
+SwiGLU 11008, RMSNorm eps 1e-5, rotary base 10000, vocab 32000, bf16): prefill with a causal mask,
+then greedy decode with a KV cache. The reference has no such model in its dispatched path; the
+semantics of the pieces follow its experimental Llama kernels
+(experimental/llama-v2/kernel/pytorch_reference.py:6-8,37-80,88-104: RMSNorm, interleaved-pair
+rotary embedding, silu(gate)·up), and every heavy op is one of the library's kernels:
+RMSNorm (kb_norm_fwd), QKV / O / gate-up / down projections (kb_linear_fwd), silu·mul
+(kb_silu_mul), causal prefill attention (kb_attention_fwd), decode attention (kb_attention_decode_fwd).
+
+Partitioning over `world` ranks (one process per GPU): heads are split (q/k/v column-parallel, the
+KV cache is sharded by head, attention is local), `o_proj` and `down_proj` are row-parallel and
+followed by an all-reduce (sum) over NVLink through `torch.distributed` (NCCL), gate/up are
+column-parallel. Embedding and LM head are replicated.
+
+Decode is shape-static so that ONE CUDA graph serves every step: attention always runs over the
+whole cache with an additive length mask kept on the device, and the position / cache slot are
+device tensors.
+"""
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+
+@dataclass
+class LlamaConfig:
+    n_layers: int = 32
+    hidden: int = 4096
+    n_heads: int = 32
+    head_dim: int = 128
+    ffn: int = 11008
+    vocab: int = 32000
+    eps: float = 1e-5
+    rope_base: float = 10000.0
+    max_seq: int = 2304  # prefill 2048 + 256 decoded tokens
+
+
+class CudaOps:
+    """The library's kernels behind the five ops the model needs."""
+
+    @staticmethod
+    def rms_norm(x, w, eps):
+        from kernl_b200.implementations.layer_norm import layer_norm
+
+        return layer_norm(x, w, None, eps, use_rms_norm=True)
+
+    @staticmethod
+    def linear(x, w):
+        from kernl_b200.implementations.linear_layer import linear_layer
+
+        return linear_layer(x, w, None)
+
+    @staticmethod
+    def silu_mul(gate_up):
+        from kernl_b200.implementations.linear_layer import silu_mul
+
+        return silu_mul(gate_up)
+
+    @staticmethod
+    def attention_prefill(q, k, v, sm_scale):
+        from kernl_b200.implementations.attention import attention_forward
+
+        return attention_forward(q, k, v, torch.empty_like(q), sm_scale, True, None)
+
+    @staticmethod
+    def attention_decode(q, k, v, sm_scale, mask):
+        from kernl_b200.implementations.attention_skinny import skinny_attention_forward
+
+        return skinny_attention_forward(q, k, v, torch.empty_like(q), sm_scale, False, mask)
+
+
+class DistComm:
+    """Sum all-reduce over the default process group; a no-op for a single rank."""
+
+    def __init__(self, world: int):
+        self.world = world
+
+    def all_reduce(self, t: torch.Tensor) -> torch.Tensor:
+        if self.world > 1:
+            import torch.distributed as dist
+
+            dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        return t
+
+
+def _seeded(shape, std, seed, device, dtype):
+    """N(0, std) tensor that is identical on every rank (same seed, same generator device)."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    return (torch.randn(shape, generator=g, device=device, dtype=torch.float32) * std).to(dtype)
+
+
+def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """Rotary embedding on interleaved pairs (x[..., 2i], x[..., 2i+1]) as in the reference's
+    experimental kernels (experimental/llama-v2/kernel/pytorch_reference.py:37-80).
+    x: [B, S, H, D]; cos/sin: [S, D/2] (or [B, S, D/2])."""
+    xf = x.float().reshape(*x.shape[:-1], -1, 2)
+    x0, x1 = xf[..., 0], xf[..., 1]
+    c = cos.reshape(*cos.shape[:-1], 1, cos.shape[-1]) if cos.dim() == 2 else cos.unsqueeze(-2)
+    s = sin.reshape(*sin.shape[:-1], 1, sin.shape[-1]) if sin.dim() == 2 else sin.unsqueeze(-2)
+    out = torch.stack((x0 * c - x1 * s, x0 * s + x1 * c), dim=-1)
+    return out.reshape(x.shape).to(x.dtype)
+
+
+class LlamaTP:
+    """One rank's shard of the decoder."""
+
+    def __init__(self, cfg: LlamaConfig, rank: int = 0, world: int = 1, device="cuda", dtype=torch.bfloat16,
+                 ops=None, comm=None, seed: int = 0, weight_device: Optional[str] = None):
+        assert cfg.n_heads % world == 0 and cfg.ffn % world == 0
+        self.cfg, self.rank, self.world, self.device, self.dtype = cfg, rank, world, torch.device(device), dtype
+        self.ops = ops if ops is not None else CudaOps()
+        self.comm = comm if comm is not None else DistComm(world)
+        self.heads_local = cfg.n_heads // world
+        self.ffn_local = cfg.ffn // world
+        wd = weight_device or device
+        H, D, F = cfg.hidden, cfg.head_dim, cfg.ffn
+        hl, fl = self.heads_local, self.ffn_local
+        r0h, r0f = rank * hl * D, rank * fl
+
+        def shard_rows(full, start, n):
+            return full[start:start + n].to(self.device).contiguous()
+
+        self.embed = _seeded((cfg.vocab, H), 0.02, seed * 1000 + 1, wd, dtype).to(self.device)
+        self.lm_head = _seeded((cfg.vocab, H), 0.02, seed * 1000 + 2, wd, dtype).to(self.device)
+        self.final_norm = torch.ones(H, dtype=dtype, device=self.device)
+        self.layers = []
+        for li in range(cfg.n_layers):
+            s = seed * 1000 + 10 * (li + 1)
+            wq = _seeded((cfg.n_heads * D, H), 0.02, s + 1, wd, dtype)
+            wk = _seeded((cfg.n_heads * D, H), 0.02, s + 2, wd, dtype)
+            wv = _seeded((cfg.n_heads * D, H), 0.02, s + 3, wd, dtype)
+            wqkv = torch.cat([shard_rows(w, r0h, hl * D) for w in (wq, wk, wv)], dim=0).contiguous()
+            del wq, wk, wv
+            wo = _seeded((H, cfg.n_heads * D), 0.02, s + 4, wd, dtype)[:, r0h:r0h + hl * D].to(self.device).contiguous()
+            wg = _seeded((F, H), 0.02, s + 5, wd, dtype)
+            wu = _seeded((F, H), 0.02, s + 6, wd, dtype)
+            wgu = torch.cat([shard_rows(wg, r0f, fl), shard_rows(wu, r0f, fl)], dim=0).contiguous()
+            del wg, wu
+            wdn = _seeded((H, F), 0.02, s + 7, wd, dtype)[:, r0f:r0f + fl].to(self.device).contiguous()
+            self.layers.append({
+                "wqkv": wqkv, "wo": wo, "wgu": wgu, "wdn": wdn,
+                "norm1": torch.ones(H, dtype=dtype, device=self.device),
+                "norm2": torch.ones(H, dtype=dtype, device=self.device),
+            })
+        half = D // 2
+        inv_freq = 1.0 / (cfg.rope_base ** (torch.arange(0, half, dtype=torch.float32) / half))
+        ang = torch.arange(cfg.max_seq, dtype=torch.float32)[:, None] * inv_freq[None, :]
+        self.cos, self.sin = torch.cos(ang).to(self.device), torch.sin(ang).to(self.device)
+        self.kcache = None
+        self.vcache = None
+        self.sm_scale = D ** -0.5
+
+    # ------------------------------------------------------------------ cache / state
+    def alloc_cache(self, batch: int):
+        cfg = self.cfg
+        shape = (cfg.n_layers, batch, self.heads_local, cfg.max_seq, cfg.head_dim)
+        self.kcache = torch.zeros(shape, dtype=self.dtype, device=self.device)
+        self.vcache = torch.zeros(shape, dtype=self.dtype, device=self.device)
+        # additive length mask for decode: 0 for filled slots, -inf beyond
+        self.len_mask = torch.full((1, 1, 1, cfg.max_seq), float("-inf"), dtype=self.dtype, device=self.device)
+        self.pos = torch.zeros(1, dtype=torch.long, device=self.device)
+
+    # ------------------------------------------------------------------ blocks
+    def _mlp(self, layer, x2d):
+        gu = self.ops.linear(x2d, layer["wgu"])
+        act = self.ops.silu_mul(gu)
+        return self.comm.all_reduce(self.ops.linear(act, layer["wdn"]))
+
+    def prefill(self, ids: torch.Tensor) -> torch.Tensor:
+        """ids [B, S] → logits [B, vocab] of the last position; fills the KV cache."""
+        cfg, hl, D = self.cfg, self.heads_local, self.cfg.head_dim
+        B, S = ids.shape
+        if self.kcache is None or self.kcache.shape[1] != B:
+            self.alloc_cache(B)
+        x = self.embed.index_select(0, ids.reshape(-1)).reshape(B * S, cfg.hidden)
+        cos, sin = self.cos[:S], self.sin[:S]
+        for li, layer in enumerate(self.layers):
+            h = self.ops.rms_norm(x, layer["norm1"], cfg.eps)
+            qkv = self.ops.linear(h, layer["wqkv"]).reshape(B, S, 3, hl, D)
+            q = apply_rope(qkv[:, :, 0], cos, sin)
+            k = apply_rope(qkv[:, :, 1], cos, sin)
+            self.kcache[li, :, :, :S] = k.transpose(1, 2)
+            self.vcache[li, :, :, :S] = qkv[:, :, 2].transpose(1, 2)
+            attn = self.ops.attention_prefill(q.transpose(1, 2), self.kcache[li, :, :, :S], self.vcache[li, :, :, :S],
+                                              self.sm_scale)  # [B, hl, S, D]
+            attn2d = attn.transpose(1, 2).reshape(B * S, hl * D)
+            x = x + self.comm.all_reduce(self.ops.linear(attn2d, layer["wo"]))
+            h = self.ops.rms_norm(x, layer["norm2"], cfg.eps)
+            x = x + self._mlp(layer, h)
+        self.len_mask[..., :S] = 0
+        self.pos.fill_(S)
+        last = x.reshape(B, S, cfg.hidden)[:, -1]
+        last = self.ops.rms_norm(last.contiguous(), self.final_norm, cfg.eps)
+        return self.ops.linear(last, self.lm_head)
+
+    def decode_step(self, tokens: torch.Tensor) -> torch.Tensor:
+        """tokens [B] → logits [B, vocab]; appends one position to the cache. Every shape is static
+        and the position lives on the device, so the step can be captured in one CUDA graph."""
+        cfg, hl, D = self.cfg, self.heads_local, self.cfg.head_dim
+        B = tokens.shape[0]
+        x = self.embed.index_select(0, tokens)
+        cos, sin = self.cos.index_select(0, self.pos), self.sin.index_select(0, self.pos)  # [1, D/2]
+        self.len_mask.index_fill_(3, self.pos, 0.0)
+        for li, layer in enumerate(self.layers):
+            h = self.ops.rms_norm(x, layer["norm1"], cfg.eps)
+            qkv = self.ops.linear(h, layer["wqkv"]).reshape(B, 1, 3, hl, D)
+            q = apply_rope(qkv[:, :, 0], cos, sin)
+            k = apply_rope(qkv[:, :, 1], cos, sin)
+            self.kcache[li].index_copy_(2, self.pos, k.transpose(1, 2))
+            self.vcache[li].index_copy_(2, self.pos, qkv[:, :, 2].transpose(1, 2))
+            attn = self.ops.attention_decode(q.transpose(1, 2).contiguous(), self.kcache[li], self.vcache[li],
+                                             self.sm_scale, self.len_mask)  # [B, hl, 1, D]
+            x = x + self.comm.all_reduce(self.ops.linear(attn.reshape(B, hl * D), layer["wo"]))
+            h = self.ops.rms_norm(x, layer["norm2"], cfg.eps)
+            x = x + self._mlp(layer, h)
+        self.pos.add_(1)
+        x = self.ops.rms_norm(x, self.final_norm, cfg.eps)
+        return self.ops.linear(x, self.lm_head)
+
+    def generate(self, ids: torch.Tensor, steps: int, use_cuda_graph: bool = True) -> torch.Tensor:
+        """Greedy decoding: prefill, then `steps` tokens. Returns [B, steps] token ids. The argmax
+        stays on the device, so no step waits for the host."""
+        logits = self.prefill(ids)
+        tok = logits.float().argmax(-1)
+        out = [tok]
+        graph = None
+        if use_cuda_graph and self.device.type == "cuda" and steps > 2:
+            static_tok = tok.clone()
+            saved = (self.pos.clone(), self.len_mask.clone())
+            # one eager warm-up step (on a side stream) and the capture both advance the position
+            # and write cache slots; the state is restored afterwards and the real steps overwrite
+            # those slots again
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                self.decode_step(static_tok)
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                static_next = self.decode_step(static_tok).float().argmax(-1)
+            self.pos.copy_(saved[0])
+            self.len_mask.copy_(saved[1])
+            for _ in range(steps - 1):
+                static_tok.copy_(out[-1])
+                graph.replay()
+                out.append(static_next.clone())
+        else:
+            for _ in range(steps - 1):
+                out.append(self.decode_step(out[-1]).float().argmax(-1))
+        return torch.stack(out, dim=1)

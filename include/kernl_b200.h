@@ -76,6 +76,10 @@ int kb_norm_fwd(const kb_norm_params* p, void* stream);
  * stride and a row stride that is a multiple of 8 elements; K must be a multiple of 8.
  * act_inputs (optional, [M,N], row stride = y_row_stride) receives the pre-activation values
  * (linear_layer.py:193-195).
+ * workspace: when the problem has fewer output tiles than SMs (few rows), K is split across work
+ * items that accumulate fp32 partial sums into `workspace` (cleared by the call itself); without a
+ * workspace the same result is computed unsplit. The reference fixes SPLIT_K = 1
+ * (linear_layer.py:121-122).
  * ------------------------------------------------------------------------------------- */
 typedef struct {
     const void* x;          /* [M,K]                                                       */
@@ -88,6 +92,8 @@ typedef struct {
     int64_t     y_row_stride;
     int32_t     activation; /* KB_ACT_*                                                    */
     int32_t     dtype;      /* KB_F16 / KB_BF16                                            */
+    void*       workspace;  /* optional scratch for split-K, 16-byte aligned, or NULL      */
+    int64_t     workspace_bytes; /* split-K is used only when >= M*N*4                     */
 } kb_linear_params;
 
 int kb_linear_fwd(const kb_linear_params* p, void* stream);

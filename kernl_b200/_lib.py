@@ -47,6 +47,7 @@ class LinearParams(Structure):
         ("M", c_int64), ("N", c_int64), ("K", c_int64),
         ("x_row_stride", c_int64), ("y_row_stride", c_int64),
         ("activation", c_int32), ("dtype", c_int32),
+        ("workspace", c_void_p), ("workspace_bytes", c_int64),
     ]
 
 
@@ -91,9 +92,10 @@ def load() -> ctypes.CDLL:
     lib.kb_status_str.argtypes = [ctypes.c_int]
     lib.kb_status_str.restype = ctypes.c_char_p
     lib.kb_version.restype = ctypes.c_int
-    if hasattr(lib, "kb_debug_force_bn"):
-        lib.kb_debug_force_bn.argtypes = [ctypes.c_int]
-        lib.kb_debug_force_bn.restype = None
+    for hook in ("kb_debug_force_bn", "kb_debug_force_splits"):
+        if hasattr(lib, hook):
+            getattr(lib, hook).argtypes = [ctypes.c_int]
+            getattr(lib, hook).restype = None
     _lib = lib
     return lib
 

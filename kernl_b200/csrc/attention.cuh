@@ -30,6 +30,15 @@ namespace kb {
 
 constexpr int kAttnThreads = 384;
 constexpr int kAttnBlock = 128;  // rows per query tile and keys per block
+// Register re-balancing between the warpgroups (setmaxnreg). The CTA is launched with
+// 65536 / 384 -> 168 registers per thread; the third warpgroup shrinks to kAttnRegsLow and the two
+// softmax warpgroups grow to kAttnRegsHigh. The increase waits (without bound) until the CTA's own
+// pool has the registers, so the totals MUST fit the launch allocation: 2*high + low <= 3*168.
+constexpr int kAttnRegsLaunch = 168;
+constexpr int kAttnRegsLow = 40;
+constexpr int kAttnRegsHigh = 232;
+static_assert(2 * kAttnRegsHigh + kAttnRegsLow <= 3 * kAttnRegsLaunch, "setmaxnreg totals exceed the CTA's register pool");
+static_assert(kAttnRegsLow % 8 == 0 && kAttnRegsHigh % 8 == 0, "setmaxnreg wants multiples of 8");
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLazyThreshold = 8.0f;
 
@@ -163,7 +172,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp >= 8) {
-      asm volatile("setmaxnreg.dec.sync.aligned.u32 48;");
+      asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kAttnRegsLow));
       if (warp == 8) {
         // ------------------------------------------------------------------ TMA producer
         if (elect_one()) {
@@ -269,7 +278,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         }
       }
     } else {
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kAttnRegsHigh));
         // ------------------------------------------------------------------ softmax groups
         const int t = warp >> 2;        // tile handled by this group
         const int q = warp & 3;         // TMEM lane quadrant of this warp

@@ -24,15 +24,10 @@ enum : int {
     KB_DEV_WAIT_EXPIRED = 1,
 };
 
-// One second of %globaltimer nanoseconds: long enough that a healthy pipeline never reaches it,
-// short enough that a broken one returns control to the host.
-constexpr unsigned long long kWaitLimitNs = 1000ull * 1000ull * 1000ull;
-
-__device__ __forceinline__ unsigned long long globaltimer_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
+// Wait limit in SM clock cycles (clock64 is cheap to read; %globaltimer is not): 2^31 cycles is a
+// little over one second at 1.9 GHz — long enough that a healthy pipeline never reaches it, short
+// enough that a broken one returns control to the host.
+constexpr long long kWaitLimitCycles = 1ll << 31;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -89,12 +84,12 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                           int site) {
     if (mbar_try_wait(bar, parity)) return true;
-    unsigned long long t0 = globaltimer_ns();
+    const long long t0 = clock64();
     for (uint32_t spins = 1;; ++spins) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((spins & 0x3F) == 0) {
+        if ((spins & 0xFF) == 0) {
             if (*abort_flag) return false;
-            if (globaltimer_ns() - t0 > kWaitLimitNs) {
+            if (clock64() - t0 > kWaitLimitCycles) {
                 *abort_flag = 1;
                 if (atomicCAS(&g_device_status[0], 0, KB_DEV_WAIT_EXPIRED) == 0) {
                     g_device_status[1] = site;

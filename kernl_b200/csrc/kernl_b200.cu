@@ -82,6 +82,7 @@ static int check_device() {
 }
 
 static int g_forced_bn = 0;
+static int g_forced_splits = 0;
 
 }  // namespace kb
 
@@ -133,6 +134,8 @@ int kb_norm_fwd(const kb_norm_params* p, void* stream) {
 
 // Test hook: force the GEMM column-tile width (0 = heuristic). Not part of the stable ABI.
 void kb_debug_force_bn(int bn) { g_forced_bn = bn; }
+// Test hook: force the number of K splits (0 = heuristic; needs a workspace).
+void kb_debug_force_splits(int splits) { g_forced_splits = splits; }
 
 int kb_linear_fwd(const kb_linear_params* p, void* stream) {
     if (p == nullptr || p->x == nullptr || p->w == nullptr || p->y == nullptr) return KB_ERR_BAD_ARG;
@@ -144,7 +147,7 @@ int kb_linear_fwd(const kb_linear_params* p, void* stream) {
     if (p->M > 0x7fffffff || p->N > 0x7fffffff || p->K > 0x7fffffff) return KB_ERR_UNSUPPORTED;
     int st = check_device();
     if (st != KB_OK) return st;
-    return launch_linear(*p, (cudaStream_t)stream, g_forced_bn);
+    return launch_linear(*p, (cudaStream_t)stream, g_forced_bn, g_forced_splits);
 }
 
 int kb_silu_mul(const void* gu, void* y, int64_t M, int64_t N, int32_t dtype, void* stream) {

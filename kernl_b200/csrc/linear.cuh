@@ -5,8 +5,13 @@
 //   warp 1      MMA issuer: one elected thread issues tcgen05.mma (M=128, N=BN, K=16) x 4 per stage,
 //               accumulators in TMEM, double-buffered (2 x BN columns) so that the epilogue of tile
 //               i overlaps the main loop of tile i+1
-//   warps 2..5  epilogue: tcgen05.ld of the accumulator (one row per thread), + bias, activation
-//               in fp32, convert, store
+//   warps 2..9  epilogue (two warps per TMEM lane quadrant, each taking half of the tile's columns):
+//               tcgen05.ld of the accumulator (one row per thread), + bias, activation in fp32,
+//               convert, store
+// Split-K: when a problem has fewer output tiles than SMs (few rows: the weight matrix is then
+// streamed from HBM by too few SMs), the K range of every tile is cut into `splits` work items; the
+// items add their fp32 partial tiles into a caller-provided workspace with vector atomics and a
+// small second kernel applies bias + activation and converts.
 // Both operands are K-major (x is [M,K], W is [N,K]) which is exactly what tcgen05 wants, so
 // no transposes are needed. Ragged M / N / K edges rely on TMA zero fill for loads and on
 // predicated stores.
@@ -17,7 +22,8 @@ namespace kb {
 
 constexpr int kGemmBM = 128;
 constexpr int kGemmBK = 64;
-constexpr int kGemmThreads = 192;
+constexpr int kGemmThreads = 320;
+constexpr int kGemmEpilogueWarps = 8;
 
 template <int BN>
 struct GemmCfg {
@@ -78,7 +84,8 @@ template <typename T, int BN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
                  const T* __restrict__ bias, T* __restrict__ y, T* __restrict__ act_inputs, int M,
-                 int N, int K, int64_t y_row_stride, int activation) {
+                 int N, int K, int64_t y_row_stride, int activation, int splits, int kps,
+                 float* __restrict__ ws) {
     using Cfg = GemmCfg<BN>;
     constexpr int STAGES = Cfg::kStages;
     extern __shared__ uint8_t smem_raw[];
@@ -112,7 +119,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(tfull_bar(a), 1);
-            mbar_init(tempty_bar(a), 4);
+            mbar_init(tempty_bar(a), kGemmEpilogueWarps);
         }
         *abort_flag = 0;
         fence_mbar_init();
@@ -134,16 +141,20 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
     const int num_n = (N + BN - 1) / BN;
     const int num_tiles = num_m * num_n;
     const int num_k = (K + kGemmBK - 1) / kGemmBK;
+    // work item w -> (tile = w % num_tiles, split = w / num_tiles); split s covers k-blocks
+    // [s*kps, min(num_k, (s+1)*kps)), never empty by construction of `splits`
+    const int num_items = num_tiles * splits;
 
     if (warp == 0) {
         if (elect_one()) {
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+            for (int w = blockIdx.x; w < num_items && ok; w += gridDim.x) {
                 int m_idx, n_idx;
-                tile_coords(t, num_m, num_n, m_idx, n_idx);
-                for (int kb = 0; kb < num_k; ++kb) {
+                tile_coords(w % num_tiles, num_m, num_n, m_idx, n_idx);
+                const int kb0 = (w / num_tiles) * kps, kb1 = min(num_k, kb0 + kps);
+                for (int kb = kb0; kb < kb1; ++kb) {
                     if (!mbar_wait(empty_bar(stage), phase ^ 1, abort_flag, 100)) { ok = false; break; }
                     mbar_arrive_expect_tx(full_bar(stage), Cfg::kStageBytes);
                     const uint32_t a_dst = smem_base + stage * Cfg::kStageBytes;
@@ -167,11 +178,12 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
             int acc = 0;
             uint32_t acc_phase = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+            for (int w = blockIdx.x; w < num_items && ok; w += gridDim.x) {
                 if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1, abort_flag, 200)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
-                for (int kb = 0; kb < num_k; ++kb) {
+                const int kb0 = (w / num_tiles) * kps, kb1 = min(num_k, kb0 + kps);
+                for (int kb = kb0; kb < kb1; ++kb) {
                     if (!mbar_wait(full_bar(stage), phase, abort_flag, 201)) { ok = false; break; }
                     tc_fence_after();
                     const uint32_t a_addr = smem_base + stage * Cfg::kStageBytes;
@@ -181,7 +193,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                     for (int k = 0; k < kGemmBK / 16; ++k) {
                         // +32 bytes along K inside the 128-byte swizzle row = +2 in the address field
                         tc_mma_ss(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc,
-                                  (kb > 0 || k > 0) ? 1u : 0u);
+                                  (kb > kb0 || k > 0) ? 1u : 0u);
                     }
                     tc_commit(empty_bar(stage));
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -194,12 +206,16 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
         }
     } else {
         const int q = warp & 3;  // TMEM lane quadrant this warp may access
+        const int col_half = (warp - 2) >> 2;  // which half of the tile's columns this warp handles
+        constexpr int kHalfCols = BN / 2 >= 32 ? BN / 2 : 32;
+        const int c_begin = col_half * kHalfCols;
+        const int c_end = (BN >= 64) ? c_begin + kHalfCols : (col_half == 0 ? BN : 0);
         int acc = 0;
         uint32_t acc_phase = 0;
         bool ok = true;
-        for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        for (int w = blockIdx.x; w < num_items && ok; w += gridDim.x) {
             int m_idx, n_idx;
-            tile_coords(t, num_m, num_n, m_idx, n_idx);
+            tile_coords(w % num_tiles, num_m, num_n, m_idx, n_idx);
             if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, 300)) { ok = false; break; }
             tc_fence_after();
             const int row = m_idx * kGemmBM + q * 32 + lane;
@@ -207,13 +223,31 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
             T* y_row = y + (int64_t)row * y_row_stride;
             T* a_row = act_inputs ? act_inputs + (int64_t)row * y_row_stride : nullptr;
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
+            for (int c0 = c_begin; c0 < c_end; c0 += 32) {
                 if (n0 + c0 >= N) break;
                 uint32_t r[32];
                 tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + c0), r);
                 tmem_ld_wait();
                 const int col0 = n0 + c0;
                 const bool full_chunk = (col0 + 32 <= N);
+                if (splits > 1) {
+                    // partial tile: fp32 vector atomics into the workspace [M, N]
+                    if (row < M) {
+                        float* wrow = ws + (int64_t)row * N + col0;
+                        if (full_chunk && ((((uintptr_t)wrow) & 15) == 0)) {
+#pragma unroll
+                            for (int v = 0; v < 8; ++v) {
+                                atomicAdd(reinterpret_cast<float4*>(wrow) + v,
+                                          make_float4(__uint_as_float(r[v * 4 + 0]), __uint_as_float(r[v * 4 + 1]),
+                                                      __uint_as_float(r[v * 4 + 2]), __uint_as_float(r[v * 4 + 3])));
+                            }
+                        } else {
+                            for (int j = 0; j < 32; ++j)
+                                if (col0 + j < N) atomicAdd(wrow + j, __uint_as_float(r[j]));
+                        }
+                    }
+                    continue;
+                }
                 float z[32];
                 if (bias != nullptr) {
                     if (full_chunk && (((uintptr_t)(bias + col0)) & 15) == 0) {
@@ -316,8 +350,82 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
     }
 }
 
+// Second pass of a split-K launch: y = act(workspace + bias), 4 columns per thread.
+template <typename T>
+__global__ void __launch_bounds__(256)
+linear_splitk_finish_kernel(const float* __restrict__ ws, const T* __restrict__ bias, T* __restrict__ y,
+                            T* __restrict__ act_inputs, int M, int N, int64_t y_row_stride, int activation) {
+    const int nq = (N + 3) / 4;
+    const int64_t total = (int64_t)M * nq;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int row = (int)(i / nq), c0 = (int)(i % nq) * 4;
+        float z[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int c = c0 + j;
+            z[j] = (c < N) ? ws[(int64_t)row * N + c] + (bias ? Elem<T>::to_f32(bias[c]) : 0.f) : 0.f;
+        }
+        if (act_inputs) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                if (c0 + j < N) act_inputs[(int64_t)row * y_row_stride + c0 + j] = Elem<T>::from_f32(z[j]);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            float v = z[j];
+            switch (activation) {
+                case KB_ACT_TANH: v = act_tanh(v); break;
+                case KB_ACT_GELU: v = act_gelu(v); break;
+                case KB_ACT_FAST_GELU: v = act_fast_gelu(v); break;
+                case KB_ACT_RELU: v = fmaxf(v, 0.f); break;
+                case KB_ACT_SILU: v = act_silu(v); break;
+                default: break;
+            }
+            if (c0 + j < N) y[(int64_t)row * y_row_stride + c0 + j] = Elem<T>::from_f32(v);
+        }
+    }
+}
+
+struct LinearPlan {
+    int bn;      // column-tile width
+    int splits;  // K splits per tile (1 = none)
+    int kps;     // k-blocks per split
+};
+
+// Cost model, in units of "bytes staged per SM": waves of work items x k-blocks per item (+2 for the
+// fixed per-item cost) x bytes per k-block. Wide tiles re-stream x less often; splitting K fills the
+// SMs when there are few tiles (few rows: the op is then bound by streaming W from HBM once, and
+// what counts is how many SMs pull on it and how many bytes each keeps in flight).
+static LinearPlan plan_linear(int64_t M, int64_t N, int64_t K, bool has_ws, int forced_bn, int forced_splits) {
+    const int sms = sm_count();
+    const int64_t num_m = (M + kGemmBM - 1) / kGemmBM;
+    const int num_k = (int)((K + kGemmBK - 1) / kGemmBK);
+    LinearPlan best{32, 1, num_k};
+    double best_cost = 1e300;
+    for (int bn : {256, 128, 64, 32}) {
+        if (forced_bn != 0 && bn != forced_bn) continue;
+        const int64_t tiles = num_m * ((N + bn - 1) / bn);
+        const int max_splits = has_ws ? (num_k / 2 < 1 ? 1 : (num_k / 2 > 32 ? 32 : num_k / 2)) : 1;
+        for (int s = 1; s <= max_splits; ++s) {
+            if (forced_splits != 0 && s != forced_splits && !(forced_splits > max_splits && s == max_splits)) continue;
+            const int kps = (num_k + s - 1) / s;
+            const int eff = (num_k + kps - 1) / kps;  // splits that are not empty
+            if (eff != s) continue;
+            const int64_t waves = (tiles * s + sms - 1) / sms;
+            // a split tile pays an extra pass over its outputs (atomics + finishing kernel)
+            const double extra = (s > 1) ? 3.0 : 0.0;
+            const double cost = (double)waves * ((double)kps + 2.0 + extra) * (double)(kGemmBM + bn);
+            if (cost < best_cost) {
+                best_cost = cost;
+                best = LinearPlan{bn, s, kps};
+            }
+        }
+    }
+    return best;
+}
+
 template <typename T, int BN>
-static int launch_linear_bn(const kb_linear_params& p, cudaStream_t stream) {
+static int launch_linear_bn(const kb_linear_params& p, cudaStream_t stream, const LinearPlan& plan) {
     using Cfg = GemmCfg<BN>;
     CUtensorMap tmap_x, tmap_w;
     {
@@ -343,39 +451,44 @@ static int launch_linear_bn(const kb_linear_params& p, cudaStream_t stream) {
         if (e != cudaSuccess) return KB_ERR_LAUNCH;
         attr_set = true;
     }
-    const int num_tiles = (int)(((p.M + kGemmBM - 1) / kGemmBM) * ((p.N + BN - 1) / BN));
-    const int grid = num_tiles < sm_count() ? num_tiles : sm_count();
+    const int64_t num_tiles = ((p.M + kGemmBM - 1) / kGemmBM) * ((p.N + BN - 1) / BN);
+    const int64_t items = num_tiles * plan.splits;
+    const int grid = (int)(items < sm_count() ? items : sm_count());
+    float* ws = reinterpret_cast<float*>(p.workspace);
+    if (plan.splits > 1) {
+        if (cudaMemsetAsync(ws, 0, (size_t)p.M * (size_t)p.N * sizeof(float), stream) != cudaSuccess) return KB_ERR_LAUNCH;
+    }
     linear_tc_kernel<T, BN><<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(
         tmap_x, tmap_w, (const T*)p.bias, (T*)p.y, (T*)p.act_inputs, (int)p.M, (int)p.N, (int)p.K,
-        p.y_row_stride, p.activation);
-    return cudaGetLastError() == cudaSuccess ? KB_OK : KB_ERR_LAUNCH;
-}
-
-// Column-tile width: the widest tile that still yields at least one tile per SM; narrow tiles for
-// problems with few rows so that the (bandwidth-bound) weight stream is spread over many SMs.
-static int pick_bn(int64_t M, int64_t N, int forced_bn) {
-    if (forced_bn == 256 || forced_bn == 128 || forced_bn == 64 || forced_bn == 32) return forced_bn;
-    const int64_t num_m = (M + kGemmBM - 1) / kGemmBM;
-    const int sms = sm_count();
-    for (int bn : {256, 128, 64}) {
-        if (num_m * ((N + bn - 1) / bn) >= sms) return bn;
+        p.y_row_stride, p.activation, plan.splits, plan.kps, ws);
+    if (cudaGetLastError() != cudaSuccess) return KB_ERR_LAUNCH;
+    if (plan.splits > 1) {
+        const int64_t total = p.M * ((p.N + 3) / 4);
+        int64_t blocks = (total + 255) / 256;
+        if (blocks > (int64_t)sm_count() * 8) blocks = (int64_t)sm_count() * 8;
+        linear_splitk_finish_kernel<T><<<(unsigned)blocks, 256, 0, stream>>>(
+            ws, (const T*)p.bias, (T*)p.y, (T*)p.act_inputs, (int)p.M, (int)p.N, p.y_row_stride, p.activation);
+        if (cudaGetLastError() != cudaSuccess) return KB_ERR_LAUNCH;
     }
-    return 32;
+    return KB_OK;
 }
 
 template <typename T>
-static int launch_linear_t(const kb_linear_params& p, cudaStream_t stream, int forced_bn) {
-    switch (pick_bn(p.M, p.N, forced_bn)) {
-        case 256: return launch_linear_bn<T, 256>(p, stream);
-        case 128: return launch_linear_bn<T, 128>(p, stream);
-        case 64: return launch_linear_bn<T, 64>(p, stream);
-        default: return launch_linear_bn<T, 32>(p, stream);
+static int launch_linear_t(const kb_linear_params& p, cudaStream_t stream, int forced_bn, int forced_splits) {
+    const bool has_ws = p.workspace != nullptr && p.workspace_bytes >= p.M * p.N * (int64_t)sizeof(float) &&
+                        (((uintptr_t)p.workspace) & 15) == 0;
+    const LinearPlan plan = plan_linear(p.M, p.N, p.K, has_ws, forced_bn, forced_splits);
+    switch (plan.bn) {
+        case 256: return launch_linear_bn<T, 256>(p, stream, plan);
+        case 128: return launch_linear_bn<T, 128>(p, stream, plan);
+        case 64: return launch_linear_bn<T, 64>(p, stream, plan);
+        default: return launch_linear_bn<T, 32>(p, stream, plan);
     }
 }
 
-static int launch_linear(const kb_linear_params& p, cudaStream_t stream, int forced_bn) {
-    if (p.dtype == KB_F16) return launch_linear_t<__half>(p, stream, forced_bn);
-    if (p.dtype == KB_BF16) return launch_linear_t<__nv_bfloat16>(p, stream, forced_bn);
+static int launch_linear(const kb_linear_params& p, cudaStream_t stream, int forced_bn, int forced_splits) {
+    if (p.dtype == KB_F16) return launch_linear_t<__half>(p, stream, forced_bn, forced_splits);
+    if (p.dtype == KB_BF16) return launch_linear_t<__nv_bfloat16>(p, stream, forced_bn, forced_splits);
     return KB_ERR_UNSUPPORTED;
 }
 

@@ -7,6 +7,22 @@ from kernl_b200 import _lib
 from kernl_b200.implementations._autocast import cast_if_autocast
 
 
+_WORKSPACE_BYTES = 32 * 1024 * 1024
+_workspaces = {}
+
+
+def _workspace(device: torch.device) -> torch.Tensor:
+    """One fp32 scratch buffer per device for split-K partial sums, allocated on first use and
+    kept (a stable address, so CUDA graphs that captured it stay valid). Calls on different
+    streams of one device would share it; the front-end is single-stream like the reference."""
+    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+    ws = _workspaces.get(key)
+    if ws is None:
+        ws = torch.empty(_WORKSPACE_BYTES // 4, dtype=torch.float32, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
 def linear_layer(
     x: torch.Tensor,
     weight: torch.Tensor,
@@ -51,11 +67,14 @@ def linear_layer(
     if act_inputs is not None:
         assert act_inputs.shape == (M, N) and act_inputs.dtype == x.dtype and act_inputs.is_contiguous()
     if M > 0:
+        ws = _workspace(x.device) if M * N * 4 <= _WORKSPACE_BYTES else None
         p = _lib.LinearParams(
             x=x_.data_ptr(), w=weight.data_ptr(), bias=bias.data_ptr() if bias is not None else None,
             y=outputs.data_ptr(), act_inputs=act_inputs.data_ptr() if act_inputs is not None else None,
             M=M, N=N, K=K, x_row_stride=x_.stride(0), y_row_stride=outputs.stride(0),
             activation=_lib.ACTIVATIONS[activation], dtype=_lib.dtype_code(x.dtype),
+            workspace=ws.data_ptr() if ws is not None else None,
+            workspace_bytes=ws.numel() * 4 if ws is not None else 0,
         )
         with torch.cuda.device(x.device):
             _lib.check(_lib.load().kb_linear_fwd(p, _lib.current_stream(x.device)), "linear_layer")

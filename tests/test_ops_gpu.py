@@ -307,6 +307,30 @@ def test_linear_every_tile_width(lib):
         lib.kb_debug_force_bn(0)
 
 
+@pytest.mark.parametrize("shape", [(16, 768, 768), (128, 3072, 768), (40, 4096, 1000), (8, 11008, 4096), (300, 520, 392)], ids=str)
+@pytest.mark.parametrize("splits", [0, 2, 5])
+def test_linear_split_k(lib, shape, splits):
+    """Split-K (fp32 atomics into the workspace + finishing kernel) against the oracle, with the
+    heuristic (0) and forced split counts; act_inputs must hold the pre-activation values."""
+    from kernl_b200.implementations.linear_layer import linear_layer
+
+    M, K, N = shape
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn((M, K), generator=g).half()
+    w = (torch.randn((N, K), generator=g) * 0.02).half()
+    b = (torch.randn((N,), generator=g) * 0.02).half()
+    xc, wc, bc = _cuda(x, w, b)
+    pre = torch.empty((M, N), dtype=torch.float16, device="cuda")
+    try:
+        lib.kb_debug_force_splits(splits)
+        for _ in range(2):  # twice: the workspace is reused and must be cleared by the call
+            out = linear_layer(xc, wc, bc, "gelu", pre)
+    finally:
+        lib.kb_debug_force_splits(0)
+    O.assert_parity(out, O.linear(x, w, b, "gelu"))
+    O.assert_parity(pre, O.linear(x, w, b, ""))
+
+
 def test_silu_mul(lib):
     from kernl_b200.implementations.linear_layer import silu_mul
 

@@ -11,7 +11,7 @@ from kernl_b200.optimizer.attention import (
 from kernl_b200.optimizer.dropout import remove_dropout
 from kernl_b200.optimizer.layer_norm import replace_layer_norm, replace_layer_norm_rms
 from kernl_b200.optimizer.linear import replace_all_linear
-from kernl_b200.optimizer.normalizer import normalize_operators
+from kernl_b200.optimizer.normalizer import normalize_operators, replace_scalar_tensor_constants
 
 
 def dynamo_backend_ofi(gm: torch.fx.GraphModule, assume_causal=False):
@@ -20,6 +20,7 @@ def dynamo_backend_ofi(gm: torch.fx.GraphModule, assume_causal=False):
     `assume_causal` sets the causal flag of every attention replacement, on top of whatever
     additive mask the model passes."""
     normalize_operators(gm)
+    replace_scalar_tensor_constants(gm)
     remove_dropout(gm)
     fuse_attention_pattern_1(gm, assume_causal)
     fuse_attention_pattern_2(gm, assume_causal)

@@ -139,6 +139,24 @@ int kb_attention_fwd(const kb_attn_params* p, void* stream);
 int64_t kb_attention_decode_scratch_bytes(int64_t B, int64_t H, int64_t M, int64_t N, int64_t D);
 int kb_attention_decode_fwd(const kb_attn_params* p, void* scratch, int64_t scratch_bytes, void* stream);
 
+/* Decode attention for callers that cannot allocate device memory. Same computation and arguments
+ * as kb_attention_decode_fwd, but the scratch is a fixed array inside the library (4 MiB of device
+ * memory on every GPU that loads the library, held until the process exits), so the caller passes
+ * only its inputs and its output. This entry point has no counterpart in the reference; it exists
+ * for hosts that own no device allocator — e.g. a custom-op hook of a serving runtime that hands a
+ * plugin nothing but tensors, or a process whose memory another framework's pool has already
+ * reserved — and it calls no cudaMalloc/cudaFree nor any allocating library routine.
+ *   - Limit: kb_attention_decode_scratch_bytes(B,H,M,N,D) must not exceed
+ *     kb_attention_decode_static_max_bytes(); larger problems return KB_ERR_TOO_LARGE and launch
+ *     nothing (use kb_attention_decode_fwd with your own scratch instead).
+ *   - The first call on each device looks up the array's device address (the device must be
+ *     current); make that first call before starting any stream capture.
+ *   - All calls share the one array: calls that can overlap on the GPU (different streams,
+ *     different threads) race on it and must be serialised by the caller. Contents left by an
+ *     earlier call are harmless: every slot that is read has been rewritten by the same call. */
+int64_t kb_attention_decode_static_max_bytes(void);
+int kb_attention_decode_fwd_static(const kb_attn_params* p, void* stream);
+
 /* ---- device status word ---------------------------------------------------------------
  * Kernels with bounded waits record a non-zero code here instead of trapping or hanging.
  * kb_device_status_read synchronises the current device, returns the word and clears it. */

@@ -24,6 +24,8 @@ EXPORTED_SYMBOLS = [
     "kb_attention_fwd",
     "kb_attention_decode_scratch_bytes",
     "kb_attention_decode_fwd",
+    "kb_attention_decode_static_max_bytes",
+    "kb_attention_decode_fwd_static",
     "kb_device_status_read",
     "kb_status_str",
     "kb_version",
@@ -87,6 +89,10 @@ def load() -> ctypes.CDLL:
     lib.kb_attention_decode_scratch_bytes.restype = c_int64
     lib.kb_attention_decode_fwd.argtypes = [POINTER(AttnParams), c_void_p, c_int64, c_void_p]
     lib.kb_attention_decode_fwd.restype = ctypes.c_int
+    lib.kb_attention_decode_static_max_bytes.argtypes = []
+    lib.kb_attention_decode_static_max_bytes.restype = c_int64
+    lib.kb_attention_decode_fwd_static.argtypes = [POINTER(AttnParams), c_void_p]
+    lib.kb_attention_decode_fwd_static.restype = ctypes.c_int
     lib.kb_device_status_read.argtypes = [POINTER(c_int32)]
     lib.kb_device_status_read.restype = ctypes.c_int
     lib.kb_status_str.argtypes = [ctypes.c_int]

@@ -202,4 +202,63 @@ int kb_attention_decode_fwd(const kb_attn_params* p, void* scratch, int64_t scra
     return launch_attention_decode(*p, scratch, scratch_bytes, (cudaStream_t)stream);
 }
 
+// -------------------------------------------------------------------------------------------------
+// Decode attention without any allocation by the caller.
+//
+// kb_attention_decode_fwd needs a scratch buffer for the per-chunk partial results, which its caller
+// has to get from somewhere. Some callers have no device allocator to ask: a custom-op hook of a
+// serving runtime that is handed nothing but input and output buffers, or a process whose device
+// memory has been reserved up front by another framework's pool so that a cudaMalloc of its own
+// would fail or fragment the pool. For them the scratch lives in the library image itself.
+//
+// The array below is device memory that every GPU loading this library carries until the process
+// exits (kStaticScratchBytes per GPU). Its name is only a host-side handle: the device address is
+// obtained with cudaGetSymbolAddress, once per device, with that device current, and cached.
+// -------------------------------------------------------------------------------------------------
+namespace kb {
+constexpr size_t kStaticScratchBytes = 4u << 20;  // 4 MiB
+static __device__ __align__(256) unsigned char g_decode_static_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+static void* g_static_scratch_addr[kMaxDevices] = {nullptr};
+static std::mutex g_static_scratch_mutex;
+
+// Device address of the static scratch on the CURRENT device (looked up on the first call per device).
+static int static_scratch_for_current_device(void** out) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return KB_ERR_NO_DEVICE;
+    if (dev < 0 || dev >= kMaxDevices) return KB_ERR_UNSUPPORTED;
+    std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+    if (g_static_scratch_addr[dev] == nullptr) {
+        void* ptr = nullptr;
+        if (cudaGetSymbolAddress(&ptr, g_decode_static_scratch) != cudaSuccess || ptr == nullptr) {
+            cudaGetLastError();
+            return KB_ERR_LAUNCH;
+        }
+        g_static_scratch_addr[dev] = ptr;
+    }
+    *out = g_static_scratch_addr[dev];
+    return KB_OK;
+}
+}  // namespace kb
+
+int64_t kb_attention_decode_static_max_bytes(void) { return (int64_t)kb::kStaticScratchBytes; }
+
+int kb_attention_decode_fwd_static(const kb_attn_params* p, void* stream) {
+    int st = check_attn(p);
+    if (st != KB_OK) return st;
+    if (p->B == 0 || p->H == 0 || p->M == 0) return KB_OK;
+    const int64_t need = decode_scratch_bytes(p->B, p->H, p->M, p->N, p->D);
+    if (need < 0) return KB_ERR_BAD_ARG;
+    if (need > (int64_t)kb::kStaticScratchBytes) return KB_ERR_TOO_LARGE;
+    st = check_device();
+    if (st != KB_OK) return st;
+    void* scratch = nullptr;
+    st = kb::static_scratch_for_current_device(&scratch);
+    if (st != KB_OK) return st;
+    // Nothing in the scratch has to start at zero: the first kernel writes every slot that the
+    // second one reads, so stale contents of an earlier call are never observed.
+    return launch_attention_decode(*p, scratch, (int64_t)kb::kStaticScratchBytes, (cudaStream_t)stream);
+}
+
 }  // extern "C"

@@ -59,7 +59,7 @@ template <int D>
 struct AttnCfg {
     static constexpr int kKvStages = D == 64 ? 3 : 2;
     static constexpr int kTileBytes = kAttnBlock * D * 2;  // one Q tile / one K block / one V block
-    static constexpr int kSmemBytes = (2 + 2 * kKvStages) * kTileBytes + 512 + 1024;
+    static constexpr int kSmemBytes = (2 + 2 * kKvStages) * kTileBytes + 512 + 2048 + 1024;
 };
 
 __device__ __forceinline__ float mask_lowest(int mask_dtype) {
@@ -74,13 +74,24 @@ __device__ __forceinline__ float mask_load(const void* base, int64_t off, int ma
     return reinterpret_cast<const float*>(base)[off];
 }
 
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+    float r;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
+
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
 
-template <typename T, int D>
+// MODE 0: no mask and positive scale (maximum taken on raw scores, one FFMA + EX2 per element);
+// MODE 1: additive mask that is the same for every query row (padding masks): warps 10-11 stage
+//         it per key block in shared memory, already clamped, scaled by log2(e) and with -inf for
+//         columns beyond N; MODE 2: anything else (per-row masks read from global memory with
+//         128-bit loads where the layout allows, non-positive scale).
+template <typename T, int D, int MODE>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                     const __grid_constant__ CUtensorMap tmap_v, const AttnDev p) {
@@ -106,9 +117,12 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     auto s_full = [&](int t) { return bar_base + 8u * (2 + 4 * KVS + t); };
     auto p_full = [&](int t) { return bar_base + 8u * (4 + 4 * KVS + t); };
     auto o_final = [&](int t) { return bar_base + 8u * (6 + 4 * KVS + t); };
-    constexpr int kNumBars = 8 + 4 * KVS;
+    auto m_full = [&](int t, int bf) { return bar_base + 8u * (8 + 4 * KVS + t * 2 + bf); };
+    auto m_empty = [&](int t, int bf) { return bar_base + 8u * (12 + 4 * KVS + t * 2 + bf); };
+    constexpr int kNumBars = 16 + 4 * KVS;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBars);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    float* mask_smem = reinterpret_cast<float*>(smem + (2 + 2 * KVS) * TILE + 512);  // [tile][buffer][128]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -147,6 +161,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             mbar_init(s_full(t), 1);
             mbar_init(p_full(t), 4);
             mbar_init(o_final(t), 1);
+            for (int bf = 0; bf < 2; ++bf) {
+                mbar_init(m_full(t, bf), 2);   // the two loader warps
+                mbar_init(m_empty(t, bf), 4);  // the four warps of the tile's softmax group
+            }
         }
         for (int s = 0; s < KVS; ++s) {
             mbar_init(k_full(s), 1);
@@ -276,6 +294,31 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                 if (j + 1 < max_blk) tc_commit(k_empty(s1));
             }
         }
+      } else if (MODE == 1) {
+        // ------------------------------------------------------------------ mask loaders (warps 10, 11)
+        const int li = (int)threadIdx.x - 320;  // 0..63, two columns each
+        const float mlow = mask_lowest(p.mask_dtype);
+        const int64_t moff = (int64_t)b * p.mask_strides[0] + (int64_t)h * p.mask_strides[1];
+        bool ok = true;
+        for (int j = 0; j < max_blk && ok; ++j) {
+            const int bf = j & 1;
+            const uint32_t ph = (uint32_t)((j >> 1) & 1);
+            for (int t = 0; t < ntl && ok; ++t) {
+                if (j >= nblk[t]) continue;
+                if (!mbar_wait(m_empty(t, bf), ph ^ 1, abort_flag, 400 + t)) { ok = false; break; }
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int idx = li + e * 64;
+                    const int col = j * kAttnBlock + idx;
+                    float a = -INFINITY;
+                    if (col < p.N)
+                        a = fmaxf(mask_load(p.mask, moff + (int64_t)col * p.mask_strides[3], p.mask_dtype), mlow) * kLog2e;
+                    mask_smem[(t * 2 + bf) * kAttnBlock + idx] = a;
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(m_full(t, bf));
+            }
+        }
       }
     } else {
         asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kAttnRegsHigh));
@@ -288,15 +331,15 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             const uint32_t s_addr = lane_addr + (uint32_t)(t * 128);
             const uint32_t o_addr = lane_addr + (uint32_t)(256 + t * 128);
             const float c = p.scale_log2;
-            const bool has_mask = p.mask != nullptr;
-            const bool plain = !has_mask && c > 0.f;
             const float mlow = mask_lowest(p.mask_dtype);
             const int64_t mask_row_off =
-                has_mask ? (int64_t)b * p.mask_strides[0] + (int64_t)h * p.mask_strides[1] +
-                               (int64_t)min(row, p.M - 1) * p.mask_strides[2]
-                         : 0;
-            float m_ref = -INFINITY;  // reference maximum used for the exponentials (log2 domain; raw S
-                                      // units when `plain`)
+                (MODE == 2 && p.mask != nullptr)
+                    ? (int64_t)b * p.mask_strides[0] + (int64_t)h * p.mask_strides[1] + (int64_t)min(row, p.M - 1) * p.mask_strides[2]
+                    : 0;
+            // In MODE 0 the running maximum is kept in raw score units and the exponent is
+            // (s - m_ref) * c; otherwise scores are first moved to the log2 domain (s*c + mask).
+            const float unit = (MODE == 0) ? c : 1.0f;
+            float m_ref = -INFINITY;
             float l = 0.f;
             bool ok = true;
             for (int j = 0; j < nblk[t]; ++j) {
@@ -308,10 +351,26 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                 tmem_ld_wait();
 
                 const int col0 = j * kAttnBlock;
-                const bool bound = (col0 + kAttnBlock > p.N) || (p.is_causal && col0 + kAttnBlock - 1 > mt[t] * kAttnBlock);
-                // ---- transform to the domain in which the maximum is taken
-                if (!plain) {
-                    if (!has_mask) {
+                const bool causal_edge = p.is_causal && col0 + kAttnBlock - 1 > mt[t] * kAttnBlock;
+                if (MODE == 1) {
+                    const int bf = j & 1;
+                    if (!mbar_wait(m_full(t, bf), (uint32_t)((j >> 1) & 1), abort_flag, 320 + t)) { ok = false; break; }
+                    const float4* ms = reinterpret_cast<const float4*>(mask_smem + (t * 2 + bf) * kAttnBlock);
+#pragma unroll
+                    for (int cch = 0; cch < 4; ++cch) {
+#pragma unroll
+                        for (int v4 = 0; v4 < 8; ++v4) {
+                            const float4 a = ms[cch * 8 + v4];  // same address in every lane: broadcast
+                            sr[cch][v4 * 4 + 0] = __float_as_uint(fmaf(__uint_as_float(sr[cch][v4 * 4 + 0]), c, a.x));
+                            sr[cch][v4 * 4 + 1] = __float_as_uint(fmaf(__uint_as_float(sr[cch][v4 * 4 + 1]), c, a.y));
+                            sr[cch][v4 * 4 + 2] = __float_as_uint(fmaf(__uint_as_float(sr[cch][v4 * 4 + 2]), c, a.z));
+                            sr[cch][v4 * 4 + 3] = __float_as_uint(fmaf(__uint_as_float(sr[cch][v4 * 4 + 3]), c, a.w));
+                        }
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(m_empty(t, bf));
+                } else if (MODE == 2) {
+                    if (p.mask == nullptr) {
 #pragma unroll
                         for (int cch = 0; cch < 4; ++cch) {
 #pragma unroll
@@ -323,8 +382,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                             const int colc = col0 + hc * 16;
                             float mvals[16];
                             if (p.mask_vec && colc + 16 <= p.N) {
-                                // 16 consecutive mask values of this row as 128-bit loads (a row-broadcast
-                                // mask makes every lane read the same address: one transaction per warp)
+                                // 16 consecutive mask values of this row as 128-bit loads
                                 if (p.mask_dtype == KB_F32) {
                                     const float4* mp = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.mask) + mask_row_off + colc);
 #pragma unroll
@@ -361,7 +419,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                         }
                     }
                 }
-                if (bound) {
+                // columns beyond N (already -inf in MODE 1) and, on the diagonal block, above the diagonal
+                if ((MODE != 1 && col0 + kAttnBlock > p.N) || causal_edge) {
 #pragma unroll
                     for (int cch = 0; cch < 4; ++cch) {
 #pragma unroll
@@ -371,14 +430,17 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                         }
                     }
                 }
-                float mx = -INFINITY;
+                // ---- row maximum (three-input max halves the instruction count)
+                float mx4[4];
 #pragma unroll
                 for (int cch = 0; cch < 4; ++cch) {
+                    float mloc = fmaxf(__uint_as_float(sr[cch][0]), __uint_as_float(sr[cch][1]));
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(sr[cch][i]));
+                    for (int i = 2; i < 32; i += 2) mloc = fmax3(mloc, __uint_as_float(sr[cch][i]), __uint_as_float(sr[cch][i + 1]));
+                    mx4[cch] = mloc;
                 }
-                // ---- lazy rescale. In `plain` mode m_ref and mx are raw scores; exponent = (s - m_ref)*c.
-                const float unit = plain ? c : 1.0f;
+                const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+                // ---- lazy rescale
                 float m_new = fmaxf(m_ref, mx);
                 if (m_new == -INFINITY) m_new = 0.f;  // row with nothing visible yet
                 const bool grow = (m_new - m_ref) * unit > kLazyThreshold;  // also true on the first block
@@ -400,8 +462,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                         tmem_st_32x16(o_addr + dch * 16, orr);
                     }
                 }
-                // ---- exponentials, row sum, pack to 16 bit, write P over the first 64 columns of S
+                // ---- exponentials, row sum (four independent partial sums), pack to 16 bit, write P over
+                //      the first 64 columns of S
                 const float neg_ref = -m_ref * unit;
+                float lp[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
                 for (int cch = 0; cch < 4; ++cch) {
                     uint32_t pk[16];
@@ -409,11 +473,12 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                     for (int i = 0; i < 16; ++i) {
                         const float e0 = fast_exp2(fmaf(__uint_as_float(sr[cch][2 * i]), unit, neg_ref));
                         const float e1 = fast_exp2(fmaf(__uint_as_float(sr[cch][2 * i + 1]), unit, neg_ref));
-                        l += e0 + e1;
+                        lp[i & 3] += e0 + e1;
                         pk[i] = Elem<T>::pack2(e0, e1);
                     }
                     tmem_st_32x16(s_addr + cch * 16, pk);
                 }
+                l += (lp[0] + lp[1]) + (lp[2] + lp[3]);
                 tmem_st_wait();
                 tc_fence_before();
                 __syncwarp();
@@ -461,8 +526,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     }
 }
 
-template <typename T, int D>
-static int launch_attention_td(const kb_attn_params& p, cudaStream_t stream) {
+template <typename T, int D, int MODE>
+static int launch_attention_tdm(const kb_attn_params& p, cudaStream_t stream) {
     using Cfg = AttnCfg<D>;
     CUtensorMap tq, tk, tv;
     auto enc = [&](CUtensorMap* out, const void* ptr, int64_t rows, const int64_t* st) -> int {
@@ -506,15 +571,22 @@ static int launch_attention_td(const kb_attn_params& p, cudaStream_t stream) {
 
     static bool attr_set = false;
     if (!attr_set) {
-        if (cudaFuncSetAttribute(attention_tc_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        if (cudaFuncSetAttribute(attention_tc_kernel<T, D, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  Cfg::kSmemBytes) != cudaSuccess)
             return KB_ERR_LAUNCH;
         attr_set = true;
     }
     const int64_t grid = (int64_t)d.num_pairs * p.B * p.H;
     if (grid > 0x7fffffff) return KB_ERR_UNSUPPORTED;
-    attention_tc_kernel<T, D><<<(unsigned)grid, kAttnThreads, Cfg::kSmemBytes, stream>>>(tq, tk, tv, d);
+    attention_tc_kernel<T, D, MODE><<<(unsigned)grid, kAttnThreads, Cfg::kSmemBytes, stream>>>(tq, tk, tv, d);
     return cudaGetLastError() == cudaSuccess ? KB_OK : KB_ERR_LAUNCH;
+}
+
+template <typename T, int D>
+static int launch_attention_td(const kb_attn_params& p, cudaStream_t stream) {
+    if (p.mask == nullptr && p.sm_scale > 0.f) return launch_attention_tdm<T, D, 0>(p, stream);
+    if (p.mask != nullptr && p.mask_strides[2] == 0) return launch_attention_tdm<T, D, 1>(p, stream);
+    return launch_attention_tdm<T, D, 2>(p, stream);
 }
 
 static int launch_attention(const kb_attn_params& p, cudaStream_t stream) {

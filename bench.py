@@ -529,6 +529,12 @@ def run_bert(args):
             for _ in range(5):
                 ref = model(input_ids=ids, attention_mask=mask).last_hidden_state
             cpu_ms = (time.perf_counter() - t0) / 5 * 1e3
+            # parity is checked against the fp32 model with the LayerNorm eps of the reference's
+            # kernel path (eps raised to 1.6e-5 for fp16 inputs, layer_norm.py:295-296)
+            for m in model.modules():
+                if isinstance(m, torch.nn.LayerNorm):
+                    m.eps = max(m.eps, 1.6e-5)
+            ref = model(input_ids=ids, attention_mask=mask).last_hidden_state
     gm = model.half().to(dev)
     optimize_model(gm)
     ids_d, mask_d = ids.to(dev), mask.to(dev)

@@ -77,9 +77,10 @@ int kb_norm_fwd(const kb_norm_params* p, void* stream);
  * act_inputs (optional, [M,N], row stride = y_row_stride) receives the pre-activation values
  * (linear_layer.py:193-195).
  * workspace: when the problem has fewer output tiles than SMs (few rows), K is split across work
- * items that accumulate fp32 partial sums into `workspace` (cleared by the call itself); without a
- * workspace the same result is computed unsplit. The reference fixes SPLIT_K = 1
- * (linear_layer.py:121-122).
+ * items that accumulate fp32 partial sums into `workspace`. The workspace must be ALL ZERO before
+ * the first call that uses it and is left all zero by every call (kb_linear_workspace_bytes gives
+ * the size a problem needs); without a workspace, or with one that is too small, the same result
+ * is computed unsplit. The reference fixes SPLIT_K = 1 (linear_layer.py:121-122).
  * ------------------------------------------------------------------------------------- */
 typedef struct {
     const void* x;          /* [M,K]                                                       */
@@ -93,10 +94,11 @@ typedef struct {
     int32_t     activation; /* KB_ACT_*                                                    */
     int32_t     dtype;      /* KB_F16 / KB_BF16                                            */
     void*       workspace;  /* optional scratch for split-K, 16-byte aligned, or NULL      */
-    int64_t     workspace_bytes; /* split-K is used only when >= M*N*4                     */
+    int64_t     workspace_bytes; /* split-K needs >= kb_linear_workspace_bytes(M, N)       */
 } kb_linear_params;
 
 int kb_linear_fwd(const kb_linear_params* p, void* stream);
+int64_t kb_linear_workspace_bytes(int64_t M, int64_t N);
 
 /* Gated linear unit for SwiGLU feed-forward blocks: y[m,n] = silu(g[m,n]) * u[m,n], where
  * gu = [M, 2*N] holds g in columns [0,N) and u in columns [N,2N). No counterpart in the

@@ -20,6 +20,7 @@ ACTIVATIONS = {"": 0, None: 0, "tanh": 1, "gelu": 2, "fast_gelu": 3, "relu": 4, 
 EXPORTED_SYMBOLS = [
     "kb_norm_fwd",
     "kb_linear_fwd",
+    "kb_linear_workspace_bytes",
     "kb_silu_mul",
     "kb_attention_fwd",
     "kb_attention_decode_scratch_bytes",
@@ -81,6 +82,8 @@ def load() -> ctypes.CDLL:
     lib.kb_norm_fwd.restype = ctypes.c_int
     lib.kb_linear_fwd.argtypes = [POINTER(LinearParams), c_void_p]
     lib.kb_linear_fwd.restype = ctypes.c_int
+    lib.kb_linear_workspace_bytes.argtypes = [c_int64, c_int64]
+    lib.kb_linear_workspace_bytes.restype = c_int64
     lib.kb_silu_mul.argtypes = [c_void_p, c_void_p, c_int64, c_int64, c_int32, c_void_p]
     lib.kb_silu_mul.restype = ctypes.c_int
     lib.kb_attention_fwd.argtypes = [POINTER(AttnParams), c_void_p]

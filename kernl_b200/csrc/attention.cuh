@@ -59,7 +59,13 @@ template <int D>
 struct AttnCfg {
     static constexpr int kKvStages = D == 64 ? 3 : 2;
     static constexpr int kTileBytes = kAttnBlock * D * 2;  // one Q tile / one K block / one V block
-    static constexpr int kSmemBytes = (2 + 2 * kKvStages) * kTileBytes + 512 + 2048 + 1024;
+    // D = 64 only: the row sums of P come out of the tensor core. V gets 16 extra columns of ones
+    // (one 128-byte-swizzled slab of ones in shared memory, shared by every stage), so O has D+16
+    // columns and column D accumulates sum_k P[r,k] of exactly the 16-bit P that multiplies V.
+    static constexpr bool kSumOnTc = (D == 64);
+    static constexpr int kOnesBytes = kSumOnTc ? kAttnBlock * 128 : 0;
+    static constexpr int kOCols = kSumOnTc ? D + 16 : D;
+    static constexpr int kSmemBytes = (2 + 2 * kKvStages) * kTileBytes + kOnesBytes + 512 + 2048 + 1024;
 };
 
 __device__ __forceinline__ float mask_lowest(int mask_dtype) {
@@ -106,7 +112,14 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     const uint32_t q_smem = smem_u32(smem);
     const uint32_t k_smem = q_smem + 2 * TILE;
     const uint32_t v_smem = k_smem + KVS * TILE;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (2 + 2 * KVS) * TILE);
+    constexpr bool kSumOnTc = Cfg::kSumOnTc;
+    // With fp16 inputs the exponentials themselves are taken two at a time in half precision
+    // (ex2.approx.f16x2): the argument s - m_ref is at most 2^3 (lazy rescaling), where fp16 still
+    // resolves 2^-8, and P is rounded to fp16 for the tensor core anyway. bf16 keeps fp32 exponentials.
+    constexpr bool kHalfExp = kSumOnTc && !Elem<T>::kIsBf16;
+    constexpr int OCOLS = Cfg::kOCols;
+    const uint32_t ones_smem = v_smem + KVS * TILE;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (2 + 2 * KVS) * TILE + Cfg::kOnesBytes);
     const uint32_t bar_base = smem_u32(bars);
     // barrier slots
     auto q_full = [&](int t) { return bar_base + 8u * t; };
@@ -122,7 +135,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     constexpr int kNumBars = 16 + 4 * KVS;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBars);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    float* mask_smem = reinterpret_cast<float*>(smem + (2 + 2 * KVS) * TILE + 512);  // [tile][buffer][128]
+    float* mask_smem = reinterpret_cast<float*>(smem + (2 + 2 * KVS) * TILE + Cfg::kOnesBytes + 512);  // [tile][buffer][128]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -175,6 +188,12 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         *abort_flag = 0;
         fence_mbar_init();
     }
+    if (kSumOnTc) {
+        const uint32_t one2 = Elem<T>::pack2(1.0f, 1.0f);
+        uint32_t* ones = reinterpret_cast<uint32_t*>(smem + (2 + 2 * KVS) * TILE);
+        for (int i = threadIdx.x; i < Cfg::kOnesBytes / 4; i += kAttnThreads) ones[i] = one2;
+        fence_proxy_async_smem();  // the tensor core reads shared memory through the async proxy
+    }
     if (warp == 9) {
         tmem_alloc(smem_u32(tmem_slot), kTmemCols);
         tmem_relinquish();
@@ -223,14 +242,16 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         // ------------------------------------------------------------------ MMA issuer
         if (elect_one()) {
             constexpr uint32_t idesc_qk = make_idesc_f16(Elem<T>::kIsBf16, 128, 128, 0, 0);
-            constexpr uint32_t idesc_pv = make_idesc_f16(Elem<T>::kIsBf16, 128, D, 0, 1);
+            constexpr uint32_t idesc_pv = make_idesc_f16(Elem<T>::kIsBf16, 128, OCOLS, 0, 1);
             bool ok = true;
             // Descriptor halves that never change: high word = stride offset 1024 B, version 1, 128-byte
             // swizzle; low word = address >> 4 (+ the leading offset for the N-major V operand).
             constexpr uint32_t desc_hi = (1024u >> 4) | (1u << 14) | (2u << 29);
             const uint32_t q_lo = (q_smem & 0x3FFFF) >> 4;
             const uint32_t k_lo = (k_smem & 0x3FFFF) >> 4;
-            const uint32_t v_lo = ((v_smem & 0x3FFFF) >> 4) | ((uint32_t)(CHUNK >> 4) << 16);
+            // leading offset of the V operand = distance to the next 64-column slab along N: the second
+            // slab of D (D = 128) or the slab of ones (D = 64, added per stage below)
+            const uint32_t v_lo = ((v_smem & 0x3FFFF) >> 4) | (kSumOnTc ? 0u : ((uint32_t)(CHUNK >> 4) << 16));
             auto desc = [&](uint32_t lo) { return ((uint64_t)desc_hi << 32) | (uint64_t)lo; };
             auto issue_qk = [&](int t, int s) {
                 const uint32_t a_lo = q_lo + (uint32_t)(t * (TILE >> 4));
@@ -243,7 +264,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                 }
             };
             auto issue_pv = [&](int t, int s, bool accumulate) {
-                const uint32_t b_lo = v_lo + (uint32_t)(s * (TILE >> 4));
+                uint32_t b_lo = v_lo + (uint32_t)(s * (TILE >> 4));
+                if (kSumOnTc) b_lo |= (uint32_t)((ones_smem - (v_smem + s * TILE)) >> 4) << 16;
                 const uint32_t d_tmem = tmem_base + (uint32_t)(256 + t * 128);
                 const uint32_t a_tmem = tmem_base + (uint32_t)(t * 128);
 #pragma unroll
@@ -453,7 +475,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                 if (j > 0 && __any_sync(0xffffffffu, grow)) {
                     // S_j complete implies P·V of block j-1 complete (issued earlier, same thread), so O is quiescent.
 #pragma unroll
-                    for (int dch = 0; dch < D / 16; ++dch) {
+                    for (int dch = 0; dch < OCOLS / 16; ++dch) {
                         uint32_t orr[16];
                         tmem_ld_32x16(o_addr + dch * 16, orr);
                         tmem_ld_wait();
@@ -471,14 +493,21 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                     uint32_t pk[16];
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
-                        const float e0 = fast_exp2(fmaf(__uint_as_float(sr[cch][2 * i]), unit, neg_ref));
-                        const float e1 = fast_exp2(fmaf(__uint_as_float(sr[cch][2 * i + 1]), unit, neg_ref));
-                        lp[i & 3] += e0 + e1;
-                        pk[i] = Elem<T>::pack2(e0, e1);
+                        const float a0 = fmaf(__uint_as_float(sr[cch][2 * i]), unit, neg_ref);
+                        const float a1 = fmaf(__uint_as_float(sr[cch][2 * i + 1]), unit, neg_ref);
+                        if (kHalfExp) {
+                            const uint32_t h2 = Elem<T>::pack2(a0, a1);
+                            asm("ex2.approx.f16x2 %0, %1;" : "=r"(pk[i]) : "r"(h2));
+                        } else {
+                            const float e0 = fast_exp2(a0);
+                            const float e1 = fast_exp2(a1);
+                            if (!kSumOnTc) lp[i & 3] += e0 + e1;
+                            pk[i] = Elem<T>::pack2(e0, e1);
+                        }
                     }
                     tmem_st_32x16(s_addr + cch * 16, pk);
                 }
-                l += (lp[0] + lp[1]) + (lp[2] + lp[3]);
+                if (!kSumOnTc) l += (lp[0] + lp[1]) + (lp[2] + lp[3]);
                 tmem_st_wait();
                 tc_fence_before();
                 __syncwarp();
@@ -487,6 +516,12 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             // ---- epilogue: O / l -> global
             if (ok && mbar_wait(o_final(t), 0, abort_flag, 310 + t)) {
                 tc_fence_after();
+                if (kSumOnTc) {
+                    uint32_t lr[16];
+                    tmem_ld_32x16(o_addr + D, lr);
+                    tmem_ld_wait();
+                    l = __uint_as_float(lr[0]);
+                }
                 const float inv_l = 1.0f / l;
                 T* o_row = reinterpret_cast<T*>(p.o) + (int64_t)b * p.o_strides[0] + (int64_t)h * p.o_strides[1] +
                            (int64_t)row * p.o_strides[2];

@@ -150,6 +150,11 @@ int kb_linear_fwd(const kb_linear_params* p, void* stream) {
     return launch_linear(*p, (cudaStream_t)stream, g_forced_bn, g_forced_splits);
 }
 
+int64_t kb_linear_workspace_bytes(int64_t M, int64_t N) {
+    if (M <= 0 || N <= 0) return 0;
+    return splitk_workspace_bytes(M, N);
+}
+
 int kb_silu_mul(const void* gu, void* y, int64_t M, int64_t N, int32_t dtype, void* stream) {
     if (gu == nullptr || y == nullptr || M < 0 || N <= 0) return KB_ERR_BAD_ARG;
     if (M == 0) return KB_OK;

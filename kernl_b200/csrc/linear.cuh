@@ -10,8 +10,9 @@
 //               convert, store
 // Split-K: when a problem has fewer output tiles than SMs (few rows: the weight matrix is then
 // streamed from HBM by too few SMs), the K range of every tile is cut into `splits` work items; the
-// items add their fp32 partial tiles into a caller-provided workspace with vector atomics and a
-// small second kernel applies bias + activation and converts.
+// items add their fp32 partial tiles into a caller-provided, zero-initialised workspace with vector
+// atomics; the epilogue warp that contributes last to a slice of a tile (arrival counters) applies
+// bias + activation, writes y and restores the zeros — one launch, no separate reduction kernel.
 // Both operands are K-major (x is [M,K], W is [N,K]) which is exactly what tcgen05 wants, so
 // no transposes are needed. Ragged M / N / K edges rely on TMA zero fill for loads and on
 // predicated stores.
@@ -80,12 +81,103 @@ __device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& m_
     n_idx = r / gsz;
 }
 
+// Epilogue of one 32-column chunk of one output row: z = acc + bias; optional store of z
+// (pre-activation); y = act(z) as 16-bit, 128-bit stores when the chunk is whole and aligned.
+template <typename T>
+__device__ __forceinline__ void epilogue_chunk(const float (&accv)[32], const T* __restrict__ bias,
+                                               T* __restrict__ y_row, T* __restrict__ a_row, int col0,
+                                               int N, bool row_ok, int activation) {
+    const bool full_chunk = (col0 + 32 <= N);
+    float z[32];
+    if (bias != nullptr) {
+        if (full_chunk && (((uintptr_t)(bias + col0)) & 15) == 0) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+                const uint4 bw = __ldg(reinterpret_cast<const uint4*>(bias + col0) + v);
+                const uint32_t w[4] = {bw.x, bw.y, bw.z, bw.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float2 bf = Elem<T>::unpack2(w[i]);
+                    z[v * 8 + 2 * i] = accv[v * 8 + 2 * i] + bf.x;
+                    z[v * 8 + 2 * i + 1] = accv[v * 8 + 2 * i + 1] + bf.y;
+                }
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                const float b = (col0 + j < N) ? Elem<T>::to_f32(bias[col0 + j]) : 0.f;
+                z[j] = accv[j] + b;
+            }
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) z[j] = accv[j];
+    }
+    if (!row_ok) return;
+    const bool vec = full_chunk && ((((uintptr_t)(y_row + col0)) & 15) == 0) &&
+                     (a_row == nullptr || (((uintptr_t)(a_row + col0)) & 15) == 0);
+    if (a_row != nullptr) {
+        if (vec) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+                uint4 o;
+                o.x = Elem<T>::pack2(z[v * 8 + 0], z[v * 8 + 1]);
+                o.y = Elem<T>::pack2(z[v * 8 + 2], z[v * 8 + 3]);
+                o.z = Elem<T>::pack2(z[v * 8 + 4], z[v * 8 + 5]);
+                o.w = Elem<T>::pack2(z[v * 8 + 6], z[v * 8 + 7]);
+                reinterpret_cast<uint4*>(a_row + col0)[v] = o;
+            }
+        } else {
+            for (int j = 0; j < 32; ++j)
+                if (col0 + j < N) a_row[col0 + j] = Elem<T>::from_f32(z[j]);
+        }
+    }
+    // The switch sits outside the element loop so that each case unrolls over registers.
+    switch (activation) {
+        case KB_ACT_TANH:
+#pragma unroll
+            for (int j = 0; j < 32; ++j) z[j] = act_tanh(z[j]);
+            break;
+        case KB_ACT_GELU:
+#pragma unroll
+            for (int j = 0; j < 32; ++j) z[j] = act_gelu(z[j]);
+            break;
+        case KB_ACT_FAST_GELU:
+#pragma unroll
+            for (int j = 0; j < 32; ++j) z[j] = act_fast_gelu(z[j]);
+            break;
+        case KB_ACT_RELU:
+#pragma unroll
+            for (int j = 0; j < 32; ++j) z[j] = fmaxf(z[j], 0.0f);
+            break;
+        case KB_ACT_SILU:
+#pragma unroll
+            for (int j = 0; j < 32; ++j) z[j] = act_silu(z[j]);
+            break;
+        default: break;
+    }
+    if (vec) {
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+            uint4 o;
+            o.x = Elem<T>::pack2(z[v * 8 + 0], z[v * 8 + 1]);
+            o.y = Elem<T>::pack2(z[v * 8 + 2], z[v * 8 + 3]);
+            o.z = Elem<T>::pack2(z[v * 8 + 4], z[v * 8 + 5]);
+            o.w = Elem<T>::pack2(z[v * 8 + 6], z[v * 8 + 7]);
+            reinterpret_cast<uint4*>(y_row + col0)[v] = o;
+        }
+    } else {
+        for (int j = 0; j < 32; ++j)
+            if (col0 + j < N) y_row[col0 + j] = Elem<T>::from_f32(z[j]);
+    }
+}
+
 template <typename T, int BN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
                  const T* __restrict__ bias, T* __restrict__ y, T* __restrict__ act_inputs, int M,
                  int N, int K, int64_t y_row_stride, int activation, int splits, int kps,
-                 float* __restrict__ ws) {
+                 float* __restrict__ ws, int* __restrict__ counters) {
     using Cfg = GemmCfg<BN>;
     constexpr int STAGES = Cfg::kStages;
     extern __shared__ uint8_t smem_raw[];
@@ -248,96 +340,63 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                     }
                     continue;
                 }
-                float z[32];
-                if (bias != nullptr) {
-                    if (full_chunk && (((uintptr_t)(bias + col0)) & 15) == 0) {
+                float accv[32];
 #pragma unroll
-                        for (int v = 0; v < 4; ++v) {
-                            const uint4 bw = __ldg(reinterpret_cast<const uint4*>(bias + col0) + v);
-                            const uint32_t w[4] = {bw.x, bw.y, bw.z, bw.w};
-#pragma unroll
-                            for (int i = 0; i < 4; ++i) {
-                                const float2 bf = Elem<T>::unpack2(w[i]);
-                                z[v * 8 + 2 * i] = __uint_as_float(r[v * 8 + 2 * i]) + bf.x;
-                                z[v * 8 + 2 * i + 1] = __uint_as_float(r[v * 8 + 2 * i + 1]) + bf.y;
-                            }
-                        }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            const float b = (col0 + j < N) ? Elem<T>::to_f32(bias[col0 + j]) : 0.f;
-                            z[j] = __uint_as_float(r[j]) + b;
-                        }
-                    }
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) z[j] = __uint_as_float(r[j]);
-                }
-                if (row < M) {
-                    const bool vec = full_chunk && ((((uintptr_t)(y_row + col0)) & 15) == 0) &&
-                                     (a_row == nullptr || (((uintptr_t)(a_row + col0)) & 15) == 0);
-                    if (a_row != nullptr) {
-                        if (vec) {
-#pragma unroll
-                            for (int v = 0; v < 4; ++v) {
-                                uint4 o;
-                                o.x = Elem<T>::pack2(z[v * 8 + 0], z[v * 8 + 1]);
-                                o.y = Elem<T>::pack2(z[v * 8 + 2], z[v * 8 + 3]);
-                                o.z = Elem<T>::pack2(z[v * 8 + 4], z[v * 8 + 5]);
-                                o.w = Elem<T>::pack2(z[v * 8 + 6], z[v * 8 + 7]);
-                                reinterpret_cast<uint4*>(a_row + col0)[v] = o;
-                            }
-                        } else {
-                            for (int j = 0; j < 32; ++j)
-                                if (col0 + j < N) a_row[col0 + j] = Elem<T>::from_f32(z[j]);
-                        }
-                    }
-                    // The switch sits outside the element loop so that each case unrolls over
-                    // registers.
-                    switch (activation) {
-                        case KB_ACT_TANH:
-#pragma unroll
-                            for (int j = 0; j < 32; ++j) z[j] = act_tanh(z[j]);
-                            break;
-                        case KB_ACT_GELU:
-#pragma unroll
-                            for (int j = 0; j < 32; ++j) z[j] = act_gelu(z[j]);
-                            break;
-                        case KB_ACT_FAST_GELU:
-#pragma unroll
-                            for (int j = 0; j < 32; ++j) z[j] = act_fast_gelu(z[j]);
-                            break;
-                        case KB_ACT_RELU:
-#pragma unroll
-                            for (int j = 0; j < 32; ++j) z[j] = fmaxf(z[j], 0.0f);
-                            break;
-                        case KB_ACT_SILU:
-#pragma unroll
-                            for (int j = 0; j < 32; ++j) z[j] = act_silu(z[j]);
-                            break;
-                        default: break;
-                    }
-                    if (vec) {
-#pragma unroll
-                        for (int v = 0; v < 4; ++v) {
-                            uint4 o;
-                            o.x = Elem<T>::pack2(z[v * 8 + 0], z[v * 8 + 1]);
-                            o.y = Elem<T>::pack2(z[v * 8 + 2], z[v * 8 + 3]);
-                            o.z = Elem<T>::pack2(z[v * 8 + 4], z[v * 8 + 5]);
-                            o.w = Elem<T>::pack2(z[v * 8 + 6], z[v * 8 + 7]);
-                            reinterpret_cast<uint4*>(y_row + col0)[v] = o;
-                        }
-                    } else {
-                        for (int j = 0; j < 32; ++j)
-                            if (col0 + j < N) y_row[col0 + j] = Elem<T>::from_f32(z[j]);
-                    }
-                }
+                for (int j = 0; j < 32; ++j) accv[j] = __uint_as_float(r[j]);
+                epilogue_chunk<T>(accv, bias, y_row, a_row, col0, N, row < M, activation);
             }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(tempty_bar(acc));
             acc ^= 1;
             if (acc == 0) acc_phase ^= 1;
+            if (splits > 1 && c_begin < c_end) {
+                // This warp's slice of the tile (32 rows x its column half) is complete once every
+                // split has added its part: the warp that arrives last applies bias + activation,
+                // writes y, and puts the zeros back so that the workspace is clean for the next call.
+                __threadfence();
+                __syncwarp();
+                const int tile = w % num_tiles;
+                int* counter = counters + tile * 8 + q * 2 + col_half;
+                int prev = 0;
+                if (lane == 0) prev = atomicAdd(counter, 1);
+                prev = __shfl_sync(0xffffffffu, prev, 0);
+                if (prev == splits - 1) {
+                    __threadfence();
+#pragma unroll 1
+                    for (int c0 = c_begin; c0 < c_end; c0 += 32) {
+                        const int col0 = n0 + c0;
+                        if (col0 >= N) break;
+                        float accv[32];
+                        if (row < M) {
+                            float* wrow = ws + (int64_t)row * N + col0;
+                            if (col0 + 32 <= N && ((((uintptr_t)wrow) & 15) == 0)) {
+#pragma unroll
+                                for (int v = 0; v < 8; ++v) {
+                                    const float4 f = __ldcg(reinterpret_cast<const float4*>(wrow) + v);
+                                    accv[v * 4 + 0] = f.x; accv[v * 4 + 1] = f.y; accv[v * 4 + 2] = f.z; accv[v * 4 + 3] = f.w;
+                                    __stcg(reinterpret_cast<float4*>(wrow) + v, make_float4(0.f, 0.f, 0.f, 0.f));
+                                }
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < 32; ++j) {
+                                    accv[j] = 0.f;
+                                    if (col0 + j < N) {
+                                        accv[j] = __ldcg(wrow + j);
+                                        __stcg(wrow + j, 0.f);
+                                    }
+                                }
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) accv[j] = 0.f;
+                        }
+                        epilogue_chunk<T>(accv, bias, y_row, a_row, col0, N, row < M, activation);
+                    }
+                    __syncwarp();
+                    if (lane == 0) *counter = 0;
+                }
+            }
         }
     }
 
@@ -350,40 +409,14 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
     }
 }
 
-// Second pass of a split-K launch: y = act(workspace + bias), 4 columns per thread.
-template <typename T>
-__global__ void __launch_bounds__(256)
-linear_splitk_finish_kernel(const float* __restrict__ ws, const T* __restrict__ bias, T* __restrict__ y,
-                            T* __restrict__ act_inputs, int M, int N, int64_t y_row_stride, int activation) {
-    const int nq = (N + 3) / 4;
-    const int64_t total = (int64_t)M * nq;
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-        const int row = (int)(i / nq), c0 = (int)(i % nq) * 4;
-        float z[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const int c = c0 + j;
-            z[j] = (c < N) ? ws[(int64_t)row * N + c] + (bias ? Elem<T>::to_f32(bias[c]) : 0.f) : 0.f;
-        }
-        if (act_inputs) {
-#pragma unroll
-            for (int j = 0; j < 4; ++j)
-                if (c0 + j < N) act_inputs[(int64_t)row * y_row_stride + c0 + j] = Elem<T>::from_f32(z[j]);
-        }
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            float v = z[j];
-            switch (activation) {
-                case KB_ACT_TANH: v = act_tanh(v); break;
-                case KB_ACT_GELU: v = act_gelu(v); break;
-                case KB_ACT_FAST_GELU: v = act_fast_gelu(v); break;
-                case KB_ACT_RELU: v = fmaxf(v, 0.f); break;
-                case KB_ACT_SILU: v = act_silu(v); break;
-                default: break;
-            }
-            if (c0 + j < N) y[(int64_t)row * y_row_stride + c0 + j] = Elem<T>::from_f32(v);
-        }
-    }
+// Split-K workspace layout: fp32 partial sums [M, N] (rounded up to 16 bytes), then one arrival
+// counter per (tile, warp slice). The whole workspace must be zero before the first call that uses
+// it; every call leaves it zero again (the finishing warp writes the zeros back).
+static int64_t splitk_sums_bytes(int64_t M, int64_t N) { return ((M * N * (int64_t)sizeof(float)) + 15) / 16 * 16; }
+static int64_t splitk_workspace_bytes(int64_t M, int64_t N) {
+    // counters for the narrowest tile width (most tiles)
+    const int64_t tiles = ((M + kGemmBM - 1) / kGemmBM) * ((N + 31) / 32);
+    return splitk_sums_bytes(M, N) + tiles * 8 * (int64_t)sizeof(int);
 }
 
 struct LinearPlan {
@@ -412,8 +445,8 @@ static LinearPlan plan_linear(int64_t M, int64_t N, int64_t K, bool has_ws, int 
             const int eff = (num_k + kps - 1) / kps;  // splits that are not empty
             if (eff != s) continue;
             const int64_t waves = (tiles * s + sms - 1) / sms;
-            // a split tile pays an extra pass over its outputs (atomics + finishing kernel)
-            const double extra = (s > 1) ? 3.0 : 0.0;
+            // a split tile pays an extra pass over its outputs (atomics, then the finishing warp)
+            const double extra = (s > 1) ? 2.0 : 0.0;
             const double cost = (double)waves * ((double)kps + 2.0 + extra) * (double)(kGemmBM + bn);
             if (cost < best_cost) {
                 best_cost = cost;
@@ -455,27 +488,16 @@ static int launch_linear_bn(const kb_linear_params& p, cudaStream_t stream, cons
     const int64_t items = num_tiles * plan.splits;
     const int grid = (int)(items < sm_count() ? items : sm_count());
     float* ws = reinterpret_cast<float*>(p.workspace);
-    if (plan.splits > 1) {
-        if (cudaMemsetAsync(ws, 0, (size_t)p.M * (size_t)p.N * sizeof(float), stream) != cudaSuccess) return KB_ERR_LAUNCH;
-    }
+    int* counters = reinterpret_cast<int*>(reinterpret_cast<char*>(p.workspace) + splitk_sums_bytes(p.M, p.N));
     linear_tc_kernel<T, BN><<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(
         tmap_x, tmap_w, (const T*)p.bias, (T*)p.y, (T*)p.act_inputs, (int)p.M, (int)p.N, (int)p.K,
-        p.y_row_stride, p.activation, plan.splits, plan.kps, ws);
-    if (cudaGetLastError() != cudaSuccess) return KB_ERR_LAUNCH;
-    if (plan.splits > 1) {
-        const int64_t total = p.M * ((p.N + 3) / 4);
-        int64_t blocks = (total + 255) / 256;
-        if (blocks > (int64_t)sm_count() * 8) blocks = (int64_t)sm_count() * 8;
-        linear_splitk_finish_kernel<T><<<(unsigned)blocks, 256, 0, stream>>>(
-            ws, (const T*)p.bias, (T*)p.y, (T*)p.act_inputs, (int)p.M, (int)p.N, p.y_row_stride, p.activation);
-        if (cudaGetLastError() != cudaSuccess) return KB_ERR_LAUNCH;
-    }
-    return KB_OK;
+        p.y_row_stride, p.activation, plan.splits, plan.kps, ws, counters);
+    return cudaGetLastError() == cudaSuccess ? KB_OK : KB_ERR_LAUNCH;
 }
 
 template <typename T>
 static int launch_linear_t(const kb_linear_params& p, cudaStream_t stream, int forced_bn, int forced_splits) {
-    const bool has_ws = p.workspace != nullptr && p.workspace_bytes >= p.M * p.N * (int64_t)sizeof(float) &&
+    const bool has_ws = p.workspace != nullptr && p.workspace_bytes >= splitk_workspace_bytes(p.M, p.N) &&
                         (((uintptr_t)p.workspace) & 15) == 0;
     const LinearPlan plan = plan_linear(p.M, p.N, p.K, has_ws, forced_bn, forced_splits);
     switch (plan.bn) {

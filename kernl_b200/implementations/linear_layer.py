@@ -12,13 +12,14 @@ _workspaces = {}
 
 
 def _workspace(device: torch.device) -> torch.Tensor:
-    """One fp32 scratch buffer per device for split-K partial sums, allocated on first use and
-    kept (a stable address, so CUDA graphs that captured it stay valid). Calls on different
-    streams of one device would share it; the front-end is single-stream like the reference."""
+    """One zero-initialised scratch buffer per device for split-K partial sums, allocated on first
+    use and kept (a stable address, so CUDA graphs that captured it stay valid). The kernel leaves
+    it zero after every call. Calls on different streams of one device would share it; the
+    front-end is single-stream like the reference."""
     key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
     ws = _workspaces.get(key)
     if ws is None:
-        ws = torch.empty(_WORKSPACE_BYTES // 4, dtype=torch.float32, device=device)
+        ws = torch.zeros(_WORKSPACE_BYTES // 4, dtype=torch.float32, device=device)
         _workspaces[key] = ws
     return ws
 
@@ -67,7 +68,7 @@ def linear_layer(
     if act_inputs is not None:
         assert act_inputs.shape == (M, N) and act_inputs.dtype == x.dtype and act_inputs.is_contiguous()
     if M > 0:
-        ws = _workspace(x.device) if M * N * 4 <= _WORKSPACE_BYTES else None
+        ws = _workspace(x.device) if _lib.load().kb_linear_workspace_bytes(M, N) <= _WORKSPACE_BYTES else None
         p = _lib.LinearParams(
             x=x_.data_ptr(), w=weight.data_ptr(), bias=bias.data_ptr() if bias is not None else None,
             y=outputs.data_ptr(), act_inputs=act_inputs.data_ptr() if act_inputs is not None else None,

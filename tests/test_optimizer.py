@@ -175,11 +175,20 @@ def test_bert_base_end_to_end(lib):
     ids = torch.randint(0, 30522, (1, 128), generator=g)
     mask = torch.ones((1, 128), dtype=torch.long)
     with torch.inference_mode():
+        plain_fp32 = model(input_ids=ids, attention_mask=mask).last_hidden_state
+        # The reference's kernel path raises every LayerNorm eps to 1.6e-5 for fp16 inputs
+        # (src/kernl/implementations/layer_norm.py:295-296); BERT's 1e-12 therefore becomes 1.6e-5.
+        # With N(0, 0.02) initialised embeddings (variance 1.2e-3 before the first LayerNorm) that
+        # is a visible change of semantics, so the expectation is the fp32 model WITH that eps.
+        for m in model.modules():
+            if isinstance(m, torch.nn.LayerNorm):
+                m.eps = max(m.eps, 1.6e-5)
         expected = model(input_ids=ids, attention_mask=mask).last_hidden_state
     gpu_model = model.half().cuda()
     with torch.inference_mode():
         eager_fp16 = gpu_model(input_ids=ids.cuda(), attention_mask=mask.cuda()).last_hidden_state
     eager = O.parity(eager_fp16, expected)
+    print(f"eps clamp alone moves the fp32 output by {O.parity(expected, plain_fp32)}")
     optimize_model(gpu_model)
     with torch.inference_mode():
         for _ in range(3):  # first call traces and captures, the next ones replay the graph

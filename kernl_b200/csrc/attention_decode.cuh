@@ -144,6 +144,138 @@ attn_decode_part1_kernel(const DecDev p) {
     }
 }
 
+// Coalesced variant of part 1 for the common layout (unit stride on the head dimension, rows 16-byte
+// aligned, D = 8 * LPK with LPK lanes per key in {8, 16, 32}): the lanes of a warp cover 32/LPK whole
+// keys per step with one 128-bit load each, so every load instruction of a warp reads 512 contiguous
+// bytes of K (or V) and each byte is requested exactly once. Scores are reduced over the LPK lanes
+// with shuffles; for P·V each lane accumulates its 8 output dimensions over the keys it sees and the
+// 128/LPK key groups of the CTA are summed through shared memory at the end.
+template <typename T, int LPK>
+__global__ void __launch_bounds__(kDecThreads)
+attn_decode_part1_vec_kernel(const DecDev p) {
+    constexpr int D = LPK * 8;
+    constexpr int KPW = 32 / LPK;                 // keys per warp per step
+    constexpr int KPS = KPW * (kDecThreads / 32);  // keys per CTA per step
+    constexpr int GROUPS = kDecThreads / LPK;      // key groups in the CTA
+    __shared__ float sc_s[kDecThreads];
+    __shared__ float red_s[kDecThreads / 32];
+    __shared__ float acc_s[GROUPS][D + 4];
+    const int split = blockIdx.x, row = blockIdx.y, bh = blockIdx.z;
+    const int b = bh / p.H, h = bh % p.H;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int sub = lane / LPK;   // which of the warp's keys this lane works on
+    const int dl = lane % LPK;    // which 8-wide slice of the head dimension
+    const int group = tid / LPK;  // == warp * KPW + sub
+
+    // this lane's slice of q, pre-scaled into the log2 domain
+    float qv[8];
+    {
+        const T* qp = reinterpret_cast<const T*>(p.q) + (int64_t)b * p.q_strides[0] + (int64_t)h * p.q_strides[1] +
+                      (int64_t)row * p.q_strides[2] + dl * 8;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) qv[i] = Elem<T>::to_f32(qp[i]) * p.scale_log2;
+    }
+    const T* kbase = reinterpret_cast<const T*>(p.k) + (int64_t)b * p.k_strides[0] + (int64_t)h * p.k_strides[1] + dl * 8;
+    const T* vbase = reinterpret_cast<const T*>(p.v) + (int64_t)b * p.v_strides[0] + (int64_t)h * p.v_strides[1] + dl * 8;
+    const float mlow = mask_lowest(p.mask_dtype);
+    const int64_t mask_off = p.mask ? (int64_t)b * p.mask_strides[0] + (int64_t)h * p.mask_strides[1] +
+                                          (int64_t)row * p.mask_strides[2]
+                                    : 0;
+    float m_run = -INFINITY, l_run = 0.f;
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+
+    const int key_begin = split * p.chunk;
+    const int key_end = min(p.N, key_begin + p.chunk);
+    for (int k0 = key_begin; k0 < key_end; k0 += kDecThreads) {
+        // ---- scores of the block's 128 keys: step s handles keys k0 + s*KPS + group
+#pragma unroll 4
+        for (int s = 0; s < kDecThreads / KPS; ++s) {
+            const int key = k0 + s * KPS + group;
+            float dot = 0.f;
+            if (key < key_end) {
+                const uint4 w = __ldg(reinterpret_cast<const uint4*>(kbase + (int64_t)key * p.k_strides[2]));
+                const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float2 f = Elem<T>::unpack2(ww[i]);
+                    dot = fmaf(f.x, qv[2 * i], dot);
+                    dot = fmaf(f.y, qv[2 * i + 1], dot);
+                }
+            }
+#pragma unroll
+            for (int o = LPK / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+            if (dl == 0) {
+                float sc = -INFINITY;
+                if (key < key_end && !(p.is_causal && key > row)) {
+                    sc = dot;
+                    if (p.mask) {
+                        const float mv = mask_load(p.mask, mask_off + (int64_t)key * p.mask_strides[3], p.mask_dtype);
+                        sc = fmaf(fmaxf(mv, mlow), kLog2e, sc);
+                    }
+                }
+                sc_s[s * KPS + group] = sc;
+            }
+        }
+        __syncthreads();
+        // ---- block maximum and exponentials (one key per thread)
+        const float sv = sc_s[tid];
+        float mx = sv;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        if (lane == 0) red_s[warp] = mx;
+        __syncthreads();
+        mx = fmaxf(fmaxf(red_s[0], red_s[1]), fmaxf(red_s[2], red_s[3]));
+        float m_new = fmaxf(m_run, mx);
+        if (m_new == -INFINITY) m_new = 0.f;
+        const float alpha = (m_run == -INFINITY) ? 0.f : fast_exp2(m_run - m_new);
+        const float pe = fast_exp2(sv - m_new);
+        __syncthreads();  // everyone has read sc_s and red_s
+        // P is rounded to the input dtype before P·V, as the reference does (attention_skinny.py:262)
+        sc_s[tid] = Elem<T>::to_f32(Elem<T>::from_f32(pe));
+        float ps = pe;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, o);
+        if (lane == 0) red_s[warp] = ps;
+        __syncthreads();
+        l_run = l_run * alpha + (red_s[0] + red_s[1] + red_s[2] + red_s[3]);
+        m_run = m_new;
+        // ---- P·V with the same key-to-lane mapping
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] *= alpha;
+#pragma unroll 4
+        for (int s = 0; s < kDecThreads / KPS; ++s) {
+            const int kk = s * KPS + group;
+            const int key = k0 + kk;
+            if (key < key_end) {
+                const float pk = sc_s[kk];
+                const uint4 w = __ldg(reinterpret_cast<const uint4*>(vbase + (int64_t)key * p.v_strides[2]));
+                const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float2 f = Elem<T>::unpack2(ww[i]);
+                    acc[2 * i] = fmaf(pk, f.x, acc[2 * i]);
+                    acc[2 * i + 1] = fmaf(pk, f.y, acc[2 * i + 1]);
+                }
+            }
+        }
+        __syncthreads();  // sc_s is rewritten by the next block
+    }
+    // ---- sum the key groups and write (m, l, acc[D])
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc_s[group][dl * 8 + i] = acc[i];
+    __syncthreads();
+    float* out = p.scratch + (((int64_t)bh * p.M + row) * p.num_splits + split) * (D + 2);
+    if (tid == 0) { out[0] = m_run; out[1] = l_run; }
+    for (int d = tid; d < D; d += kDecThreads) {
+        float a = 0.f;
+#pragma unroll
+        for (int g = 0; g < GROUPS; ++g) a += acc_s[g][d];
+        out[2 + d] = a;
+    }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kDecThreads)
 attn_decode_part2_kernel(const DecDev p) {
@@ -190,11 +322,21 @@ static int launch_attention_decode(const kb_attn_params& p, void* scratch, int64
     d.scratch = reinterpret_cast<float*>(scratch);
     const dim3 g1((unsigned)d.num_splits, (unsigned)p.M, (unsigned)(p.B * p.H));
     const dim3 g2((unsigned)p.M, (unsigned)(p.B * p.H));
+    const bool vec_ok = (p.D == 64 || p.D == 128 || p.D == 256) && p.q_strides[3] == 1 && p.k_strides[3] == 1 &&
+                        p.v_strides[3] == 1 && (p.k_strides[2] % 8) == 0 && (p.v_strides[2] % 8) == 0 &&
+                        (p.k_strides[1] % 8) == 0 && (p.v_strides[1] % 8) == 0 && (p.k_strides[0] % 8) == 0 &&
+                        (p.v_strides[0] % 8) == 0 && (((uintptr_t)p.k) & 15) == 0 && (((uintptr_t)p.v) & 15) == 0;
     if (p.dtype == KB_F16) {
-        attn_decode_part1_kernel<__half><<<g1, kDecThreads, 0, stream>>>(d);
+        if (vec_ok && p.D == 64) attn_decode_part1_vec_kernel<__half, 8><<<g1, kDecThreads, 0, stream>>>(d);
+        else if (vec_ok && p.D == 128) attn_decode_part1_vec_kernel<__half, 16><<<g1, kDecThreads, 0, stream>>>(d);
+        else if (vec_ok && p.D == 256) attn_decode_part1_vec_kernel<__half, 32><<<g1, kDecThreads, 0, stream>>>(d);
+        else attn_decode_part1_kernel<__half><<<g1, kDecThreads, 0, stream>>>(d);
         attn_decode_part2_kernel<__half><<<g2, kDecThreads, 0, stream>>>(d);
     } else {
-        attn_decode_part1_kernel<__nv_bfloat16><<<g1, kDecThreads, 0, stream>>>(d);
+        if (vec_ok && p.D == 64) attn_decode_part1_vec_kernel<__nv_bfloat16, 8><<<g1, kDecThreads, 0, stream>>>(d);
+        else if (vec_ok && p.D == 128) attn_decode_part1_vec_kernel<__nv_bfloat16, 16><<<g1, kDecThreads, 0, stream>>>(d);
+        else if (vec_ok && p.D == 256) attn_decode_part1_vec_kernel<__nv_bfloat16, 32><<<g1, kDecThreads, 0, stream>>>(d);
+        else attn_decode_part1_kernel<__nv_bfloat16><<<g1, kDecThreads, 0, stream>>>(d);
         attn_decode_part2_kernel<__nv_bfloat16><<<g2, kDecThreads, 0, stream>>>(d);
     }
     return cudaGetLastError() == cudaSuccess ? KB_OK : KB_ERR_LAUNCH;

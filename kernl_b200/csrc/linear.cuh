@@ -11,8 +11,9 @@
 // Split-K: when a problem has fewer output tiles than SMs (few rows: the weight matrix is then
 // streamed from HBM by too few SMs), the K range of every tile is cut into `splits` work items; the
 // items add their fp32 partial tiles into a caller-provided, zero-initialised workspace with vector
-// atomics; the epilogue warp that contributes last to a slice of a tile (arrival counters) applies
-// bias + activation, writes y and restores the zeros — one launch, no separate reduction kernel.
+// atomics, and a small second kernel applies bias + activation, converts, and writes the zeros back.
+// (Letting the last-arriving epilogue warp finish its slice inside the GEMM kernel was tried and was
+// slower: the finishing warps serialise on L2 round trips that a separate, fully parallel pass hides.)
 // Both operands are K-major (x is [M,K], W is [N,K]) which is exactly what tcgen05 wants, so
 // no transposes are needed. Ragged M / N / K edges rely on TMA zero fill for loads and on
 // predicated stores.
@@ -177,7 +178,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
                  const T* __restrict__ bias, T* __restrict__ y, T* __restrict__ act_inputs, int M,
                  int N, int K, int64_t y_row_stride, int activation, int splits, int kps,
-                 float* __restrict__ ws, int* __restrict__ counters) {
+                 float* __restrict__ ws) {
     using Cfg = GemmCfg<BN>;
     constexpr int STAGES = Cfg::kStages;
     extern __shared__ uint8_t smem_raw[];
@@ -350,53 +351,6 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
             if (lane == 0) mbar_arrive(tempty_bar(acc));
             acc ^= 1;
             if (acc == 0) acc_phase ^= 1;
-            if (splits > 1 && c_begin < c_end) {
-                // This warp's slice of the tile (32 rows x its column half) is complete once every
-                // split has added its part: the warp that arrives last applies bias + activation,
-                // writes y, and puts the zeros back so that the workspace is clean for the next call.
-                __threadfence();
-                __syncwarp();
-                const int tile = w % num_tiles;
-                int* counter = counters + tile * 8 + q * 2 + col_half;
-                int prev = 0;
-                if (lane == 0) prev = atomicAdd(counter, 1);
-                prev = __shfl_sync(0xffffffffu, prev, 0);
-                if (prev == splits - 1) {
-                    __threadfence();
-#pragma unroll 1
-                    for (int c0 = c_begin; c0 < c_end; c0 += 32) {
-                        const int col0 = n0 + c0;
-                        if (col0 >= N) break;
-                        float accv[32];
-                        if (row < M) {
-                            float* wrow = ws + (int64_t)row * N + col0;
-                            if (col0 + 32 <= N && ((((uintptr_t)wrow) & 15) == 0)) {
-#pragma unroll
-                                for (int v = 0; v < 8; ++v) {
-                                    const float4 f = __ldcg(reinterpret_cast<const float4*>(wrow) + v);
-                                    accv[v * 4 + 0] = f.x; accv[v * 4 + 1] = f.y; accv[v * 4 + 2] = f.z; accv[v * 4 + 3] = f.w;
-                                    __stcg(reinterpret_cast<float4*>(wrow) + v, make_float4(0.f, 0.f, 0.f, 0.f));
-                                }
-                            } else {
-#pragma unroll
-                                for (int j = 0; j < 32; ++j) {
-                                    accv[j] = 0.f;
-                                    if (col0 + j < N) {
-                                        accv[j] = __ldcg(wrow + j);
-                                        __stcg(wrow + j, 0.f);
-                                    }
-                                }
-                            }
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 32; ++j) accv[j] = 0.f;
-                        }
-                        epilogue_chunk<T>(accv, bias, y_row, a_row, col0, N, row < M, activation);
-                    }
-                    __syncwarp();
-                    if (lane == 0) *counter = 0;
-                }
-            }
         }
     }
 
@@ -409,15 +363,58 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
     }
 }
 
-// Split-K workspace layout: fp32 partial sums [M, N] (rounded up to 16 bytes), then one arrival
-// counter per (tile, warp slice). The whole workspace must be zero before the first call that uses
-// it; every call leaves it zero again (the finishing warp writes the zeros back).
-static int64_t splitk_sums_bytes(int64_t M, int64_t N) { return ((M * N * (int64_t)sizeof(float)) + 15) / 16 * 16; }
-static int64_t splitk_workspace_bytes(int64_t M, int64_t N) {
-    // counters for the narrowest tile width (most tiles)
-    const int64_t tiles = ((M + kGemmBM - 1) / kGemmBM) * ((N + 31) / 32);
-    return splitk_sums_bytes(M, N) + tiles * 8 * (int64_t)sizeof(int);
+// Second pass of a split-K launch: y = act(workspace + bias), four columns per thread; the sums are
+// replaced by zeros as they are read, so the workspace is clean again for the next call.
+template <typename T>
+__global__ void __launch_bounds__(256)
+linear_splitk_finish_kernel(float* __restrict__ ws, const T* __restrict__ bias, T* __restrict__ y,
+                            T* __restrict__ act_inputs, int M, int N, int64_t y_row_stride, int activation) {
+    const int nq = (N + 3) / 4;
+    const int64_t total = (int64_t)M * nq;
+    const bool vec4 = (N % 4) == 0;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int row = (int)(i / nq), c0 = (int)(i % nq) * 4;
+        float z[4] = {0.f, 0.f, 0.f, 0.f};
+        float* wp = ws + (int64_t)row * N + c0;
+        if (vec4) {
+            const float4 f = __ldcg(reinterpret_cast<const float4*>(wp));
+            __stcg(reinterpret_cast<float4*>(wp), make_float4(0.f, 0.f, 0.f, 0.f));
+            z[0] = f.x; z[1] = f.y; z[2] = f.z; z[3] = f.w;
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                if (c0 + j < N) { z[j] = __ldcg(wp + j); __stcg(wp + j, 0.f); }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            if (bias != nullptr && c0 + j < N) z[j] += Elem<T>::to_f32(bias[c0 + j]);
+        if (act_inputs) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                if (c0 + j < N) act_inputs[(int64_t)row * y_row_stride + c0 + j] = Elem<T>::from_f32(z[j]);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            float v = z[j];
+            switch (activation) {
+                case KB_ACT_TANH: v = act_tanh(v); break;
+                case KB_ACT_GELU: v = act_gelu(v); break;
+                case KB_ACT_FAST_GELU: v = act_fast_gelu(v); break;
+                case KB_ACT_RELU: v = fmaxf(v, 0.f); break;
+                case KB_ACT_SILU: v = act_silu(v); break;
+                default: break;
+            }
+            if (c0 + j < N) y[(int64_t)row * y_row_stride + c0 + j] = Elem<T>::from_f32(v);
+        }
+    }
 }
+
+// Split-K workspace: fp32 partial sums [M, N]. It must be all zero before the first call that uses
+// it; every call leaves it zero again (the finishing kernel writes the zeros back as it reads).
+static int64_t splitk_workspace_bytes(int64_t M, int64_t N) { return ((M * N * (int64_t)sizeof(float)) + 15) / 16 * 16; }
+// Splitting pays only while the extra pass over the output is small next to streaming W once:
+// few row tiles and a bounded output.
+static bool splitk_allowed(int64_t M, int64_t N) { return M <= 1024 && M * N <= (int64_t)4 << 20; }
 
 struct LinearPlan {
     int bn;      // column-tile width
@@ -445,8 +442,8 @@ static LinearPlan plan_linear(int64_t M, int64_t N, int64_t K, bool has_ws, int 
             const int eff = (num_k + kps - 1) / kps;  // splits that are not empty
             if (eff != s) continue;
             const int64_t waves = (tiles * s + sms - 1) / sms;
-            // a split tile pays an extra pass over its outputs (atomics, then the finishing warp)
-            const double extra = (s > 1) ? 2.0 : 0.0;
+            // a split tile pays an extra pass over its outputs (atomics, then the finishing kernel)
+            const double extra = (s > 1) ? 3.0 : 0.0;
             const double cost = (double)waves * ((double)kps + 2.0 + extra) * (double)(kGemmBM + bn);
             if (cost < best_cost) {
                 best_cost = cost;
@@ -488,17 +485,25 @@ static int launch_linear_bn(const kb_linear_params& p, cudaStream_t stream, cons
     const int64_t items = num_tiles * plan.splits;
     const int grid = (int)(items < sm_count() ? items : sm_count());
     float* ws = reinterpret_cast<float*>(p.workspace);
-    int* counters = reinterpret_cast<int*>(reinterpret_cast<char*>(p.workspace) + splitk_sums_bytes(p.M, p.N));
     linear_tc_kernel<T, BN><<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(
         tmap_x, tmap_w, (const T*)p.bias, (T*)p.y, (T*)p.act_inputs, (int)p.M, (int)p.N, (int)p.K,
-        p.y_row_stride, p.activation, plan.splits, plan.kps, ws, counters);
-    return cudaGetLastError() == cudaSuccess ? KB_OK : KB_ERR_LAUNCH;
+        p.y_row_stride, p.activation, plan.splits, plan.kps, ws);
+    if (cudaGetLastError() != cudaSuccess) return KB_ERR_LAUNCH;
+    if (plan.splits > 1) {
+        const int64_t total = p.M * ((p.N + 3) / 4);
+        int64_t blocks = (total + 255) / 256;
+        if (blocks > (int64_t)sm_count() * 8) blocks = (int64_t)sm_count() * 8;
+        linear_splitk_finish_kernel<T><<<(unsigned)blocks, 256, 0, stream>>>(
+            ws, (const T*)p.bias, (T*)p.y, (T*)p.act_inputs, (int)p.M, (int)p.N, p.y_row_stride, p.activation);
+        if (cudaGetLastError() != cudaSuccess) return KB_ERR_LAUNCH;
+    }
+    return KB_OK;
 }
 
 template <typename T>
 static int launch_linear_t(const kb_linear_params& p, cudaStream_t stream, int forced_bn, int forced_splits) {
     const bool has_ws = p.workspace != nullptr && p.workspace_bytes >= splitk_workspace_bytes(p.M, p.N) &&
-                        (((uintptr_t)p.workspace) & 15) == 0;
+                        (((uintptr_t)p.workspace) & 15) == 0 && (splitk_allowed(p.M, p.N) || forced_splits > 1);
     const LinearPlan plan = plan_linear(p.M, p.N, p.K, has_ws, forced_bn, forced_splits);
     switch (plan.bn) {
         case 256: return launch_linear_bn<T, 256>(p, stream, plan);

@@ -189,6 +189,7 @@ class LlamaTP:
             x = x + self.comm.all_reduce(self.ops.linear(attn2d, layer["wo"]))
             h = self.ops.rms_norm(x, layer["norm2"], cfg.eps)
             x = x + self._mlp(layer, h)
+        self.len_mask.fill_(float("-inf"))
         self.len_mask[..., :S] = 0
         self.pos.fill_(S)
         last = x.reshape(B, S, cfg.hidden)[:, -1]
@@ -219,33 +220,38 @@ class LlamaTP:
         x = self.ops.rms_norm(x, self.final_norm, cfg.eps)
         return self.ops.linear(x, self.lm_head)
 
+    def capture_decode(self, tokens: torch.Tensor):
+        """Capture one decode step in a CUDA graph (after the prefill). Returns (replay, static_tok,
+        static_next): copy the current tokens into `static_tok`, call `replay()`, read the greedy
+        next tokens from `static_next`. The warm-up step and the capture advance the position and
+        write cache slots; that state is restored here and the real steps overwrite the slots."""
+        static_tok = tokens.clone()
+        saved = (self.pos.clone(), self.len_mask.clone())
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            self.decode_step(static_tok)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            static_next = self.decode_step(static_tok).float().argmax(-1)
+        self.pos.copy_(saved[0])
+        self.len_mask.copy_(saved[1])
+        self._decode_graph = graph  # keep the graph alive
+        return graph.replay, static_tok, static_next
+
     def generate(self, ids: torch.Tensor, steps: int, use_cuda_graph: bool = True) -> torch.Tensor:
         """Greedy decoding: prefill, then `steps` tokens. Returns [B, steps] token ids. The argmax
         stays on the device, so no step waits for the host."""
         logits = self.prefill(ids)
         tok = logits.float().argmax(-1)
         out = [tok]
-        graph = None
         if use_cuda_graph and self.device.type == "cuda" and steps > 2:
-            static_tok = tok.clone()
-            saved = (self.pos.clone(), self.len_mask.clone())
-            # one eager warm-up step (on a side stream) and the capture both advance the position
-            # and write cache slots; the state is restored afterwards and the real steps overwrite
-            # those slots again
-            side = torch.cuda.Stream()
-            side.wait_stream(torch.cuda.current_stream())
-            with torch.cuda.stream(side):
-                self.decode_step(static_tok)
-            torch.cuda.current_stream().wait_stream(side)
-            torch.cuda.synchronize()
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, stream=side):
-                static_next = self.decode_step(static_tok).float().argmax(-1)
-            self.pos.copy_(saved[0])
-            self.len_mask.copy_(saved[1])
+            replay, static_tok, static_next = self.capture_decode(tok)
             for _ in range(steps - 1):
                 static_tok.copy_(out[-1])
-                graph.replay()
+                replay()
                 out.append(static_next.clone())
         else:
             for _ in range(steps - 1):

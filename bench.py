@@ -403,6 +403,7 @@ def run_sweep(args):
     from kernl_b200.implementations.linear_layer import linear_layer
 
     build.build()
+    _lib.load().kb_debug_attention_variant(args.attn_variant)
     peaks, _ = load_peaks()
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(0)
@@ -684,6 +685,8 @@ def main():
     ap.add_argument("--sweep", choices=["all", "attention", "linear", "norm", "decode"], default=None,
                     help="per-shape kernel timings instead of the headline line")
     ap.add_argument("--case", default=None, help="with --sweep: only cases whose name contains this")
+    ap.add_argument("--attn-variant", type=int, default=0, help="with --sweep: fused-attention kernel, 0 = dispatcher's choice, "
+                    "1 = 128-key blocks, 2 = 64-key blocks")
     ap.add_argument("--workload", choices=["attention", "bert", "llama"], default="attention",
                     help="attention = headline (default); bert / llama = the model configs")
     ap.add_argument("--layers", type=int, default=32, help="llama workload: number of layers")

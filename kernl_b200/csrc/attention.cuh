@@ -624,7 +624,7 @@ static int launch_attention_td(const kb_attn_params& p, cudaStream_t stream) {
     return launch_attention_tdm<T, D, 2>(p, stream);
 }
 
-static int launch_attention(const kb_attn_params& p, cudaStream_t stream) {
+static int launch_attention128(const kb_attn_params& p, cudaStream_t stream) {
     if (p.N <= 0) return KB_ERR_UNSUPPORTED;
     if (p.M > 0x7fffffff || p.N > 0x7fffffff || p.B * p.H > 0x7fffffff) return KB_ERR_UNSUPPORTED;
     if (p.dtype == KB_F16) {

@@ -8,6 +8,7 @@
 #include "norm.cuh"
 #include "linear.cuh"
 #include "attention.cuh"
+#include "attention_kb64.cuh"
 #include "attention_decode.cuh"
 
 namespace kb {
@@ -134,6 +135,8 @@ int kb_norm_fwd(const kb_norm_params* p, void* stream) {
 
 // Test hook: force the GEMM column-tile width (0 = heuristic). Not part of the stable ABI.
 void kb_debug_force_bn(int bn) { g_forced_bn = bn; }
+// Test hook: choose the fused-attention kernel (0 = by head dimension, 1 = 128-key blocks, 2 = 64-key blocks).
+void kb_debug_attention_variant(int v) { g_attn_variant = v; }
 // Test hook: force the number of K splits (0 = heuristic; needs a workspace).
 void kb_debug_force_splits(int splits) { g_forced_splits = splits; }
 

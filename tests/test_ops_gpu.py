@@ -84,6 +84,22 @@ def test_attention_head_dim_128(lib, dtype, tol, causal):
     O.assert_parity(out, expected, max_abs=tol, what="attention d=128")
 
 
+@pytest.mark.parametrize("variant", [1, 2], ids=["blocks128", "blocks64"])
+@pytest.mark.parametrize("d,dtype,tol", [(64, torch.float16, 1e-2), (64, torch.bfloat16, 3e-2), (128, torch.float16, 1e-2), (128, torch.bfloat16, 3e-2)],
+                         ids=["d64_fp16", "d64_bf16", "d128_fp16", "d128_bf16"])
+@pytest.mark.parametrize("mask_kind,causal,m,n", [("none", False, 512, 512), ("pad", False, 300, 300), ("bias", True, 257, 257),
+                                                  ("none", True, 640, 640), ("bias", False, 100, 700), ("none", False, 1, 24)])
+def test_attention_both_kernels(lib, variant, d, dtype, tol, mask_kind, causal, m, n):
+    """Both fused kernels (128-key blocks; 64-key blocks with double-buffered scores) on every
+    head dimension and dtype, whatever the dispatcher would pick."""
+    try:
+        lib.kb_debug_attention_variant(variant)
+        out, expected = _run_attention(2, 3, m, n, d, dtype, causal, mask_kind, d ** -0.5)
+    finally:
+        lib.kb_debug_attention_variant(0)
+    O.assert_parity(out, expected, max_abs=tol, what=f"variant {variant} d={d}")
+
+
 def test_attention_fp32_mask_and_row_broadcast(lib):
     out, expected = _run_attention(2, 4, 200, 200, 64, torch.float16, False, "pad", 0.125, mask_dtype=torch.float32)
     O.assert_parity(out, expected)

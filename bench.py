@@ -452,6 +452,24 @@ def run_sweep(args):
                 d = timed(make_set, 4 * B * H * S * D * 2)
                 fl = 4.0 * B * H * D * (S * (S + 1) / 2 if causal else S * S)
                 emit(name, d, flops=fl)
+    # the same kernels with enough (batch x heads) to fill the GPU several times over: the sweep
+    # above holds batch*seq at 4096 tokens, i.e. 192 CTAs on 148 SMs for head_dim 64
+    for (B, H, S, D, dt, tag, causal) in ((8, 12, 4096, 64, torch.float16, "f16_d64_s4096_b8_full", False),
+                                          (8, 12, 4096, 64, torch.float16, "f16_d64_s4096_b8_causal", True),
+                                          (64, 12, 512, 64, torch.float16, "f16_d64_s512_b64_full", False),
+                                          (8, 12, 4096, 64, torch.bfloat16, "bf16_d64_s4096_b8_full", False),
+                                          (4, 32, 4096, 128, torch.float16, "f16_d128_s4096_b4_full", False)):
+        name = f"attention_big:{tag}"
+        if not want(name):
+            continue
+
+        def make_set():
+            q, k, v = (torch.randn((B, H, S, D), generator=g).to(dt).to(dev) for _ in range(3))
+            o = torch.empty_like(q)
+            return lambda: attention_forward(q, k, v, o, D ** -0.5, causal, None)
+
+        d = timed(make_set, 4 * B * H * S * D * 2)
+        emit(name, d, flops=4.0 * B * H * D * (S * (S + 1) / 2 if causal else S * S))
     for M in (16, 128, 1024, 8192):
         for (K, N) in ((768, 768), (768, 3072), (3072, 768), (4096, 11008), (11008, 4096)):
             for act in ("", "gelu", "relu"):
@@ -682,7 +700,7 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--sweep", choices=["all", "attention", "linear", "norm", "decode"], default=None,
+    ap.add_argument("--sweep", choices=["all", "attention", "attention_big", "linear", "norm", "decode"], default=None,
                     help="per-shape kernel timings instead of the headline line")
     ap.add_argument("--case", default=None, help="with --sweep: only cases whose name contains this")
     ap.add_argument("--attn-variant", type=int, default=0, help="with --sweep: fused-attention kernel, 0 = dispatcher's choice, "

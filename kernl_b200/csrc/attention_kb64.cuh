@@ -53,8 +53,10 @@ attention_tc64_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kTilesBytes);
     const uint32_t bar_base = smem_u32(bars);
     auto q_full = [&](int t) { return bar_base + 8u * t; };
-    auto p_full = [&](int t) { return bar_base + 8u * (2 + t); };
-    auto pv_done = [&](int t) { return bar_base + 8u * (4 + t); };
+    // P_j written (softmax -> issuer), one barrier per block parity: a softmax group may finish block
+    // j+1 before the issuer has looked at block j, and a single barrier's phase parity could not tell
+    // those two completions apart
+    auto p_full = [&](int t, int bf) { return bar_base + 8u * (2 + t * 2 + bf); };
     auto o_final = [&](int t) { return bar_base + 8u * (6 + t); };
     auto s_full = [&](int t, int bf) { return bar_base + 8u * (8 + t * 2 + bf); };
     auto m_full = [&](int t, int bf) { return bar_base + 8u * (12 + t * 2 + bf); };
@@ -63,7 +65,9 @@ attention_tc64_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     auto k_empty = [&](int s) { return bar_base + 8u * (20 + KVS + s); };
     auto v_full = [&](int s) { return bar_base + 8u * (20 + 2 * KVS + s); };
     auto v_empty = [&](int s) { return bar_base + 8u * (20 + 3 * KVS + s); };
-    constexpr int kNumBars = 20 + 4 * KVS;
+    // completion of O_t += P_j·V_j, one barrier per block parity (see the rescale path below)
+    auto pv_done = [&](int t, int bf) { return bar_base + 8u * (20 + 4 * KVS + t * 2 + bf); };
+    constexpr int kNumBars = 24 + 4 * KVS;
     static_assert(kNumBars * 8 + 16 <= 512, "barrier area too small");
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBars);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -99,11 +103,11 @@ attention_tc64_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     if (threadIdx.x == 0) {
         for (int t = 0; t < 2; ++t) {
             mbar_init(q_full(t), 1);
-            mbar_init(p_full(t), 4);
-            mbar_init(pv_done(t), 1);
             mbar_init(o_final(t), 1);
             for (int bf = 0; bf < 2; ++bf) {
                 mbar_init(s_full(t, bf), 1);
+                mbar_init(pv_done(t, bf), 1);
+                mbar_init(p_full(t, bf), 4);
                 mbar_init(m_full(t, bf), 2);
                 mbar_init(m_empty(t, bf), 4);
             }
@@ -221,10 +225,10 @@ attention_tc64_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
                 }
                 for (int t = 0; t < ntl; ++t) {
                     if (j >= nblk[t]) continue;
-                    if (!mbar_wait(p_full(t), (uint32_t)(j & 1), abort_flag, 204)) { ok = false; break; }
+                    if (!mbar_wait(p_full(t, j & 1), (uint32_t)((j >> 1) & 1), abort_flag, 204)) { ok = false; break; }
                     tc_fence_after();
                     issue_pv(t, j);
-                    tc_commit(pv_done(t));
+                    tc_commit(pv_done(t, j & 1));
                     if (j2 < nblk[t]) {
                         issue_qk(t, j2);  // into the buffer that P_j has just been read from (in-order execution)
                         tc_commit(s_full(t, j & 1));
@@ -382,22 +386,22 @@ attention_tc64_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
                     m_ref = m_new;
                     l *= alpha;
                 }
-                if (j > 0) {
-                    // O_t must be quiescent before it is rescaled: P·V of block j-1 done. Waiting
-                    // in every block (it is almost always already complete) keeps the phase parity
-                    // of this barrier unambiguous.
-                    if (!mbar_wait(pv_done(t), (uint32_t)((j - 1) & 1), abort_flag, 330 + t)) { ok = false; break; }
-                    if (__any_sync(0xffffffffu, grow)) {
-                        tc_fence_after();
+                if (j > 0 && __any_sync(0xffffffffu, grow)) {
+                    // O_t must be quiescent before it is rescaled: P·V of block j-1 complete. That is
+                    // the ((j-1)>>1)-th completion of the barrier of parity (j-1)&1. S_j being ready
+                    // implies P·V of block j-2 (hence j-3) complete, i.e. every earlier completion of
+                    // this barrier, so the phase parity below cannot be mistaken for an older phase
+                    // even though most blocks never wait here.
+                    if (!mbar_wait(pv_done(t, (j - 1) & 1), (uint32_t)(((j - 1) >> 1) & 1), abort_flag, 330 + t)) { ok = false; break; }
+                    tc_fence_after();
 #pragma unroll
-                        for (int dch = 0; dch < OCOLS / 16; ++dch) {
-                            uint32_t orr[16];
-                            tmem_ld_32x16(o_addr + dch * 16, orr);
-                            tmem_ld_wait();
+                    for (int dch = 0; dch < OCOLS / 16; ++dch) {
+                        uint32_t orr[16];
+                        tmem_ld_32x16(o_addr + dch * 16, orr);
+                        tmem_ld_wait();
 #pragma unroll
-                            for (int i = 0; i < 16; ++i) orr[i] = __float_as_uint(__uint_as_float(orr[i]) * alpha);
-                            tmem_st_32x16(o_addr + dch * 16, orr);
-                        }
+                        for (int i = 0; i < 16; ++i) orr[i] = __float_as_uint(__uint_as_float(orr[i]) * alpha);
+                        tmem_st_32x16(o_addr + dch * 16, orr);
                     }
                 }
                 const float neg_ref = -m_ref * unit;
@@ -425,7 +429,7 @@ attention_tc64_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
                 tmem_st_wait();
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(p_full(t));
+                if (lane == 0) mbar_arrive(p_full(t, bf));
             }
             // ---- epilogue: O / l -> global
             if (ok && mbar_wait(o_final(t), 0, abort_flag, 310 + t)) {

@@ -1,8 +1,8 @@
 // LayerNorm / RMSNorm forward for sm_100a. HBM-bound: x is read once and y written once.
 //
 // Fast path: one warp per row, the whole row held in registers as 128-bit vectors (8 elements of
-// a 16-bit type per load), statistics by warp shuffles in fp32, two-pass variance taken from the
-// registers (no second trip to memory). Algorithmic traffic per row is 2*cols*2 bytes.
+// a 16-bit type per load), statistics by warp shuffles in fp32 in one sweep over the registers
+// (shifted sums, no second trip to memory). Algorithmic traffic per row is 2*cols*2 bytes.
 // Generic path: arbitrary strides / column counts, one warp per row, re-reads the row (served by
 // L1/L2) — correctness path for the strided cases the reference accepts
 // (src/kernl/implementations/layer_norm.py:321-324).
@@ -54,21 +54,13 @@ norm_fwd_rowwarp_kernel(const T* __restrict__ x, T* __restrict__ y, const T* __r
 
     const float inv_n = 1.0f / (float)cols;
     float mean = 0.f, rstd;
-    if (!RMS) {
-        float s = 0.f;
-#pragma unroll
-        for (int c = 0; c < CHUNKS; ++c) {
-            const uint32_t w[4] = {v[c].x, v[c].y, v[c].z, v[c].w};
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                float2 f = Elem<T>::unpack2(w[i]);
-                s += f.x + f.y;
-            }
-        }
-        mean = warp_sum(s) * inv_n;
-    }
     {
-        float s = 0.f;
+        // One sweep over the registers. LayerNorm accumulates sum(x-K) and sum((x-K)^2) with K = the
+        // row's first element: shifting by a value of the row itself keeps the subtraction
+        // E[(x-K)^2] - E[x-K]^2 well conditioned even when |mean| >> std (rows like -20 +- 0.5).
+        float shift = 0.f;
+        if (!RMS) shift = __shfl_sync(0xffffffffu, Elem<T>::unpack2(v[0].x).x, 0);
+        float s1 = 0.f, s2 = 0.f;
 #pragma unroll
         for (int c = 0; c < CHUNKS; ++c) {
             const int col = (c * 32 + lane) * 8;
@@ -76,13 +68,20 @@ norm_fwd_rowwarp_kernel(const T* __restrict__ x, T* __restrict__ y, const T* __r
                 const uint32_t w[4] = {v[c].x, v[c].y, v[c].z, v[c].w};
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    float2 f = Elem<T>::unpack2(w[i]);
-                    const float a = f.x - mean, b = f.y - mean;
-                    s += a * a + b * b;
+                    const float2 f = Elem<T>::unpack2(w[i]);
+                    const float a = f.x - shift, b = f.y - shift;
+                    if (!RMS) s1 += a + b;
+                    s2 = fmaf(a, a, fmaf(b, b, s2));
                 }
             }
         }
-        rstd = rsqrtf(warp_sum(s) * inv_n + eps);
+        s2 = warp_sum(s2) * inv_n;
+        if (!RMS) {
+            const float d = warp_sum(s1) * inv_n;
+            mean = shift + d;
+            s2 = fmaxf(s2 - d * d, 0.f);
+        }
+        rstd = rsqrtf(s2 + eps);
     }
     if (lane == 0) {
         if (mean_out) mean_out[row] = mean;

@@ -1,7 +1,7 @@
 // Fused attention forward for sm_100a, variant with 64-key blocks and double-buffered scores.
 //
-// Same roles and the same maths as attention.cuh (two 128-row query tiles per CTA, two softmax
-// warpgroups, one TMA warp, one tcgen05 issuer warp), but the keys are streamed in blocks of 64 and
+// Same maths as attention.cuh and the same two softmax warpgroups (one 128-row query tile each) and
+// TMA warp, with one tcgen05 issuer warp PER TILE (warps 9 and 10; warp 11 stages broadcast masks), but the keys are streamed in blocks of 64 and
 // every tile owns TWO score buffers in TMEM. The issuer keeps the scores two blocks ahead of the
 // softmax: S_{j+2} = Q·K_{j+2}ᵀ is issued into the buffer that P_j has just left, so a softmax group
 // that finishes block j finds S_{j+1} already complete and never waits for the tensor core, and
@@ -19,7 +19,7 @@ constexpr int kBlkN = 64;
 
 template <int D>
 struct Attn64Cfg {
-    static constexpr int kKvStages = D == 64 ? 6 : 4;
+    static constexpr int kKvStages = D == 64 ? 8 : 4;
     static constexpr int kQTileBytes = kAttnBlock * D * 2;
     static constexpr int kKvBytes = kBlkN * D * 2;
     static constexpr bool kSumOnTc = (D == 64);
@@ -108,15 +108,15 @@ attention_tc64_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
                 mbar_init(s_full(t, bf), 1);
                 mbar_init(pv_done(t, bf), 1);
                 mbar_init(p_full(t, bf), 4);
-                mbar_init(m_full(t, bf), 2);
+                mbar_init(m_full(t, bf), 1);
                 mbar_init(m_empty(t, bf), 4);
             }
         }
         for (int s = 0; s < KVS; ++s) {
             mbar_init(k_full(s), 1);
-            mbar_init(k_empty(s), 1);
+            mbar_init(k_empty(s), ntl);  // one arrival per live tile's issuer
             mbar_init(v_full(s), 1);
-            mbar_init(v_empty(s), 1);
+            mbar_init(v_empty(s), ntl);
         }
         *abort_flag = 0;
         fence_mbar_init();
@@ -168,28 +168,32 @@ attention_tc64_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
                 for (int i = 0; i < 64; ++i) __nanosleep(2000);
             }
         }
-      } else if (warp == 9) {
-        // ------------------------------------------------------------------ MMA issuer
+      } else if (warp == 9 || warp == 10) {
+        // ------------------------------------------------------------------ MMA issuers, one per tile
+        // A single thread pushing the tcgen05 work of both tiles is itself a bottleneck (its serial
+        // stream of barrier polls, fences, sixteen MMA issues and commits per key block is slower
+        // than the softmax groups), so warp 9 serves tile 0 and warp 10 serves tile 1. A K or V
+        // stage is released when BOTH have arrived on its "empty" barrier.
+        const int t = warp - 9;
         if (elect_one()) {
             constexpr uint32_t idesc_qk = make_idesc_f16(Elem<T>::kIsBf16, 128, kBlkN, 0, 0);
             constexpr uint32_t idesc_pv = make_idesc_f16(Elem<T>::kIsBf16, 128, OCOLS, 0, 1);
             constexpr uint32_t desc_hi = (1024u >> 4) | (1u << 14) | (2u << 29);
-            const uint32_t q_lo = (q_smem & 0x3FFFF) >> 4;
+            const uint32_t q_lo = ((q_smem + t * QTILE) & 0x3FFFF) >> 4;
             const uint32_t k_lo = (k_smem & 0x3FFFF) >> 4;
             const uint32_t v_lo = ((v_smem & 0x3FFFF) >> 4) | (kSumOnTc ? 0u : ((uint32_t)(KSLAB >> 4) << 16));
             auto desc = [&](uint32_t lo) { return ((uint64_t)desc_hi << 32) | (uint64_t)lo; };
-            auto issue_qk = [&](int t, int j) {  // S[t][j&1] = Q_t · K_jᵀ
-                const uint32_t a_lo = q_lo + (uint32_t)(t * (QTILE >> 4));
+            auto issue_qk = [&](int j) {  // S[t][j&1] = Q_t · K_jᵀ
                 const uint32_t b_lo = k_lo + (uint32_t)((j % KVS) * (KVB >> 4));
                 const uint32_t d_tmem = tmem_base + (uint32_t)((t * 2 + (j & 1)) * kBlkN);
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks) {
                     const uint32_t a_off = (uint32_t)(((ks / 4) * QSLAB + (ks % 4) * 32) >> 4);
                     const uint32_t b_off = (uint32_t)(((ks / 4) * KSLAB + (ks % 4) * 32) >> 4);
-                    tc_mma_ss(d_tmem, desc(a_lo + a_off), desc(b_lo + b_off), idesc_qk, ks > 0 ? 1u : 0u);
+                    tc_mma_ss(d_tmem, desc(q_lo + a_off), desc(b_lo + b_off), idesc_qk, ks > 0 ? 1u : 0u);
                 }
             };
-            auto issue_pv = [&](int t, int j) {  // O_t (+)= P_j · V_j
+            auto issue_pv = [&](int j) {  // O_t (+)= P_j · V_j
                 const int s = j % KVS;
                 uint32_t b_lo = v_lo + (uint32_t)(s * (KVB >> 4));
                 if (kSumOnTc) b_lo |= (uint32_t)((ones_smem - (v_smem + s * KVB)) >> 4) << 16;
@@ -201,48 +205,53 @@ attention_tc64_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
                               (j > 0 || ks > 0) ? 1u : 0u);
                 }
             };
+            const int my_blk = (t < ntl) ? nblk[t] : 0;
             bool ok = true;
-            for (int t = 0; t < ntl && ok; ++t)
-                if (!mbar_wait(q_full(t), 0, abort_flag, 200)) ok = false;
+            if (t < ntl && !mbar_wait(q_full(t), 0, abort_flag, 200)) ok = false;
             // prologue: scores of blocks 0 and 1
-            for (int jj = 0; jj < 2 && jj < max_blk && ok; ++jj) {
+            for (int jj = 0; jj < 2 && jj < max_blk && ok && t < ntl; ++jj) {
                 if (!mbar_wait(k_full(jj % KVS), (uint32_t)((jj / KVS) & 1), abort_flag, 201)) { ok = false; break; }
-                tc_fence_after();
-                for (int t = 0; t < ntl; ++t) {
-                    if (jj < nblk[t]) {
-                        issue_qk(t, jj);
-                        tc_commit(s_full(t, jj & 1));
-                    }
+                if (jj < my_blk) {
+                    tc_fence_after();
+                    issue_qk(jj);
+                    tc_commit(s_full(t, jj & 1));
+                    tc_commit(k_empty(jj % KVS));
+                } else {
+                    mbar_arrive(k_empty(jj % KVS));  // a block this tile does not need (shorter causal range)
                 }
-                tc_commit(k_empty(jj % KVS));
             }
-            for (int j = 0; j < max_blk && ok; ++j) {
+            for (int j = 0; j < max_blk && ok && t < ntl; ++j) {
                 const int s = j % KVS;
                 if (!mbar_wait(v_full(s), (uint32_t)((j / KVS) & 1), abort_flag, 202)) { ok = false; break; }
                 const int j2 = j + 2;
                 if (j2 < max_blk) {
                     if (!mbar_wait(k_full(j2 % KVS), (uint32_t)((j2 / KVS) & 1), abort_flag, 203)) { ok = false; break; }
                 }
-                for (int t = 0; t < ntl; ++t) {
-                    if (j >= nblk[t]) continue;
+                if (j < my_blk) {
                     if (!mbar_wait(p_full(t, j & 1), (uint32_t)((j >> 1) & 1), abort_flag, 204)) { ok = false; break; }
                     tc_fence_after();
-                    issue_pv(t, j);
+                    issue_pv(j);
                     tc_commit(pv_done(t, j & 1));
-                    if (j2 < nblk[t]) {
-                        issue_qk(t, j2);  // into the buffer that P_j has just been read from (in-order execution)
+                    if (j2 < my_blk) {
+                        issue_qk(j2);  // into the buffer that P_j has just been read from (in-order execution)
                         tc_commit(s_full(t, j & 1));
                     }
-                    if (j + 1 == nblk[t]) tc_commit(o_final(t));
+                    if (j + 1 == my_blk) tc_commit(o_final(t));
+                    tc_commit(v_empty(s));
+                    if (j2 < max_blk) {
+                        if (j2 < my_blk) tc_commit(k_empty(j2 % KVS));
+                        else mbar_arrive(k_empty(j2 % KVS));
+                    }
+                } else {
+                    // blocks beyond this tile's causal range: hand the stages back untouched, but only
+                    // once they have been loaded, so that the arrival lands in the right phase
+                    mbar_arrive(v_empty(s));
+                    if (j2 < max_blk) mbar_arrive(k_empty(j2 % KVS));
                 }
-                if (!ok) break;
-                tc_commit(v_empty(s));
-                if (j2 < max_blk) tc_commit(k_empty(j2 % KVS));
             }
         }
-      } else if (MODE == 1) {
-        // ------------------------------------------------------------------ mask loaders (warps 10, 11)
-        const int li = (int)threadIdx.x - 320;  // 0..63: one column of the block each
+      } else if (MODE == 1 && warp == 11) {
+        // ------------------------------------------------------------------ mask loader (warp 11)
         const float mlow = mask_lowest(p.mask_dtype);
         const int64_t moff = (int64_t)b * p.mask_strides[0] + (int64_t)h * p.mask_strides[1];
         bool ok = true;
@@ -252,11 +261,15 @@ attention_tc64_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
             for (int t = 0; t < ntl && ok; ++t) {
                 if (j >= nblk[t]) continue;
                 if (!mbar_wait(m_empty(t, bf), ph ^ 1, abort_flag, 400 + t)) { ok = false; break; }
-                const int col = j * kBlkN + li;
-                float a = -INFINITY;
-                if (col < p.N)
-                    a = fmaxf(mask_load(p.mask, moff + (int64_t)col * p.mask_strides[3], p.mask_dtype), mlow) * kLog2e;
-                mask_smem[(t * 2 + bf) * kBlkN + li] = a;
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int idx = lane + e * 32;
+                    const int col = j * kBlkN + idx;
+                    float a = -INFINITY;
+                    if (col < p.N)
+                        a = fmaxf(mask_load(p.mask, moff + (int64_t)col * p.mask_strides[3], p.mask_dtype), mlow) * kLog2e;
+                    mask_smem[(t * 2 + bf) * kBlkN + idx] = a;
+                }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(m_full(t, bf));
             }

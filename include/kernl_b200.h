@@ -141,6 +141,33 @@ int kb_attention_fwd(const kb_attn_params* p, void* stream);
 int64_t kb_attention_decode_scratch_bytes(int64_t B, int64_t H, int64_t M, int64_t N, int64_t D);
 int kb_attention_decode_fwd(const kb_attn_params* p, void* scratch, int64_t scratch_bytes, void* stream);
 
+/* ---------------------------------------------------------------------------------------
+ * All-reduce (sum over ranks) fused with a residual add, over NVLink peer memory:
+ *   out = residual + sum_r partials[r]        (fp32 accumulation, rank order, 16-bit in/out)
+ * for the row-parallel linears of a tensor-parallel decoder. The reference has no multi-GPU path at
+ * all (single process, single GPU), so this entry point has no counterpart there.
+ *   partials[r]  rank r's partial-sum buffer as mapped into THIS process (partials[rank] is local);
+ *                each rank's GEMM writes its partial there before the call
+ *   flags[r]     rank r's flag block (>= 32 uint32, peer-mapped, zeroed once at set-up)
+ * Every rank of the group must make the same sequence of calls. One-shot algorithm (each rank reads
+ * every peer's buffer): meant for latency-bound messages; count*2 bytes <= 1 MiB is enforced.
+ * The call returns only after every peer has finished reading this rank's partial, so the buffer
+ * may be overwritten right away. All device-side waits are bounded (status word on expiry).
+ * ------------------------------------------------------------------------------------- */
+#define KB_ALLREDUCE_MAX_WORLD 8
+#define KB_ALLREDUCE_MAX_BYTES (1 << 20)
+typedef struct {
+    const void* partials[KB_ALLREDUCE_MAX_WORLD];
+    uint32_t*   flags[KB_ALLREDUCE_MAX_WORLD];
+    const void* residual;   /* [count] local, or NULL                                      */
+    void*       out;        /* [count] local                                               */
+    int64_t     count;      /* elements, multiple of 8                                     */
+    int32_t     rank, world;
+    int32_t     dtype;      /* KB_F16 / KB_BF16                                            */
+} kb_allreduce_params;
+
+int kb_allreduce_residual_fwd(const kb_allreduce_params* p, void* stream);
+
 /* Decode attention for callers that cannot allocate device memory. Same computation and arguments
  * as kb_attention_decode_fwd, but the scratch is a fixed array inside the library (4 MiB of device
  * memory on every GPU that loads the library, held until the process exits), so the caller passes

@@ -25,6 +25,7 @@ EXPORTED_SYMBOLS = [
     "kb_attention_fwd",
     "kb_attention_decode_scratch_bytes",
     "kb_attention_decode_fwd",
+    "kb_allreduce_residual_fwd",
     "kb_attention_decode_static_max_bytes",
     "kb_attention_decode_fwd_static",
     "kb_device_status_read",
@@ -64,6 +65,13 @@ class AttnParams(Structure):
     ]
 
 
+class AllReduceParams(Structure):
+    _fields_ = [
+        ("partials", c_void_p * 8), ("flags", c_void_p * 8), ("residual", c_void_p), ("out", c_void_p),
+        ("count", c_int64), ("rank", c_int32), ("world", c_int32), ("dtype", c_int32),
+    ]
+
+
 _lib = None
 
 
@@ -96,6 +104,8 @@ def load() -> ctypes.CDLL:
     lib.kb_attention_decode_static_max_bytes.restype = c_int64
     lib.kb_attention_decode_fwd_static.argtypes = [POINTER(AttnParams), c_void_p]
     lib.kb_attention_decode_fwd_static.restype = ctypes.c_int
+    lib.kb_allreduce_residual_fwd.argtypes = [POINTER(AllReduceParams), c_void_p]
+    lib.kb_allreduce_residual_fwd.restype = ctypes.c_int
     lib.kb_device_status_read.argtypes = [POINTER(c_int32)]
     lib.kb_device_status_read.restype = ctypes.c_int
     lib.kb_status_str.argtypes = [ctypes.c_int]

@@ -10,6 +10,7 @@
 #include "attention.cuh"
 #include "attention_kb64.cuh"
 #include "attention_decode.cuh"
+#include "allreduce.cuh"
 
 namespace kb {
 
@@ -208,6 +209,32 @@ int kb_attention_decode_fwd(const kb_attn_params* p, void* scratch, int64_t scra
     st = check_device();
     if (st != KB_OK) return st;
     return launch_attention_decode(*p, scratch, scratch_bytes, (cudaStream_t)stream);
+}
+
+int kb_allreduce_residual_fwd(const kb_allreduce_params* p, void* stream) {
+    if (p == nullptr || p->out == nullptr) return KB_ERR_BAD_ARG;
+    if (p->world < 1 || p->world > KB_ALLREDUCE_MAX_WORLD || p->rank < 0 || p->rank >= p->world) return KB_ERR_BAD_ARG;
+    if (p->count < 0 || p->count % 8 != 0) return KB_ERR_UNSUPPORTED;
+    if (p->count * 2 > KB_ALLREDUCE_MAX_BYTES) return KB_ERR_TOO_LARGE;
+    if (p->dtype != KB_F16 && p->dtype != KB_BF16) return KB_ERR_UNSUPPORTED;
+    if (p->count == 0) return KB_OK;
+    ArDev d;
+    for (int r = 0; r < KB_ALLREDUCE_MAX_WORLD; ++r) {
+        d.bufs[r] = r < p->world ? p->partials[r] : nullptr;
+        d.flags[r] = r < p->world ? p->flags[r] : nullptr;
+        if (r < p->world && (p->partials[r] == nullptr || p->flags[r] == nullptr)) return KB_ERR_BAD_ARG;
+        if (r < p->world && (((uintptr_t)p->partials[r]) & 15)) return KB_ERR_UNSUPPORTED;
+    }
+    if ((((uintptr_t)p->out) & 15) || (p->residual != nullptr && (((uintptr_t)p->residual) & 15))) return KB_ERR_UNSUPPORTED;
+    d.residual = p->residual;
+    d.out = p->out;
+    d.n = p->count;
+    d.rank = p->rank;
+    d.world = p->world;
+    int st = check_device();
+    if (st != KB_OK) return st;
+    return p->dtype == KB_F16 ? launch_allreduce_t<__half>(d, (cudaStream_t)stream)
+                              : launch_allreduce_t<__nv_bfloat16>(d, (cudaStream_t)stream);
 }
 
 // -------------------------------------------------------------------------------------------------

@@ -30,6 +30,7 @@ def linear_layer(
     bias: Optional[torch.Tensor],
     activation="",
     act_inputs: Optional[torch.Tensor] = None,
+    out: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
     """activation(x @ weight.T + bias) on the tcgen05 GEMM kernel.
 
@@ -38,7 +39,8 @@ def linear_layer(
     [N, K] contiguous, bias [N] contiguous or None, activation in {"", "tanh", "gelu",
     "fast_gelu", "relu"} (plus "silu"); `act_inputs`, if given, receives the pre-activation
     values. Returns [M, N], or [x.shape[0], -1, N] for 3-D x. fp32 inputs (tf32 in the
-    reference) are not supported: fp16/bf16 only.
+    reference) are not supported: fp16/bf16 only. `out` (an extension over the reference's
+    signature) lets the caller provide the [M, N] contiguous result buffer, e.g. a peer-mapped one.
     """
     x, weight, bias = cast_if_autocast(x, weight, bias)
     x_ = x if x.ndim == 2 else x.flatten(0, 1)
@@ -64,7 +66,11 @@ def linear_layer(
         x_ = torch.nn.functional.pad(x_, (0, pad))
         weight = torch.nn.functional.pad(weight, (0, pad))
         K += pad
-    outputs = torch.empty((M, N), device=x.device, dtype=x.dtype)
+    if out is not None:
+        assert out.shape == (M, N) and out.dtype == x.dtype and out.is_contiguous() and out.device == x.device
+        outputs = out
+    else:
+        outputs = torch.empty((M, N), device=x.device, dtype=x.dtype)
     if act_inputs is not None:
         assert act_inputs.shape == (M, N) and act_inputs.dtype == x.dtype and act_inputs.is_contiguous()
     if M > 0:

@@ -47,10 +47,10 @@ class CudaOps:
         return layer_norm(x, w, None, eps, use_rms_norm=True)
 
     @staticmethod
-    def linear(x, w):
+    def linear(x, w, out=None):
         from kernl_b200.implementations.linear_layer import linear_layer
 
-        return linear_layer(x, w, None)
+        return linear_layer(x, w, None, out=out)
 
     @staticmethod
     def silu_mul(gate_up):
@@ -72,10 +72,15 @@ class CudaOps:
 
 
 class DistComm:
-    """Sum all-reduce over the default process group; a no-op for a single rank."""
+    """Sum all-reduce over the default process group (NCCL on GPUs, gloo on CPU); a no-op for a
+    single rank. `kernl_b200.comm.PeerAllReduce` offers the same two methods on top of the
+    library's fused peer-memory kernel."""
 
     def __init__(self, world: int):
         self.world = world
+
+    def partial_buffer(self, rows, cols, dtype, device):
+        return None
 
     def all_reduce(self, t: torch.Tensor) -> torch.Tensor:
         if self.world > 1:
@@ -83,6 +88,9 @@ class DistComm:
 
             dist.all_reduce(t, op=dist.ReduceOp.SUM)
         return t
+
+    def reduce_add(self, partial: torch.Tensor, residual: torch.Tensor) -> torch.Tensor:
+        return residual + self.all_reduce(partial)
 
 
 def _seeded(shape, std, seed, device, dtype):
@@ -163,10 +171,17 @@ class LlamaTP:
         self.pos = torch.zeros(1, dtype=torch.long, device=self.device)
 
     # ------------------------------------------------------------------ blocks
-    def _mlp(self, layer, x2d):
+    def _row_parallel(self, x2d, w, residual):
+        """residual + all_reduce(x2d · wᵀ): the GEMM writes its partial into the communicator's
+        buffer when it has one (peer-mapped memory), then one call reduces and adds."""
+        buf = self.comm.partial_buffer(x2d.shape[0], w.shape[0], x2d.dtype, x2d.device)
+        partial = self.ops.linear(x2d, w, out=buf) if buf is not None else self.ops.linear(x2d, w)
+        return self.comm.reduce_add(partial, residual)
+
+    def _mlp(self, layer, x2d, residual):
         gu = self.ops.linear(x2d, layer["wgu"])
         act = self.ops.silu_mul(gu)
-        return self.comm.all_reduce(self.ops.linear(act, layer["wdn"]))
+        return self._row_parallel(act, layer["wdn"], residual)
 
     def prefill(self, ids: torch.Tensor) -> torch.Tensor:
         """ids [B, S] → logits [B, vocab] of the last position; fills the KV cache."""
@@ -186,9 +201,9 @@ class LlamaTP:
             attn = self.ops.attention_prefill(q.transpose(1, 2), self.kcache[li, :, :, :S], self.vcache[li, :, :, :S],
                                               self.sm_scale)  # [B, hl, S, D]
             attn2d = attn.transpose(1, 2).reshape(B * S, hl * D)
-            x = x + self.comm.all_reduce(self.ops.linear(attn2d, layer["wo"]))
+            x = self._row_parallel(attn2d, layer["wo"], x)
             h = self.ops.rms_norm(x, layer["norm2"], cfg.eps)
-            x = x + self._mlp(layer, h)
+            x = self._mlp(layer, h, x)
         self.len_mask.fill_(float("-inf"))
         self.len_mask[..., :S] = 0
         self.pos.fill_(S)
@@ -213,9 +228,9 @@ class LlamaTP:
             self.vcache[li].index_copy_(2, self.pos, qkv[:, :, 2].transpose(1, 2))
             attn = self.ops.attention_decode(q.transpose(1, 2).contiguous(), self.kcache[li], self.vcache[li],
                                              self.sm_scale, self.len_mask)  # [B, hl, 1, D]
-            x = x + self.comm.all_reduce(self.ops.linear(attn.reshape(B, hl * D), layer["wo"]))
+            x = self._row_parallel(attn.reshape(B, hl * D), layer["wo"], x)
             h = self.ops.rms_norm(x, layer["norm2"], cfg.eps)
-            x = x + self._mlp(layer, h)
+            x = self._mlp(layer, h, x)
         self.pos.add_(1)
         x = self.ops.rms_norm(x, self.final_norm, cfg.eps)
         return self.ops.linear(x, self.lm_head)

@@ -21,7 +21,7 @@ class OracleOps:
         return O.rms_norm(x, w, eps).to(x.dtype)
 
     @staticmethod
-    def linear(x, w):
+    def linear(x, w, out=None):
         return O.linear(x, w).to(x.dtype)
 
     @staticmethod

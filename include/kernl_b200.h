@@ -168,6 +168,17 @@ typedef struct {
 
 int kb_allreduce_residual_fwd(const kb_allreduce_params* p, void* stream);
 
+/* Set-up helpers for the peer-mapped buffers above (the only entry points of this library that
+ * allocate; they synchronise and are meant to be called once, outside any stream capture):
+ * the owner allocates (zero-filled) and exports a 64-byte CUDA IPC handle, every other process of
+ * the node opens it and receives a pointer valid in its own address space. No NVLS / multicast
+ * object is involved. */
+int kb_peer_alloc(int64_t bytes, void** out);
+int kb_peer_free(void* p);
+int kb_peer_export(void* p, void* handle64);
+int kb_peer_open(const void* handle64, void** out);
+int kb_peer_close(void* p);
+
 /* Decode attention for callers that cannot allocate device memory. Same computation and arguments
  * as kb_attention_decode_fwd, but the scratch is a fixed array inside the library (4 MiB of device
  * memory on every GPU that loads the library, held until the process exits), so the caller passes

@@ -26,6 +26,7 @@ EXPORTED_SYMBOLS = [
     "kb_attention_decode_scratch_bytes",
     "kb_attention_decode_fwd",
     "kb_allreduce_residual_fwd",
+    "kb_peer_alloc", "kb_peer_free", "kb_peer_export", "kb_peer_open", "kb_peer_close",
     "kb_attention_decode_static_max_bytes",
     "kb_attention_decode_fwd_static",
     "kb_device_status_read",
@@ -106,6 +107,13 @@ def load() -> ctypes.CDLL:
     lib.kb_attention_decode_fwd_static.restype = ctypes.c_int
     lib.kb_allreduce_residual_fwd.argtypes = [POINTER(AllReduceParams), c_void_p]
     lib.kb_allreduce_residual_fwd.restype = ctypes.c_int
+    lib.kb_peer_alloc.argtypes = [c_int64, POINTER(c_void_p)]
+    lib.kb_peer_export.argtypes = [c_void_p, ctypes.c_char_p]
+    lib.kb_peer_open.argtypes = [ctypes.c_char_p, POINTER(c_void_p)]
+    lib.kb_peer_free.argtypes = [c_void_p]
+    lib.kb_peer_close.argtypes = [c_void_p]
+    for name in ("kb_peer_alloc", "kb_peer_export", "kb_peer_open", "kb_peer_free", "kb_peer_close"):
+        getattr(lib, name).restype = ctypes.c_int
     lib.kb_device_status_read.argtypes = [POINTER(c_int32)]
     lib.kb_device_status_read.restype = ctypes.c_int
     lib.kb_status_str.argtypes = [ctypes.c_int]

@@ -1,12 +1,13 @@
 """Tensor-parallel communication for the row-parallel linears: all-reduce + residual add.
 
 `PeerAllReduce` is the B200-native path for the latency-bound decode messages: every rank's GEMM
-writes its partial sum into a symmetric (peer-mapped) buffer and ONE kernel of the library
+writes its partial sum into a peer-mapped buffer and ONE kernel of the library
 (`kb_allreduce_residual_fwd`) signals, pulls the peers' partials over NVLink with plain loads, adds
-the residual and stores the result. Messages above 1 MiB (prefill) fall back to NCCL through
-`torch.distributed`. Symmetric memory comes from `torch.distributed._symmetric_memory` (allocation
-and handle exchange only — no kernel of that module is called); NVLS / multimem is not used.
+the residual and stores the result. Messages above 1 MiB (prefill) go through NCCL
+(`torch.distributed`). The peer mapping is plain CUDA IPC (`kb_peer_*`): handles are exchanged with
+`all_gather_object`; no NVLS / multimem / multicast object is created.
 """
+import ctypes
 from typing import Optional
 
 import torch
@@ -14,6 +15,14 @@ import torch
 from kernl_b200 import _lib
 
 MAX_BYTES = 1 << 20
+_FLAG_BYTES = 256
+
+
+class _DevicePtr:
+    """Exposes raw device memory to torch through the CUDA array interface."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3}
 
 
 class NcclAllReduce:
@@ -37,22 +46,38 @@ class NcclAllReduce:
 
 
 class PeerAllReduce(NcclAllReduce):
-    def __init__(self, rank: int, world: int, device, dtype, group=None):
+    def __init__(self, rank: int, world: int, device, dtype):
         import torch.distributed as dist
-        import torch.distributed._symmetric_memory as symm_mem
 
         super().__init__(world)
         assert 1 < world <= 8
         self.rank, self.device, self.dtype = rank, torch.device(device), dtype
-        group = group if group is not None else dist.group.WORLD
-        self.buf = symm_mem.empty(MAX_BYTES // 2, dtype=dtype, device=self.device)
-        self.flags = symm_mem.empty(64, dtype=torch.int32, device=self.device)
-        self.flags.zero_()
-        torch.cuda.synchronize(self.device)
-        self._buf_handle = symm_mem.rendezvous(self.buf, group)
-        self._flag_handle = symm_mem.rendezvous(self.flags, group)
-        self.buf_ptrs = [int(p) for p in self._buf_handle.buffer_ptrs]
-        self.flag_ptrs = [int(p) for p in self._flag_handle.buffer_ptrs]
+        lib = _lib.load()
+        self._lib = lib
+        with torch.cuda.device(self.device):
+            buf, flags = ctypes.c_void_p(), ctypes.c_void_p()
+            _lib.check(lib.kb_peer_alloc(MAX_BYTES, ctypes.byref(buf)), "kb_peer_alloc")
+            _lib.check(lib.kb_peer_alloc(_FLAG_BYTES, ctypes.byref(flags)), "kb_peer_alloc")
+            handles = []
+            for p in (buf, flags):
+                h = ctypes.create_string_buffer(64)
+                _lib.check(lib.kb_peer_export(p, h), "kb_peer_export")
+                handles.append(h.raw)
+            gathered = [None] * world
+            dist.all_gather_object(gathered, handles)
+            self.buf_ptrs, self.flag_ptrs, self._opened = [], [], []
+            for r in range(world):
+                if r == rank:
+                    self.buf_ptrs.append(buf.value)
+                    self.flag_ptrs.append(flags.value)
+                    continue
+                for which, dst in ((0, self.buf_ptrs), (1, self.flag_ptrs)):
+                    out = ctypes.c_void_p()
+                    _lib.check(lib.kb_peer_open(gathered[r][which], ctypes.byref(out)), "kb_peer_open")
+                    dst.append(out.value)
+                    self._opened.append(out.value)
+            self._own = (buf.value, flags.value)
+            self.buf = torch.as_tensor(_DevicePtr(buf.value, MAX_BYTES), device=self.device).view(dtype)
         dist.barrier()
 
     def partial_buffer(self, rows: int, cols: int, dtype, device) -> Optional[torch.Tensor]:
@@ -65,6 +90,7 @@ class PeerAllReduce(NcclAllReduce):
     def reduce_add(self, partial: torch.Tensor, residual: torch.Tensor) -> torch.Tensor:
         if partial.data_ptr() != self.buf.data_ptr():
             return super().reduce_add(partial, residual)
+        residual = residual.contiguous()
         out = torch.empty_like(residual)
         p = _lib.AllReduceParams()
         for r in range(self.world):
@@ -76,5 +102,16 @@ class PeerAllReduce(NcclAllReduce):
         p.rank, p.world = self.rank, self.world
         p.dtype = _lib.dtype_code(partial.dtype)
         with torch.cuda.device(self.device):
-            _lib.check(_lib.load().kb_allreduce_residual_fwd(p, _lib.current_stream(self.device)), "allreduce_residual")
+            _lib.check(self._lib.kb_allreduce_residual_fwd(p, _lib.current_stream(self.device)), "allreduce_residual")
         return out
+
+    def close(self):
+        """Unmap the peers' buffers and free this rank's. Call on every rank, between steps, after a
+        barrier, with no kernel in flight."""
+        torch.cuda.synchronize(self.device)
+        for ptr in self._opened:
+            self._lib.kb_peer_close(ptr)
+        self._opened = []
+        for ptr in self._own:
+            self._lib.kb_peer_free(ptr)
+        self._own = ()

@@ -237,6 +237,42 @@ int kb_allreduce_residual_fwd(const kb_allreduce_params* p, void* stream) {
                               : launch_allreduce_t<__nv_bfloat16>(d, (cudaStream_t)stream);
 }
 
+// Peer-mapped buffers for kb_allreduce_residual_fwd. Plain CUDA IPC: the owner allocates with
+// cudaMalloc and exports a 64-byte handle, every peer process opens it (which enables peer access
+// over NVLink). No multicast / NVLS object is created for these buffers.
+int kb_peer_alloc(int64_t bytes, void** out) {
+    if (out == nullptr || bytes <= 0) return KB_ERR_BAD_ARG;
+    int st = check_device();
+    if (st != KB_OK) return st;
+    void* p = nullptr;
+    if (cudaMalloc(&p, (size_t)bytes) != cudaSuccess) { cudaGetLastError(); return KB_ERR_LAUNCH; }
+    if (cudaMemset(p, 0, (size_t)bytes) != cudaSuccess || cudaDeviceSynchronize() != cudaSuccess) {
+        cudaFree(p);
+        return KB_ERR_LAUNCH;
+    }
+    *out = p;
+    return KB_OK;
+}
+int kb_peer_free(void* p) { return (p == nullptr || cudaFree(p) == cudaSuccess) ? KB_OK : KB_ERR_LAUNCH; }
+int kb_peer_export(void* p, void* handle64) {
+    if (p == nullptr || handle64 == nullptr) return KB_ERR_BAD_ARG;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    cudaIpcMemHandle_t h;
+    if (cudaIpcGetMemHandle(&h, p) != cudaSuccess) { cudaGetLastError(); return KB_ERR_LAUNCH; }
+    memcpy(handle64, &h, 64);
+    return KB_OK;
+}
+int kb_peer_open(const void* handle64, void** out) {
+    if (handle64 == nullptr || out == nullptr) return KB_ERR_BAD_ARG;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, 64);
+    void* p = nullptr;
+    if (cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) { cudaGetLastError(); return KB_ERR_LAUNCH; }
+    *out = p;
+    return KB_OK;
+}
+int kb_peer_close(void* p) { return (p == nullptr || cudaIpcCloseMemHandle(p) == cudaSuccess) ? KB_OK : KB_ERR_LAUNCH; }
+
 // -------------------------------------------------------------------------------------------------
 // Decode attention without any allocation by the caller.
 //

@@ -63,6 +63,8 @@ def _worker(rank, world, port, out_path):
         # greedy generation under one CUDA graph, fused all-reduce inside the graph
         outs[name + "_tokens"] = m.generate(ids, 6, use_cuda_graph=True).cpu()
     _lib.device_status()
+    dist.barrier()
+    peer.close()
     if rank == 0:
         single = LlamaTP(cfg, rank=0, world=1, device=dev, dtype=torch.bfloat16, seed=0)
         logits = [single.prefill(ids)]

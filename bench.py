@@ -636,7 +636,12 @@ def run_llama(args):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     dev = torch.device("cuda", local_rank)
     cfg = LlamaConfig(n_layers=args.layers)
-    model = LlamaTP(cfg, rank=rank, world=world, device=dev, dtype=torch.bfloat16, seed=0)
+    comm = None
+    if world > 1 and args.comm == "peer":
+        from kernl_b200.comm import PeerAllReduce
+
+        comm = PeerAllReduce(rank, world, dev, torch.bfloat16)
+    model = LlamaTP(cfg, rank=rank, world=world, device=dev, dtype=torch.bfloat16, seed=0, comm=comm)
     ids = torch.randint(0, cfg.vocab, (8, 2048), generator=torch.Generator().manual_seed(0)).to(dev)
     decode_steps = args.decode_steps
     # warm-up: one prefill and a few decode steps
@@ -686,7 +691,9 @@ def run_llama(args):
             "steps": len(pre), "warmup": 1, "ms_per_step": prefill_ms, "higher_is_better": False, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": f"Llama-2-7B-shaped decoder ({cfg.n_layers} layers), prefill batch 8 x 2048 causal, then {decode_steps} greedy decode steps (baseline config 5)",
-                       "parallelism": f"tp{world}", "prefill_tokens_per_s": 8 * 2048 / prefill_ms * 1e3,
+                       "parallelism": f"tp{world}", "all_reduce": ("fused peer-memory kernel for messages <= 1 MiB (decode), NCCL above"
+                                                                    if comm is not None else "NCCL" if world > 1 else "none"),
+                       "prefill_tokens_per_s": 8 * 2048 / prefill_ms * 1e3,
                        "decode_ms_per_step": dec_ms / decode_steps, "decode_tokens_per_s": 8 * decode_steps / dec_ms * 1e3,
                        "tokens_sample": toks[0, :8].tolist()},
         }), flush=True)
@@ -708,6 +715,8 @@ def main():
     ap.add_argument("--workload", choices=["attention", "bert", "llama"], default="attention",
                     help="attention = headline (default); bert / llama = the model configs")
     ap.add_argument("--layers", type=int, default=32, help="llama workload: number of layers")
+    ap.add_argument("--comm", choices=["nccl", "peer"], default="peer",
+                    help="llama workload, N > 1: all-reduce through NCCL only, or the fused peer-memory kernel for decode-size messages")
     ap.add_argument("--decode-steps", type=int, default=256, help="llama workload: greedy decode steps")
     args = ap.parse_args()
     if args.workload == "bert":

@@ -189,7 +189,7 @@ def event_time(fn, steps, warmup, flush):
     return [s.elapsed_time(e) for s, e in pairs]
 
 
-def graph_time(step_for_set, n_sets, steps, warmup):
+def graph_time(step_for_set, n_sets, steps, warmup, min_total_ms=0.0):
     """Device time per step (ms) of `steps` back-to-back steps that cycle through `n_sets`
     independent input sets whose total size exceeds L2, so every step finds its inputs cold
     without any flush inside the timed region. The steps are enqueued as replays of one CUDA graph
@@ -215,16 +215,22 @@ def graph_time(step_for_set, n_sets, steps, warmup):
         for _ in range(10):
             graph.replay()
         torch.cuda.synchronize()
-    replays, rest = divmod(steps, n_sets)
-    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    s.record()
-    for _ in range(replays):
-        graph.replay()
-    for i in range(rest):
-        step_for_set(i)
-    e.record()
-    torch.cuda.synchronize()
-    return s.elapsed_time(e) / steps
+    while True:
+        replays, rest = divmod(steps, n_sets)
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(replays):
+            graph.replay()
+        for i in range(rest):
+            step_for_set(i)
+        e.record()
+        torch.cuda.synchronize()
+        total = s.elapsed_time(e)
+        if total >= min_total_ms or steps >= 20000:
+            return total / steps
+        # microsecond kernels: a handful of steps is dominated by the latency of the first
+        # launch, so repeat with enough steps (whole replays only) to fill min_total_ms
+        steps = n_sets * max(replays + 1, int(1.5 * min_total_ms / max(total, 1e-3) * max(replays, 1)) + 1)
 
 
 def run_ours(args):
@@ -427,7 +433,7 @@ def run_sweep(args):
         exceed twice the L2."""
         n_sets = int(min(16, max(2, -(-256 * 1024 * 1024 // max(1, int(bytes_per_set))))))
         fns = [make_set() for _ in range(n_sets)]
-        ms = graph_time(lambda i: fns[i](), n_sets, max(iters, n_sets), warm)
+        ms = graph_time(lambda i: fns[i](), n_sets, max(iters, n_sets), warm, min_total_ms=3.0)
         return [ms]
 
     for S in (128, 256, 512, 1024, 2048, 4096):

@@ -704,6 +704,10 @@ def run_llama(args):
                        "tokens_sample": toks[0, :8].tolist()},
         }), flush=True)
     if dist is not None:
+        # drop the captured graph (it holds NCCL work when --comm nccl) before tearing NCCL down
+        del replay, static_tok, static_next, model
+        torch.cuda.synchronize()
+        dist.barrier()
         dist.destroy_process_group()
 
 

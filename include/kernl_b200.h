@@ -51,6 +51,9 @@ extern "C" {
  * Statistics are computed in fp32 with the biased variance. The fp16 eps clamp
  * (eps = max(eps, 1.6e-5), layer_norm.py:295-296) is the CALLER's job: eps is used as given.
  * mean / rstd are optional fp32 [rows] side outputs (NULL to skip).
+ * residual / sum_out (an addition over the reference, for pre-norm decoders): the kernel first forms
+ * s = x + residual, stores s to sum_out and normalises s. Needs unit column strides, cols % 8 == 0,
+ * cols <= 6144.
  * ------------------------------------------------------------------------------------- */
 typedef struct {
     const void* x;          /* [rows, cols], strides x_row_stride / x_col_stride          */
@@ -65,6 +68,8 @@ typedef struct {
     float       eps;
     int32_t     is_rms;
     int32_t     dtype;      /* KB_F16 / KB_BF16 (x, y, gamma, beta share it)              */
+    const void* residual;   /* optional [rows, cols] contiguous: normalise x + residual   */
+    void*       sum_out;    /* required with residual: receives x + residual (contiguous) */
 } kb_norm_params;
 
 int kb_norm_fwd(const kb_norm_params* p, void* stream);
@@ -104,6 +109,23 @@ int64_t kb_linear_workspace_bytes(int64_t M, int64_t N);
  * gu = [M, 2*N] holds g in columns [0,N) and u in columns [N,2N). No counterpart in the
  * reference's dispatched path; semantics follow experimental/llama-v2/kernel/fused_kernel_ff.py:10-114. */
 int kb_silu_mul(const void* gu, void* y, int64_t M, int64_t N, int32_t dtype, void* stream);
+
+/* Rotary embedding fused with the KV-cache write (Llama-shaped decoder). qkv is the fused
+ * projection output [B*S, 3, H, D]; q (rotated) goes to q_out [B, S, H, D]; rotated k and v go to
+ * k_cache / v_cache [B, H, max_seq, D] at positions start .. start+S-1, where start is read from
+ * pos_dev (device int64) when it is not NULL, else pos_host. cos/sin: fp32 [max_seq, D/2].
+ * Rotation on interleaved pairs as in the reference's experimental Llama kernels
+ * (experimental/llama-v2/kernel/pytorch_reference.py:37-80, fused_kernel_proj_qkv.py:116-347);
+ * nothing in the reference's dispatched path corresponds to it. D must be a multiple of 8. */
+typedef struct {
+    const void* qkv; void* q_out; void* k_cache; void* v_cache;
+    const float* cos; const float* sin;
+    const int64_t* pos_dev; int64_t pos_host;
+    int64_t B, S, H, D, max_seq;
+    int32_t dtype;
+} kb_rope_params;
+
+int kb_rope_kv_write(const kb_rope_params* p, void* stream);
 
 /* ---------------------------------------------------------------------------------------
  * Fused attention forward: O = softmax(sm_scale · Q·Kᵀ + mask [causal]) · V, online softmax.

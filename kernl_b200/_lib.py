@@ -25,6 +25,7 @@ EXPORTED_SYMBOLS = [
     "kb_attention_fwd",
     "kb_attention_decode_scratch_bytes",
     "kb_attention_decode_fwd",
+    "kb_rope_kv_write",
     "kb_allreduce_residual_fwd",
     "kb_peer_alloc", "kb_peer_free", "kb_peer_export", "kb_peer_open", "kb_peer_close",
     "kb_attention_decode_static_max_bytes",
@@ -43,6 +44,7 @@ class NormParams(Structure):
         ("x_row_stride", c_int64), ("x_col_stride", c_int64),
         ("y_row_stride", c_int64), ("y_col_stride", c_int64),
         ("eps", c_float), ("is_rms", c_int32), ("dtype", c_int32),
+        ("residual", c_void_p), ("sum_out", c_void_p),
     ]
 
 
@@ -63,6 +65,15 @@ class AttnParams(Structure):
         ("q_strides", c_int64 * 4), ("k_strides", c_int64 * 4), ("v_strides", c_int64 * 4),
         ("o_strides", c_int64 * 4), ("mask_strides", c_int64 * 4),
         ("sm_scale", c_float), ("is_causal", c_int32), ("dtype", c_int32), ("mask_dtype", c_int32),
+    ]
+
+
+class RopeParams(Structure):
+    _fields_ = [
+        ("qkv", c_void_p), ("q_out", c_void_p), ("k_cache", c_void_p), ("v_cache", c_void_p),
+        ("cos", c_void_p), ("sin", c_void_p), ("pos_dev", c_void_p), ("pos_host", c_int64),
+        ("B", c_int64), ("S", c_int64), ("H", c_int64), ("D", c_int64), ("max_seq", c_int64),
+        ("dtype", c_int32),
     ]
 
 
@@ -105,6 +116,8 @@ def load() -> ctypes.CDLL:
     lib.kb_attention_decode_static_max_bytes.restype = c_int64
     lib.kb_attention_decode_fwd_static.argtypes = [POINTER(AttnParams), c_void_p]
     lib.kb_attention_decode_fwd_static.restype = ctypes.c_int
+    lib.kb_rope_kv_write.argtypes = [POINTER(RopeParams), c_void_p]
+    lib.kb_rope_kv_write.restype = ctypes.c_int
     lib.kb_allreduce_residual_fwd.argtypes = [POINTER(AllReduceParams), c_void_p]
     lib.kb_allreduce_residual_fwd.restype = ctypes.c_int
     lib.kb_peer_alloc.argtypes = [c_int64, POINTER(c_void_p)]

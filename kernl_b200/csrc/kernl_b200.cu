@@ -11,6 +11,7 @@
 #include "attention_kb64.cuh"
 #include "attention_decode.cuh"
 #include "allreduce.cuh"
+#include "rope.cuh"
 
 namespace kb {
 
@@ -126,6 +127,8 @@ int kb_device_status_read(int32_t* status_out) {
 int kb_norm_fwd(const kb_norm_params* p, void* stream) {
     if (p == nullptr || p->x == nullptr || p->y == nullptr || p->gamma == nullptr) return KB_ERR_BAD_ARG;
     if (p->rows < 0 || p->cols <= 0) return KB_ERR_BAD_ARG;
+    if (p->residual != nullptr && p->sum_out == nullptr) return KB_ERR_BAD_ARG;
+    if (p->residual != nullptr && ((((uintptr_t)p->residual) | ((uintptr_t)p->sum_out)) & 15)) return KB_ERR_UNSUPPORTED;
     if (p->rows == 0) return KB_OK;
     int st = check_device();
     if (st != KB_OK) return st;
@@ -209,6 +212,29 @@ int kb_attention_decode_fwd(const kb_attn_params* p, void* scratch, int64_t scra
     st = check_device();
     if (st != KB_OK) return st;
     return launch_attention_decode(*p, scratch, scratch_bytes, (cudaStream_t)stream);
+}
+
+int kb_rope_kv_write(const kb_rope_params* p, void* stream) {
+    if (p == nullptr || p->qkv == nullptr || p->q_out == nullptr || p->k_cache == nullptr || p->v_cache == nullptr ||
+        p->cos == nullptr || p->sin == nullptr)
+        return KB_ERR_BAD_ARG;
+    if (p->B < 0 || p->S < 0 || p->H <= 0 || p->D <= 0 || p->max_seq <= 0) return KB_ERR_BAD_ARG;
+    if (p->D % 8 != 0) return KB_ERR_UNSUPPORTED;
+    if ((((uintptr_t)p->qkv) | ((uintptr_t)p->q_out) | ((uintptr_t)p->k_cache) | ((uintptr_t)p->v_cache) |
+         ((uintptr_t)p->cos) | ((uintptr_t)p->sin)) & 15)
+        return KB_ERR_UNSUPPORTED;
+    if (p->B == 0 || p->S == 0) return KB_OK;
+    int st = check_device();
+    if (st != KB_OK) return st;
+    RopeDev d;
+    d.qkv = p->qkv; d.q_out = p->q_out; d.k_cache = p->k_cache; d.v_cache = p->v_cache;
+    d.cos_t = p->cos; d.sin_t = p->sin;
+    d.pos_dev = reinterpret_cast<const long long*>(p->pos_dev);
+    d.pos_host = p->pos_host;
+    d.B = (int)p->B; d.S = (int)p->S; d.H = (int)p->H; d.D = (int)p->D; d.max_seq = (int)p->max_seq;
+    if (p->dtype == KB_F16) return launch_rope_t<__half>(d, (cudaStream_t)stream);
+    if (p->dtype == KB_BF16) return launch_rope_t<__nv_bfloat16>(d, (cudaStream_t)stream);
+    return KB_ERR_UNSUPPORTED;
 }
 
 int kb_allreduce_residual_fwd(const kb_allreduce_params* p, void* stream) {

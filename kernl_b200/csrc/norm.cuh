@@ -37,7 +37,8 @@ __global__ void __launch_bounds__(128)
 norm_fwd_rowwarp_kernel(const T* __restrict__ x, T* __restrict__ y, const T* __restrict__ gamma,
                         const T* __restrict__ beta, float* __restrict__ mean_out,
                         float* __restrict__ rstd_out, int64_t rows, int cols, int64_t x_row_stride,
-                        int64_t y_row_stride, float eps) {
+                        int64_t y_row_stride, float eps, const T* __restrict__ residual,
+                        T* __restrict__ sum_out) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + warp;
     if (row >= rows) return;
@@ -50,6 +51,27 @@ norm_fwd_rowwarp_kernel(const T* __restrict__ x, T* __restrict__ y, const T* __r
         const int col = (c * 32 + lane) * 8;
         if (col < cols) v[c] = ld_stream_16B(xr + col);
         else v[c] = make_uint4(0, 0, 0, 0);
+    }
+    if (residual != nullptr) {
+        // pre-norm residual stream: s = x + residual (rounded to the 16-bit type, as a separate add
+        // kernel would store it), written out once and normalised from the registers
+#pragma unroll
+        for (int c = 0; c < CHUNKS; ++c) {
+            const int col = (c * 32 + lane) * 8;
+            if (col < cols) {
+                const uint4 r = ld_stream_16B(residual + row * (int64_t)cols + col);
+                const uint32_t xw[4] = {v[c].x, v[c].y, v[c].z, v[c].w};
+                const uint32_t rw[4] = {r.x, r.y, r.z, r.w};
+                uint32_t sw[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float2 a = Elem<T>::unpack2(xw[i]), b = Elem<T>::unpack2(rw[i]);
+                    sw[i] = Elem<T>::pack2(a.x + b.x, a.y + b.y);
+                }
+                v[c] = make_uint4(sw[0], sw[1], sw[2], sw[3]);
+                st_stream_16B(sum_out + row * (int64_t)cols + col, v[c]);
+            }
+        }
     }
 
     const float inv_n = 1.0f / (float)cols;
@@ -170,7 +192,7 @@ static int launch_norm_t(const kb_norm_params& p, cudaStream_t stream) {
     if (chunks <= C) {                                                                           \
         norm_fwd_rowwarp_kernel<T, C, RMS><<<grid, kWarps * 32, 0, stream>>>(                    \
             x, y, g, b, p.mean, p.rstd, p.rows, (int)p.cols, p.x_row_stride, p.y_row_stride,     \
-            p.eps);                                                                              \
+            p.eps, (const T*)p.residual, (T*)p.sum_out);                                         \
         return KB_OK;                                                                            \
     }
         KB_NORM_CASE(1)
@@ -184,6 +206,7 @@ static int launch_norm_t(const kb_norm_params& p, cudaStream_t stream) {
         KB_NORM_CASE(24)
 #undef KB_NORM_CASE
     }
+    if (p.residual != nullptr) return KB_ERR_UNSUPPORTED;  // the fused add needs the vector layout
     norm_fwd_generic_kernel<T, RMS><<<grid, kWarps * 32, 0, stream>>>(
         x, y, g, b, p.mean, p.rstd, p.rows, p.cols, p.x_row_stride, p.x_col_stride, p.y_row_stride,
         p.y_col_stride, p.eps);

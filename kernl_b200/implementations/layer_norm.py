@@ -33,13 +33,16 @@ def layer_norm(
     eps: float,
     implementation=None,
     use_rms_norm: bool = False,
-) -> torch.Tensor:
+    residual: Optional[torch.Tensor] = None,
+):
     """y = LayerNorm(x) or RMSNorm(x) over the last dimension on the sm_100a kernel.
 
     Same contract as the reference's `layer_norm` (layer_norm.py:338-346 → LayerNorm.forward
     :279-335): x/weight/bias share a dtype, fp16 inputs clamp eps to 1.6e-5 (:295-296), a new
     tensor shaped like x is returned. `implementation` selected one of several Triton kernels in
     the reference; there is a single CUDA implementation here, so it is accepted and ignored.
+    `residual` (an extension for pre-norm decoders): normalise x + residual in the same kernel and
+    return the pair (y, x + residual).
     """
     x, weight, bias = cast_if_autocast(x, weight, bias)
     assert x.dtype == weight.dtype, f"input and weight bias must have the same dtype: {x.dtype}, {weight.dtype}"
@@ -61,8 +64,14 @@ def layer_norm(
         out = torch.empty(x.shape, dtype=x.dtype, device=x.device)
         out2 = out.view(-1, n)
     rows = x2.shape[0]
+    sum_out = None
+    if residual is not None:
+        assert residual.shape == x.shape and residual.dtype == x.dtype
+        x2 = x2.contiguous()
+        residual = residual.contiguous()
+        sum_out = torch.empty(x.shape, dtype=x.dtype, device=x.device)
     if rows == 0:
-        return out
+        return out if residual is None else (out, sum_out)
     p = _lib.NormParams(
         x=x2.data_ptr(), y=out2.data_ptr(), gamma=weight.data_ptr(),
         beta=bias.data_ptr() if bias is not None else None, mean=None, rstd=None,
@@ -70,7 +79,9 @@ def layer_norm(
         x_row_stride=x2.stride(0), x_col_stride=x2.stride(1),
         y_row_stride=out2.stride(0), y_col_stride=out2.stride(1),
         eps=float(eps), is_rms=1 if use_rms_norm else 0, dtype=_lib.dtype_code(x.dtype),
+        residual=residual.data_ptr() if residual is not None else None,
+        sum_out=sum_out.data_ptr() if sum_out is not None else None,
     )
     with torch.cuda.device(x.device):
         _lib.check(_lib.load().kb_norm_fwd(p, _lib.current_stream(x.device)), "layer_norm")
-    return out
+    return out if residual is None else (out, sum_out)

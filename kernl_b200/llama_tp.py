@@ -59,6 +59,12 @@ class CudaOps:
         return silu_mul(gate_up)
 
     @staticmethod
+    def rope_kv_write(qkv, k_cache, v_cache, cos, sin, pos, batch, seq):
+        from kernl_b200.implementations.rope import rope_kv_write
+
+        return rope_kv_write(qkv, k_cache, v_cache, cos, sin, pos, batch, seq)
+
+    @staticmethod
     def attention_prefill(q, k, v, sm_scale):
         from kernl_b200.implementations.attention import attention_forward
 
@@ -190,14 +196,11 @@ class LlamaTP:
         if self.kcache is None or self.kcache.shape[1] != B:
             self.alloc_cache(B)
         x = self.embed.index_select(0, ids.reshape(-1)).reshape(B * S, cfg.hidden)
-        cos, sin = self.cos[:S], self.sin[:S]
         for li, layer in enumerate(self.layers):
             h = self.ops.rms_norm(x, layer["norm1"], cfg.eps)
-            qkv = self.ops.linear(h, layer["wqkv"]).reshape(B, S, 3, hl, D)
-            q = apply_rope(qkv[:, :, 0], cos, sin)
-            k = apply_rope(qkv[:, :, 1], cos, sin)
-            self.kcache[li, :, :, :S] = k.transpose(1, 2)
-            self.vcache[li, :, :, :S] = qkv[:, :, 2].transpose(1, 2)
+            qkv = self.ops.linear(h, layer["wqkv"])
+            # rotate q and k, write k and v into the cache at positions 0..S-1: one kernel
+            q = self.ops.rope_kv_write(qkv, self.kcache[li], self.vcache[li], self.cos, self.sin, 0, B, S)
             attn = self.ops.attention_prefill(q.transpose(1, 2), self.kcache[li, :, :, :S], self.vcache[li, :, :, :S],
                                               self.sm_scale)  # [B, hl, S, D]
             attn2d = attn.transpose(1, 2).reshape(B * S, hl * D)
@@ -217,16 +220,12 @@ class LlamaTP:
         cfg, hl, D = self.cfg, self.heads_local, self.cfg.head_dim
         B = tokens.shape[0]
         x = self.embed.index_select(0, tokens)
-        cos, sin = self.cos.index_select(0, self.pos), self.sin.index_select(0, self.pos)  # [1, D/2]
         self.len_mask.index_fill_(3, self.pos, 0.0)
         for li, layer in enumerate(self.layers):
             h = self.ops.rms_norm(x, layer["norm1"], cfg.eps)
-            qkv = self.ops.linear(h, layer["wqkv"]).reshape(B, 1, 3, hl, D)
-            q = apply_rope(qkv[:, :, 0], cos, sin)
-            k = apply_rope(qkv[:, :, 1], cos, sin)
-            self.kcache[li].index_copy_(2, self.pos, k.transpose(1, 2))
-            self.vcache[li].index_copy_(2, self.pos, qkv[:, :, 2].transpose(1, 2))
-            attn = self.ops.attention_decode(q.transpose(1, 2).contiguous(), self.kcache[li], self.vcache[li],
+            qkv = self.ops.linear(h, layer["wqkv"])
+            q = self.ops.rope_kv_write(qkv, self.kcache[li], self.vcache[li], self.cos, self.sin, self.pos, B, 1)
+            attn = self.ops.attention_decode(q.transpose(1, 2), self.kcache[li], self.vcache[li],
                                              self.sm_scale, self.len_mask)  # [B, hl, 1, D]
             x = self._row_parallel(attn.reshape(B, hl * D), layer["wo"], x)
             h = self.ops.rms_norm(x, layer["norm2"], cfg.eps)

@@ -50,6 +50,6 @@ def test_bad_arguments_are_rejected_before_any_device_call():
 
 def test_struct_layouts_match_the_header():
     # sizes follow from the field lists in include/kernl_b200.h (LP64)
-    assert ctypes.sizeof(_lib.NormParams) == 6 * 8 + 6 * 8 + 3 * 4 + 4
+    assert ctypes.sizeof(_lib.NormParams) == 6 * 8 + 6 * 8 + 3 * 4 + 4 + 2 * 8
     assert ctypes.sizeof(_lib.LinearParams) == 5 * 8 + 5 * 8 + 2 * 4 + 2 * 8
     assert ctypes.sizeof(_lib.AttnParams) == 5 * 8 + 5 * 8 + 5 * 32 + 4 * 4

@@ -30,6 +30,18 @@ class OracleOps:
         return (torch.nn.functional.silu(gu[..., :n].float()) * gu[..., n:].float()).to(gu.dtype)
 
     @staticmethod
+    def rope_kv_write(qkv, k_cache, v_cache, cos, sin, pos, batch, seq):
+        B, H, max_seq, D = k_cache.shape
+        start = int(pos.item()) if isinstance(pos, torch.Tensor) else int(pos)
+        x = qkv.reshape(batch, seq, 3, H, D)
+        c, s = cos[start:start + seq], sin[start:start + seq]
+        q = apply_rope(x[:, :, 0], c, s)
+        k = apply_rope(x[:, :, 1], c, s)
+        k_cache[:, :, start:start + seq] = k.transpose(1, 2)
+        v_cache[:, :, start:start + seq] = x[:, :, 2].transpose(1, 2)
+        return q
+
+    @staticmethod
     def attention_prefill(q, k, v, sm_scale):
         return O.attention(q, k, v, sm_scale, True, None).to(q.dtype)
 
@@ -92,6 +104,32 @@ def test_two_rank_tensor_parallel_matches_single_rank(tmp_path):
     m = _cpu_model()
     ref = [m.prefill(ids[:, :10])] + [m.decode_step(ids[:, t]) for t in range(10, 12)]
     assert torch.allclose(tp2, torch.stack(ref), atol=2e-4)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16], ids=["fp16", "bf16"])
+def test_rope_kv_write_kernel(lib, dtype):
+    """The fused rotary + cache-write kernel against the eager rotation, for a prefill-shaped call
+    (host start position) and a decode-shaped call (start position on the device)."""
+    from kernl_b200.implementations.rope import rope_kv_write
+
+    B, H, D, max_seq = 2, 3, 128, 40
+    g = torch.Generator().manual_seed(0)
+    half = D // 2
+    inv_freq = 1.0 / (10000.0 ** (torch.arange(0, half, dtype=torch.float32) / half))
+    ang = torch.arange(max_seq, dtype=torch.float32)[:, None] * inv_freq[None, :]
+    cos, sin = torch.cos(ang), torch.sin(ang)
+    kc, vc = torch.zeros((B, H, max_seq, D), dtype=dtype), torch.zeros((B, H, max_seq, D), dtype=dtype)
+    kc_d, vc_d = kc.cuda(), vc.cuda()
+    for (S, start, on_device) in [(17, 0, False), (1, 17, True), (1, 18, True)]:
+        qkv = torch.randn((B * S, 3 * H * D), generator=g).to(dtype)
+        q_ref = OracleOps.rope_kv_write(qkv.float(), kc, vc, cos, sin, start, B, S)
+        pos = torch.tensor([start], dtype=torch.long, device="cuda") if on_device else start
+        q = rope_kv_write(qkv.cuda(), kc_d, vc_d, cos.cuda(), sin.cuda(), pos, B, S)
+        tol = 1e-2 if dtype == torch.float16 else 4e-2
+        O.assert_parity(q, q_ref, max_abs=tol)
+        O.assert_parity(kc_d, kc, max_abs=tol)
+        assert torch.equal(vc_d.cpu(), vc)  # v is copied bit for bit
 
 
 @pytest.mark.gpu

@@ -186,6 +186,14 @@ typedef struct {
     int64_t     count;      /* elements, multiple of 8                                     */
     int32_t     rank, world;
     int32_t     dtype;      /* KB_F16 / KB_BF16                                            */
+    /* Optional fused RMSNorm of the reduced rows (the norm that opens the next decoder block): when
+     * norm_weight != NULL, count is rows x cols, cols % 8 == 0, cols <= 8192, and
+     * norm_out[r, :] = out[r, :] * rsqrt(mean(out[r, :]^2) + eps) * norm_weight, computed from the
+     * 16-bit values stored in out. */
+    const void* norm_weight; /* [cols]                                                     */
+    void*       norm_out;    /* [count], local                                             */
+    int64_t     cols;
+    float       eps;
 } kb_allreduce_params;
 
 int kb_allreduce_residual_fwd(const kb_allreduce_params* p, void* stream);

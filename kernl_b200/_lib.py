@@ -81,6 +81,7 @@ class AllReduceParams(Structure):
     _fields_ = [
         ("partials", c_void_p * 8), ("flags", c_void_p * 8), ("residual", c_void_p), ("out", c_void_p),
         ("count", c_int64), ("rank", c_int32), ("world", c_int32), ("dtype", c_int32),
+        ("norm_weight", c_void_p), ("norm_out", c_void_p), ("cols", c_int64), ("eps", c_float),
     ]
 
 

@@ -44,6 +44,12 @@ class NcclAllReduce:
     def reduce_add(self, partial: torch.Tensor, residual: torch.Tensor) -> torch.Tensor:
         return residual + self.all_reduce(partial)
 
+    def reduce_add_norm(self, partial, residual, weight, eps, ops):
+        """x = residual + all_reduce(partial); returns (x, rms_norm(x) * weight). After NCCL the add
+        and the norm are one kernel."""
+        h, x = ops.add_rms_norm(self.all_reduce(partial), residual, weight, eps)
+        return x, h
+
 
 class PeerAllReduce(NcclAllReduce):
     def __init__(self, rank: int, world: int, device, dtype):
@@ -90,9 +96,24 @@ class PeerAllReduce(NcclAllReduce):
     def reduce_add(self, partial: torch.Tensor, residual: torch.Tensor) -> torch.Tensor:
         if partial.data_ptr() != self.buf.data_ptr():
             return super().reduce_add(partial, residual)
+        return self._launch(partial, residual, None, 0.0)[0]
+
+    def reduce_add_norm(self, partial, residual, weight, eps, ops):
+        """All-reduce, residual add and the following RMSNorm in ONE kernel over peer memory."""
+        if partial.data_ptr() != self.buf.data_ptr() or partial.shape[-1] > 8192 or partial.shape[-1] % 8:
+            return super().reduce_add_norm(partial, residual, weight, eps, ops)
+        return self._launch(partial, residual, weight, eps)
+
+    def _launch(self, partial, residual, weight, eps):
         residual = residual.contiguous()
         out = torch.empty_like(residual)
+        normed = torch.empty_like(residual) if weight is not None else None
         p = _lib.AllReduceParams()
+        if weight is not None:
+            p.norm_weight = weight.data_ptr()
+            p.norm_out = normed.data_ptr()
+            p.cols = partial.shape[-1]
+            p.eps = float(eps)
         for r in range(self.world):
             p.partials[r] = self.buf_ptrs[r]
             p.flags[r] = self.flag_ptrs[r]
@@ -103,7 +124,7 @@ class PeerAllReduce(NcclAllReduce):
         p.dtype = _lib.dtype_code(partial.dtype)
         with torch.cuda.device(self.device):
             _lib.check(self._lib.kb_allreduce_residual_fwd(p, _lib.current_stream(self.device)), "allreduce_residual")
-        return out
+        return out, normed
 
     def close(self):
         """Unmap the peers' buffers and free this rank's. Call on every rank, between steps, after a

@@ -33,6 +33,11 @@ struct ArDev {
     void* out;
     int64_t n;  // elements, multiple of 8
     int rank, world;
+    // optional fused RMSNorm of the reduced rows (norm_weight != nullptr)
+    const void* norm_weight;
+    void* norm_out;
+    int cols;  // row length, multiple of 8, <= kArNormMaxCols; n % cols == 0
+    float eps;
 };
 
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
@@ -143,8 +148,138 @@ allreduce_residual_kernel(const ArDev p) {
     }
 }
 
+// Same protocol, plus the RMSNorm that follows the residual add in a pre-norm decoder block:
+//   out = residual + sum_r partial_r      (the new residual stream, rounded to T)
+//   norm_out = out * rsqrt(mean(out^2) + eps) * weight   (computed from the rounded values, i.e.
+//              what a separate RMSNorm kernel reading `out` would produce)
+// One CTA per row (grid-strided), the row held in registers between the sum and the scaling.
+constexpr int kArNormMaxCols = 8192;
+constexpr int kArNormVecs = kArNormMaxCols / 8 / kArThreads;  // 4
+
+template <typename T>
+__global__ void __launch_bounds__(kArThreads)
+allreduce_residual_rmsnorm_kernel(const ArDev p) {
+    __shared__ uint32_t s_epoch;
+    __shared__ int s_last;
+    __shared__ float s_red[kArThreads / 32];
+    uint32_t* my = p.flags[p.rank];
+    if (threadIdx.x == 0) s_epoch = *reinterpret_cast<volatile uint32_t*>(my + 16) + 1u;
+    __syncthreads();
+    const uint32_t epoch = s_epoch;
+    const int tid = threadIdx.x;
+
+    if (blockIdx.x == 0 && tid < p.world && tid != p.rank) {
+        __threadfence_system();
+        st_release_sys(p.flags[tid] + p.rank, epoch);
+    }
+    if (tid < p.world && tid != p.rank) ar_wait_flag(my + tid, epoch, 540 + tid);
+    __syncthreads();
+
+    const int vec_per_row = p.cols / 8;
+    const int64_t rows = p.n / p.cols;
+    for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+        uint4 keep[kArNormVecs];
+        float ss = 0.f;
+#pragma unroll
+        for (int c = 0; c < kArNormVecs; ++c) {
+            const int vi = c * kArThreads + tid;
+            if (vi < vec_per_row) {
+                const int64_t i = row * vec_per_row + vi;
+                float acc[8];
+#pragma unroll
+                for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+                for (int r = 0; r < p.world; ++r) {
+                    const uint4 w = ld_peer_16B(reinterpret_cast<const uint4*>(p.bufs[r]) + i);
+                    const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const float2 f = Elem<T>::unpack2(ww[k]);
+                        acc[2 * k] += f.x;
+                        acc[2 * k + 1] += f.y;
+                    }
+                }
+                if (p.residual != nullptr) {
+                    const uint4 w = *(reinterpret_cast<const uint4*>(p.residual) + i);
+                    const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const float2 f = Elem<T>::unpack2(ww[k]);
+                        acc[2 * k] += f.x;
+                        acc[2 * k + 1] += f.y;
+                    }
+                }
+                uint4 o;
+                o.x = Elem<T>::pack2(acc[0], acc[1]);
+                o.y = Elem<T>::pack2(acc[2], acc[3]);
+                o.z = Elem<T>::pack2(acc[4], acc[5]);
+                o.w = Elem<T>::pack2(acc[6], acc[7]);
+                *(reinterpret_cast<uint4*>(p.out) + i) = o;
+                keep[c] = o;
+                const uint32_t ow[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const float2 f = Elem<T>::unpack2(ow[k]);
+                    ss += f.x * f.x + f.y * f.y;
+                }
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if ((tid & 31) == 0) s_red[tid >> 5] = ss;
+        __syncthreads();
+        float tot = 0.f;
+#pragma unroll
+        for (int w = 0; w < kArThreads / 32; ++w) tot += s_red[w];
+        __syncthreads();  // s_red is reused by the next row
+        const float rstd = rsqrtf(tot / (float)p.cols + p.eps);
+#pragma unroll
+        for (int c = 0; c < kArNormVecs; ++c) {
+            const int vi = c * kArThreads + tid;
+            if (vi < vec_per_row) {
+                const uint4 g = *(reinterpret_cast<const uint4*>(p.norm_weight) + vi);
+                const uint32_t xw[4] = {keep[c].x, keep[c].y, keep[c].z, keep[c].w};
+                const uint32_t gw[4] = {g.x, g.y, g.z, g.w};
+                uint32_t yw[4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const float2 f = Elem<T>::unpack2(xw[k]);
+                    const float2 w = Elem<T>::unpack2(gw[k]);
+                    yw[k] = Elem<T>::pack2(f.x * rstd * w.x, f.y * rstd * w.y);
+                }
+                *(reinterpret_cast<uint4*>(p.norm_out) + row * vec_per_row + vi) =
+                    make_uint4(yw[0], yw[1], yw[2], yw[3]);
+            }
+        }
+    }
+
+    __syncthreads();
+    if (tid == 0) {
+        __threadfence();
+        s_last = (atomicAdd(reinterpret_cast<unsigned int*>(my + 17), 1u) == gridDim.x - 1) ? 1 : 0;
+    }
+    __syncthreads();
+    if (s_last) {
+        if (tid < p.world && tid != p.rank) {
+            st_release_sys(p.flags[tid] + 8 + p.rank, epoch);
+            ar_wait_flag(my + 8 + tid, epoch, 560 + tid);
+        }
+        __syncthreads();
+        if (tid == 0) {
+            my[17] = 0;
+            __threadfence();
+            *reinterpret_cast<volatile uint32_t*>(my + 16) = epoch;
+        }
+    }
+}
+
 template <typename T>
 static int launch_allreduce_t(const ArDev& d, cudaStream_t stream) {
+    if (d.norm_weight != nullptr) {
+        int64_t rows = d.n / d.cols;
+        if (rows > 128) rows = 128;
+        allreduce_residual_rmsnorm_kernel<T><<<(unsigned)rows, kArThreads, 0, stream>>>(d);
+        return cudaGetLastError() == cudaSuccess ? KB_OK : KB_ERR_LAUNCH;
+    }
     const int64_t nvec = d.n / 8;
     int64_t blocks = (nvec + kArThreads - 1) / kArThreads;
     if (blocks > 64) blocks = 64;  // latency-bound messages: a few dozen CTAs saturate NVLink reads

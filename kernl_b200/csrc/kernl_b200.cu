@@ -257,6 +257,15 @@ int kb_allreduce_residual_fwd(const kb_allreduce_params* p, void* stream) {
     d.n = p->count;
     d.rank = p->rank;
     d.world = p->world;
+    d.norm_weight = p->norm_weight;
+    d.norm_out = p->norm_out;
+    d.cols = (int)p->cols;
+    d.eps = p->eps;
+    if (p->norm_weight != nullptr) {
+        if (p->norm_out == nullptr || p->cols <= 0) return KB_ERR_BAD_ARG;
+        if (p->cols % 8 != 0 || p->cols > kArNormMaxCols || p->count % p->cols != 0) return KB_ERR_UNSUPPORTED;
+        if ((((uintptr_t)p->norm_weight) | ((uintptr_t)p->norm_out)) & 15) return KB_ERR_UNSUPPORTED;
+    }
     int st = check_device();
     if (st != KB_OK) return st;
     return p->dtype == KB_F16 ? launch_allreduce_t<__half>(d, (cudaStream_t)stream)

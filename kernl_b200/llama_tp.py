@@ -59,6 +59,13 @@ class CudaOps:
         return silu_mul(gate_up)
 
     @staticmethod
+    def add_rms_norm(x, residual, w, eps):
+        """(rms_norm(x + residual), x + residual) in one kernel."""
+        from kernl_b200.implementations.layer_norm import layer_norm
+
+        return layer_norm(x, w, None, eps, use_rms_norm=True, residual=residual)
+
+    @staticmethod
     def rope_kv_write(qkv, k_cache, v_cache, cos, sin, pos, batch, seq):
         from kernl_b200.implementations.rope import rope_kv_write
 
@@ -97,6 +104,11 @@ class DistComm:
 
     def reduce_add(self, partial: torch.Tensor, residual: torch.Tensor) -> torch.Tensor:
         return residual + self.all_reduce(partial)
+
+    def reduce_add_norm(self, partial, residual, weight, eps, ops):
+        """x = residual + all_reduce(partial); returns (x, rms_norm(x) * weight)."""
+        h, x = ops.add_rms_norm(self.all_reduce(partial), residual, weight, eps)
+        return x, h
 
 
 def _seeded(shape, std, seed, device, dtype):
@@ -177,17 +189,21 @@ class LlamaTP:
         self.pos = torch.zeros(1, dtype=torch.long, device=self.device)
 
     # ------------------------------------------------------------------ blocks
-    def _row_parallel(self, x2d, w, residual):
-        """residual + all_reduce(x2d · wᵀ): the GEMM writes its partial into the communicator's
-        buffer when it has one (peer-mapped memory), then one call reduces and adds."""
+    def _row_parallel(self, x2d, w, residual, next_norm):
+        """x = residual + all_reduce(x2d · wᵀ) and h = rms_norm(x) · next_norm, the input of the next
+        sub-block. The GEMM writes its partial into the communicator's buffer when it has one
+        (peer-mapped memory); reduce, residual add and norm are then one kernel. Returns (x, h)."""
         buf = self.comm.partial_buffer(x2d.shape[0], w.shape[0], x2d.dtype, x2d.device)
         partial = self.ops.linear(x2d, w, out=buf) if buf is not None else self.ops.linear(x2d, w)
-        return self.comm.reduce_add(partial, residual)
+        return self.comm.reduce_add_norm(partial, residual, next_norm, self.cfg.eps, self.ops)
 
-    def _mlp(self, layer, x2d, residual):
-        gu = self.ops.linear(x2d, layer["wgu"])
+    def _mlp(self, layer, h, residual, next_norm):
+        gu = self.ops.linear(h, layer["wgu"])
         act = self.ops.silu_mul(gu)
-        return self._row_parallel(act, layer["wdn"], residual)
+        return self._row_parallel(act, layer["wdn"], residual, next_norm)
+
+    def _next_norm(self, li):
+        return self.layers[li + 1]["norm1"] if li + 1 < len(self.layers) else self.final_norm
 
     def prefill(self, ids: torch.Tensor) -> torch.Tensor:
         """ids [B, S] → logits [B, vocab] of the last position; fills the KV cache."""
@@ -196,22 +212,20 @@ class LlamaTP:
         if self.kcache is None or self.kcache.shape[1] != B:
             self.alloc_cache(B)
         x = self.embed.index_select(0, ids.reshape(-1)).reshape(B * S, cfg.hidden)
+        h = self.ops.rms_norm(x, self.layers[0]["norm1"], cfg.eps)
         for li, layer in enumerate(self.layers):
-            h = self.ops.rms_norm(x, layer["norm1"], cfg.eps)
             qkv = self.ops.linear(h, layer["wqkv"])
             # rotate q and k, write k and v into the cache at positions 0..S-1: one kernel
             q = self.ops.rope_kv_write(qkv, self.kcache[li], self.vcache[li], self.cos, self.sin, 0, B, S)
             attn = self.ops.attention_prefill(q.transpose(1, 2), self.kcache[li, :, :, :S], self.vcache[li, :, :, :S],
                                               self.sm_scale)  # [B, hl, S, D]
             attn2d = attn.transpose(1, 2).reshape(B * S, hl * D)
-            x = self._row_parallel(attn2d, layer["wo"], x)
-            h = self.ops.rms_norm(x, layer["norm2"], cfg.eps)
-            x = self._mlp(layer, h, x)
+            x, h = self._row_parallel(attn2d, layer["wo"], x, layer["norm2"])
+            x, h = self._mlp(layer, h, x, self._next_norm(li))
         self.len_mask.fill_(float("-inf"))
         self.len_mask[..., :S] = 0
         self.pos.fill_(S)
-        last = x.reshape(B, S, cfg.hidden)[:, -1]
-        last = self.ops.rms_norm(last.contiguous(), self.final_norm, cfg.eps)
+        last = h.reshape(B, S, cfg.hidden)[:, -1].contiguous()  # already through the final norm
         return self.ops.linear(last, self.lm_head)
 
     def decode_step(self, tokens: torch.Tensor) -> torch.Tensor:
@@ -221,18 +235,16 @@ class LlamaTP:
         B = tokens.shape[0]
         x = self.embed.index_select(0, tokens)
         self.len_mask.index_fill_(3, self.pos, 0.0)
+        h = self.ops.rms_norm(x, self.layers[0]["norm1"], cfg.eps)
         for li, layer in enumerate(self.layers):
-            h = self.ops.rms_norm(x, layer["norm1"], cfg.eps)
             qkv = self.ops.linear(h, layer["wqkv"])
             q = self.ops.rope_kv_write(qkv, self.kcache[li], self.vcache[li], self.cos, self.sin, self.pos, B, 1)
             attn = self.ops.attention_decode(q.transpose(1, 2), self.kcache[li], self.vcache[li],
                                              self.sm_scale, self.len_mask)  # [B, hl, 1, D]
-            x = self._row_parallel(attn.reshape(B, hl * D), layer["wo"], x)
-            h = self.ops.rms_norm(x, layer["norm2"], cfg.eps)
-            x = self._mlp(layer, h, x)
+            x, h = self._row_parallel(attn.reshape(B, hl * D), layer["wo"], x, layer["norm2"])
+            x, h = self._mlp(layer, h, x, self._next_norm(li))
         self.pos.add_(1)
-        x = self.ops.rms_norm(x, self.final_norm, cfg.eps)
-        return self.ops.linear(x, self.lm_head)
+        return self.ops.linear(h, self.lm_head)
 
     def capture_decode(self, tokens: torch.Tensor):
         """Capture one decode step in a CUDA graph (after the prefill). Returns (replay, static_tok,

@@ -30,6 +30,11 @@ class OracleOps:
         return (torch.nn.functional.silu(gu[..., :n].float()) * gu[..., n:].float()).to(gu.dtype)
 
     @staticmethod
+    def add_rms_norm(x, residual, w, eps):
+        s = (x.float() + residual.float()).to(x.dtype)
+        return O.rms_norm(s, w, eps).to(x.dtype), s
+
+    @staticmethod
     def rope_kv_write(qkv, k_cache, v_cache, cos, sin, pos, batch, seq):
         B, H, max_seq, D = k_cache.shape
         start = int(pos.item()) if isinstance(pos, torch.Tensor) else int(pos)

@@ -426,6 +426,31 @@ def test_norm_full_size_properties(lib):
     O.assert_parity(y[rows.cuda()], O.layer_norm(x[rows.cuda()].cpu(), one.cpu(), zero.cpu(), 1.6e-5))
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(8, 4096), (3, 7, 768), (1, 8), (513, 6144)])
+@pytest.mark.parametrize("rms", [False, True])
+def test_norm_with_residual(lib, shape, rms, dtype):
+    """Fused pre-norm add: the returned sum is the exactly rounded x + residual, the normed output
+    matches the oracle applied to that sum."""
+    from kernl_b200.implementations.layer_norm import layer_norm
+
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(shape, generator=g).to(dtype)
+    res = (2 * torch.randn(shape, generator=g)).to(dtype)
+    n = shape[-1]
+    w = (torch.rand((n,), generator=g) + 0.5).to(dtype)
+    b = (torch.randn((n,), generator=g) * 0.1).to(dtype)
+    xc, rc, wc, bc = _cuda(x, res, w, b)
+    y, s = layer_norm(xc, wc, None if rms else bc, 1e-5, use_rms_norm=rms, residual=rc)
+    want_sum = (x.float() + res.float()).to(dtype)
+    assert torch.equal(s.cpu(), want_sum)
+    eps = O.kernel_eps(1e-5, dtype)
+    expected = O.rms_norm(want_sum, w, eps) if rms else O.layer_norm(want_sum, w, b, eps)
+    O.assert_parity(y, expected, max_abs=1e-2 if dtype == torch.float16 else 4e-2)
+    # the plain call on the sum gives the same bits
+    assert torch.equal(y, layer_norm(s, wc, None if rms else bc, 1e-5, use_rms_norm=rms))
+
+
 def test_eps_clamp_only_for_fp16(lib):
     """fp16 clamps eps to 1.6e-5 (reference layer_norm.py:295-296); bf16 does not."""
     from kernl_b200.implementations.layer_norm import layer_norm

@@ -47,6 +47,25 @@ def _worker(rank, world, port, out_path):
             ref = (ref + resid.float())
             worst = max(worst, (got.float() - ref).abs().max().item())
     results["fused_vs_nccl_max_abs"] = worst
+    # ---- the same kernel with the next block's RMSNorm fused in: the sum must be bit-identical to
+    # the plain call, the normed rows must match an RMSNorm of that sum
+    from kernl_b200.llama_tp import CudaOps
+
+    worst_norm, sums_equal = 0.0, True
+    for (rows, cols) in [(8, 4096), (1, 64), (5, 8192), (130, 512)]:
+        part = torch.randn((rows, cols), generator=g, device=dev).bfloat16()
+        resid = torch.randn((rows, cols), generator=torch.Generator(device=dev).manual_seed(8), device=dev).bfloat16()
+        w = (1 + 0.1 * torch.randn(cols, generator=torch.Generator(device=dev).manual_seed(9), device=dev)).bfloat16()
+        buf = peer.partial_buffer(rows, cols, torch.bfloat16, dev)
+        buf.copy_(part)
+        plain = peer.reduce_add(buf, resid)
+        x, h = peer.reduce_add_norm(buf, resid, w, 1e-5, CudaOps())
+        sums_equal = sums_equal and bool(torch.equal(x, plain))
+        xf = x.float()
+        ref = xf * torch.rsqrt((xf * xf).mean(-1, keepdim=True) + 1e-5) * w.float()
+        worst_norm = max(worst_norm, (h.float() - ref).abs().max().item())
+    results["fused_norm_sums_equal"] = sums_equal
+    results["fused_norm_max_abs"] = worst_norm
     assert peer.partial_buffer(1024, 4096, torch.bfloat16, dev) is None  # too large for the one-shot kernel
     # ---- model: TP=2 with both communicators vs the same model on one GPU
     cfg = LlamaConfig(n_layers=2, hidden=512, n_heads=4, head_dim=128, ffn=1408, vocab=1000, max_seq=208)
@@ -91,6 +110,8 @@ def test_two_gpu_tensor_parallel(lib, tmp_path):
     r = torch.load(out_path)
     # same additions in another order (per-rank partial sums rounded to bf16 before the reduction)
     assert r["fused_vs_nccl_max_abs"] < 0.13, r["fused_vs_nccl_max_abs"]
+    assert r["fused_norm_sums_equal"]
+    assert r["fused_norm_max_abs"] < 4e-2, r["fused_norm_max_abs"]  # bf16 rounding of values up to ~8
     O.assert_parity(r["nccl"], r["single"], max_abs=6e-2, cos=0.999, what="TP2 (NCCL) vs single GPU")
     O.assert_parity(r["peer"], r["single"], max_abs=6e-2, cos=0.999, what="TP2 (fused kernel) vs single GPU")
     O.assert_parity(r["peer"], r["nccl"], max_abs=6e-2, cos=0.999, what="fused kernel vs NCCL")

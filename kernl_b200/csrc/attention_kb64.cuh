@@ -550,13 +550,16 @@ static int launch_attention64_td(const kb_attn_params& p, cudaStream_t stream) {
     return launch_attention64_tdm<T, D, 2>(p, stream);
 }
 
-// Which kernel serves a call: 0 = by head dimension (below), 1 = 128-key blocks, 2 = 64-key blocks.
+// Which kernel serves a call: 0 = by head dimension (below), 1 = 128-key blocks, 2 = 64-key blocks,
+// 3 = 64-key blocks with two threads per query row (head dimension 64 only).
 static int g_attn_variant = 0;
+static int launch_attention_split(const kb_attn_params& p, cudaStream_t stream);
 
 static int launch_attention(const kb_attn_params& p, cudaStream_t stream) {
     if (p.N <= 0) return KB_ERR_UNSUPPORTED;
     if (p.M > 0x7fffffff || p.N > 0x7fffffff || p.B * p.H > 0x7fffffff) return KB_ERR_UNSUPPORTED;
-    const bool use64 = g_attn_variant == 2 || (g_attn_variant == 0 && p.D == 64);
+    if (p.D == 64 && (g_attn_variant == 3 || g_attn_variant == 0)) return launch_attention_split(p, stream);
+    const bool use64 = g_attn_variant == 2 || g_attn_variant == 3;
     if (!use64) return launch_attention128(p, stream);
     if (p.dtype == KB_F16) {
         if (p.D == 64) return launch_attention64_td<__half, 64>(p, stream);

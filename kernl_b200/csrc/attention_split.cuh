@@ -1,0 +1,565 @@
+// Fused attention forward for sm_100a, head dimension 64, "split-row" variant.
+//
+// Same tiling as attention_kb64.cuh (two 128-row query tiles per CTA, keys in blocks of 64, K/V
+// through an 8-stage TMA ring, one tcgen05 issuer warp per tile), but SIXTEEN softmax warps instead
+// of eight: every query row is shared by two threads of different warps, one owning key columns
+// [0,32) of each block, the other [32,64). The two halves never talk to each other inside the key
+// loop: each keeps its own running maximum and row sum, writes its own half of P, and its P·V goes
+// into its own accumulator in TMEM (O_a from the keys of the first halves, O_b from the second
+// halves; two K=32 tcgen05.mma chains instead of one K=64 chain, the same tensor-core work). The
+// halves are merged once, in the epilogue: O = (w_a·O_a + w_b·O_b) / (w_a·l_a + w_b·l_b) with
+// w_x = 2^(m_x - max(m_a, m_b)).
+//
+// Why: a softmax warp's block is a serial chain of fixed latencies (barrier poll, TMEM load, the
+// dependent maximum reduction, special-function-unit results, TMEM store, hand-off) that one warp
+// cannot overlap with itself, and with one row per thread there are only two such warps per SM
+// sub-partition. Clock stamps taken inside the kernel showed a block taking ~2200 cycles of which
+// the special-function unit was busy for 512. Four warps per sub-partition overlap those chains.
+//
+// Warps (640 threads): 0..7 tile 0 (0..3 first halves, 4..7 second halves), 8..15 tile 1,
+// 16 TMA producer, 17/18 tcgen05 issuers of tile 0/1, 19 mask loader (MODE 1).
+// TMEM columns per tile t (base 256·t): S ring slot s at 64·s (s = 0,1; 64 fp32 columns; P of the
+// first half overwrites columns [0,16), P of the second half columns [32,48) of the same slot),
+// O_a at 128, O_b at 192.
+#pragma once
+#include "attention_kb64.cuh"
+
+namespace kb {
+
+constexpr int kSplitThreads = 640;
+// Launch allocation 65536 / 640 -> 96 registers per thread; the four softmax warpgroups grow to
+// kSplitRegsHigh and the fifth warpgroup (TMA, issuers, mask loader) shrinks to kSplitRegsLow.
+// The increase waits without bound until the CTA's pool has the registers, so the totals must fit.
+constexpr int kSplitRegsLaunch = 96;
+constexpr int kSplitRegsHigh = 104;
+constexpr int kSplitRegsLow = 64;
+static_assert(4 * kSplitRegsHigh + kSplitRegsLow <= 5 * kSplitRegsLaunch, "setmaxnreg totals exceed the CTA's register pool");
+static_assert(kSplitRegsHigh % 8 == 0 && kSplitRegsLow % 8 == 0, "setmaxnreg wants multiples of 8");
+
+struct AttnSplitCfg {
+    static constexpr int D = 64;
+    static constexpr int kKvStages = 8;
+    static constexpr int kQTileBytes = kAttnBlock * D * 2;
+    static constexpr int kKvBytes = kBlkN * D * 2;
+    static constexpr int kTilesBytes = 2 * kQTileBytes + 2 * kKvStages * kKvBytes;
+    static constexpr int kBarBytes = 1024;
+    static constexpr int kMaskBytes = 2 * 2 * kBlkN * 4;      // [tile][slot][64] floats
+    static constexpr int kXchBytes = 2 * 2 * kAttnBlock * 8;  // [tile][half][row] (m, l)
+    static constexpr int kSmemBytes = kTilesBytes + kBarBytes + kMaskBytes + kXchBytes + 1024;
+};
+
+template <typename T, int MODE>
+__global__ void __launch_bounds__(kSplitThreads, 1)
+attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                       const __grid_constant__ CUtensorMap tmap_v, const AttnDev p) {
+    using Cfg = AttnSplitCfg;
+    constexpr int D = 64;
+    constexpr int KVS = Cfg::kKvStages;
+    constexpr int QTILE = Cfg::kQTileBytes;
+    constexpr int KVB = Cfg::kKvBytes;
+    constexpr int NB = 2;
+    constexpr uint32_t kTmemCols = 512;
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    const uint32_t q_smem = smem_u32(smem);
+    const uint32_t k_smem = q_smem + 2 * QTILE;
+    const uint32_t v_smem = k_smem + KVS * KVB;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kTilesBytes);
+    const uint32_t bar_base = smem_u32(bars);
+    // q_full[2] | o_final[2] | p_full, s_full, m_full, m_empty, pv_done [2][2] each | ep[2][4] |
+    // k_full, k_empty, v_full, v_empty [KVS] each
+    auto q_full = [&](int t) { return bar_base + 8u * t; };
+    auto o_final = [&](int t) { return bar_base + 8u * (2 + t); };
+    auto p_full = [&](int t, int bf) { return bar_base + 8u * (4 + t * NB + bf); };
+    auto s_full = [&](int t, int bf) { return bar_base + 8u * (8 + t * NB + bf); };
+    auto m_full = [&](int t, int bf) { return bar_base + 8u * (12 + t * NB + bf); };
+    auto m_empty = [&](int t, int bf) { return bar_base + 8u * (16 + t * NB + bf); };
+    auto pv_done = [&](int t, int bf) { return bar_base + 8u * (20 + t * NB + bf); };
+    auto ep_bar = [&](int t, int q) { return bar_base + 8u * (24 + t * 4 + q); };
+    auto k_full = [&](int s) { return bar_base + 8u * (32 + s); };
+    auto k_empty = [&](int s) { return bar_base + 8u * (32 + KVS + s); };
+    auto v_full = [&](int s) { return bar_base + 8u * (32 + 2 * KVS + s); };
+    auto v_empty = [&](int s) { return bar_base + 8u * (32 + 3 * KVS + s); };
+    constexpr int kNumBars = 32 + 4 * KVS;
+    static_assert(kNumBars * 8 + 16 <= Cfg::kBarBytes, "barrier area too small");
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBars);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    float* mask_smem = reinterpret_cast<float*>(smem + Cfg::kTilesBytes + Cfg::kBarBytes);
+    float2* xch = reinterpret_cast<float2*>(smem + Cfg::kTilesBytes + Cfg::kBarBytes + Cfg::kMaskBytes);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    {
+        __shared__ int s_skip;
+        if (threadIdx.x == 0) s_skip = *reinterpret_cast<volatile int*>(&g_device_status[0]);
+        __syncthreads();
+        if (s_skip != 0) return;
+    }
+
+    const int BH = p.B * p.H;
+    const int pair = p.num_pairs - 1 - (int)(blockIdx.x / BH);  // heavy (late) tiles first
+    const int bh = (int)(blockIdx.x % BH);
+    const int b = bh / p.H, h = bh % p.H;
+    const int num_m_tiles = (p.M + kAttnBlock - 1) / kAttnBlock;
+    const int num_n_blocks = (p.N + kBlkN - 1) / kBlkN;
+    int mt[2], nblk[2];
+    int ntl = 0;
+    for (int t = 0; t < 2; ++t) {
+        mt[t] = pair * 2 + t;
+        if (mt[t] < num_m_tiles) {
+            ntl = t + 1;
+            nblk[t] = p.is_causal ? min(num_n_blocks, (mt[t] + 1) * (kAttnBlock / kBlkN)) : num_n_blocks;
+        } else {
+            nblk[t] = 0;
+        }
+    }
+    const int max_blk = max(nblk[0], nblk[1]);
+
+    if (threadIdx.x == 0) {
+        for (int t = 0; t < 2; ++t) {
+            mbar_init(q_full(t), 1);
+            mbar_init(o_final(t), 1);
+            for (int q = 0; q < 4; ++q) mbar_init(ep_bar(t, q), 2);
+            for (int bf = 0; bf < NB; ++bf) {
+                mbar_init(s_full(t, bf), 1);
+                mbar_init(pv_done(t, bf), 1);
+                mbar_init(p_full(t, bf), 8);
+                mbar_init(m_full(t, bf), 1);
+                mbar_init(m_empty(t, bf), 8);
+            }
+        }
+        for (int s = 0; s < KVS; ++s) {
+            mbar_init(k_full(s), 1);
+            mbar_init(k_empty(s), ntl);  // one arrival per live tile's issuer
+            mbar_init(v_full(s), 1);
+            mbar_init(v_empty(s), ntl);
+        }
+        *abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == 17) {
+        tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+        tmem_relinquish();
+    }
+    if (warp == 16 && lane == 0) {
+        tma_prefetch_desc(&tmap_q);
+        tma_prefetch_desc(&tmap_k);
+        tma_prefetch_desc(&tmap_v);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp >= 16) {
+      asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kSplitRegsLow));
+      if (warp == 16) {
+        // ------------------------------------------------------------------ TMA producer
+        if (elect_one()) {
+            bool ok = true;
+            for (int t = 0; t < ntl; ++t) {
+                mbar_arrive_expect_tx(q_full(t), QTILE);
+                tma_load_4d(q_smem + t * QTILE, &tmap_q, q_full(t), 0, mt[t] * kAttnBlock, h, b);
+            }
+            for (int j = 0; j < max_blk && ok; ++j) {
+                const int s = j % KVS;
+                const uint32_t ph = (uint32_t)((j / KVS) & 1);
+                if (!mbar_wait(k_empty(s), ph ^ 1, abort_flag, 600)) { ok = false; break; }
+                mbar_arrive_expect_tx(k_full(s), KVB);
+                tma_load_4d(k_smem + s * KVB, &tmap_k, k_full(s), 0, j * kBlkN, h, b);
+                if (!mbar_wait(v_empty(s), ph ^ 1, abort_flag, 601)) { ok = false; break; }
+                mbar_arrive_expect_tx(v_full(s), KVB);
+                tma_load_4d(v_smem + s * KVB, &tmap_v, v_full(s), 0, j * kBlkN, h, b);
+            }
+            if (!ok) {
+                for (int i = 0; i < 64; ++i) __nanosleep(2000);
+            }
+        }
+      } else if (warp == 17 || warp == 18) {
+        // ------------------------------------------------------------------ MMA issuers, one per tile
+        const int t = warp - 17;
+        if (elect_one()) {
+            constexpr uint32_t idesc_qk = make_idesc_f16(Elem<T>::kIsBf16, 128, kBlkN, 0, 0);
+            constexpr uint32_t idesc_pv = make_idesc_f16(Elem<T>::kIsBf16, 128, D, 0, 1);
+            constexpr uint32_t desc_hi = (1024u >> 4) | (1u << 14) | (2u << 29);
+            const uint32_t q_lo = ((q_smem + t * QTILE) & 0x3FFFF) >> 4;
+            const uint32_t k_lo = (k_smem & 0x3FFFF) >> 4;
+            const uint32_t v_lo = (v_smem & 0x3FFFF) >> 4;
+            const uint32_t t_base = tmem_base + (uint32_t)(t * 256);
+            auto desc = [&](uint32_t lo) { return ((uint64_t)desc_hi << 32) | (uint64_t)lo; };
+            auto issue_qk = [&](int j) {  // S[t][j & 1] = Q_t · K_jᵀ
+                const uint32_t b_lo = k_lo + (uint32_t)((j % KVS) * (KVB >> 4));
+                const uint32_t d_tmem = t_base + (uint32_t)((j & 1) * kBlkN);
+#pragma unroll
+                for (int ks = 0; ks < D / 16; ++ks)
+                    tc_mma_ss(d_tmem, desc(q_lo + (uint32_t)((ks * 32) >> 4)), desc(b_lo + (uint32_t)((ks * 32) >> 4)), idesc_qk,
+                              ks > 0 ? 1u : 0u);
+            };
+            auto issue_pv = [&](int j) {  // O_a += P_j[:, 0:32] · V_j[0:32, :],  O_b += P_j[:, 32:64] · V_j[32:64, :]
+                const uint32_t b_lo = v_lo + (uint32_t)((j % KVS) * (KVB >> 4));
+                const uint32_t s_tmem = t_base + (uint32_t)((j & 1) * kBlkN);
+#pragma unroll
+                for (int hf = 0; hf < 2; ++hf) {
+#pragma unroll
+                    for (int ks = 0; ks < 2; ++ks) {
+                        tc_mma_ts(t_base + (uint32_t)(128 + hf * 64), s_tmem + (uint32_t)(hf * 32 + ks * 8),
+                                  desc(b_lo + (uint32_t)((hf * 2 + ks) * (2048 >> 4))), idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+                    }
+                }
+            };
+            const int my_blk = (t < ntl) ? nblk[t] : 0;
+            bool ok = true;
+            if (t < ntl && !mbar_wait(q_full(t), 0, abort_flag, 610)) ok = false;
+            for (int jj = 0; jj < NB && jj < max_blk && ok && t < ntl; ++jj) {
+                if (!mbar_wait(k_full(jj % KVS), (uint32_t)((jj / KVS) & 1), abort_flag, 611)) { ok = false; break; }
+                if (jj < my_blk) {
+                    tc_fence_after();
+                    issue_qk(jj);
+                    tc_commit(s_full(t, jj & 1));
+                    tc_commit(k_empty(jj % KVS));
+                } else {
+                    mbar_arrive(k_empty(jj % KVS));  // a block this tile does not need (shorter causal range)
+                }
+            }
+            for (int j = 0; j < max_blk && ok && t < ntl; ++j) {
+                const int s = j % KVS;
+                if (!mbar_wait(v_full(s), (uint32_t)((j / KVS) & 1), abort_flag, 612)) { ok = false; break; }
+                const int j2 = j + NB;
+                if (j2 < max_blk) {
+                    if (!mbar_wait(k_full(j2 % KVS), (uint32_t)((j2 / KVS) & 1), abort_flag, 613)) { ok = false; break; }
+                }
+                if (j < my_blk) {
+                    if (!mbar_wait(p_full(t, j & 1), (uint32_t)((j >> 1) & 1), abort_flag, 614)) { ok = false; break; }
+                    tc_fence_after();
+                    issue_pv(j);
+                    tc_commit(pv_done(t, j & 1));
+                    if (j2 < my_blk) {
+                        issue_qk(j2);  // into the slot that P_j has just been read from (in-order execution)
+                        tc_commit(s_full(t, j & 1));
+                    }
+                    if (j + 1 == my_blk) tc_commit(o_final(t));
+                    tc_commit(v_empty(s));
+                    if (j2 < max_blk) {
+                        if (j2 < my_blk) tc_commit(k_empty(j2 % KVS));
+                        else mbar_arrive(k_empty(j2 % KVS));
+                    }
+                } else {
+                    mbar_arrive(v_empty(s));
+                    if (j2 < max_blk) mbar_arrive(k_empty(j2 % KVS));
+                }
+            }
+        }
+      } else if (MODE == 1 && warp == 19) {
+        // ------------------------------------------------------------------ mask loader
+        const float mlow = mask_lowest(p.mask_dtype);
+        const int64_t moff = (int64_t)b * p.mask_strides[0] + (int64_t)h * p.mask_strides[1];
+        bool ok = true;
+        for (int j = 0; j < max_blk && ok; ++j) {
+            const int bf = j & 1;
+            const uint32_t ph = (uint32_t)((j >> 1) & 1);
+            for (int t = 0; t < ntl && ok; ++t) {
+                if (j >= nblk[t]) continue;
+                if (!mbar_wait(m_empty(t, bf), ph ^ 1, abort_flag, 620 + t)) { ok = false; break; }
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int idx = lane + e * 32;
+                    const int col = j * kBlkN + idx;
+                    float a = -INFINITY;
+                    if (col < p.N)
+                        a = fmaxf(mask_load(p.mask, moff + (int64_t)col * p.mask_strides[3], p.mask_dtype), mlow) * kLog2e;
+                    mask_smem[(t * NB + bf) * kBlkN + idx] = a;
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(m_full(t, bf));
+            }
+        }
+      }
+    } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kSplitRegsHigh));
+        // ------------------------------------------------------------------ softmax warps
+        const int t = warp >> 3;
+        const int hf = (warp >> 2) & 1;  // which 32 key columns of every block
+        const int q = warp & 3;          // TMEM lane quarter = 32 query rows
+        if (t < ntl && nblk[t] > 0) {
+            const int nb = nblk[t];
+            const int r_in_tile = q * 32 + lane;
+            const int row = mt[t] * kAttnBlock + r_in_tile;
+            const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(t * 256);
+            const uint32_t o_own = lane_addr + (uint32_t)(128 + hf * 64);
+            const float c = p.scale_log2;
+            const float mlow = mask_lowest(p.mask_dtype);
+            const int64_t mask_row_off =
+                (MODE == 2 && p.mask != nullptr)
+                    ? (int64_t)b * p.mask_strides[0] + (int64_t)h * p.mask_strides[1] + (int64_t)min(row, p.M - 1) * p.mask_strides[2]
+                    : 0;
+            const float unit = (MODE == 0) ? c : 1.0f;
+            float m_ref = -INFINITY;
+            float l = 0.f;
+            bool ok = true;
+            for (int j = 0; j < nb; ++j) {
+                const int bf = j & 1;
+                const uint32_t ph = (uint32_t)((j >> 1) & 1);
+                const uint32_t s_addr = lane_addr + (uint32_t)(bf * kBlkN + hf * 32);
+                if (!mbar_wait(s_full(t, bf), ph, abort_flag, 630 + t)) { ok = false; break; }
+                if (MODE == 1) {
+                    if (!mbar_wait(m_full(t, bf), ph, abort_flag, 640 + t)) { ok = false; break; }
+                }
+                tc_fence_after();
+                uint32_t sr[32];
+                tmem_ld_32x32(s_addr, sr);
+                tmem_ld_wait();
+
+                const int col0 = j * kBlkN + hf * 32;
+                if (MODE == 1) {
+                    const float4* ms = reinterpret_cast<const float4*>(mask_smem + (t * NB + bf) * kBlkN + hf * 32);
+#pragma unroll
+                    for (int v4 = 0; v4 < 8; ++v4) {
+                        const float4 a = ms[v4];
+                        sr[v4 * 4 + 0] = __float_as_uint(fmaf(__uint_as_float(sr[v4 * 4 + 0]), c, a.x));
+                        sr[v4 * 4 + 1] = __float_as_uint(fmaf(__uint_as_float(sr[v4 * 4 + 1]), c, a.y));
+                        sr[v4 * 4 + 2] = __float_as_uint(fmaf(__uint_as_float(sr[v4 * 4 + 2]), c, a.z));
+                        sr[v4 * 4 + 3] = __float_as_uint(fmaf(__uint_as_float(sr[v4 * 4 + 3]), c, a.w));
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(m_empty(t, bf));
+                } else if (MODE == 2) {
+                    if (p.mask == nullptr) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) sr[i] = __float_as_uint(__uint_as_float(sr[i]) * c);
+                    } else {
+#pragma unroll
+                        for (int hc = 0; hc < 2; ++hc) {
+                            const int colc = col0 + hc * 16;
+                            float mvals[16];
+                            if (p.mask_vec && colc + 16 <= p.N) {
+                                if (p.mask_dtype == KB_F32) {
+                                    const float4* mp = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.mask) + mask_row_off + colc);
+#pragma unroll
+                                    for (int v4 = 0; v4 < 4; ++v4) {
+                                        const float4 f = __ldg(mp + v4);
+                                        mvals[v4 * 4 + 0] = f.x; mvals[v4 * 4 + 1] = f.y; mvals[v4 * 4 + 2] = f.z; mvals[v4 * 4 + 3] = f.w;
+                                    }
+                                } else {
+                                    const uint4* mp = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.mask) + mask_row_off + colc);
+#pragma unroll
+                                    for (int v4 = 0; v4 < 2; ++v4) {
+                                        const uint4 w = __ldg(mp + v4);
+                                        const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+                                        for (int i = 0; i < 4; ++i) {
+                                            const float2 f = (p.mask_dtype == KB_F16) ? Elem<__half>::unpack2(ww[i]) : Elem<__nv_bfloat16>::unpack2(ww[i]);
+                                            mvals[v4 * 8 + 2 * i] = f.x;
+                                            mvals[v4 * 8 + 2 * i + 1] = f.y;
+                                        }
+                                    }
+                                }
+                            } else {
+#pragma unroll
+                                for (int i = 0; i < 16; ++i) {
+                                    const int col = colc + i;
+                                    mvals[i] = (col < p.N) ? mask_load(p.mask, mask_row_off + (int64_t)col * p.mask_strides[3], p.mask_dtype) : 0.f;
+                                }
+                            }
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) {
+                                uint32_t& sv = sr[hc * 16 + i];
+                                sv = __float_as_uint(fmaf(fmaxf(mvals[i], mlow), kLog2e, __uint_as_float(sv) * c));
+                            }
+                        }
+                    }
+                }
+                const bool causal_edge = p.is_causal && col0 + 31 > mt[t] * kAttnBlock;
+                if ((MODE != 1 && col0 + 32 > p.N) || causal_edge) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const int col = col0 + i;
+                        if (col >= p.N || (p.is_causal && col > row)) sr[i] = __float_as_uint(-INFINITY);
+                    }
+                }
+                float m4[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) m4[i] = fmaxf(__uint_as_float(sr[2 * i]), __uint_as_float(sr[2 * i + 1]));
+#pragma unroll
+                for (int i = 4; i < 16; ++i) m4[i & 3] = fmax3(m4[i & 3], __uint_as_float(sr[2 * i]), __uint_as_float(sr[2 * i + 1]));
+                const float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+                float m_new = fmaxf(m_ref, mx);
+                if (m_new == -INFINITY) m_new = 0.f;
+                const bool grow = (m_new - m_ref) * unit > kLazyThreshold;
+                float alpha = 1.0f;
+                if (grow) {
+                    alpha = (m_ref == -INFINITY) ? 0.f : fast_exp2((m_ref - m_new) * unit);
+                    m_ref = m_new;
+                    l *= alpha;
+                }
+                if (j > 0 && __any_sync(0xffffffffu, grow)) {
+                    // This half's accumulator must be quiescent before it is rescaled: P·V of block j-1
+                    // complete, the ((j-1)>>1)-th completion of the barrier of parity (j-1)&1. S_j
+                    // being ready implies P·V of block j-2 (hence j-3) complete, i.e. every earlier
+                    // completion of this barrier, so the parity cannot be mistaken for an older phase.
+                    if (!mbar_wait(pv_done(t, (j - 1) & 1), (uint32_t)(((j - 1) >> 1) & 1), abort_flag, 650 + t)) { ok = false; break; }
+                    tc_fence_after();
+#pragma unroll
+                    for (int dch = 0; dch < D / 16; ++dch) {
+                        uint32_t orr[16];
+                        tmem_ld_32x16(o_own + dch * 16, orr);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) orr[i] = __float_as_uint(__uint_as_float(orr[i]) * alpha);
+                        tmem_st_32x16(o_own + dch * 16, orr);
+                    }
+                }
+                const float neg_ref = -m_ref * unit;
+                const float2 unit2 = make_float2(unit, unit);
+                const float2 neg2 = make_float2(neg_ref, neg_ref);
+                float2 lp[2] = {{0.f, 0.f}, {0.f, 0.f}};
+                uint32_t pk[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const float2 a = __ffma2_rn(make_float2(__uint_as_float(sr[2 * i]), __uint_as_float(sr[2 * i + 1])), unit2, neg2);
+                    float2 e;
+                    e.x = fast_exp2(a.x);
+                    e.y = fast_exp2(a.y);
+                    lp[i & 1] = __fadd2_rn(lp[i & 1], e);
+                    pk[i] = Elem<T>::pack2(e.x, e.y);
+                }
+                tmem_st_32x16(s_addr, pk);
+                {
+                    const float2 st = __fadd2_rn(lp[0], lp[1]);
+                    l += st.x + st.y;
+                }
+                tmem_st_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(p_full(t, bf));
+            }
+            // ---- epilogue: merge the two halves of every row, O / l -> global
+            // (m, l) of this half to the partner warp (same rows, other half) through shared memory
+            // a half that never saw a finite score (all of its columns beyond N) must not set the scale
+            const float m_own = (l > 0.f) ? m_ref * unit : -INFINITY;
+            xch[(t * 2 + hf) * kAttnBlock + r_in_tile] = make_float2(m_own, l);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(ep_bar(t, q));
+            if (ok && mbar_wait(ep_bar(t, q), 0, abort_flag, 660 + t) && mbar_wait(o_final(t), 0, abort_flag, 670 + t)) {
+                tc_fence_after();
+                const float2 other = xch[(t * 2 + (hf ^ 1)) * kAttnBlock + r_in_tile];
+                float m_all = fmaxf(m_own, other.x);
+                if (m_all == -INFINITY) m_all = 0.f;
+                const float w_own = fast_exp2(m_own - m_all), w_oth = fast_exp2(other.x - m_all);
+                const float inv_l = 1.0f / (w_own * l + w_oth * other.y);
+                const float wa = (hf == 0 ? w_own : w_oth) * inv_l;  // weight of O_a
+                const float wb = (hf == 0 ? w_oth : w_own) * inv_l;  // weight of O_b
+                // this warp writes output columns [32·hf, 32·hf + 32) of its 32 rows
+                uint32_t oa[32], ob[32];
+                tmem_ld_32x32(lane_addr + (uint32_t)(128 + hf * 32), oa);
+                tmem_ld_32x32(lane_addr + (uint32_t)(192 + hf * 32), ob);
+                tmem_ld_wait();
+                T* o_row = reinterpret_cast<T*>(p.o) + (int64_t)b * p.o_strides[0] + (int64_t)h * p.o_strides[1] +
+                           (int64_t)row * p.o_strides[2];
+                const bool vec = p.o_strides[3] == 1 && ((((uintptr_t)o_row) & 15) == 0);
+                if (row < p.M) {
+                    if (vec) {
+#pragma unroll
+                        for (int v = 0; v < 4; ++v) {
+                            uint32_t w4[4];
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const int e = v * 8 + 2 * i;
+                                w4[i] = Elem<T>::pack2(fmaf(__uint_as_float(oa[e]), wa, __uint_as_float(ob[e]) * wb),
+                                                       fmaf(__uint_as_float(oa[e + 1]), wa, __uint_as_float(ob[e + 1]) * wb));
+                            }
+                            reinterpret_cast<uint4*>(o_row + hf * 32)[v] = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+                        }
+                    } else {
+                        for (int i = 0; i < 32; ++i)
+                            o_row[(int64_t)(hf * 32 + i) * p.o_strides[3]] =
+                                Elem<T>::from_f32(fmaf(__uint_as_float(oa[i]), wa, __uint_as_float(ob[i]) * wb));
+                    }
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 17) {
+        __syncwarp();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+template <typename T, int MODE>
+static int launch_attention_split_tm(const kb_attn_params& p, cudaStream_t stream) {
+    using Cfg = AttnSplitCfg;
+    constexpr int D = 64;
+    CUtensorMap tq, tk, tv;
+    auto enc = [&](CUtensorMap* out, const void* ptr, int64_t rows, const int64_t* st, uint32_t box_rows) -> int {
+        if (st[3] != 1) return KB_ERR_UNSUPPORTED;
+        const uint64_t dims[4] = {(uint64_t)D, (uint64_t)rows, (uint64_t)p.H, (uint64_t)p.B};
+        auto fix = [](int64_t extent, int64_t stride) -> uint64_t { return (extent == 1) ? 16u : (uint64_t)stride * 2u; };
+        const uint64_t strides[4] = {0, fix(rows, st[2]), fix(p.H, st[1]), fix(p.B, st[0])};
+        const uint32_t box[4] = {64, box_rows, 1, 1};
+        return encode_tmap_16bit(out, ptr, 4, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B,
+                                 CU_TENSOR_MAP_L2_PROMOTION_L2_128B);
+    };
+    int st = enc(&tq, p.q, p.M, p.q_strides, kAttnBlock);
+    if (st != KB_OK) return st;
+    st = enc(&tk, p.k, p.N, p.k_strides, kBlkN);
+    if (st != KB_OK) return st;
+    st = enc(&tv, p.v, p.N, p.v_strides, kBlkN);
+    if (st != KB_OK) return st;
+
+    AttnDev d;
+    d.o = p.o;
+    d.mask = p.mask;
+    for (int i = 0; i < 4; ++i) {
+        d.o_strides[i] = p.o_strides[i];
+        d.mask_strides[i] = p.mask ? p.mask_strides[i] : 0;
+    }
+    d.B = (int)p.B; d.H = (int)p.H; d.M = (int)p.M; d.N = (int)p.N;
+    d.scale_log2 = p.sm_scale * kLog2e;
+    d.is_causal = p.is_causal ? 1 : 0;
+    d.mask_dtype = p.mask ? p.mask_dtype : KB_F32;
+    d.mask_vec = 0;
+    if (p.mask != nullptr && p.mask_strides[3] == 1 && (((uintptr_t)p.mask) & 15) == 0) {
+        const int64_t per16 = (p.mask_dtype == KB_F32) ? 4 : 8;
+        d.mask_vec = (p.mask_strides[0] % per16 == 0 && p.mask_strides[1] % per16 == 0 && p.mask_strides[2] % per16 == 0) ? 1 : 0;
+    }
+    const int num_m_tiles = (int)((p.M + kAttnBlock - 1) / kAttnBlock);
+    d.num_pairs = (num_m_tiles + 1) / 2;
+    static int ready = 0;  // 0 = not checked, 1 = usable, -1 = register allocation does not fit
+    if (ready == 0) {
+        // setmaxnreg.inc blocks until the CTA's pool holds the registers: refuse to launch a build
+        // whose launch allocation is smaller than the redistribution assumes.
+        cudaFuncAttributes fa;
+        if (cudaFuncGetAttributes(&fa, attention_split_kernel<T, MODE>) != cudaSuccess) return KB_ERR_LAUNCH;
+        if (fa.numRegs < kSplitRegsLaunch) {
+            ready = -1;
+        } else {
+            if (cudaFuncSetAttribute(attention_split_kernel<T, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     Cfg::kSmemBytes) != cudaSuccess)
+                return KB_ERR_LAUNCH;
+            ready = 1;
+        }
+    }
+    if (ready < 0) return KB_ERR_UNSUPPORTED;
+    const int64_t grid = (int64_t)d.num_pairs * p.B * p.H;
+    if (grid > 0x7fffffff) return KB_ERR_UNSUPPORTED;
+    attention_split_kernel<T, MODE><<<(unsigned)grid, kSplitThreads, Cfg::kSmemBytes, stream>>>(tq, tk, tv, d);
+    return cudaGetLastError() == cudaSuccess ? KB_OK : KB_ERR_LAUNCH;
+}
+
+template <typename T>
+static int launch_attention_split_t(const kb_attn_params& p, cudaStream_t stream) {
+    if (p.mask == nullptr && p.sm_scale > 0.f) return launch_attention_split_tm<T, 0>(p, stream);
+    if (p.mask != nullptr && p.mask_strides[2] == 0) return launch_attention_split_tm<T, 1>(p, stream);
+    return launch_attention_split_tm<T, 2>(p, stream);
+}
+
+static int launch_attention_split(const kb_attn_params& p, cudaStream_t stream) {
+    if (p.D != 64) return KB_ERR_UNSUPPORTED;
+    if (p.dtype == KB_F16) return launch_attention_split_t<__half>(p, stream);
+    if (p.dtype == KB_BF16) return launch_attention_split_t<__nv_bfloat16>(p, stream);
+    return KB_ERR_UNSUPPORTED;
+}
+
+}  // namespace kb

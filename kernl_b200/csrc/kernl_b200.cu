@@ -9,6 +9,7 @@
 #include "linear.cuh"
 #include "attention.cuh"
 #include "attention_kb64.cuh"
+#include "attention_split.cuh"
 #include "attention_decode.cuh"
 #include "allreduce.cuh"
 #include "rope.cuh"

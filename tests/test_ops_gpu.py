@@ -84,14 +84,17 @@ def test_attention_head_dim_128(lib, dtype, tol, causal):
     O.assert_parity(out, expected, max_abs=tol, what="attention d=128")
 
 
-@pytest.mark.parametrize("variant", [1, 2], ids=["blocks128", "blocks64"])
+@pytest.mark.parametrize("variant", [1, 2, 3], ids=["blocks128", "blocks64", "split_rows"])
 @pytest.mark.parametrize("d,dtype,tol", [(64, torch.float16, 1e-2), (64, torch.bfloat16, 3e-2), (128, torch.float16, 1e-2), (128, torch.bfloat16, 3e-2)],
                          ids=["d64_fp16", "d64_bf16", "d128_fp16", "d128_bf16"])
 @pytest.mark.parametrize("mask_kind,causal,m,n", [("none", False, 512, 512), ("pad", False, 300, 300), ("bias", True, 257, 257),
                                                   ("none", True, 640, 640), ("bias", False, 100, 700), ("none", False, 1, 24)])
 def test_attention_both_kernels(lib, variant, d, dtype, tol, mask_kind, causal, m, n):
-    """Both fused kernels (128-key blocks; 64-key blocks with double-buffered scores) on every
-    head dimension and dtype, whatever the dispatcher would pick."""
+    """Every fused kernel (128-key blocks; 64-key blocks with double-buffered scores; 64-key blocks
+    with two threads per query row, head dimension 64 only) on every head dimension and dtype it
+    supports, whatever the dispatcher would pick."""
+    if variant == 3 and d != 64:
+        pytest.skip("the split-row kernel serves head dimension 64 only")
     try:
         lib.kb_debug_attention_variant(variant)
         out, expected = _run_attention(2, 3, m, n, d, dtype, causal, mask_kind, d ** -0.5)

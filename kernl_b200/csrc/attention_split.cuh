@@ -43,9 +43,14 @@ struct AttnSplitCfg {
     static constexpr int kKvBytes = kBlkN * D * 2;
     static constexpr int kTilesBytes = 2 * kQTileBytes + 2 * kKvStages * kKvBytes;
     static constexpr int kBarBytes = 1024;
-    static constexpr int kMaskBytes = 2 * 2 * kBlkN * 4;      // [tile][slot][64] floats
     static constexpr int kXchBytes = 2 * 2 * kAttnBlock * 8;  // [tile][half][row] (m, l)
-    static constexpr int kSmemBytes = kTilesBytes + kBarBytes + kMaskBytes + kXchBytes + 1024;
+    // MODE 1 keeps the whole row-broadcast mask of its (batch, head) in shared memory, as fp32 in the
+    // log2 domain, loaded once in chunks of 512 columns; longer rows take the general path (MODE 2)
+    static constexpr int kMaskChunk = 512;
+    static constexpr int kMaskMaxN = 8192;
+    static constexpr int kMaskChunks = kMaskMaxN / kMaskChunk;
+    static constexpr int kSmemBase = kTilesBytes + kBarBytes + kXchBytes + 1024;
+    static constexpr int kSmemMax = kSmemBase + kMaskMaxN * 4;
 };
 
 template <typename T, int MODE>
@@ -67,26 +72,26 @@ attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     const uint32_t v_smem = k_smem + KVS * KVB;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kTilesBytes);
     const uint32_t bar_base = smem_u32(bars);
-    // q_full[2] | o_final[2] | p_full, s_full, m_full, m_empty, pv_done [2][2] each | ep[2][4] |
+    // q_full[2] | o_final[2] | p_full, s_full, pv_done [2][2] each | ep[2][4] | m_chunk[16] |
     // k_full, k_empty, v_full, v_empty [KVS] each
     auto q_full = [&](int t) { return bar_base + 8u * t; };
     auto o_final = [&](int t) { return bar_base + 8u * (2 + t); };
     auto p_full = [&](int t, int bf) { return bar_base + 8u * (4 + t * NB + bf); };
     auto s_full = [&](int t, int bf) { return bar_base + 8u * (8 + t * NB + bf); };
-    auto m_full = [&](int t, int bf) { return bar_base + 8u * (12 + t * NB + bf); };
-    auto m_empty = [&](int t, int bf) { return bar_base + 8u * (16 + t * NB + bf); };
-    auto pv_done = [&](int t, int bf) { return bar_base + 8u * (20 + t * NB + bf); };
-    auto ep_bar = [&](int t, int q) { return bar_base + 8u * (24 + t * 4 + q); };
-    auto k_full = [&](int s) { return bar_base + 8u * (32 + s); };
-    auto k_empty = [&](int s) { return bar_base + 8u * (32 + KVS + s); };
-    auto v_full = [&](int s) { return bar_base + 8u * (32 + 2 * KVS + s); };
-    auto v_empty = [&](int s) { return bar_base + 8u * (32 + 3 * KVS + s); };
-    constexpr int kNumBars = 32 + 4 * KVS;
+    auto pv_done = [&](int t, int bf) { return bar_base + 8u * (12 + t * NB + bf); };
+    auto ep_bar = [&](int t, int q) { return bar_base + 8u * (16 + t * 4 + q); };
+    auto m_chunk = [&](int c) { return bar_base + 8u * (24 + c); };
+    constexpr int kKvBar = 24 + Cfg::kMaskChunks;
+    auto k_full = [&](int s) { return bar_base + 8u * (kKvBar + s); };
+    auto k_empty = [&](int s) { return bar_base + 8u * (kKvBar + KVS + s); };
+    auto v_full = [&](int s) { return bar_base + 8u * (kKvBar + 2 * KVS + s); };
+    auto v_empty = [&](int s) { return bar_base + 8u * (kKvBar + 3 * KVS + s); };
+    constexpr int kNumBars = kKvBar + 4 * KVS;
     static_assert(kNumBars * 8 + 16 <= Cfg::kBarBytes, "barrier area too small");
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBars);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    float* mask_smem = reinterpret_cast<float*>(smem + Cfg::kTilesBytes + Cfg::kBarBytes);
-    float2* xch = reinterpret_cast<float2*>(smem + Cfg::kTilesBytes + Cfg::kBarBytes + Cfg::kMaskBytes);
+    float2* xch = reinterpret_cast<float2*>(smem + Cfg::kTilesBytes + Cfg::kBarBytes);
+    float* mask_smem = reinterpret_cast<float*>(smem + Cfg::kTilesBytes + Cfg::kBarBytes + Cfg::kXchBytes);  // [N rounded up to 64]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     {
@@ -115,36 +120,55 @@ attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     }
     const int max_blk = max(nblk[0], nblk[1]);
 
-    if (threadIdx.x == 0) {
-        for (int t = 0; t < 2; ++t) {
-            mbar_init(q_full(t), 1);
-            mbar_init(o_final(t), 1);
-            for (int q = 0; q < 4; ++q) mbar_init(ep_bar(t, q), 2);
-            for (int bf = 0; bf < NB; ++bf) {
-                mbar_init(s_full(t, bf), 1);
-                mbar_init(pv_done(t, bf), 1);
-                mbar_init(p_full(t, bf), 8);
-                mbar_init(m_full(t, bf), 1);
-                mbar_init(m_empty(t, bf), 8);
+    // Set-up is spread over three warps so that the first loads are in flight as early as possible:
+    // the TMA warp initialises the barriers its loads complete on and issues both Q tiles and the
+    // first ring of K/V blocks at once; warp 0 initialises the other barriers, one per lane; warp 17
+    // allocates TMEM. Everybody else meets them at the barrier below.
+    const int first_kv = min(KVS, max_blk);
+    if (warp == 16) {
+        if (lane == 0) {
+            tma_prefetch_desc(&tmap_q);
+            tma_prefetch_desc(&tmap_k);
+            tma_prefetch_desc(&tmap_v);
+            for (int t = 0; t < 2; ++t) mbar_init(q_full(t), 1);
+            for (int s = 0; s < KVS; ++s) {
+                mbar_init(k_full(s), 1);
+                mbar_init(k_empty(s), ntl);  // one arrival per live tile's issuer
+                mbar_init(v_full(s), 1);
+                mbar_init(v_empty(s), ntl);
+            }
+            fence_mbar_init();
+            for (int t = 0; t < ntl; ++t) {
+                mbar_arrive_expect_tx(q_full(t), QTILE);
+                tma_load_4d(q_smem + t * QTILE, &tmap_q, q_full(t), 0, mt[t] * kAttnBlock, h, b);
+                if (t == 0 && first_kv > 0) {  // K_0 right behind the first Q tile: the first Q·Kᵀ needs just these two
+                    mbar_arrive_expect_tx(k_full(0), KVB);
+                    tma_load_4d(k_smem, &tmap_k, k_full(0), 0, 0, h, b);
+                }
+            }
+            for (int j = 0; j < first_kv; ++j) {
+                if (j > 0) {
+                    mbar_arrive_expect_tx(k_full(j), KVB);
+                    tma_load_4d(k_smem + j * KVB, &tmap_k, k_full(j), 0, j * kBlkN, h, b);
+                }
+                mbar_arrive_expect_tx(v_full(j), KVB);
+                tma_load_4d(v_smem + j * KVB, &tmap_v, v_full(j), 0, j * kBlkN, h, b);
             }
         }
-        for (int s = 0; s < KVS; ++s) {
-            mbar_init(k_full(s), 1);
-            mbar_init(k_empty(s), ntl);  // one arrival per live tile's issuer
-            mbar_init(v_full(s), 1);
-            mbar_init(v_empty(s), ntl);
+    } else if (warp == 0) {
+        if (lane < 2) mbar_init(o_final(lane), 1);
+        if (lane < 4) {
+            mbar_init(p_full(lane >> 1, lane & 1), 8);
+            mbar_init(s_full(lane >> 1, lane & 1), 1);
+            mbar_init(pv_done(lane >> 1, lane & 1), 1);
         }
-        *abort_flag = 0;
+        if (lane < 8) mbar_init(ep_bar(lane >> 2, lane & 3), 2);
+        if (lane < Cfg::kMaskChunks) mbar_init(m_chunk(lane), 1);
+        if (lane == 0) *abort_flag = 0;
         fence_mbar_init();
-    }
-    if (warp == 17) {
+    } else if (warp == 17) {
         tmem_alloc(smem_u32(tmem_slot), kTmemCols);
         tmem_relinquish();
-    }
-    if (warp == 16 && lane == 0) {
-        tma_prefetch_desc(&tmap_q);
-        tma_prefetch_desc(&tmap_k);
-        tma_prefetch_desc(&tmap_v);
     }
     tc_fence_before();
     __syncthreads();
@@ -157,11 +181,7 @@ attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
         // ------------------------------------------------------------------ TMA producer
         if (elect_one()) {
             bool ok = true;
-            for (int t = 0; t < ntl; ++t) {
-                mbar_arrive_expect_tx(q_full(t), QTILE);
-                tma_load_4d(q_smem + t * QTILE, &tmap_q, q_full(t), 0, mt[t] * kAttnBlock, h, b);
-            }
-            for (int j = 0; j < max_blk && ok; ++j) {
+            for (int j = first_kv; j < max_blk && ok; ++j) {  // the first ring was issued during set-up
                 const int s = j % KVS;
                 const uint32_t ph = (uint32_t)((j / KVS) & 1);
                 if (!mbar_wait(k_empty(s), ph ^ 1, abort_flag, 600)) { ok = false; break; }
@@ -251,27 +271,25 @@ attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
         }
       } else if (MODE == 1 && warp == 19) {
         // ------------------------------------------------------------------ mask loader
+        // The whole mask row of this (batch, head), clamped, in the log2 domain, -inf beyond N; one
+        // barrier per chunk of 512 columns so that the first key blocks do not wait for the last.
         const float mlow = mask_lowest(p.mask_dtype);
         const int64_t moff = (int64_t)b * p.mask_strides[0] + (int64_t)h * p.mask_strides[1];
-        bool ok = true;
-        for (int j = 0; j < max_blk && ok; ++j) {
-            const int bf = j & 1;
-            const uint32_t ph = (uint32_t)((j >> 1) & 1);
-            for (int t = 0; t < ntl && ok; ++t) {
-                if (j >= nblk[t]) continue;
-                if (!mbar_wait(m_empty(t, bf), ph ^ 1, abort_flag, 620 + t)) { ok = false; break; }
+        const int ncols = max_blk * kBlkN;
+        for (int c0 = 0; c0 < ncols; c0 += Cfg::kMaskChunk) {
+            float vals[Cfg::kMaskChunk / 32];
 #pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                    const int idx = lane + e * 32;
-                    const int col = j * kBlkN + idx;
-                    float a = -INFINITY;
-                    if (col < p.N)
-                        a = fmaxf(mask_load(p.mask, moff + (int64_t)col * p.mask_strides[3], p.mask_dtype), mlow) * kLog2e;
-                    mask_smem[(t * NB + bf) * kBlkN + idx] = a;
-                }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(m_full(t, bf));
+            for (int e = 0; e < Cfg::kMaskChunk / 32; ++e) {
+                const int col = c0 + e * 32 + lane;
+                vals[e] = (col < p.N) ? mask_load(p.mask, moff + (int64_t)col * p.mask_strides[3], p.mask_dtype) : -INFINITY;
             }
+#pragma unroll
+            for (int e = 0; e < Cfg::kMaskChunk / 32; ++e) {
+                const int col = c0 + e * 32 + lane;
+                if (col < ncols) mask_smem[col] = (col < p.N) ? fmaxf(vals[e], mlow) * kLog2e : -INFINITY;
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(m_chunk(c0 / Cfg::kMaskChunk));
         }
       }
     } else {
@@ -301,8 +319,8 @@ attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
                 const uint32_t ph = (uint32_t)((j >> 1) & 1);
                 const uint32_t s_addr = lane_addr + (uint32_t)(bf * kBlkN + hf * 32);
                 if (!mbar_wait(s_full(t, bf), ph, abort_flag, 630 + t)) { ok = false; break; }
-                if (MODE == 1) {
-                    if (!mbar_wait(m_full(t, bf), ph, abort_flag, 640 + t)) { ok = false; break; }
+                if (MODE == 1 && (j & (Cfg::kMaskChunk / kBlkN - 1)) == 0) {
+                    if (!mbar_wait(m_chunk(j / (Cfg::kMaskChunk / kBlkN)), 0u, abort_flag, 640 + t)) { ok = false; break; }
                 }
                 tc_fence_after();
                 uint32_t sr[32];
@@ -311,7 +329,7 @@ attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
 
                 const int col0 = j * kBlkN + hf * 32;
                 if (MODE == 1) {
-                    const float4* ms = reinterpret_cast<const float4*>(mask_smem + (t * NB + bf) * kBlkN + hf * 32);
+                    const float4* ms = reinterpret_cast<const float4*>(mask_smem + col0);
 #pragma unroll
                     for (int v4 = 0; v4 < 8; ++v4) {
                         const float4 a = ms[v4];
@@ -320,8 +338,6 @@ attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
                         sr[v4 * 4 + 2] = __float_as_uint(fmaf(__uint_as_float(sr[v4 * 4 + 2]), c, a.z));
                         sr[v4 * 4 + 3] = __float_as_uint(fmaf(__uint_as_float(sr[v4 * 4 + 3]), c, a.w));
                     }
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(m_empty(t, bf));
                 } else if (MODE == 2) {
                     if (p.mask == nullptr) {
 #pragma unroll
@@ -536,7 +552,7 @@ static int launch_attention_split_tm(const kb_attn_params& p, cudaStream_t strea
             ready = -1;
         } else {
             if (cudaFuncSetAttribute(attention_split_kernel<T, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     Cfg::kSmemBytes) != cudaSuccess)
+                                     Cfg::kSmemMax) != cudaSuccess)
                 return KB_ERR_LAUNCH;
             ready = 1;
         }
@@ -544,14 +560,16 @@ static int launch_attention_split_tm(const kb_attn_params& p, cudaStream_t strea
     if (ready < 0) return KB_ERR_UNSUPPORTED;
     const int64_t grid = (int64_t)d.num_pairs * p.B * p.H;
     if (grid > 0x7fffffff) return KB_ERR_UNSUPPORTED;
-    attention_split_kernel<T, MODE><<<(unsigned)grid, kSplitThreads, Cfg::kSmemBytes, stream>>>(tq, tk, tv, d);
+    const int num_n_blocks = (int)((p.N + kBlkN - 1) / kBlkN);
+    const size_t smem_bytes = (size_t)Cfg::kSmemBase + (MODE == 1 ? (size_t)num_n_blocks * kBlkN * 4 : 0);
+    attention_split_kernel<T, MODE><<<(unsigned)grid, kSplitThreads, smem_bytes, stream>>>(tq, tk, tv, d);
     return cudaGetLastError() == cudaSuccess ? KB_OK : KB_ERR_LAUNCH;
 }
 
 template <typename T>
 static int launch_attention_split_t(const kb_attn_params& p, cudaStream_t stream) {
     if (p.mask == nullptr && p.sm_scale > 0.f) return launch_attention_split_tm<T, 0>(p, stream);
-    if (p.mask != nullptr && p.mask_strides[2] == 0) return launch_attention_split_tm<T, 1>(p, stream);
+    if (p.mask != nullptr && p.mask_strides[2] == 0 && p.N <= AttnSplitCfg::kMaskMaxN) return launch_attention_split_tm<T, 1>(p, stream);
     return launch_attention_split_tm<T, 2>(p, stream);
 }
 

@@ -27,6 +27,37 @@
 namespace kb {
 
 constexpr int kSplitThreads = 640;
+
+// 2^x for a pair of x <= 0 on the FMA pipe (no special-function unit): x = r + f with r = round(x),
+// f in [-0.5, 0.5]; 2^f by a cubic (max relative error 7.5e-5, below the rounding of a 16-bit P);
+// 2^r by adding r to the exponent field. The magic constant 1.5 * 2^23 makes the fp32 adder do the
+// rounding and leaves r in the low mantissa bits of the sum. Inputs below -126 (masked keys are -inf)
+// are clamped and come out as 2^-126 * 2^f, which the 16-bit conversion flushes to zero.
+__device__ __forceinline__ float2 exp2_poly_pair(float2 x) {
+    x.x = fmaxf(x.x, -126.0f);
+    x.y = fmaxf(x.y, -126.0f);
+    const float2 fl = __fadd2_rn(x, make_float2(12582912.0f, 12582912.0f));
+    const float2 r = __fadd2_rn(fl, make_float2(-12582912.0f, -12582912.0f));
+    const float2 f = __ffma2_rn(r, make_float2(-1.0f, -1.0f), x);
+    float2 pl = __ffma2_rn(make_float2(0.05517137795686722f, 0.05517137795686722f), f,
+                           make_float2(0.24261121451854706f, 0.24261121451854706f));
+    pl = __ffma2_rn(pl, f, make_float2(0.6932610273361206f, 0.6932610273361206f));
+    pl = __ffma2_rn(pl, f, make_float2(0.9999280571937561f, 0.9999280571937561f));
+    float2 out;
+    out.x = __uint_as_float(__float_as_uint(pl.x) + (__float_as_uint(fl.x) << 23));
+    out.y = __uint_as_float(__float_as_uint(pl.y) + (__float_as_uint(fl.y) << 23));
+    return out;
+}
+// Which pairs of a block go to the FMA pipe: bit (i & 3) of this mask, i = pair index. The
+// special-function unit evaluates 16 exponentials per clock per SM, which at head dimension 64
+// is twice the time the tensor core needs for the same block, so moving some of them looked
+// promising; measured on B200 (B8 H12 S4096 fp16) it is not: 0/4 of the pairs 0.571 ms, 1/4 0.591,
+// 2/4 0.596, 3/4 0.669. The softmax warps are bound by their own dependent instruction stream, and
+// the polynomial adds eleven instructions per pair. Kept switchable, off by default.
+#ifndef KB_POLY_MASK
+#define KB_POLY_MASK 0x0u
+#endif
+constexpr unsigned kPolyPairMask = KB_POLY_MASK;
 // Launch allocation 65536 / 640 -> 96 registers per thread; the four softmax warpgroups grow to
 // kSplitRegsHigh and the fifth warpgroup (TMA, issuers, mask loader) shrinks to kSplitRegsLow.
 // The increase waits without bound until the CTA's pool has the registers, so the totals must fit.
@@ -433,8 +464,12 @@ attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
                 for (int i = 0; i < 16; ++i) {
                     const float2 a = __ffma2_rn(make_float2(__uint_as_float(sr[2 * i]), __uint_as_float(sr[2 * i + 1])), unit2, neg2);
                     float2 e;
-                    e.x = fast_exp2(a.x);
-                    e.y = fast_exp2(a.y);
+                    if ((kPolyPairMask >> (i & 3)) & 1u) {
+                        e = exp2_poly_pair(a);
+                    } else {
+                        e.x = fast_exp2(a.x);
+                        e.y = fast_exp2(a.y);
+                    }
                     lp[i & 1] = __fadd2_rn(lp[i & 1], e);
                     pk[i] = Elem<T>::pack2(e.x, e.y);
                 }

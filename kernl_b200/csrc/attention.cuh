@@ -53,7 +53,31 @@ struct AttnDev {
     int mask_dtype;
     int mask_vec;   // mask rows can be read with aligned 128-bit loads
     int num_pairs;  // ceil(ceil(M/128)/2)
+    int head_group; // heads whose CTAs are interleaved (see attn_work_item)
 };
+
+// CTA -> (batch*head, query-tile pair). Heads are taken in groups of p.head_group; inside a group
+// the order is pair-major with the late (causally heavier) pairs first, so the tail of a causal
+// launch is made of light tiles, and consecutive CTAs are different heads of the same group. The
+// group is sized on the host so that the K/V of all its heads (what the resident CTAs stream) stay
+// in L2: with one group over all heads, 148 resident CTAs of a long-sequence launch streamed the
+// K/V of 148 heads and DRAM read traffic was ten times the algorithmic bytes.
+__device__ __forceinline__ void attn_work_item(const AttnDev& p, int BH, int& bh, int& pair) {
+    const int per_group = p.num_pairs * p.head_group;
+    const int g = (int)(blockIdx.x / per_group);
+    const int rem = (int)(blockIdx.x % per_group);
+    const int first = g * p.head_group;
+    const int gsz = min(p.head_group, BH - first);
+    pair = p.num_pairs - 1 - rem / gsz;
+    bh = first + rem % gsz;
+}
+static int attn_head_group(int64_t BH, int64_t N, int64_t D) {
+    const int64_t kv_bytes = 2 * N * D * 2;
+    int64_t g = ((int64_t)32 << 20) / (kv_bytes > 0 ? kv_bytes : 1);
+    if (g < 1) g = 1;
+    if (g > BH) g = BH;
+    return (int)g;
+}
 
 template <int D>
 struct AttnCfg {
@@ -150,8 +174,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
 
     // Work assignment: heavy (late) query tiles first so that causal work is balanced.
     const int BH = p.B * p.H;
-    const int pair = p.num_pairs - 1 - (int)(blockIdx.x / BH);
-    const int bh = (int)(blockIdx.x % BH);
+    int bh, pair;
+    attn_work_item(p, BH, bh, pair);
     const int b = bh / p.H, h = bh % p.H;
     const int num_m_tiles = (p.M + kAttnBlock - 1) / kAttnBlock;
     const int num_n_blocks = (p.N + kAttnBlock - 1) / kAttnBlock;
@@ -603,6 +627,7 @@ static int launch_attention_tdm(const kb_attn_params& p, cudaStream_t stream) {
     }
     const int num_m_tiles = (int)((p.M + kAttnBlock - 1) / kAttnBlock);
     d.num_pairs = (num_m_tiles + 1) / 2;
+    d.head_group = attn_head_group(p.B * p.H, p.N, p.D);
 
     static bool attr_set = false;
     if (!attr_set) {

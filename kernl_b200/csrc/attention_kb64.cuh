@@ -82,8 +82,8 @@ attention_tc64_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     }
 
     const int BH = p.B * p.H;
-    const int pair = p.num_pairs - 1 - (int)(blockIdx.x / BH);  // heavy (late) tiles first
-    const int bh = (int)(blockIdx.x % BH);
+    int bh, pair;
+    attn_work_item(p, BH, bh, pair);
     const int b = bh / p.H, h = bh % p.H;
     const int num_m_tiles = (p.M + kAttnBlock - 1) / kAttnBlock;
     const int num_n_blocks = (p.N + kBlkN - 1) / kBlkN;
@@ -530,6 +530,7 @@ static int launch_attention64_tdm(const kb_attn_params& p, cudaStream_t stream) 
     }
     const int num_m_tiles = (int)((p.M + kAttnBlock - 1) / kAttnBlock);
     d.num_pairs = (num_m_tiles + 1) / 2;
+    d.head_group = attn_head_group(p.B * p.H, p.N, p.D);
     static bool attr_set = false;
     if (!attr_set) {
         if (cudaFuncSetAttribute(attention_tc64_kernel<T, D, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,

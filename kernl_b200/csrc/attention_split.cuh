@@ -133,8 +133,8 @@ attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     }
 
     const int BH = p.B * p.H;
-    const int pair = p.num_pairs - 1 - (int)(blockIdx.x / BH);  // heavy (late) tiles first
-    const int bh = (int)(blockIdx.x % BH);
+    int bh, pair;
+    attn_work_item(p, BH, bh, pair);
     const int b = bh / p.H, h = bh % p.H;
     const int num_m_tiles = (p.M + kAttnBlock - 1) / kAttnBlock;
     const int num_n_blocks = (p.N + kBlkN - 1) / kBlkN;
@@ -577,6 +577,7 @@ static int launch_attention_split_tm(const kb_attn_params& p, cudaStream_t strea
     }
     const int num_m_tiles = (int)((p.M + kAttnBlock - 1) / kAttnBlock);
     d.num_pairs = (num_m_tiles + 1) / 2;
+    d.head_group = attn_head_group(p.B * p.H, p.N, p.D);
     static int ready = 0;  // 0 = not checked, 1 = usable, -1 = register allocation does not fit
     if (ready == 0) {
         // setmaxnreg.inc blocks until the CTA's pool holds the registers: refuse to launch a build

@@ -58,6 +58,44 @@ __device__ __forceinline__ float2 exp2_poly_pair(float2 x) {
 #define KB_POLY_MASK 0x0u
 #endif
 constexpr unsigned kPolyPairMask = KB_POLY_MASK;
+// Key blocks of a MODE 1 launch whose mask is "minus infinity" for every key (the padding behind a
+// sequence) contribute exp(-65504 + ...) = 0 to every row and are skipped: not loaded, not multiplied,
+// not exponentiated. A block is skipped only if all of its mask values are below kSkipBelow (in the
+// log2 domain), far beyond where fp32 exp underflows for any score difference up to 2^14; if the
+// whole row is like that (a fully padded sequence, where the mask cancels and the reference
+// returns a plain softmax) nothing is skipped. At most 128 blocks (N <= 8192): a 128-bit set.
+constexpr float kSkipBelow = -30000.0f * 1.4426950408889634f;
+__device__ __forceinline__ int bits_next(const uint32_t (&w)[4], int from) {  // smallest set bit >= from
+    int r = 1 << 20;
+#pragma unroll
+    for (int wi = 3; wi >= 0; --wi) {
+        uint32_t m = w[wi];
+        const int lo = from - wi * 32;
+        if (lo >= 32) m = 0u;
+        else if (lo > 0) m &= 0xffffffffu << lo;
+        if (m != 0u) r = wi * 32 + __ffs((int)m) - 1;
+    }
+    return r;
+}
+__device__ __forceinline__ int bits_count_below(const uint32_t (&w)[4], int limit) {  // set bits with index < limit
+    int n = 0;
+#pragma unroll
+    for (int wi = 0; wi < 4; ++wi) {
+        const int hi = limit - wi * 32;
+        uint32_t m = w[wi];
+        if (hi <= 0) m = 0u;
+        else if (hi < 32) m &= (1u << hi) - 1u;
+        n += __popc(m);
+    }
+    return n;
+}
+__device__ __forceinline__ void tma_prefetch_l2_4d(const CUtensorMap* map, int c0, int c1, int c2, int c3) {
+    asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.tile [%0, {%1, %2, %3, %4}];" ::"l"(
+                     reinterpret_cast<uint64_t>(map)),
+                 "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+                 : "memory");
+}
+
 // Launch allocation 65536 / 640 -> 96 registers per thread; the four softmax warpgroups grow to
 // kSplitRegsHigh and the fifth warpgroup (TMA, issuers, mask loader) shrinks to kSplitRegsLow.
 // The increase waits without bound until the CTA's pool has the registers, so the totals must fit.
@@ -76,10 +114,9 @@ struct AttnSplitCfg {
     static constexpr int kBarBytes = 1024;
     static constexpr int kXchBytes = 2 * 2 * kAttnBlock * 8;  // [tile][half][row] (m, l)
     // MODE 1 keeps the whole row-broadcast mask of its (batch, head) in shared memory, as fp32 in the
-    // log2 domain, loaded once in chunks of 512 columns; longer rows take the general path (MODE 2)
-    static constexpr int kMaskChunk = 512;
+    // log2 domain, staged by all threads during set-up; longer rows take the general path (MODE 2)
     static constexpr int kMaskMaxN = 8192;
-    static constexpr int kMaskChunks = kMaskMaxN / kMaskChunk;
+    static constexpr int kMaskLoads = (kMaskMaxN + kSplitThreads - 1) / kSplitThreads;  // per thread
     static constexpr int kSmemBase = kTilesBytes + kBarBytes + kXchBytes + 1024;
     static constexpr int kSmemMax = kSmemBase + kMaskMaxN * 4;
 };
@@ -103,7 +140,7 @@ attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     const uint32_t v_smem = k_smem + KVS * KVB;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kTilesBytes);
     const uint32_t bar_base = smem_u32(bars);
-    // q_full[2] | o_final[2] | p_full, s_full, pv_done [2][2] each | ep[2][4] | m_chunk[16] |
+    // q_full[2] | o_final[2] | p_full, s_full, pv_done [2][2] each | ep[2][4] |
     // k_full, k_empty, v_full, v_empty [KVS] each
     auto q_full = [&](int t) { return bar_base + 8u * t; };
     auto o_final = [&](int t) { return bar_base + 8u * (2 + t); };
@@ -111,16 +148,16 @@ attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     auto s_full = [&](int t, int bf) { return bar_base + 8u * (8 + t * NB + bf); };
     auto pv_done = [&](int t, int bf) { return bar_base + 8u * (12 + t * NB + bf); };
     auto ep_bar = [&](int t, int q) { return bar_base + 8u * (16 + t * 4 + q); };
-    auto m_chunk = [&](int c) { return bar_base + 8u * (24 + c); };
-    constexpr int kKvBar = 24 + Cfg::kMaskChunks;
+    constexpr int kKvBar = 24;
     auto k_full = [&](int s) { return bar_base + 8u * (kKvBar + s); };
     auto k_empty = [&](int s) { return bar_base + 8u * (kKvBar + KVS + s); };
     auto v_full = [&](int s) { return bar_base + 8u * (kKvBar + 2 * KVS + s); };
     auto v_empty = [&](int s) { return bar_base + 8u * (kKvBar + 3 * KVS + s); };
     constexpr int kNumBars = kKvBar + 4 * KVS;
-    static_assert(kNumBars * 8 + 16 <= Cfg::kBarBytes, "barrier area too small");
+    static_assert(kNumBars * 8 + 32 <= Cfg::kBarBytes, "barrier area too small");
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBars);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    uint32_t* act_bits = tmem_slot + 4;  // MODE 1: which key blocks have at least one unmasked key
     float2* xch = reinterpret_cast<float2*>(smem + Cfg::kTilesBytes + Cfg::kBarBytes);
     float* mask_smem = reinterpret_cast<float*>(smem + Cfg::kTilesBytes + Cfg::kBarBytes + Cfg::kXchBytes);  // [N rounded up to 64]
 
@@ -128,6 +165,7 @@ attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     {
         __shared__ int s_skip;
         if (threadIdx.x == 0) s_skip = *reinterpret_cast<volatile int*>(&g_device_status[0]);
+        if (MODE == 1 && threadIdx.x < 4) act_bits[threadIdx.x] = 0u;
         __syncthreads();
         if (s_skip != 0) return;
     }
@@ -155,7 +193,9 @@ attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     // the TMA warp initialises the barriers its loads complete on and issues both Q tiles and the
     // first ring of K/V blocks at once; warp 0 initialises the other barriers, one per lane; warp 17
     // allocates TMEM. Everybody else meets them at the barrier below.
-    const int first_kv = min(KVS, max_blk);
+    // MODE 1 does not know which key blocks it will visit before the mask has been looked at: it
+    // only pulls the first ring of K/V blocks into L2 and issues the real loads after the set-up barrier.
+    const int first_kv = (MODE == 1) ? 0 : min(KVS, max_blk);
     if (warp == 16) {
         if (lane == 0) {
             tma_prefetch_desc(&tmap_q);
@@ -172,6 +212,12 @@ attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
             for (int t = 0; t < ntl; ++t) {
                 mbar_arrive_expect_tx(q_full(t), QTILE);
                 tma_load_4d(q_smem + t * QTILE, &tmap_q, q_full(t), 0, mt[t] * kAttnBlock, h, b);
+                if (MODE == 1 && t == 0) {
+                    for (int j = 0; j < min(KVS, max_blk); ++j) {
+                        tma_prefetch_l2_4d(&tmap_k, 0, j * kBlkN, h, b);
+                        tma_prefetch_l2_4d(&tmap_v, 0, j * kBlkN, h, b);
+                    }
+                }
                 if (t == 0 && first_kv > 0) {  // K_0 right behind the first Q tile: the first Q·Kᵀ needs just these two
                     mbar_arrive_expect_tx(k_full(0), KVB);
                     tma_load_4d(k_smem, &tmap_k, k_full(0), 0, 0, h, b);
@@ -194,17 +240,56 @@ attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
             mbar_init(pv_done(lane >> 1, lane & 1), 1);
         }
         if (lane < 8) mbar_init(ep_bar(lane >> 2, lane & 3), 2);
-        if (lane < Cfg::kMaskChunks) mbar_init(m_chunk(lane), 1);
         if (lane == 0) *abort_flag = 0;
         fence_mbar_init();
     } else if (warp == 17) {
         tmem_alloc(smem_u32(tmem_slot), kTmemCols);
         tmem_relinquish();
     }
+    if (MODE == 1) {
+        // every thread stages its share of the mask row: clamped, in the log2 domain, -inf beyond N
+        const float mlow = mask_lowest(p.mask_dtype);
+        const int64_t moff = (int64_t)b * p.mask_strides[0] + (int64_t)h * p.mask_strides[1];
+        const int ncols = max_blk * kBlkN;
+        float vals[Cfg::kMaskLoads];
+#pragma unroll
+        for (int e = 0; e < Cfg::kMaskLoads; ++e) {
+            const int col = e * kSplitThreads + (int)threadIdx.x;
+            vals[e] = (col < p.N && col < ncols) ? mask_load(p.mask, moff + (int64_t)col * p.mask_strides[3], p.mask_dtype) : -INFINITY;
+        }
+#pragma unroll
+        for (int e = 0; e < Cfg::kMaskLoads; ++e) {
+            const int col = e * kSplitThreads + (int)threadIdx.x;  // a warp covers half of one key block
+            if (e * kSplitThreads < ncols) {
+                const bool inside = col < p.N && col < ncols;
+                const float v = inside ? fmaxf(vals[e], mlow) * kLog2e : -INFINITY;
+                if (col < ncols) mask_smem[col] = v;
+                const bool live = __any_sync(0xffffffffu, inside && v > kSkipBelow);
+                if (live && lane == 0) atomicOr(&act_bits[col >> 11], 1u << ((col >> 6) & 31));
+            }
+        }
+    }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // the key blocks this CTA visits: all of them, or (MODE 1) those with an unmasked key
+    uint32_t act[4] = {0u, 0u, 0u, 0u};
+    int n_union = max_blk, n_tile[2] = {nblk[0], nblk[1]};
+    if (MODE == 1) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) act[i] = act_bits[i];
+        // Causal rows see a prefix of the keys, which may consist of masked keys only even when the
+        // row as a whole has live ones: no skipping then.
+        if ((act[0] | act[1] | act[2] | act[3]) == 0u || p.is_causal) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) act[i] = 0xffffffffu;
+        }
+        n_union = bits_count_below(act, max_blk);
+        n_tile[0] = bits_count_below(act, nblk[0]);
+        n_tile[1] = bits_count_below(act, nblk[1]);
+    }
+    auto next_blk = [&](int from) { return MODE == 1 ? bits_next(act, from) : from; };
 
     if (warp >= 16) {
       asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kSplitRegsLow));
@@ -212,15 +297,17 @@ attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
         // ------------------------------------------------------------------ TMA producer
         if (elect_one()) {
             bool ok = true;
-            for (int j = first_kv; j < max_blk && ok; ++j) {  // the first ring was issued during set-up
-                const int s = j % KVS;
-                const uint32_t ph = (uint32_t)((j / KVS) & 1);
+            int jb = next_blk(first_kv);
+            for (int i = first_kv; i < n_union && ok; ++i) {  // (MODE 0/2: the first ring was issued during set-up)
+                const int s = i % KVS;
+                const uint32_t ph = (uint32_t)((i / KVS) & 1);
                 if (!mbar_wait(k_empty(s), ph ^ 1, abort_flag, 600)) { ok = false; break; }
                 mbar_arrive_expect_tx(k_full(s), KVB);
-                tma_load_4d(k_smem + s * KVB, &tmap_k, k_full(s), 0, j * kBlkN, h, b);
+                tma_load_4d(k_smem + s * KVB, &tmap_k, k_full(s), 0, jb * kBlkN, h, b);
                 if (!mbar_wait(v_empty(s), ph ^ 1, abort_flag, 601)) { ok = false; break; }
                 mbar_arrive_expect_tx(v_full(s), KVB);
-                tma_load_4d(v_smem + s * KVB, &tmap_v, v_full(s), 0, j * kBlkN, h, b);
+                tma_load_4d(v_smem + s * KVB, &tmap_v, v_full(s), 0, jb * kBlkN, h, b);
+                jb = next_blk(jb + 1);
             }
             if (!ok) {
                 for (int i = 0; i < 64; ++i) __nanosleep(2000);
@@ -258,7 +345,10 @@ attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
                     }
                 }
             };
-            const int my_blk = (t < ntl) ? nblk[t] : 0;
+            // j below counts visited blocks (ring positions), not key-block numbers; a tile's blocks are
+            // a prefix of the CTA's visit list (causal tiles stop early)
+            const int my_blk = (t < ntl) ? n_tile[t] : 0;
+            const int max_blk = n_union;
             bool ok = true;
             if (t < ntl && !mbar_wait(q_full(t), 0, abort_flag, 610)) ok = false;
             for (int jj = 0; jj < NB && jj < max_blk && ok && t < ntl; ++jj) {
@@ -300,28 +390,6 @@ attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
                 }
             }
         }
-      } else if (MODE == 1 && warp == 19) {
-        // ------------------------------------------------------------------ mask loader
-        // The whole mask row of this (batch, head), clamped, in the log2 domain, -inf beyond N; one
-        // barrier per chunk of 512 columns so that the first key blocks do not wait for the last.
-        const float mlow = mask_lowest(p.mask_dtype);
-        const int64_t moff = (int64_t)b * p.mask_strides[0] + (int64_t)h * p.mask_strides[1];
-        const int ncols = max_blk * kBlkN;
-        for (int c0 = 0; c0 < ncols; c0 += Cfg::kMaskChunk) {
-            float vals[Cfg::kMaskChunk / 32];
-#pragma unroll
-            for (int e = 0; e < Cfg::kMaskChunk / 32; ++e) {
-                const int col = c0 + e * 32 + lane;
-                vals[e] = (col < p.N) ? mask_load(p.mask, moff + (int64_t)col * p.mask_strides[3], p.mask_dtype) : -INFINITY;
-            }
-#pragma unroll
-            for (int e = 0; e < Cfg::kMaskChunk / 32; ++e) {
-                const int col = c0 + e * 32 + lane;
-                if (col < ncols) mask_smem[col] = (col < p.N) ? fmaxf(vals[e], mlow) * kLog2e : -INFINITY;
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(m_chunk(c0 / Cfg::kMaskChunk));
-        }
       }
     } else {
         asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kSplitRegsHigh));
@@ -330,7 +398,7 @@ attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
         const int hf = (warp >> 2) & 1;  // which 32 key columns of every block
         const int q = warp & 3;          // TMEM lane quarter = 32 query rows
         if (t < ntl && nblk[t] > 0) {
-            const int nb = nblk[t];
+            const int nb = n_tile[t];
             const int r_in_tile = q * 32 + lane;
             const int row = mt[t] * kAttnBlock + r_in_tile;
             const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(t * 256);
@@ -345,20 +413,18 @@ attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
             float m_ref = -INFINITY;
             float l = 0.f;
             bool ok = true;
-            for (int j = 0; j < nb; ++j) {
+            int jb = next_blk(0);  // key-block number of visit j
+            for (int j = 0; j < nb; ++j, jb = next_blk(jb + 1)) {
                 const int bf = j & 1;
                 const uint32_t ph = (uint32_t)((j >> 1) & 1);
                 const uint32_t s_addr = lane_addr + (uint32_t)(bf * kBlkN + hf * 32);
                 if (!mbar_wait(s_full(t, bf), ph, abort_flag, 630 + t)) { ok = false; break; }
-                if (MODE == 1 && (j & (Cfg::kMaskChunk / kBlkN - 1)) == 0) {
-                    if (!mbar_wait(m_chunk(j / (Cfg::kMaskChunk / kBlkN)), 0u, abort_flag, 640 + t)) { ok = false; break; }
-                }
                 tc_fence_after();
                 uint32_t sr[32];
                 tmem_ld_32x32(s_addr, sr);
                 tmem_ld_wait();
 
-                const int col0 = j * kBlkN + hf * 32;
+                const int col0 = jb * kBlkN + hf * 32;
                 if (MODE == 1) {
                     const float4* ms = reinterpret_cast<const float4*>(mask_smem + col0);
 #pragma unroll

@@ -103,6 +103,32 @@ def test_attention_both_kernels(lib, variant, d, dtype, tol, mask_kind, causal, 
     O.assert_parity(out, expected, max_abs=tol, what=f"variant {variant} d={d}")
 
 
+@pytest.mark.parametrize("fill", [float("-inf"), -65504.0, -10000.0], ids=["neg_inf", "fp16_lowest", "minus_1e4"])
+@pytest.mark.parametrize("causal", [False, True], ids=["full", "causal"])
+def test_attention_padding_mask_with_fully_masked_key_blocks(lib, fill, causal):
+    """Row-broadcast masks that blank out whole 64-key blocks: the head-dimension-64 kernel does not
+    visit such blocks. Right padding, left padding, a hole in the middle, a single live key, and one
+    fully masked sequence (where nothing may be skipped) in one batch."""
+    from kernl_b200.implementations.attention import attention_forward
+
+    g = torch.Generator().manual_seed(5)
+    B, H, S, D = 6, 2, 448, 64
+    q, k, v = (torch.randn((B, H, S, D), generator=g).half() for _ in range(3))
+    mask = torch.zeros((B, 1, 1, S))
+    mask[0, ..., 200:] = fill          # right padding: blocks 4..6 blank
+    mask[1, ..., :130] = fill          # left padding: blocks 0..1 blank
+    mask[2, ..., 64:320] = fill        # hole: blocks 1..4 blank
+    mask[3, ..., :] = fill
+    mask[3, ..., 257] = 0.0            # one live key
+    mask[4, ..., :] = fill             # fully masked sequence
+    mask = mask.half()
+    expected = O.attention(q, k, v, 0.125, causal, mask)
+    qc, kc, vc, mc = _cuda(q, k, v, mask)
+    out = attention_forward(qc, kc, vc, torch.empty_like(qc), 0.125, causal, mc)
+    assert torch.isfinite(out).all()
+    O.assert_parity(out, expected, max_abs=2e-2 if fill != -10000.0 else 1e-2, cos=0.999)
+
+
 def test_attention_fp32_mask_and_row_broadcast(lib):
     out, expected = _run_attention(2, 4, 200, 200, 64, torch.float16, False, "pad", 0.125, mask_dtype=torch.float32)
     O.assert_parity(out, expected)

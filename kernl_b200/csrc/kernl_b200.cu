@@ -7,6 +7,7 @@
 #include "common.cuh"
 #include "norm.cuh"
 #include "linear.cuh"
+#include "linear_smallm.cuh"
 #include "attention.cuh"
 #include "attention_kb64.cuh"
 #include "attention_split.cuh"
@@ -155,6 +156,9 @@ int kb_linear_fwd(const kb_linear_params* p, void* stream) {
     if (p->M > 0x7fffffff || p->N > 0x7fffffff || p->K > 0x7fffffff) return KB_ERR_UNSUPPORTED;
     int st = check_device();
     if (st != KB_OK) return st;
+    // a handful of rows: one pass over W, no tensor map / TMEM / split-K finish (unless a test forces
+    // a tile shape or a split count of the GEMM kernel)
+    if (g_forced_bn == 0 && g_forced_splits == 0 && smallm_applicable(*p)) return launch_linear_smallm(*p, (cudaStream_t)stream);
     return launch_linear(*p, (cudaStream_t)stream, g_forced_bn, g_forced_splits);
 }
 

@@ -352,6 +352,29 @@ def test_linear_every_tile_width(lib):
         lib.kb_debug_force_bn(0)
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16], ids=["fp16", "bf16"])
+@pytest.mark.parametrize("shape", [(1, 4096, 4096), (5, 520, 1000), (8, 11008, 4096), (9, 264, 17), (16, 8, 40), (13, 4096, 12288)], ids=str)
+def test_linear_few_rows(lib, shape, dtype):
+    """M <= 16 goes to the weight-streaming kernel: ragged N, K tails that are not a multiple of 32,
+    a row-strided x, the pre-activation side output, and an output written into a strided view."""
+    from kernl_b200.implementations.linear_layer import linear_layer
+
+    M, K, N = shape
+    g = torch.Generator().manual_seed(2)
+    xfull = torch.randn((M, K + 24), generator=g).to(dtype)
+    w = (torch.randn((N, K), generator=g) * 0.02).to(dtype)
+    b = (torch.randn((N,), generator=g) * 0.02).to(dtype)
+    x = xfull[:, 8:8 + K]  # row stride K + 24, 16-byte aligned start
+    tol = 1e-2 if dtype == torch.float16 else 4e-2
+    xc, wc, bc = _cuda(xfull, w, b)
+    xv = xc[:, 8:8 + K]
+    pre = torch.empty((M, N), dtype=dtype, device="cuda")
+    out = linear_layer(xv, wc, bc, "gelu", act_inputs=pre)
+    O.assert_parity(out, O.linear(x, w, b, "gelu"), max_abs=tol)
+    O.assert_parity(pre, O.linear(x, w, b, ""), max_abs=tol)
+    O.assert_parity(linear_layer(xv, wc, None, ""), O.linear(x, w, None, ""), max_abs=tol)
+
+
 @pytest.mark.parametrize("shape", [(16, 768, 768), (128, 3072, 768), (40, 4096, 1000), (8, 11008, 4096), (300, 520, 392)], ids=str)
 @pytest.mark.parametrize("splits", [0, 2, 5])
 def test_linear_split_k(lib, shape, splits):

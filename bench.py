@@ -647,6 +647,70 @@ def run_bert(args):
         dist.destroy_process_group()
 
 
+def run_t5(args):
+    """Baseline config 4: T5-base-shaped encoder-decoder, random init (seed 0), batch B (default 1),
+    encoder input 512 uniform-random ids, greedy decode of 128 tokens with the static KV cache under
+    one CUDA graph, fp16. Value = latency of encode + 128 decode steps; with --gpus N each rank runs
+    its own replica on its own batch (batch-sharded, no collective)."""
+    import torch
+    from transformers import T5Config, T5ForConditionalGeneration
+
+    from kernl_b200 import _lib
+    from kernl_b200.t5_generate import T5Kernl
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    dev = torch.device("cuda", local_rank)
+    torch.manual_seed(0)
+    cfg = T5Config(d_model=768, d_ff=3072, num_layers=12, num_decoder_layers=12, num_heads=12, d_kv=64, vocab_size=32128,
+                   feed_forward_proj="relu", relative_attention_num_buckets=32, decoder_start_token_id=0, pad_token_id=0,
+                   eos_token_id=1)
+    model = T5ForConditionalGeneration(cfg).eval()
+    B, S, T = args.t5_batch, 512, 128
+    ids = torch.randint(2, 32128, (B, S), generator=torch.Generator().manual_seed(rank)).to(dev)
+    runner = T5Kernl(model, device=dev, dtype=torch.float16, max_new_tokens=T)
+    del model
+    steps, warmup = max(1, min(args.steps, 10)), 1
+    with torch.inference_mode():
+        for _ in range(warmup):
+            toks = runner.generate(ids, T, use_cuda_graph=True)
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            toks = runner.generate(ids, T, use_cuda_graph=True)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+    _lib.device_status()
+    if dist is not None:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    if rank == 0:
+        print(json.dumps({
+            "metric": "T5-base generate latency (encode 512 + 128 greedy tokens)", "value": ms, "unit": "ms", "n_gpus": world,
+            "steps": steps, "warmup": warmup, "ms_per_step": ms, "higher_is_better": False, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": f"T5-base shape, random init seed 0, batch {B} per GPU, encoder 512 ids, 128 greedy decode "
+                                   "steps with static KV cache, one CUDA graph per decode step (baseline config 4)",
+                       "parallelism": f"replicas x{world}", "tokens_per_s_all_gpus": world * B * T / (ms * 1e-3),
+                       "includes": "encoder, cross K/V projection, 128 graph replays; the decode graph is captured once (warm-up)",
+                       "tokens_sample": toks[0, :8].tolist()}}), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
 def run_llama(args):
     """Baseline config 5: Llama-2-7B-shaped decoder, random init bf16, prefill 8 x 2048 then greedy
     decode with KV cache; tensor parallel over the ranks of this job (NCCL all-reduce after o_proj
@@ -748,8 +812,9 @@ def main():
     ap.add_argument("--case", default=None, help="with --sweep: only cases whose name contains this")
     ap.add_argument("--attn-variant", type=int, default=0, help="with --sweep: fused-attention kernel, 0 = dispatcher's choice, "
                     "1 = 128-key blocks, 2 = 64-key blocks")
-    ap.add_argument("--workload", choices=["attention", "bert", "llama"], default="attention",
+    ap.add_argument("--workload", choices=["attention", "bert", "llama", "t5"], default="attention",
                     help="attention = headline (default); bert / llama = the model configs")
+    ap.add_argument("--t5-batch", type=int, default=1, help="t5 workload: sequences per GPU")
     ap.add_argument("--layers", type=int, default=32, help="llama workload: number of layers")
     ap.add_argument("--comm", choices=["nccl", "peer"], default="peer",
                     help="llama workload, N > 1: all-reduce through NCCL only, or the fused peer-memory kernel for decode-size messages")
@@ -758,6 +823,8 @@ def main():
     if args.workload == "bert":
         run_bert(args)
         return
+    if args.workload == "t5":
+        return run_t5(args)
     if args.workload == "llama":
         run_llama(args)
         return

@@ -48,3 +48,23 @@ def test_t5_generate_matches_hf_fp32(lib, use_graph):
     toks = runner.generate(ids.cuda(), steps, use_cuda_graph=use_graph).cpu()
     agree = (toks == torch.stack(ref_tokens, dim=1)).float().mean().item()
     assert agree >= 0.8, f"greedy tokens agree on {agree:.0%} of positions"
+
+
+def test_t5_generate_reuses_its_graph_across_requests(lib):
+    """A second request of the same shape reuses the buffers and the captured decode graph; its
+    tokens must equal those of a fresh runner that decodes the same input eagerly."""
+    from kernl_b200.t5_generate import T5Kernl
+
+    model = _small_t5()
+    g = torch.Generator().manual_seed(3)
+    ids_a = torch.randint(2, 1000, (2, 70), generator=g).cuda()
+    ids_b = torch.randint(2, 1000, (2, 70), generator=g).cuda()
+    runner = T5Kernl(model, device="cuda", dtype=torch.float16, max_new_tokens=12)
+    first = runner.generate(ids_a, 12, use_cuda_graph=True)
+    graph_obj = runner._graph[0]
+    second = runner.generate(ids_b, 12, use_cuda_graph=True)
+    assert runner._graph[0] is graph_obj
+    again = runner.generate(ids_a, 12, use_cuda_graph=True)
+    assert torch.equal(first, again)
+    eager = T5Kernl(model, device="cuda", dtype=torch.float16, max_new_tokens=12).generate(ids_b, 12, use_cuda_graph=False)
+    assert (second == eager).float().mean().item() >= 0.9

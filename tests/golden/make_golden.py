@@ -1,7 +1,6 @@
 """Generates tests/golden/*.npz from the reference's own eager functions.
 
-Run in a container that has the reference tree (default /root/reference, override with
-KERNL_REFERENCE_ROOT): it imports `attention_reference`, `pytorch_naive_layernorm` and
+Run where the reference tree is checked out and point KERNL_REFERENCE_ROOT at it: it imports `attention_reference`, `pytorch_naive_layernorm` and
 `pytorch_naive_rmsnorm` from the reference's sources, evaluates them on seeded CPU inputs and
 stores inputs and outputs. The fixtures are small (a few hundred KB in total) and committed; the
 tests only read the .npz files, never the reference tree.
@@ -17,7 +16,7 @@ import sys
 import numpy as np
 import torch
 
-REF_ROOT = os.environ.get("KERNL_REFERENCE_ROOT", "/root/reference")
+REF_ROOT = os.environ.get("KERNL_REFERENCE_ROOT", os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "..", "..", "reference"))
 sys.path.insert(0, os.path.join(REF_ROOT, "src"))
 HERE = os.path.dirname(os.path.abspath(__file__))
 

@@ -10,7 +10,7 @@ from kernl_b200.optimizer.attention import (
 )
 from kernl_b200.optimizer.dropout import remove_dropout
 from kernl_b200.optimizer.layer_norm import replace_layer_norm, replace_layer_norm_rms
-from kernl_b200.optimizer.linear import replace_all_linear
+from kernl_b200.optimizer.linear import fuse_parallel_linears, replace_all_linear
 from kernl_b200.optimizer.normalizer import normalize_operators, replace_scalar_tensor_constants
 
 
@@ -27,6 +27,7 @@ def dynamo_backend_ofi(gm: torch.fx.GraphModule, assume_causal=False):
     fuse_attention_pattern_3(gm, assume_causal)
     fuse_attention_sdpa(gm, assume_causal)
     replace_all_linear(gm)
+    fuse_parallel_linears(gm)
     replace_layer_norm(gm)
     replace_layer_norm_rms(gm)
     return gm

@@ -140,7 +140,7 @@ def test_bert_graph_is_fully_rewritten():
     model = BertModel(BertConfig(num_hidden_layers=2)).eval()
     c = _rewritten_ops(model, input_ids=torch.randint(0, 1000, (1, 16)), attention_mask=torch.ones(1, 16, dtype=torch.long))
     assert c["attention_wrapper"] == 2
-    assert c["linear_wrapper"] == 2 * 6 + 1  # q, k, v, o, ffn up (+GELU), ffn down per layer; pooler (+tanh)
+    assert c["linear_wrapper"] == 2 * 4 + 1  # qkv (one stacked linear), o, ffn up (+GELU), ffn down per layer; pooler (+tanh)
     assert c["layer_norm_wrapper"] == 1 + 2 * 2
     assert c["module:Linear"] == 0 and c["module:LayerNorm"] == 0 and c["module:Dropout"] == 0
     assert c["scaled_dot_product_attention"] == 0 and c["gelu"] == 0
@@ -153,7 +153,7 @@ def test_t5_encoder_graph_is_fully_rewritten():
     model = T5EncoderModel(cfg).eval()
     c = _rewritten_ops(model, input_ids=torch.randint(0, 1000, (1, 16)))
     assert c["attention_wrapper"] == 2
-    assert c["linear_wrapper"] == 2 * 6
+    assert c["linear_wrapper"] == 2 * 4  # q, k, v are one stacked linear
     assert c["layer_norm_rms_wrapper"] == 2 * 2 + 1
     assert c["softmax"] == 0 and c["matmul"] == 0 and c["module:Linear"] == 0 and c["rsqrt"] == 0
 

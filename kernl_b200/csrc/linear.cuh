@@ -442,9 +442,19 @@ static LinearPlan plan_linear(int64_t M, int64_t N, int64_t K, bool has_ws, int 
             const int eff = (num_k + kps - 1) / kps;  // splits that are not empty
             if (eff != s) continue;
             const int64_t waves = (tiles * s + sms - 1) / sms;
-            // a split tile pays an extra pass over its outputs (atomics, then the finishing kernel)
-            const double extra = (s > 1) ? 3.0 : 0.0;
-            const double cost = (double)waves * ((double)kps + 2.0 + extra) * (double)(kGemmBM + bn);
+            double cost = (double)waves * ((double)kps + 2.0) * (double)(kGemmBM + bn);
+            if (s > 1) {
+                // Splitting K is not free: every split adds its tile into the fp32 workspace with
+                // atomics (8 bytes of traffic per output element and split) and a second kernel reads
+                // the sums back, applies the epilogue and clears the workspace. Measured on B200: about
+                // 2.6 µs for the extra launch plus the traffic at ~2 TB/s, against ~0.13 µs per k-block of
+                // a 128x32 tile (0.0008 µs per cost unit). With the earlier, far smaller penalty the
+                // heuristic split [512,768]x[3072,768] (25 µs instead of 10) and [128,4096]x[11008,4096]
+                // (33 µs instead of 21).
+                const double mn = (double)M * (double)N;
+                const double extra_us = 2.6 + (double)s * mn * 8.0 / 2.0e6 + mn * 6.0 / 3.0e6;
+                cost += extra_us / 0.0008;
+            }
             if (cost < best_cost) {
                 best_cost = cost;
                 best = LinearPlan{bn, s, kps};

@@ -814,12 +814,18 @@ def main():
                     "1 = 128-key blocks, 2 = 64-key blocks")
     ap.add_argument("--workload", choices=["attention", "bert", "llama", "t5"], default="attention",
                     help="attention = headline (default); bert / llama = the model configs")
+    ap.add_argument("--no-pdl", action="store_true", help="model workloads: launch the light kernels without programmatic "
+                    "dependent launch (A/B timing)")
     ap.add_argument("--t5-batch", type=int, default=1, help="t5 workload: sequences per GPU")
     ap.add_argument("--layers", type=int, default=32, help="llama workload: number of layers")
     ap.add_argument("--comm", choices=["nccl", "peer"], default="peer",
                     help="llama workload, N > 1: all-reduce through NCCL only, or the fused peer-memory kernel for decode-size messages")
     ap.add_argument("--decode-steps", type=int, default=256, help="llama workload: greedy decode steps")
     args = ap.parse_args()
+    if args.no_pdl:
+        from kernl_b200 import _lib as _kb_lib
+
+        _kb_lib.load().kb_debug_pdl(0)
     if args.workload == "bert":
         run_bert(args)
         return

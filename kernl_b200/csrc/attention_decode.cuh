@@ -45,6 +45,8 @@ static int64_t decode_scratch_bytes(int64_t B, int64_t H, int64_t M, int64_t N, 
 template <typename T>
 __global__ void __launch_bounds__(kDecThreads)
 attn_decode_part1_kernel(const DecDev p) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float q_s[kDecMaxD];
     __shared__ float sc_s[kDecThreads];
     __shared__ float red_s[kDecThreads / 32];
@@ -153,6 +155,8 @@ attn_decode_part1_kernel(const DecDev p) {
 template <typename T, int LPK>
 __global__ void __launch_bounds__(kDecThreads)
 attn_decode_part1_vec_kernel(const DecDev p) {
+    pdl_launch_dependents();
+    pdl_wait();
     constexpr int D = LPK * 8;
     constexpr int KPW = 32 / LPK;                 // keys per warp per step
     constexpr int KPS = KPW * (kDecThreads / 32);  // keys per CTA per step
@@ -279,6 +283,8 @@ attn_decode_part1_vec_kernel(const DecDev p) {
 template <typename T>
 __global__ void __launch_bounds__(kDecThreads)
 attn_decode_part2_kernel(const DecDev p) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int row = blockIdx.x, bh = blockIdx.y;
     const int b = bh / p.H, h = bh % p.H;
     const int D = p.D;
@@ -327,17 +333,17 @@ static int launch_attention_decode(const kb_attn_params& p, void* scratch, int64
                         (p.k_strides[1] % 8) == 0 && (p.v_strides[1] % 8) == 0 && (p.k_strides[0] % 8) == 0 &&
                         (p.v_strides[0] % 8) == 0 && (((uintptr_t)p.k) & 15) == 0 && (((uintptr_t)p.v) & 15) == 0;
     if (p.dtype == KB_F16) {
-        if (vec_ok && p.D == 64) attn_decode_part1_vec_kernel<__half, 8><<<g1, kDecThreads, 0, stream>>>(d);
-        else if (vec_ok && p.D == 128) attn_decode_part1_vec_kernel<__half, 16><<<g1, kDecThreads, 0, stream>>>(d);
-        else if (vec_ok && p.D == 256) attn_decode_part1_vec_kernel<__half, 32><<<g1, kDecThreads, 0, stream>>>(d);
-        else attn_decode_part1_kernel<__half><<<g1, kDecThreads, 0, stream>>>(d);
-        attn_decode_part2_kernel<__half><<<g2, kDecThreads, 0, stream>>>(d);
+        if (vec_ok && p.D == 64) launch_pdl(attn_decode_part1_vec_kernel<__half, 8>, g1, kDecThreads, 0, stream, d);
+        else if (vec_ok && p.D == 128) launch_pdl(attn_decode_part1_vec_kernel<__half, 16>, g1, kDecThreads, 0, stream, d);
+        else if (vec_ok && p.D == 256) launch_pdl(attn_decode_part1_vec_kernel<__half, 32>, g1, kDecThreads, 0, stream, d);
+        else launch_pdl(attn_decode_part1_kernel<__half>, g1, kDecThreads, 0, stream, d);
+        launch_pdl(attn_decode_part2_kernel<__half>, g2, kDecThreads, 0, stream, d);
     } else {
-        if (vec_ok && p.D == 64) attn_decode_part1_vec_kernel<__nv_bfloat16, 8><<<g1, kDecThreads, 0, stream>>>(d);
-        else if (vec_ok && p.D == 128) attn_decode_part1_vec_kernel<__nv_bfloat16, 16><<<g1, kDecThreads, 0, stream>>>(d);
-        else if (vec_ok && p.D == 256) attn_decode_part1_vec_kernel<__nv_bfloat16, 32><<<g1, kDecThreads, 0, stream>>>(d);
-        else attn_decode_part1_kernel<__nv_bfloat16><<<g1, kDecThreads, 0, stream>>>(d);
-        attn_decode_part2_kernel<__nv_bfloat16><<<g2, kDecThreads, 0, stream>>>(d);
+        if (vec_ok && p.D == 64) launch_pdl(attn_decode_part1_vec_kernel<__nv_bfloat16, 8>, g1, kDecThreads, 0, stream, d);
+        else if (vec_ok && p.D == 128) launch_pdl(attn_decode_part1_vec_kernel<__nv_bfloat16, 16>, g1, kDecThreads, 0, stream, d);
+        else if (vec_ok && p.D == 256) launch_pdl(attn_decode_part1_vec_kernel<__nv_bfloat16, 32>, g1, kDecThreads, 0, stream, d);
+        else launch_pdl(attn_decode_part1_kernel<__nv_bfloat16>, g1, kDecThreads, 0, stream, d);
+        launch_pdl(attn_decode_part2_kernel<__nv_bfloat16>, g2, kDecThreads, 0, stream, d);
     }
     return cudaGetLastError() == cudaSuccess ? KB_OK : KB_ERR_LAUNCH;
 }

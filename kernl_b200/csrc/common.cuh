@@ -103,6 +103,38 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 }
 
 // ---------------------------------------------------------------------------------------------
+// Programmatic dependent launch. The light kernels of a decode step (few-row linear, norms, rotary,
+// gate, decode attention) run for a few microseconds each, and between two of them the GPU idles for
+// about as long: launch latency, ramp-up, tail. A kernel launched with launch_pdl() may start as
+// soon as every CTA of its predecessor has called pdl_launch_dependents() (they do so first thing);
+// it sets itself up — and may prefetch what does not depend on the predecessor, e.g. weights — and
+// then blocks in pdl_wait() until the predecessor has completed and its writes are visible.
+// Rules every such kernel keeps: no global write and no read of a predecessor's output before
+// pdl_wait(). Launched without the attribute (or after a kernel that never triggers) both calls
+// are no-ops, so the same kernels work in any stream order and next to foreign kernels.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+static int g_use_pdl = 1;  // kb_debug_pdl() switches it off for A/B timing
+
+template <typename... KArgs, typename... Args>
+static cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_use_pdl ? 1u : 0u;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+// ---------------------------------------------------------------------------------------------
 // TMA tiled loads (no multicast anywhere in this library). The innermost coordinate times the
 // element size must be a multiple of 16 bytes; callers only pass multiples of 8 (16-bit types).
 // ---------------------------------------------------------------------------------------------

@@ -143,6 +143,8 @@ int kb_norm_fwd(const kb_norm_params* p, void* stream) {
 void kb_debug_force_bn(int bn) { g_forced_bn = bn; }
 // Test hook: choose the fused-attention kernel (0 = by head dimension, 1 = 128-key blocks, 2 = 64-key blocks).
 void kb_debug_attention_variant(int v) { g_attn_variant = v; }
+// Test / measurement hook: 0 launches the light kernels without programmatic dependent launch.
+void kb_debug_pdl(int on) { g_use_pdl = on ? 1 : 0; }
 // Test hook: force the number of K splits (0 = heuristic; needs a workspace).
 void kb_debug_force_splits(int splits) { g_forced_splits = splits; }
 
@@ -178,10 +180,10 @@ int kb_silu_mul(const void* gu, void* y, int64_t M, int64_t N, int32_t dtype, vo
     int64_t blocks = (total + threads - 1) / threads;
     if (blocks > (int64_t)sm_count() * 16) blocks = (int64_t)sm_count() * 16;
     if (dtype == KB_F16)
-        silu_mul_kernel<__half><<<(unsigned)blocks, threads, 0, (cudaStream_t)stream>>>((const __half*)gu, (__half*)y, M, N);
+        launch_pdl(silu_mul_kernel<__half>, (unsigned)blocks, threads, 0, (cudaStream_t)stream, (const __half*)gu, (__half*)y, M, N);
     else if (dtype == KB_BF16)
-        silu_mul_kernel<__nv_bfloat16><<<(unsigned)blocks, threads, 0, (cudaStream_t)stream>>>(
-            (const __nv_bfloat16*)gu, (__nv_bfloat16*)y, M, N);
+        launch_pdl(silu_mul_kernel<__nv_bfloat16>, (unsigned)blocks, threads, 0, (cudaStream_t)stream,
+                   (const __nv_bfloat16*)gu, (__nv_bfloat16*)y, M, N);
     else
         return KB_ERR_UNSUPPORTED;
     return cudaGetLastError() == cudaSuccess ? KB_OK : KB_ERR_LAUNCH;

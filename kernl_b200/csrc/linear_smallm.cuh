@@ -11,6 +11,8 @@
 //     streaming loads, four rounds ahead, and feeds them as the B fragments of two
 //     mma.sync.m16n8k16 (the k order inside an MMA is permuted consistently for A and B, which a dot
 //     product does not notice); x rows are the A fragments, read through L1;
+//   * launched with programmatic dependent launch: its first weight loads are in flight before the
+//     kernel that produces x has finished;
 //   * the 8 partial 16x16 tiles meet in shared memory, 256 threads add them and apply bias and
 //     activation. No workspace, no atomics, no second launch.
 // Same contract as the reference's linear_layer (src/kernl/implementations/linear_layer.py:213-282).
@@ -56,6 +58,7 @@ linear_smallm_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* 
                      T* __restrict__ act_inputs, int M, int N, int K, int64_t x_row_stride, int64_t y_row_stride,
                      int activation) {
     __shared__ float red[kSmallMThreads / 32][16][kSmallMCols + 1];
+    pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, c = lane & 3;
     const int n0 = blockIdx.x * kSmallMCols;
@@ -80,17 +83,27 @@ linear_smallm_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* 
         for (int i = 0; i < 4; ++i) acc[grp][i] = 0.f;
 
     // piece p covers k in [32p, 32p + 32); warp `warp` takes pieces warp, warp + 8, ...; inside a piece
-    // this thread owns the 8 elements at 32p + 8c
+    // this thread owns the 8 elements at 32p + 8c. The weights do not depend on the kernel that
+    // produced x, so the first batch of weight loads is issued BEFORE waiting for that kernel.
     const int pieces = (K + 31) / 32;
     const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
-    for (int p0 = warp; p0 < pieces; p0 += 8 * kSmallMRounds) {
-        uint4 bw[kSmallMRounds][2], alo[kSmallMRounds], ahi[kSmallMRounds];
+    uint4 bw[kSmallMRounds][2];
+    auto load_w = [&](int p0) {
 #pragma unroll
         for (int r = 0; r < kSmallMRounds; ++r) {
             const int k = (p0 + r * 8) * 32 + c * 8;
-            const bool kin = k < K;  // K is a multiple of 8, so a piece is in or out as a whole per thread
 #pragma unroll
-            for (int grp = 0; grp < 2; ++grp) bw[r][grp] = (kin && wlive[grp]) ? ld_stream_nc_16B(wrow[grp] + k) : zero4;
+            for (int grp = 0; grp < 2; ++grp) bw[r][grp] = (k < K && wlive[grp]) ? ld_stream_nc_16B(wrow[grp] + k) : zero4;
+        }
+    };
+    load_w(warp);
+    pdl_wait();
+    for (int p0 = warp; p0 < pieces; p0 += 8 * kSmallMRounds) {
+        uint4 alo[kSmallMRounds], ahi[kSmallMRounds];
+#pragma unroll
+        for (int r = 0; r < kSmallMRounds; ++r) {
+            const int k = (p0 + r * 8) * 32 + c * 8;
+            const bool kin = k < K;  // K is a multiple of 8, so a thread's 8 elements are in or out as a whole
             alo[r] = (kin && lo_live) ? __ldg(reinterpret_cast<const uint4*>(xlo + k)) : zero4;
             if (HI) ahi[r] = (kin && hi_live) ? __ldg(reinterpret_cast<const uint4*>(xhi + k)) : zero4;
             else ahi[r] = zero4;
@@ -103,6 +116,7 @@ linear_smallm_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* 
                 mma_16816<T>(acc[grp], alo[r].z, ahi[r].z, alo[r].w, ahi[r].w, bw[r][grp].z, bw[r][grp].w);
             }
         }
+        if (p0 + 8 * kSmallMRounds < pieces) load_w(p0 + 8 * kSmallMRounds);
     }
     // accumulator fragment: c0,c1 -> (row g, cols 2c, 2c+1); c2,c3 -> (row g+8, same cols)
 #pragma unroll
@@ -143,13 +157,13 @@ template <typename T>
 static int launch_linear_smallm_t(const kb_linear_params& p, cudaStream_t stream) {
     const unsigned grid = (unsigned)((p.N + kSmallMCols - 1) / kSmallMCols);
     if (p.M > 8)
-        linear_smallm_kernel<T, true><<<grid, kSmallMThreads, 0, stream>>>(
-            (const T*)p.x, (const T*)p.w, (const T*)p.bias, (T*)p.y, (T*)p.act_inputs, (int)p.M, (int)p.N, (int)p.K,
-            p.x_row_stride, p.y_row_stride, p.activation);
+        launch_pdl(linear_smallm_kernel<T, true>, grid, kSmallMThreads, 0, stream, (const T*)p.x, (const T*)p.w,
+                   (const T*)p.bias, (T*)p.y, (T*)p.act_inputs, (int)p.M, (int)p.N, (int)p.K, p.x_row_stride,
+                   p.y_row_stride, p.activation);
     else
-        linear_smallm_kernel<T, false><<<grid, kSmallMThreads, 0, stream>>>(
-            (const T*)p.x, (const T*)p.w, (const T*)p.bias, (T*)p.y, (T*)p.act_inputs, (int)p.M, (int)p.N, (int)p.K,
-            p.x_row_stride, p.y_row_stride, p.activation);
+        launch_pdl(linear_smallm_kernel<T, false>, grid, kSmallMThreads, 0, stream, (const T*)p.x, (const T*)p.w,
+                   (const T*)p.bias, (T*)p.y, (T*)p.act_inputs, (int)p.M, (int)p.N, (int)p.K, p.x_row_stride,
+                   p.y_row_stride, p.activation);
     return cudaGetLastError() == cudaSuccess ? KB_OK : KB_ERR_LAUNCH;
 }
 

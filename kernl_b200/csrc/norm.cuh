@@ -39,6 +39,8 @@ norm_fwd_rowwarp_kernel(const T* __restrict__ x, T* __restrict__ y, const T* __r
                         float* __restrict__ rstd_out, int64_t rows, int cols, int64_t x_row_stride,
                         int64_t y_row_stride, float eps, const T* __restrict__ residual,
                         T* __restrict__ sum_out) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + warp;
     if (row >= rows) return;
@@ -143,6 +145,8 @@ norm_fwd_generic_kernel(const T* __restrict__ x, T* __restrict__ y, const T* __r
                         float* __restrict__ rstd_out, int64_t rows, int64_t cols,
                         int64_t x_row_stride, int64_t x_col_stride, int64_t y_row_stride,
                         int64_t y_col_stride, float eps) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + warp;
     if (row >= rows) return;
@@ -190,9 +194,9 @@ static int launch_norm_t(const kb_norm_params& p, cudaStream_t stream) {
         const int chunks = (int)((p.cols + 255) / 256);
 #define KB_NORM_CASE(C)                                                                          \
     if (chunks <= C) {                                                                           \
-        norm_fwd_rowwarp_kernel<T, C, RMS><<<grid, kWarps * 32, 0, stream>>>(                    \
-            x, y, g, b, p.mean, p.rstd, p.rows, (int)p.cols, p.x_row_stride, p.y_row_stride,     \
-            p.eps, (const T*)p.residual, (T*)p.sum_out);                                         \
+        launch_pdl(norm_fwd_rowwarp_kernel<T, C, RMS>, grid, kWarps * 32, 0, stream,             \
+                   x, y, g, b, p.mean, p.rstd, p.rows, (int)p.cols, p.x_row_stride,              \
+                   p.y_row_stride, p.eps, (const T*)p.residual, (T*)p.sum_out);                  \
         return KB_OK;                                                                            \
     }
         KB_NORM_CASE(1)
@@ -207,9 +211,8 @@ static int launch_norm_t(const kb_norm_params& p, cudaStream_t stream) {
 #undef KB_NORM_CASE
     }
     if (p.residual != nullptr) return KB_ERR_UNSUPPORTED;  // the fused add needs the vector layout
-    norm_fwd_generic_kernel<T, RMS><<<grid, kWarps * 32, 0, stream>>>(
-        x, y, g, b, p.mean, p.rstd, p.rows, p.cols, p.x_row_stride, p.x_col_stride, p.y_row_stride,
-        p.y_col_stride, p.eps);
+    launch_pdl(norm_fwd_generic_kernel<T, RMS>, grid, kWarps * 32, 0, stream, x, y, g, b, p.mean, p.rstd, p.rows,
+               p.cols, p.x_row_stride, p.x_col_stride, p.y_row_stride, p.y_col_stride, p.eps);
     return KB_OK;
 }
 

@@ -28,6 +28,8 @@ struct RopeDev {
 template <typename T>
 __global__ void __launch_bounds__(256)
 rope_kv_write_kernel(const RopeDev p) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int vec_per_head = p.D / 8;
     const long long total = (long long)p.B * p.S * p.H * vec_per_head;
     const long long start = p.pos_dev ? *p.pos_dev : p.pos_host;
@@ -70,7 +72,7 @@ static int launch_rope_t(const RopeDev& d, cudaStream_t stream) {
     const long long cap = (long long)sm_count() * 16;
     if (blocks > cap) blocks = cap;
     if (blocks < 1) blocks = 1;
-    rope_kv_write_kernel<T><<<(unsigned)blocks, 256, 0, stream>>>(d);
+    launch_pdl(rope_kv_write_kernel<T>, (unsigned)blocks, 256, 0, stream, d);
     return cudaGetLastError() == cudaSuccess ? KB_OK : KB_ERR_LAUNCH;
 }
 

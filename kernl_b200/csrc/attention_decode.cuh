@@ -27,9 +27,15 @@ struct DecDev {
     float* scratch;         // [B*H, M, num_splits, D+2]
 };
 
-static void decode_split(int64_t N, int* num_splits, int* chunk) {
+// Keys per CTA: 128 when there are few (batch x head x row) problems, so that the key dimension
+// supplies the parallelism; doubled (up to 1024) while the launch still has about one full wave of
+// CTAs (16 per SM). Longer chunks amortise a CTA's fixed phases (q load, three barriers per 128 keys,
+// the final cross-warp sum) and leave fewer partial results for the second kernel to merge.
+static void decode_split(int64_t N, int64_t problems, int* num_splits, int* chunk) {
     int64_t c = 128;
     while ((N + c - 1) / c > kDecMaxSplits) c *= 2;
+    const int64_t want = 2000;
+    while (c < 1024 && problems * ((N + 2 * c - 1) / (2 * c)) >= want) c *= 2;
     *chunk = (int)c;
     *num_splits = (int)((N + c - 1) / c);
     if (*num_splits < 1) *num_splits = 1;
@@ -38,7 +44,7 @@ static void decode_split(int64_t N, int* num_splits, int* chunk) {
 static int64_t decode_scratch_bytes(int64_t B, int64_t H, int64_t M, int64_t N, int64_t D) {
     if (B < 0 || H < 0 || M < 0 || N < 0 || D <= 0) return -1;
     int splits, chunk;
-    decode_split(N, &splits, &chunk);
+    decode_split(N, B * H * M, &splits, &chunk);
     return B * H * M * (int64_t)splits * (D + 2) * (int64_t)sizeof(float);
 }
 
@@ -324,7 +330,7 @@ static int launch_attention_decode(const kb_attn_params& p, void* scratch, int64
     d.scale_log2 = p.sm_scale * kLog2e;
     d.is_causal = p.is_causal ? 1 : 0;
     d.mask_dtype = p.mask ? p.mask_dtype : KB_F32;
-    decode_split(p.N, &d.num_splits, &d.chunk);
+    decode_split(p.N, p.B * p.H * p.M, &d.num_splits, &d.chunk);
     d.scratch = reinterpret_cast<float*>(scratch);
     const dim3 g1((unsigned)d.num_splits, (unsigned)p.M, (unsigned)(p.B * p.H));
     const dim3 g2((unsigned)p.M, (unsigned)(p.B * p.H));

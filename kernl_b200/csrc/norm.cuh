@@ -30,9 +30,11 @@ __device__ __forceinline__ void st_stream_16B(void* p, uint4 v) {
                  : "memory");
 }
 
-// CHUNKS = ceil(cols / 256): each lane owns CHUNKS vectors of 8 elements; vector c of lane l covers
-// columns (c*32 + l)*8 .. +8. cols must be a multiple of 8.
-template <typename T, int CHUNKS, bool RMS>
+// WPR warps share one row (1: a warp per row, for many rows; 4: the whole CTA on one row, for the
+// few rows of a decode step, where a single warp walking 4096 columns is a 19 µs chain of dependent
+// loads). CHUNKS = ceil(cols / (256 * WPR)): each lane owns CHUNKS vectors of 8 elements; vector c of
+// lane l of warp w covers columns ((c*WPR + w)*32 + l)*8 .. +8. cols must be a multiple of 8.
+template <typename T, int CHUNKS, bool RMS, int WPR = 1>
 __global__ void __launch_bounds__(128)
 norm_fwd_rowwarp_kernel(const T* __restrict__ x, T* __restrict__ y, const T* __restrict__ gamma,
                         const T* __restrict__ beta, float* __restrict__ mean_out,
@@ -41,16 +43,19 @@ norm_fwd_rowwarp_kernel(const T* __restrict__ x, T* __restrict__ y, const T* __r
                         T* __restrict__ sum_out) {
     pdl_launch_dependents();
     pdl_wait();
+    __shared__ float red_s[2][4];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + warp;
-    if (row >= rows) return;
+    const int wir = warp % WPR;  // this warp's position inside its row
+    const int64_t row = (int64_t)blockIdx.x * (4 / WPR) + warp / WPR;
+    if (row >= rows) return;  // (WPR > 1: the whole CTA leaves together)
     const T* xr = x + row * x_row_stride;
     T* yr = y + row * y_row_stride;
+#define KB_NORM_COL(c) ((((c) * WPR + wir) * 32 + lane) * 8)
 
     uint4 v[CHUNKS];
 #pragma unroll
     for (int c = 0; c < CHUNKS; ++c) {
-        const int col = (c * 32 + lane) * 8;
+        const int col = KB_NORM_COL(c);
         if (col < cols) v[c] = ld_stream_16B(xr + col);
         else v[c] = make_uint4(0, 0, 0, 0);
     }
@@ -59,7 +64,7 @@ norm_fwd_rowwarp_kernel(const T* __restrict__ x, T* __restrict__ y, const T* __r
         // kernel would store it), written out once and normalised from the registers
 #pragma unroll
         for (int c = 0; c < CHUNKS; ++c) {
-            const int col = (c * 32 + lane) * 8;
+            const int col = KB_NORM_COL(c);
             if (col < cols) {
                 const uint4 r = ld_stream_16B(residual + row * (int64_t)cols + col);
                 const uint32_t xw[4] = {v[c].x, v[c].y, v[c].z, v[c].w};
@@ -83,11 +88,19 @@ norm_fwd_rowwarp_kernel(const T* __restrict__ x, T* __restrict__ y, const T* __r
         // row's first element: shifting by a value of the row itself keeps the subtraction
         // E[(x-K)^2] - E[x-K]^2 well conditioned even when |mean| >> std (rows like -20 +- 0.5).
         float shift = 0.f;
-        if (!RMS) shift = __shfl_sync(0xffffffffu, Elem<T>::unpack2(v[0].x).x, 0);
+        if (!RMS) {
+            if (WPR == 1) {
+                shift = __shfl_sync(0xffffffffu, Elem<T>::unpack2(v[0].x).x, 0);
+            } else {  // every thread reads the row's first element itself (the sum, when a residual is added)
+                float x0 = Elem<T>::to_f32(xr[0]);
+                if (residual != nullptr) x0 = Elem<T>::to_f32(Elem<T>::from_f32(x0 + Elem<T>::to_f32(residual[row * (int64_t)cols])));
+                shift = x0;
+            }
+        }
         float s1 = 0.f, s2 = 0.f;
 #pragma unroll
         for (int c = 0; c < CHUNKS; ++c) {
-            const int col = (c * 32 + lane) * 8;
+            const int col = KB_NORM_COL(c);
             if (col < cols) {
                 const uint32_t w[4] = {v[c].x, v[c].y, v[c].z, v[c].w};
 #pragma unroll
@@ -99,22 +112,33 @@ norm_fwd_rowwarp_kernel(const T* __restrict__ x, T* __restrict__ y, const T* __r
                 }
             }
         }
-        s2 = warp_sum(s2) * inv_n;
+        s2 = warp_sum(s2);
+        if (!RMS) s1 = warp_sum(s1);
+        if (WPR > 1) {  // WPR == 4: the CTA is one row
+            if (lane == 0) {
+                red_s[0][warp] = s1;
+                red_s[1][warp] = s2;
+            }
+            __syncthreads();
+            s1 = (red_s[0][0] + red_s[0][1]) + (red_s[0][2] + red_s[0][3]);
+            s2 = (red_s[1][0] + red_s[1][1]) + (red_s[1][2] + red_s[1][3]);
+        }
+        s2 *= inv_n;
         if (!RMS) {
-            const float d = warp_sum(s1) * inv_n;
+            const float d = s1 * inv_n;
             mean = shift + d;
             s2 = fmaxf(s2 - d * d, 0.f);
         }
         rstd = rsqrtf(s2 + eps);
     }
-    if (lane == 0) {
+    if (lane == 0 && wir == 0) {
         if (mean_out) mean_out[row] = mean;
         if (rstd_out) rstd_out[row] = rstd;
     }
 
 #pragma unroll
     for (int c = 0; c < CHUNKS; ++c) {
-        const int col = (c * 32 + lane) * 8;
+        const int col = KB_NORM_COL(c);
         if (col < cols) {
             const uint4 g = *reinterpret_cast<const uint4*>(gamma + col);
             uint4 b = make_uint4(0, 0, 0, 0);
@@ -190,6 +214,24 @@ static int launch_norm_t(const kb_norm_params& p, cudaStream_t stream) {
                         ((uintptr_t)p.x % 16) == 0 && ((uintptr_t)p.y % 16) == 0 &&
                         ((uintptr_t)p.gamma % 16) == 0 &&
                         (p.beta == nullptr || ((uintptr_t)p.beta % 16) == 0) && p.cols <= 6144;
+    if (vec_ok && p.rows <= 1024) {
+        // few rows (a decode step, BERT at batch 1): one CTA per row, so that every row is read by 128
+        // threads at once instead of one warp walking it
+        const int chunks4 = (int)((p.cols + 1023) / 1024);
+        const unsigned grid4 = (unsigned)p.rows;
+#define KB_NORM_CASE4(C)                                                                         \
+    if (chunks4 <= C) {                                                                          \
+        launch_pdl(norm_fwd_rowwarp_kernel<T, C, RMS, 4>, grid4, kWarps * 32, 0, stream,         \
+                   x, y, g, b, p.mean, p.rstd, p.rows, (int)p.cols, p.x_row_stride,              \
+                   p.y_row_stride, p.eps, (const T*)p.residual, (T*)p.sum_out);                  \
+        return KB_OK;                                                                            \
+    }
+        KB_NORM_CASE4(1)
+        KB_NORM_CASE4(2)
+        KB_NORM_CASE4(4)
+        KB_NORM_CASE4(6)
+#undef KB_NORM_CASE4
+    }
     if (vec_ok) {
         const int chunks = (int)((p.cols + 255) / 256);
 #define KB_NORM_CASE(C)                                                                          \

@@ -51,8 +51,8 @@ static int64_t decode_scratch_bytes(int64_t B, int64_t H, int64_t M, int64_t N, 
 template <typename T>
 __global__ void __launch_bounds__(kDecThreads)
 attn_decode_part1_kernel(const DecDev p) {
-    pdl_launch_dependents();
     pdl_wait();
+    pdl_launch_dependents();
     __shared__ float q_s[kDecMaxD];
     __shared__ float sc_s[kDecThreads];
     __shared__ float red_s[kDecThreads / 32];
@@ -127,8 +127,10 @@ attn_decode_part1_kernel(const DecDev p) {
         for (int o = 16; o > 0; o >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, o);
         if (lane == 0) red_s[warp] = ps;
         __syncthreads();
+        asm volatile("cp.async.wait_group 0;" ::: "memory");  // this thread's V copies have landed
         l_run = l_run * alpha + (red_s[0] + red_s[1] + red_s[2] + red_s[3]);
         m_run = m_new;
+        __syncthreads();  // every thread's V copies are visible
         // ---- P·V: thread d accumulates output dimension d over the block's keys
         const int nk = min(kDecThreads, key_end - k0);
 #pragma unroll
@@ -161,8 +163,8 @@ attn_decode_part1_kernel(const DecDev p) {
 template <typename T, int LPK>
 __global__ void __launch_bounds__(kDecThreads)
 attn_decode_part1_vec_kernel(const DecDev p) {
-    pdl_launch_dependents();
     pdl_wait();
+    pdl_launch_dependents();
     constexpr int D = LPK * 8;
     constexpr int KPW = 32 / LPK;                 // keys per warp per step
     constexpr int KPS = KPW * (kDecThreads / 32);  // keys per CTA per step
@@ -170,23 +172,53 @@ attn_decode_part1_vec_kernel(const DecDev p) {
     __shared__ float sc_s[kDecThreads];
     __shared__ float red_s[kDecThreads / 32];
     __shared__ float acc_s[GROUPS][D + 4];
+    // K and V tiles of 128 keys, staged with asynchronous 16-byte copies: a thread issues all of its
+    // 2 x 16 copies for a tile up front and holds no registers for them, so a CTA has its whole
+    // tile (64 KB at D = 128) in flight and three CTAs share an SM. With plain loads into registers
+    // the kernel was bound by memory latency (ncu: 42 % of the warps resident, 22 long-scoreboard
+    // stall cycles per issued instruction, 3.7 TB/s). Chunk j (16 bytes) of row r sits at
+    // r * LPK + (j ^ ((r & 1) << 2)), which makes both read patterns below bank-conflict free.
+    extern __shared__ uint4 kv_tiles[];
+    uint4* k_tile = kv_tiles;
+    uint4* v_tile = kv_tiles + kDecThreads * LPK;
     const int split = blockIdx.x, row = blockIdx.y, bh = blockIdx.z;
     const int b = bh / p.H, h = bh % p.H;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int sub = lane / LPK;   // which of the warp's keys this lane works on
     const int dl = lane % LPK;    // which 8-wide slice of the head dimension
     const int group = tid / LPK;  // == warp * KPW + sub
 
-    // this lane's slice of q, pre-scaled into the log2 domain
-    float qv[8];
+    // Scores on the tensor core: one mma.sync.m16n8k16 chain per group of 8 keys, q in row 0 of the A
+    // operand (rows 1..15 are zero), the 8 keys as the columns of B. K is [key][d] with d contiguous,
+    // which is exactly the "col" layout of B; every thread feeds the 16 bytes it loads (8 consecutive
+    // d of one key) into two MMAs, with the same permutation of d inside an MMA for q and K. One
+    // load and two MMAs per 16 bytes instead of one load, 8 conversions, 8 FMAs and log2(LPK)
+    // shuffles: the scalar version spent ~45 instructions per 32 bytes of K/V and ran out of issue slots
+    // at two thirds of the HBM bandwidth.
+    const int g8 = lane >> 2, c4 = lane & 3;
+    uint4 qf[D / 32];
     {
         const T* qp = reinterpret_cast<const T*>(p.q) + (int64_t)b * p.q_strides[0] + (int64_t)h * p.q_strides[1] +
-                      (int64_t)row * p.q_strides[2] + dl * 8;
+                      (int64_t)row * p.q_strides[2];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) qv[i] = Elem<T>::to_f32(qp[i]) * p.scale_log2;
+        for (int i = 0; i < D / 32; ++i)
+            qf[i] = (g8 == 0) ? __ldg(reinterpret_cast<const uint4*>(qp + 32 * i + 8 * c4)) : make_uint4(0u, 0u, 0u, 0u);
     }
-    const T* kbase = reinterpret_cast<const T*>(p.k) + (int64_t)b * p.k_strides[0] + (int64_t)h * p.k_strides[1] + dl * 8;
-    const T* vbase = reinterpret_cast<const T*>(p.v) + (int64_t)b * p.v_strides[0] + (int64_t)h * p.v_strides[1] + dl * 8;
+    const T* kbase0 = reinterpret_cast<const T*>(p.k) + (int64_t)b * p.k_strides[0] + (int64_t)h * p.k_strides[1];
+    const T* vbase0 = reinterpret_cast<const T*>(p.v) + (int64_t)b * p.v_strides[0] + (int64_t)h * p.v_strides[1];
+    auto stage_tile = [&](uint4* tile, const T* base, int64_t row_stride, int k0, int key_end) {
+#pragma unroll 4
+        for (int it = 0; it < LPK; ++it) {
+            const int idx = it * kDecThreads + tid;
+            const int r = idx / LPK, j = idx % LPK;
+            const int key = k0 + r;
+            const bool live = key < key_end;
+            const T* src = base + (int64_t)(live ? key : k0) * row_stride + j * 8;
+            const uint32_t dst = smem_u32(tile + r * LPK + (j ^ ((r & 1) << 2)));
+            // src-size 0 for rows beyond the chunk: the 16 bytes are zero-filled, nothing is read
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(live ? 16 : 0) : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
     const float mlow = mask_lowest(p.mask_dtype);
     const int64_t mask_off = p.mask ? (int64_t)b * p.mask_strides[0] + (int64_t)h * p.mask_strides[1] +
                                           (int64_t)row * p.mask_strides[2]
@@ -199,33 +231,38 @@ attn_decode_part1_vec_kernel(const DecDev p) {
     const int key_begin = split * p.chunk;
     const int key_end = min(p.N, key_begin + p.chunk);
     for (int k0 = key_begin; k0 < key_end; k0 += kDecThreads) {
-        // ---- scores of the block's 128 keys: step s handles keys k0 + s*KPS + group
-#pragma unroll 4
-        for (int s = 0; s < kDecThreads / KPS; ++s) {
-            const int key = k0 + s * KPS + group;
-            float dot = 0.f;
-            if (key < key_end) {
-                const uint4 w = __ldg(reinterpret_cast<const uint4*>(kbase + (int64_t)key * p.k_strides[2]));
-                const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+        stage_tile(k_tile, kbase0, p.k_strides[2], k0, key_end);
+        stage_tile(v_tile, vbase0, p.v_strides[2], k0, key_end);
+        asm volatile("cp.async.wait_group 1;" ::: "memory");  // this thread's K copies have landed
+        __syncthreads();                                       // ... and everybody else's
+        // ---- scores of the block's 128 keys: step s, warp w, group row g8 -> tile row 32 s + 8 w + g8
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const float2 f = Elem<T>::unpack2(ww[i]);
-                    dot = fmaf(f.x, qv[2 * i], dot);
-                    dot = fmaf(f.y, qv[2 * i + 1], dot);
-                }
+        for (int s = 0; s < kDecThreads / 32; ++s) {
+            const int r = s * 32 + warp * 8 + g8;
+            uint4 kf[D / 32];
+#pragma unroll
+            for (int i = 0; i < D / 32; ++i) kf[i] = k_tile[r * LPK + ((4 * i + c4) ^ ((r & 1) << 2))];
+            float cacc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int i = 0; i < D / 32; ++i) {
+                mma_16816<T>(cacc, qf[i].x, 0u, qf[i].y, 0u, kf[i].x, kf[i].y);
+                mma_16816<T>(cacc, qf[i].z, 0u, qf[i].w, 0u, kf[i].z, kf[i].w);
             }
+            if (g8 == 0) {  // row 0 of the accumulator: lane c4 holds the scores of keys 2 c4 and 2 c4 + 1 of the group
 #pragma unroll
-            for (int o = LPK / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-            if (dl == 0) {
-                float sc = -INFINITY;
-                if (key < key_end && !(p.is_causal && key > row)) {
-                    sc = dot;
-                    if (p.mask) {
-                        const float mv = mask_load(p.mask, mask_off + (int64_t)key * p.mask_strides[3], p.mask_dtype);
-                        sc = fmaf(fmaxf(mv, mlow), kLog2e, sc);
+                for (int e = 0; e < 2; ++e) {
+                    const int kk = s * 32 + warp * 8 + 2 * c4 + e;
+                    const int key2 = k0 + kk;
+                    float sc = -INFINITY;
+                    if (key2 < key_end && !(p.is_causal && key2 > row)) {
+                        sc = cacc[e] * p.scale_log2;
+                        if (p.mask) {
+                            const float mv = mask_load(p.mask, mask_off + (int64_t)key2 * p.mask_strides[3], p.mask_dtype);
+                            sc = fmaf(fmaxf(mv, mlow), kLog2e, sc);
+                        }
                     }
+                    sc_s[kk] = sc;
                 }
-                sc_s[s * KPS + group] = sc;
             }
         }
         __syncthreads();
@@ -260,7 +297,7 @@ attn_decode_part1_vec_kernel(const DecDev p) {
             const int key = k0 + kk;
             if (key < key_end) {
                 const float pk = sc_s[kk];
-                const uint4 w = __ldg(reinterpret_cast<const uint4*>(vbase + (int64_t)key * p.v_strides[2]));
+                const uint4 w = v_tile[kk * LPK + (dl ^ ((kk & 1) << 2))];
                 const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
@@ -270,7 +307,7 @@ attn_decode_part1_vec_kernel(const DecDev p) {
                 }
             }
         }
-        __syncthreads();  // sc_s is rewritten by the next block
+        __syncthreads();  // sc_s and both tiles are rewritten by the next block
     }
     // ---- sum the key groups and write (m, l, acc[D])
 #pragma unroll
@@ -289,8 +326,8 @@ attn_decode_part1_vec_kernel(const DecDev p) {
 template <typename T>
 __global__ void __launch_bounds__(kDecThreads)
 attn_decode_part2_kernel(const DecDev p) {
-    pdl_launch_dependents();
     pdl_wait();
+    pdl_launch_dependents();
     const int row = blockIdx.x, bh = blockIdx.y;
     const int b = bh / p.H, h = bh % p.H;
     const int D = p.D;
@@ -312,6 +349,17 @@ attn_decode_part2_kernel(const DecDev p) {
         }
         op[(int64_t)d * p.o_strides[3]] = Elem<T>::from_f32(a / l_tot);
     }
+}
+
+template <typename T, int LPK>
+static void launch_decode_vec(dim3 grid, cudaStream_t stream, const DecDev& d) {
+    constexpr size_t smem = 2 * (size_t)kDecThreads * LPK * sizeof(uint4);  // K tile + V tile
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaFuncSetAttribute(attn_decode_part1_vec_kernel<T, LPK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        attr_set = true;
+    }
+    launch_pdl(attn_decode_part1_vec_kernel<T, LPK>, grid, kDecThreads, smem, stream, d);
 }
 
 static int launch_attention_decode(const kb_attn_params& p, void* scratch, int64_t scratch_bytes, cudaStream_t stream) {
@@ -337,17 +385,19 @@ static int launch_attention_decode(const kb_attn_params& p, void* scratch, int64
     const bool vec_ok = (p.D == 64 || p.D == 128 || p.D == 256) && p.q_strides[3] == 1 && p.k_strides[3] == 1 &&
                         p.v_strides[3] == 1 && (p.k_strides[2] % 8) == 0 && (p.v_strides[2] % 8) == 0 &&
                         (p.k_strides[1] % 8) == 0 && (p.v_strides[1] % 8) == 0 && (p.k_strides[0] % 8) == 0 &&
-                        (p.v_strides[0] % 8) == 0 && (((uintptr_t)p.k) & 15) == 0 && (((uintptr_t)p.v) & 15) == 0;
+                        (p.v_strides[0] % 8) == 0 && (((uintptr_t)p.k) & 15) == 0 && (((uintptr_t)p.v) & 15) == 0 &&
+                        (((uintptr_t)p.q) & 15) == 0 && (p.q_strides[0] % 8) == 0 && (p.q_strides[1] % 8) == 0 &&
+                        (p.q_strides[2] % 8) == 0;
     if (p.dtype == KB_F16) {
-        if (vec_ok && p.D == 64) launch_pdl(attn_decode_part1_vec_kernel<__half, 8>, g1, kDecThreads, 0, stream, d);
-        else if (vec_ok && p.D == 128) launch_pdl(attn_decode_part1_vec_kernel<__half, 16>, g1, kDecThreads, 0, stream, d);
-        else if (vec_ok && p.D == 256) launch_pdl(attn_decode_part1_vec_kernel<__half, 32>, g1, kDecThreads, 0, stream, d);
+        if (vec_ok && p.D == 64) launch_decode_vec<__half, 8>(g1, stream, d);
+        else if (vec_ok && p.D == 128) launch_decode_vec<__half, 16>(g1, stream, d);
+        else if (vec_ok && p.D == 256) launch_decode_vec<__half, 32>(g1, stream, d);
         else launch_pdl(attn_decode_part1_kernel<__half>, g1, kDecThreads, 0, stream, d);
         launch_pdl(attn_decode_part2_kernel<__half>, g2, kDecThreads, 0, stream, d);
     } else {
-        if (vec_ok && p.D == 64) launch_pdl(attn_decode_part1_vec_kernel<__nv_bfloat16, 8>, g1, kDecThreads, 0, stream, d);
-        else if (vec_ok && p.D == 128) launch_pdl(attn_decode_part1_vec_kernel<__nv_bfloat16, 16>, g1, kDecThreads, 0, stream, d);
-        else if (vec_ok && p.D == 256) launch_pdl(attn_decode_part1_vec_kernel<__nv_bfloat16, 32>, g1, kDecThreads, 0, stream, d);
+        if (vec_ok && p.D == 64) launch_decode_vec<__nv_bfloat16, 8>(g1, stream, d);
+        else if (vec_ok && p.D == 128) launch_decode_vec<__nv_bfloat16, 16>(g1, stream, d);
+        else if (vec_ok && p.D == 256) launch_decode_vec<__nv_bfloat16, 32>(g1, stream, d);
         else launch_pdl(attn_decode_part1_kernel<__nv_bfloat16>, g1, kDecThreads, 0, stream, d);
         launch_pdl(attn_decode_part2_kernel<__nv_bfloat16>, g2, kDecThreads, 0, stream, d);
     }

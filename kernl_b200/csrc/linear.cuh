@@ -532,8 +532,8 @@ static int launch_linear(const kb_linear_params& p, cudaStream_t stream, int for
 // y = silu(g) * u with gu = [g | u] along columns.
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ y, int64_t M, int64_t N) {
-    pdl_launch_dependents();
     pdl_wait();
+    pdl_launch_dependents();
     const int64_t nvec = N / 8;
     const int64_t total = M * nvec;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;

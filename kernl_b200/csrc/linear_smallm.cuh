@@ -11,8 +11,8 @@
 //     streaming loads, four rounds ahead, and feeds them as the B fragments of two
 //     mma.sync.m16n8k16 (the k order inside an MMA is permuted consistently for A and B, which a dot
 //     product does not notice); x rows are the A fragments, read through L1;
-//   * launched with programmatic dependent launch: its first weight loads are in flight before the
-//     kernel that produces x has finished;
+//   * launched with programmatic dependent launch: its set-up overlaps the tail of the kernel that
+//     produces x;
 //   * the 8 partial 16x16 tiles meet in shared memory, 256 threads add them and apply bias and
 //     activation. No workspace, no atomics, no second launch.
 // Same contract as the reference's linear_layer (src/kernl/implementations/linear_layer.py:213-282).
@@ -25,32 +25,6 @@ constexpr int kSmallMThreads = 256;
 constexpr int kSmallMCols = 16;    // output columns per CTA
 constexpr int kSmallMRounds = 4;   // 32-element k pieces in flight per warp
 
-__device__ __forceinline__ uint4 ld_stream_nc_16B(const void* p) {
-    uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                 : "l"(p));
-    return v;
-}
-
-template <typename T>
-__device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                          uint32_t b1);
-template <>
-__device__ __forceinline__ void mma_16816<__half>(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                                  uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-template <>
-__device__ __forceinline__ void mma_16816<__nv_bfloat16>(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                                         uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
 // HI: rows 8..15 exist (M > 8); otherwise their A fragments are zero and are not loaded.
 template <typename T, bool HI>
 __global__ void __launch_bounds__(kSmallMThreads, 2)
@@ -58,7 +32,6 @@ linear_smallm_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* 
                      T* __restrict__ act_inputs, int M, int N, int K, int64_t x_row_stride, int64_t y_row_stride,
                      int activation) {
     __shared__ float red[kSmallMThreads / 32][16][kSmallMCols + 1];
-    pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, c = lane & 3;
     const int n0 = blockIdx.x * kSmallMCols;
@@ -83,8 +56,7 @@ linear_smallm_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* 
         for (int i = 0; i < 4; ++i) acc[grp][i] = 0.f;
 
     // piece p covers k in [32p, 32p + 32); warp `warp` takes pieces warp, warp + 8, ...; inside a piece
-    // this thread owns the 8 elements at 32p + 8c. The weights do not depend on the kernel that
-    // produced x, so the first batch of weight loads is issued BEFORE waiting for that kernel.
+    // this thread owns the 8 elements at 32p + 8c.
     const int pieces = (K + 31) / 32;
     const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
     uint4 bw[kSmallMRounds][2];
@@ -96,8 +68,9 @@ linear_smallm_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* 
             for (int grp = 0; grp < 2; ++grp) bw[r][grp] = (k < K && wlive[grp]) ? ld_stream_nc_16B(wrow[grp] + k) : zero4;
         }
     };
+    pdl_wait();  // (W could in principle have been written by the previous kernel, e.g. a dtype conversion)
+    pdl_launch_dependents();
     load_w(warp);
-    pdl_wait();
     for (int p0 = warp; p0 < pieces; p0 += 8 * kSmallMRounds) {
         uint4 alo[kSmallMRounds], ahi[kSmallMRounds];
 #pragma unroll

@@ -41,8 +41,8 @@ norm_fwd_rowwarp_kernel(const T* __restrict__ x, T* __restrict__ y, const T* __r
                         float* __restrict__ rstd_out, int64_t rows, int cols, int64_t x_row_stride,
                         int64_t y_row_stride, float eps, const T* __restrict__ residual,
                         T* __restrict__ sum_out) {
-    pdl_launch_dependents();
     pdl_wait();
+    pdl_launch_dependents();
     __shared__ float red_s[2][4];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int wir = warp % WPR;  // this warp's position inside its row
@@ -169,8 +169,8 @@ norm_fwd_generic_kernel(const T* __restrict__ x, T* __restrict__ y, const T* __r
                         float* __restrict__ rstd_out, int64_t rows, int64_t cols,
                         int64_t x_row_stride, int64_t x_col_stride, int64_t y_row_stride,
                         int64_t y_col_stride, float eps) {
-    pdl_launch_dependents();
     pdl_wait();
+    pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + warp;
     if (row >= rows) return;

@@ -28,8 +28,8 @@ struct RopeDev {
 template <typename T>
 __global__ void __launch_bounds__(256)
 rope_kv_write_kernel(const RopeDev p) {
-    pdl_launch_dependents();
     pdl_wait();
+    pdl_launch_dependents();
     const int vec_per_head = p.D / 8;
     const long long total = (long long)p.B * p.S * p.H * vec_per_head;
     const long long start = p.pos_dev ? *p.pos_dev : p.pos_host;

@@ -137,6 +137,8 @@ def load() -> ctypes.CDLL:
         if hasattr(lib, hook):
             getattr(lib, hook).argtypes = [ctypes.c_int]
             getattr(lib, hook).restype = None
+    if os.environ.get("KERNL_B200_PDL", "1") == "0" and hasattr(lib, "kb_debug_pdl"):
+        lib.kb_debug_pdl(0)  # launch every kernel with plain stream ordering (A/B measurements)
     _lib = lib
     return lib
 

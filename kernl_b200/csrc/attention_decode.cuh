@@ -127,10 +127,8 @@ attn_decode_part1_kernel(const DecDev p) {
         for (int o = 16; o > 0; o >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, o);
         if (lane == 0) red_s[warp] = ps;
         __syncthreads();
-        asm volatile("cp.async.wait_group 0;" ::: "memory");  // this thread's V copies have landed
         l_run = l_run * alpha + (red_s[0] + red_s[1] + red_s[2] + red_s[3]);
         m_run = m_new;
-        __syncthreads();  // every thread's V copies are visible
         // ---- P·V: thread d accumulates output dimension d over the block's keys
         const int nk = min(kDecThreads, key_end - k0);
 #pragma unroll
@@ -243,6 +241,10 @@ attn_decode_part1_vec_kernel(const DecDev p) {
 #pragma unroll
             for (int i = 0; i < D / 32; ++i) kf[i] = k_tile[r * LPK + ((4 * i + c4) ^ ((r & 1) << 2))];
             float cacc[4] = {0.f, 0.f, 0.f, 0.f};
+            // mma.sync.aligned needs the whole warp converged; the lanes that stored the previous
+            // group's scores (g8 == 0, below) may still be apart from the others. Without this
+            // barrier the kernel produced garbage for some CTAs whenever the GPU was busy.
+            __syncwarp();
 #pragma unroll
             for (int i = 0; i < D / 32; ++i) {
                 mma_16816<T>(cacc, qf[i].x, 0u, qf[i].y, 0u, kf[i].x, kf[i].y);
@@ -286,8 +288,10 @@ attn_decode_part1_vec_kernel(const DecDev p) {
         for (int o = 16; o > 0; o >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, o);
         if (lane == 0) red_s[warp] = ps;
         __syncthreads();
+        asm volatile("cp.async.wait_group 0;" ::: "memory");  // this thread's V copies have landed
         l_run = l_run * alpha + (red_s[0] + red_s[1] + red_s[2] + red_s[3]);
         m_run = m_new;
+        __syncthreads();  // every thread's V copies are visible
         // ---- P·V with the same key-to-lane mapping
 #pragma unroll
         for (int i = 0; i < 8; ++i) acc[i] *= alpha;

@@ -245,6 +245,28 @@ def test_skinny_attention_shapes(lib, m, n, d, dtype):
     O.assert_parity(out, expected, max_abs=1e-2 if dtype == torch.float16 else 3e-2)
 
 
+@pytest.mark.parametrize("d,dtype,tol", [(64, torch.float16, 1e-2), (128, torch.bfloat16, 3e-2)], ids=["d64_fp16", "d128_bf16"])
+def test_skinny_attention_right_behind_a_long_kernel(lib, d, dtype, tol):
+    """Many (batch, head) problems launched while the GPU is still draining a large fill: the first
+    wave of CTAs then sees slow asynchronous copies, which is what exposes a missing wait on the
+    staged K/V tiles (this case failed once with errors of 1e18)."""
+    from kernl_b200.implementations.attention_skinny import skinny_attention_forward
+
+    g = torch.Generator().manual_seed(0)
+    B, H, N = 8, 32, 1500
+    q = (torch.rand((B, H, 1, d), generator=g) * 2).to(dtype)
+    k = (torch.rand((B, H, N, d), generator=g) * 2).to(dtype)
+    v = (torch.rand((B, H, N, d), generator=g) * 2).to(dtype)
+    expected = O.attention(q, k, v, 0.3, False, None)
+    qc, kc, vc = _cuda(q, k, v)
+    for _ in range(4):
+        junk = torch.full((64 * 1024 * 1024,), float("nan"), device="cuda")
+        out = torch.empty_like(qc)
+        skinny_attention_forward(qc, kc, vc, out, 0.3, False, None)
+        del junk
+        O.assert_parity(out, expected, max_abs=tol)
+
+
 def test_skinny_matches_fused_kernel(lib):
     from kernl_b200.implementations.attention import attention_forward
     from kernl_b200.implementations.attention_skinny import skinny_attention_forward

@@ -629,12 +629,11 @@ static int launch_attention_tdm(const kb_attn_params& p, cudaStream_t stream) {
     d.num_pairs = (num_m_tiles + 1) / 2;
     d.head_group = attn_head_group(p.B * p.H, p.N, p.D);
 
-    static bool attr_set = false;
-    if (!attr_set) {
+    static PerDeviceOnce attr_once;
+    if (attr_once.first_time()) {
         if (cudaFuncSetAttribute(attention_tc_kernel<T, D, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  Cfg::kSmemBytes) != cudaSuccess)
             return KB_ERR_LAUNCH;
-        attr_set = true;
     }
     const int64_t grid = (int64_t)d.num_pairs * p.B * p.H;
     if (grid > 0x7fffffff) return KB_ERR_UNSUPPORTED;

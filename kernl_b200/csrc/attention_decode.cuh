@@ -358,10 +358,9 @@ attn_decode_part2_kernel(const DecDev p) {
 template <typename T, int LPK>
 static void launch_decode_vec(dim3 grid, cudaStream_t stream, const DecDev& d) {
     constexpr size_t smem = 2 * (size_t)kDecThreads * LPK * sizeof(uint4);  // K tile + V tile
-    static bool attr_set = false;
-    if (!attr_set) {
+    static PerDeviceOnce attr_once;
+    if (attr_once.first_time()) {
         cudaFuncSetAttribute(attn_decode_part1_vec_kernel<T, LPK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        attr_set = true;
     }
     launch_pdl(attn_decode_part1_vec_kernel<T, LPK>, grid, kDecThreads, smem, stream, d);
 }

@@ -644,22 +644,21 @@ static int launch_attention_split_tm(const kb_attn_params& p, cudaStream_t strea
     const int num_m_tiles = (int)((p.M + kAttnBlock - 1) / kAttnBlock);
     d.num_pairs = (num_m_tiles + 1) / 2;
     d.head_group = attn_head_group(p.B * p.H, p.N, p.D);
-    static int ready = 0;  // 0 = not checked, 1 = usable, -1 = register allocation does not fit
-    if (ready == 0) {
+    static int regs_ok = 0;  // 0 = not checked, 1 = usable, -1 = register allocation does not fit
+    if (regs_ok == 0) {
         // setmaxnreg.inc blocks until the CTA's pool holds the registers: refuse to launch a build
         // whose launch allocation is smaller than the redistribution assumes.
         cudaFuncAttributes fa;
         if (cudaFuncGetAttributes(&fa, attention_split_kernel<T, MODE>) != cudaSuccess) return KB_ERR_LAUNCH;
-        if (fa.numRegs < kSplitRegsLaunch) {
-            ready = -1;
-        } else {
-            if (cudaFuncSetAttribute(attention_split_kernel<T, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     Cfg::kSmemMax) != cudaSuccess)
-                return KB_ERR_LAUNCH;
-            ready = 1;
-        }
+        regs_ok = (fa.numRegs < kSplitRegsLaunch) ? -1 : 1;
     }
-    if (ready < 0) return KB_ERR_UNSUPPORTED;
+    if (regs_ok < 0) return KB_ERR_UNSUPPORTED;
+    static PerDeviceOnce attr_once;
+    if (attr_once.first_time()) {
+        if (cudaFuncSetAttribute(attention_split_kernel<T, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 Cfg::kSmemMax) != cudaSuccess)
+            return KB_ERR_LAUNCH;
+    }
     const int64_t grid = (int64_t)d.num_pairs * p.B * p.H;
     if (grid > 0x7fffffff) return KB_ERR_UNSUPPORTED;
     const int num_n_blocks = (int)((p.N + kBlkN - 1) / kBlkN);

@@ -102,6 +102,19 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
 }
 
+// Function attributes (dynamic shared memory size) are per device: a process that drives several
+// GPUs has to set them once on each. Not synchronised: setting an attribute twice is harmless.
+struct PerDeviceOnce {
+    bool done[64] = {};
+    bool first_time() {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return true;
+        if (done[dev]) return false;
+        done[dev] = true;
+        return true;
+    }
+};
+
 // ---------------------------------------------------------------------------------------------
 // Warp-level mma.sync (m16n8k16, fp32 accumulate) and streaming loads for the HBM-bound kernels that
 // have only a few rows of A (few-row linear, decode attention): there the tensor-core generation

@@ -484,12 +484,11 @@ static int launch_linear_bn(const kb_linear_params& p, cudaStream_t stream, cons
                                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
         if (st != KB_OK) return st;
     }
-    static bool attr_set = false;  // per instantiation
-    if (!attr_set) {
+    static PerDeviceOnce attr_once;
+    if (attr_once.first_time()) {
         cudaError_t e = cudaFuncSetAttribute(linear_tc_kernel<T, BN>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
         if (e != cudaSuccess) return KB_ERR_LAUNCH;
-        attr_set = true;
     }
     const int64_t num_tiles = ((p.M + kGemmBM - 1) / kGemmBM) * ((p.N + BN - 1) / BN);
     const int64_t items = num_tiles * plan.splits;

@@ -21,6 +21,7 @@ import torch
 from kernl_b200.implementations.attention import attention_forward
 from kernl_b200.implementations.attention_skinny import skinny_attention_forward
 from kernl_b200.implementations.layer_norm import layer_norm
+from kernl_b200.implementations.rope import rope_kv_write
 from kernl_b200.implementations.linear_layer import linear_layer
 
 
@@ -67,10 +68,17 @@ class T5Kernl:
             dec_bias = hf_model.decoder.block[0].layer[0].SelfAttention.compute_bias(self.max_len, self.max_len)[0]
         self.dec_bias = dec_bias.to(device=d, dtype=dt).permute(1, 0, 2).contiguous()  # [L(query), H, L(key)]
         self._enc_bias_cache = {}
+        # T5 has no rotary embedding: identity rotation tables for the shared cache-write kernel
+        self.rot_cos = torch.ones((self.max_len, self.Dh // 2), dtype=torch.float32, device=d)
+        self.rot_sin = torch.zeros((self.max_len, self.Dh // 2), dtype=torch.float32, device=d)
 
     # ------------------------------------------------------------------ helpers
     def _rms(self, x, w):
         return layer_norm(x, w, None, self.eps, use_rms_norm=True)
+
+    def _add_rms(self, y, residual, w):
+        """(rms_norm(y + residual) * w, y + residual) in one kernel."""
+        return layer_norm(y, w, None, self.eps, use_rms_norm=True, residual=residual)
 
     def _enc_bias(self, S: int) -> torch.Tensor:
         if S not in self._enc_bias_cache:
@@ -85,15 +93,15 @@ class T5Kernl:
         H, Dh = self.H, self.Dh
         x = self.embed.index_select(0, ids.reshape(-1))
         bias = self._enc_bias(S)
-        for L in self.enc_layers:
-            h = self._rms(x, L["ln1"])
+        h = self._rms(x, self.enc_layers[0]["ln1"])
+        for li, L in enumerate(self.enc_layers):
             qkv = linear_layer(h, L["attn"]["qkv"], None).reshape(B, S, 3, H, Dh)
             q, k, v = (qkv[:, :, i].transpose(1, 2) for i in range(3))  # [B, H, S, Dh] views
             o = attention_forward(q, k, v, torch.empty_like(q), 1.0, False, bias)
-            x = x + linear_layer(o.transpose(1, 2).reshape(B * S, H * Dh), L["attn"]["o"], None)
-            h = self._rms(x, L["ln2"])
-            x = x + linear_layer(linear_layer(h, L["wi"], None, "relu"), L["wo"], None)
-        return self._rms(x, self.enc_final_ln).reshape(B, S, self.dm)
+            h, x = self._add_rms(linear_layer(o.transpose(1, 2).reshape(B * S, H * Dh), L["attn"]["o"], None), x, L["ln2"])
+            nxt = self.enc_layers[li + 1]["ln1"] if li + 1 < len(self.enc_layers) else self.enc_final_ln
+            h, x = self._add_rms(linear_layer(linear_layer(h, L["wi"], None, "relu"), L["wo"], None), x, nxt)
+        return h.reshape(B, S, self.dm)  # already through the final norm
 
     # ------------------------------------------------------------------ decoder
     def start(self, enc_out: torch.Tensor):
@@ -133,22 +141,25 @@ class T5Kernl:
         self.len_mask.index_fill_(3, self.pos, 0.0)
         # bias row of the current query position + the length mask: [1, H, 1, L]
         self_mask = (self.dec_bias.index_select(0, self.pos).reshape(1, H, 1, self.max_len) + self.len_mask).contiguous()
+        # The residual stream is carried as (x, h): every "x + sublayer" and the norm that follows it
+        # are one kernel, and the k/v of the new token go into the cache through the same kernel that
+        # the Llama decoder uses for rotary + cache write (with cos = 1, sin = 0 it only moves data).
+        h = self._rms(x, self.dec_layers[0]["ln1"])
+        n_layers = len(self.dec_layers)
         for li, L in enumerate(self.dec_layers):
-            h = self._rms(x, L["ln1"])
-            qkv = linear_layer(h, L["self"]["qkv"], None).reshape(B, 3, H, 1, Dh)
-            self.kcache[li].index_copy_(2, self.pos, qkv[:, 1])
-            self.vcache[li].index_copy_(2, self.pos, qkv[:, 2])
-            q = qkv[:, 0].contiguous()
-            o = skinny_attention_forward(q, self.kcache[li], self.vcache[li], torch.empty_like(q), 1.0, False, self_mask)
-            x = x + linear_layer(o.reshape(B, H * Dh), L["self"]["o"], None)
-            h = self._rms(x, L["ln2"])
+            qkv = linear_layer(h, L["self"]["qkv"], None)
+            q = rope_kv_write(qkv, self.kcache[li], self.vcache[li], self.rot_cos, self.rot_sin, self.pos, B, 1)
+            q = q.transpose(1, 2)  # [B, H, 1, Dh] view
+            o = skinny_attention_forward(q, self.kcache[li], self.vcache[li], torch.empty((B, H, 1, Dh), dtype=q.dtype, device=q.device),
+                                         1.0, False, self_mask)
+            h, x = self._add_rms(linear_layer(o.reshape(B, H * Dh), L["self"]["o"], None), x, L["ln2"])
             q = linear_layer(h, L["cross"]["q"], None).reshape(B, H, 1, Dh)
             o = skinny_attention_forward(q, self.cross_k[li], self.cross_v[li], torch.empty_like(q), 1.0, False, None)
-            x = x + linear_layer(o.reshape(B, H * Dh), L["cross"]["o"], None)
-            h = self._rms(x, L["ln3"])
-            x = x + linear_layer(linear_layer(h, L["wi"], None, "relu"), L["wo"], None)
+            h, x = self._add_rms(linear_layer(o.reshape(B, H * Dh), L["cross"]["o"], None), x, L["ln3"])
+            nxt = self.dec_layers[li + 1]["ln1"] if li + 1 < n_layers else self.dec_final_ln
+            h, x = self._add_rms(linear_layer(linear_layer(h, L["wi"], None, "relu"), L["wo"], None), x, nxt)
         self.pos.add_(1)
-        x = self._rms(x, self.dec_final_ln)
+        x = h  # already through the final norm
         if self.tied:
             x = x * (self.dm ** -0.5)
         return linear_layer(x, self.lm_head, None)

@@ -9,7 +9,7 @@ from kernl_b200.optimizer.attention import (
     fuse_attention_sdpa,
 )
 from kernl_b200.optimizer.dropout import remove_dropout
-from kernl_b200.optimizer.layer_norm import replace_layer_norm, replace_layer_norm_rms
+from kernl_b200.optimizer.layer_norm import fuse_add_layer_norm, replace_layer_norm, replace_layer_norm_rms
 from kernl_b200.optimizer.linear import fuse_parallel_linears, replace_all_linear
 from kernl_b200.optimizer.normalizer import normalize_operators, replace_scalar_tensor_constants
 
@@ -29,5 +29,6 @@ def dynamo_backend_ofi(gm: torch.fx.GraphModule, assume_causal=False):
     replace_all_linear(gm)
     fuse_parallel_linears(gm)
     replace_layer_norm(gm)
+    fuse_add_layer_norm(gm)
     replace_layer_norm_rms(gm)
     return gm

@@ -141,7 +141,7 @@ def test_bert_graph_is_fully_rewritten():
     c = _rewritten_ops(model, input_ids=torch.randint(0, 1000, (1, 16)), attention_mask=torch.ones(1, 16, dtype=torch.long))
     assert c["attention_wrapper"] == 2
     assert c["linear_wrapper"] == 2 * 4 + 1  # qkv (one stacked linear), o, ffn up (+GELU), ffn down per layer; pooler (+tanh)
-    assert c["layer_norm_wrapper"] == 1 + 2 * 2
+    assert c["layer_norm_residual_wrapper"] == 1 + 2 * 2 and c["layer_norm_wrapper"] == 0  # every LayerNorm follows an add
     assert c["module:Linear"] == 0 and c["module:LayerNorm"] == 0 and c["module:Dropout"] == 0
     assert c["scaled_dot_product_attention"] == 0 and c["gelu"] == 0
 

@@ -59,6 +59,22 @@ norm_fwd_rowwarp_kernel(const T* __restrict__ x, T* __restrict__ y, const T* __r
         if (col < cols) v[c] = ld_stream_16B(xr + col);
         else v[c] = make_uint4(0, 0, 0, 0);
     }
+    // Short rows: fetch gamma/beta now, next to the row itself, instead of after the statistics, where
+    // their (L1/L2) latency would sit at the end of a warp that has nothing left to overlap it with.
+    constexpr bool kEarlyAffine = CHUNKS <= 4;
+    uint4 gv[kEarlyAffine ? CHUNKS : 1], bv[kEarlyAffine ? CHUNKS : 1];
+    if (kEarlyAffine) {
+#pragma unroll
+        for (int c = 0; c < CHUNKS; ++c) {
+            const int col = KB_NORM_COL(c);
+            gv[c] = make_uint4(0, 0, 0, 0);
+            bv[c] = make_uint4(0, 0, 0, 0);
+            if (col < cols) {
+                gv[c] = *reinterpret_cast<const uint4*>(gamma + col);
+                if (!RMS && beta != nullptr) bv[c] = *reinterpret_cast<const uint4*>(beta + col);
+            }
+        }
+    }
     if (residual != nullptr) {
         // pre-norm residual stream: s = x + residual (rounded to the 16-bit type, as a separate add
         // kernel would store it), written out once and normalised from the registers
@@ -140,9 +156,14 @@ norm_fwd_rowwarp_kernel(const T* __restrict__ x, T* __restrict__ y, const T* __r
     for (int c = 0; c < CHUNKS; ++c) {
         const int col = KB_NORM_COL(c);
         if (col < cols) {
-            const uint4 g = *reinterpret_cast<const uint4*>(gamma + col);
-            uint4 b = make_uint4(0, 0, 0, 0);
-            if (!RMS && beta != nullptr) b = *reinterpret_cast<const uint4*>(beta + col);
+            uint4 g, b = make_uint4(0, 0, 0, 0);
+            if (kEarlyAffine) {
+                g = gv[c];
+                b = bv[c];
+            } else {
+                g = *reinterpret_cast<const uint4*>(gamma + col);
+                if (!RMS && beta != nullptr) b = *reinterpret_cast<const uint4*>(beta + col);
+            }
             const uint32_t xw[4] = {v[c].x, v[c].y, v[c].z, v[c].w};
             const uint32_t gw[4] = {g.x, g.y, g.z, g.w};
             const uint32_t bw[4] = {b.x, b.y, b.z, b.w};

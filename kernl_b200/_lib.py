@@ -133,7 +133,7 @@ def load() -> ctypes.CDLL:
     lib.kb_status_str.argtypes = [ctypes.c_int]
     lib.kb_status_str.restype = ctypes.c_char_p
     lib.kb_version.restype = ctypes.c_int
-    for hook in ("kb_debug_force_bn", "kb_debug_force_splits", "kb_debug_attention_variant", "kb_debug_pdl"):
+    for hook in ("kb_debug_force_bn", "kb_debug_force_splits", "kb_debug_attention_variant", "kb_debug_pdl", "kb_debug_split_tiles"):
         if hasattr(lib, hook):
             getattr(lib, hook).argtypes = [ctypes.c_int]
             getattr(lib, hook).restype = None

@@ -26,7 +26,24 @@
 
 namespace kb {
 
-constexpr int kSplitThreads = 640;
+// TILES = 2: the CTA described above (640 threads, all 512 TMEM columns, one CTA per SM). TILES = 1:
+// half of it (one query tile, 8 softmax warps + TMA + one issuer = 384 threads, 256 TMEM columns, a
+// 4-stage K/V ring), so that TWO CTAs share an SM. A launch that is only one or two waves of
+// two-tile CTAs spends a third of its time in per-CTA fixed costs (set-up, first loads from DRAM,
+// epilogue, exit) with the SM idle; with two independent CTAs per SM one CTA's fixed costs overlap
+// the other's key loop, and the second wave starts per tile, not per pair. Large launches keep
+// TILES = 2, which loads K/V once for two query tiles.
+template <int TILES>
+struct SplitShape {
+    static constexpr int kThreads = TILES * 256 + 128;
+    static constexpr int kAuxWarp = TILES * 8;  // first non-softmax warp: TMA producer; issuers follow
+    static constexpr int kRegsLaunch = TILES == 2 ? 96 : 80;  // 65536 / 640 and 65536 / (2 x 384), rounded down to 8
+    static constexpr int kRegsHigh = TILES == 2 ? 104 : 96;
+    static constexpr int kRegsLow = TILES == 2 ? 64 : 48;
+    static_assert(TILES * 2 * kRegsHigh + kRegsLow <= (TILES * 2 + 1) * kRegsLaunch, "setmaxnreg totals exceed the CTA's register pool");
+    static_assert(kRegsHigh % 8 == 0 && kRegsLow % 8 == 0, "setmaxnreg wants multiples of 8");
+};
+static int g_split_tiles = 0;  // test hook: 0 = by launch size, 1 / 2 = force the number of query tiles per CTA
 
 // 2^x for a pair of x <= 0 on the FMA pipe (no special-function unit): x = r + f with r = round(x),
 // f in [-0.5, 0.5]; 2^f by a cubic (max relative error 7.5e-5, below the rounding of a 16-bit P);
@@ -96,47 +113,44 @@ __device__ __forceinline__ void tma_prefetch_l2_4d(const CUtensorMap* map, int c
                  : "memory");
 }
 
-// Launch allocation 65536 / 640 -> 96 registers per thread; the four softmax warpgroups grow to
-// kSplitRegsHigh and the fifth warpgroup (TMA, issuers, mask loader) shrinks to kSplitRegsLow.
-// The increase waits without bound until the CTA's pool has the registers, so the totals must fit.
-constexpr int kSplitRegsLaunch = 96;
-constexpr int kSplitRegsHigh = 104;
-constexpr int kSplitRegsLow = 64;
-static_assert(4 * kSplitRegsHigh + kSplitRegsLow <= 5 * kSplitRegsLaunch, "setmaxnreg totals exceed the CTA's register pool");
-static_assert(kSplitRegsHigh % 8 == 0 && kSplitRegsLow % 8 == 0, "setmaxnreg wants multiples of 8");
-
-struct AttnSplitCfg {
+template <int TILES>
+struct AttnSplitCfgT {
     static constexpr int D = 64;
-    static constexpr int kKvStages = 8;
+    static constexpr int kKvStages = TILES == 2 ? 8 : 4;
     static constexpr int kQTileBytes = kAttnBlock * D * 2;
     static constexpr int kKvBytes = kBlkN * D * 2;
-    static constexpr int kTilesBytes = 2 * kQTileBytes + 2 * kKvStages * kKvBytes;
+    static constexpr int kTilesBytes = TILES * kQTileBytes + 2 * kKvStages * kKvBytes;
     static constexpr int kBarBytes = 1024;
     static constexpr int kXchBytes = 2 * 2 * kAttnBlock * 8;  // [tile][half][row] (m, l)
     // MODE 1 keeps the whole row-broadcast mask of its (batch, head) in shared memory, as fp32 in the
     // log2 domain, staged by all threads during set-up; longer rows take the general path (MODE 2)
     static constexpr int kMaskMaxN = 8192;
-    static constexpr int kMaskLoads = (kMaskMaxN + kSplitThreads - 1) / kSplitThreads;  // per thread
+    static constexpr int kMaskLoads = (kMaskMaxN + SplitShape<TILES>::kThreads - 1) / SplitShape<TILES>::kThreads;  // per thread
     static constexpr int kSmemBase = kTilesBytes + kBarBytes + kXchBytes + 1024;
     static constexpr int kSmemMax = kSmemBase + kMaskMaxN * 4;
 };
 
-template <typename T, int MODE>
-__global__ void __launch_bounds__(kSplitThreads, 1)
+using AttnSplitCfg = AttnSplitCfgT<2>;
+
+template <typename T, int MODE, int TILES>
+__global__ void __launch_bounds__(SplitShape<TILES>::kThreads, TILES == 2 ? 1 : 2)
 attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                        const __grid_constant__ CUtensorMap tmap_v, const AttnDev p) {
-    using Cfg = AttnSplitCfg;
+    using Cfg = AttnSplitCfgT<TILES>;
+    using Shape = SplitShape<TILES>;
+    constexpr int kThreads = Shape::kThreads;
+    constexpr int W0 = Shape::kAuxWarp;
     constexpr int D = 64;
     constexpr int KVS = Cfg::kKvStages;
     constexpr int QTILE = Cfg::kQTileBytes;
     constexpr int KVB = Cfg::kKvBytes;
     constexpr int NB = 2;
-    constexpr uint32_t kTmemCols = 512;
+    constexpr uint32_t kTmemCols = TILES * 256;
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const uint32_t q_smem = smem_u32(smem);
-    const uint32_t k_smem = q_smem + 2 * QTILE;
+    const uint32_t k_smem = q_smem + TILES * QTILE;
     const uint32_t v_smem = k_smem + KVS * KVB;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kTilesBytes);
     const uint32_t bar_base = smem_u32(bars);
@@ -179,8 +193,8 @@ attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     int mt[2], nblk[2];
     int ntl = 0;
     for (int t = 0; t < 2; ++t) {
-        mt[t] = pair * 2 + t;
-        if (mt[t] < num_m_tiles) {
+        mt[t] = pair * TILES + t;
+        if (t < TILES && mt[t] < num_m_tiles) {
             ntl = t + 1;
             nblk[t] = p.is_causal ? min(num_n_blocks, (mt[t] + 1) * (kAttnBlock / kBlkN)) : num_n_blocks;
         } else {
@@ -196,7 +210,7 @@ attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     // MODE 1 does not know which key blocks it will visit before the mask has been looked at: it
     // only pulls the first ring of K/V blocks into L2 and issues the real loads after the set-up barrier.
     const int first_kv = (MODE == 1) ? 0 : min(KVS, max_blk);
-    if (warp == 16) {
+    if (warp == W0) {
         if (lane == 0) {
             tma_prefetch_desc(&tmap_q);
             tma_prefetch_desc(&tmap_k);
@@ -242,7 +256,7 @@ attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
         if (lane < 8) mbar_init(ep_bar(lane >> 2, lane & 3), 2);
         if (lane == 0) *abort_flag = 0;
         fence_mbar_init();
-    } else if (warp == 17) {
+    } else if (warp == W0 + 1) {
         tmem_alloc(smem_u32(tmem_slot), kTmemCols);
         tmem_relinquish();
     }
@@ -254,13 +268,13 @@ attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
         float vals[Cfg::kMaskLoads];
 #pragma unroll
         for (int e = 0; e < Cfg::kMaskLoads; ++e) {
-            const int col = e * kSplitThreads + (int)threadIdx.x;
+            const int col = e * kThreads + (int)threadIdx.x;
             vals[e] = (col < p.N && col < ncols) ? mask_load(p.mask, moff + (int64_t)col * p.mask_strides[3], p.mask_dtype) : -INFINITY;
         }
 #pragma unroll
         for (int e = 0; e < Cfg::kMaskLoads; ++e) {
-            const int col = e * kSplitThreads + (int)threadIdx.x;  // a warp covers half of one key block
-            if (e * kSplitThreads < ncols) {
+            const int col = e * kThreads + (int)threadIdx.x;  // a warp covers half of one key block
+            if (e * kThreads < ncols) {
                 const bool inside = col < p.N && col < ncols;
                 const float v = inside ? fmaxf(vals[e], mlow) * kLog2e : -INFINITY;
                 if (col < ncols) mask_smem[col] = v;
@@ -291,9 +305,9 @@ attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     }
     auto next_blk = [&](int from) { return MODE == 1 ? bits_next(act, from) : from; };
 
-    if (warp >= 16) {
-      asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kSplitRegsLow));
-      if (warp == 16) {
+    if (warp >= W0) {
+      asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(Shape::kRegsLow));
+      if (warp == W0) {
         // ------------------------------------------------------------------ TMA producer
         if (elect_one()) {
             bool ok = true;
@@ -313,9 +327,9 @@ attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
                 for (int i = 0; i < 64; ++i) __nanosleep(2000);
             }
         }
-      } else if (warp == 17 || warp == 18) {
+      } else if (warp >= W0 + 1 && warp <= W0 + TILES) {
         // ------------------------------------------------------------------ MMA issuers, one per tile
-        const int t = warp - 17;
+        const int t = warp - (W0 + 1);
         if (elect_one()) {
             constexpr uint32_t idesc_qk = make_idesc_f16(Elem<T>::kIsBf16, 128, kBlkN, 0, 0);
             constexpr uint32_t idesc_pv = make_idesc_f16(Elem<T>::kIsBf16, 128, D, 0, 1);
@@ -392,7 +406,7 @@ attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
         }
       }
     } else {
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kSplitRegsHigh));
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(Shape::kRegsHigh));
         // ------------------------------------------------------------------ softmax warps
         const int t = warp >> 3;
         const int hf = (warp >> 2) & 1;  // which 32 key columns of every block
@@ -598,15 +612,16 @@ attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
 
     tc_fence_before();
     __syncthreads();
-    if (warp == 17) {
+    if (warp == W0 + 1) {
         __syncwarp();
         tmem_dealloc(tmem_base, kTmemCols);
     }
 }
 
-template <typename T, int MODE>
-static int launch_attention_split_tm(const kb_attn_params& p, cudaStream_t stream) {
-    using Cfg = AttnSplitCfg;
+template <typename T, int MODE, int TILES>
+static int launch_attention_split_tmt(const kb_attn_params& p, cudaStream_t stream) {
+    using Cfg = AttnSplitCfgT<TILES>;
+    using Shape = SplitShape<TILES>;
     constexpr int D = 64;
     CUtensorMap tq, tk, tv;
     auto enc = [&](CUtensorMap* out, const void* ptr, int64_t rows, const int64_t* st, uint32_t box_rows) -> int {
@@ -642,20 +657,20 @@ static int launch_attention_split_tm(const kb_attn_params& p, cudaStream_t strea
         d.mask_vec = (p.mask_strides[0] % per16 == 0 && p.mask_strides[1] % per16 == 0 && p.mask_strides[2] % per16 == 0) ? 1 : 0;
     }
     const int num_m_tiles = (int)((p.M + kAttnBlock - 1) / kAttnBlock);
-    d.num_pairs = (num_m_tiles + 1) / 2;
+    d.num_pairs = (num_m_tiles + TILES - 1) / TILES;  // work items per (batch, head): tile pairs, or tiles
     d.head_group = attn_head_group(p.B * p.H, p.N, p.D);
     static int regs_ok = 0;  // 0 = not checked, 1 = usable, -1 = register allocation does not fit
     if (regs_ok == 0) {
         // setmaxnreg.inc blocks until the CTA's pool holds the registers: refuse to launch a build
         // whose launch allocation is smaller than the redistribution assumes.
         cudaFuncAttributes fa;
-        if (cudaFuncGetAttributes(&fa, attention_split_kernel<T, MODE>) != cudaSuccess) return KB_ERR_LAUNCH;
-        regs_ok = (fa.numRegs < kSplitRegsLaunch) ? -1 : 1;
+        if (cudaFuncGetAttributes(&fa, attention_split_kernel<T, MODE, TILES>) != cudaSuccess) return KB_ERR_LAUNCH;
+        regs_ok = (fa.numRegs < Shape::kRegsLaunch) ? -1 : 1;
     }
     if (regs_ok < 0) return KB_ERR_UNSUPPORTED;
     static PerDeviceOnce attr_once;
     if (attr_once.first_time()) {
-        if (cudaFuncSetAttribute(attention_split_kernel<T, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        if (cudaFuncSetAttribute(attention_split_kernel<T, MODE, TILES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  Cfg::kSmemMax) != cudaSuccess)
             return KB_ERR_LAUNCH;
     }
@@ -663,8 +678,18 @@ static int launch_attention_split_tm(const kb_attn_params& p, cudaStream_t strea
     if (grid > 0x7fffffff) return KB_ERR_UNSUPPORTED;
     const int num_n_blocks = (int)((p.N + kBlkN - 1) / kBlkN);
     const size_t smem_bytes = (size_t)Cfg::kSmemBase + (MODE == 1 ? (size_t)num_n_blocks * kBlkN * 4 : 0);
-    attention_split_kernel<T, MODE><<<(unsigned)grid, kSplitThreads, smem_bytes, stream>>>(tq, tk, tv, d);
+    attention_split_kernel<T, MODE, TILES><<<(unsigned)grid, Shape::kThreads, smem_bytes, stream>>>(tq, tk, tv, d);
     return cudaGetLastError() == cudaSuccess ? KB_OK : KB_ERR_LAUNCH;
+}
+
+// One tile per CTA (two CTAs per SM) while the launch is small: fewer than four waves of two-tile CTAs.
+template <typename T, int MODE>
+static int launch_attention_split_tm(const kb_attn_params& p, cudaStream_t stream) {
+    const int64_t tiles = (p.M + kAttnBlock - 1) / kAttnBlock;
+    const int64_t pair_ctas = ((tiles + 1) / 2) * p.B * p.H;
+    if (g_split_tiles == 1 || (g_split_tiles == 0 && pair_ctas < 4 * (int64_t)sm_count()))
+        return launch_attention_split_tmt<T, MODE, 1>(p, stream);
+    return launch_attention_split_tmt<T, MODE, 2>(p, stream);
 }
 
 template <typename T>

@@ -143,6 +143,8 @@ int kb_norm_fwd(const kb_norm_params* p, void* stream) {
 void kb_debug_force_bn(int bn) { g_forced_bn = bn; }
 // Test hook: choose the fused-attention kernel (0 = by head dimension, 1 = 128-key blocks, 2 = 64-key blocks).
 void kb_debug_attention_variant(int v) { g_attn_variant = v; }
+// Test hook: query tiles per CTA of the split-row attention kernel (0 = by launch size, 1, 2).
+void kb_debug_split_tiles(int v) { g_split_tiles = v; }
 // Test / measurement hook: 0 launches the light kernels without programmatic dependent launch.
 void kb_debug_pdl(int on) { g_use_pdl = on ? 1 : 0; }
 // Test hook: force the number of K splits (0 = heuristic; needs a workspace).

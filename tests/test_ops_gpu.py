@@ -103,6 +103,22 @@ def test_attention_both_kernels(lib, variant, d, dtype, tol, mask_kind, causal, 
     O.assert_parity(out, expected, max_abs=tol, what=f"variant {variant} d={d}")
 
 
+@pytest.mark.parametrize("tiles", [1, 2], ids=["one_tile_per_cta", "two_tiles_per_cta"])
+@pytest.mark.parametrize("dtype,tol", [(torch.float16, 1e-2), (torch.bfloat16, 3e-2)], ids=["fp16", "bf16"])
+@pytest.mark.parametrize("mask_kind,causal,m,n", [("none", False, 512, 512), ("pad", False, 300, 300), ("bias", True, 257, 257),
+                                                  ("none", True, 640, 640), ("bias", False, 100, 700), ("none", False, 1, 24),
+                                                  ("pad", False, 1100, 1100)])
+def test_attention_split_rows_both_cta_shapes(lib, tiles, dtype, tol, mask_kind, causal, m, n):
+    """The head-dimension-64 kernel in both of its CTA shapes (one query tile per CTA, two CTAs per
+    SM, for small launches; two tiles per CTA otherwise), whatever the launch size would select."""
+    try:
+        lib.kb_debug_split_tiles(tiles)
+        out, expected = _run_attention(2, 3, m, n, 64, dtype, causal, mask_kind, 0.125)
+    finally:
+        lib.kb_debug_split_tiles(0)
+    O.assert_parity(out, expected, max_abs=tol, what=f"split rows, {tiles} tile(s) per CTA")
+
+
 @pytest.mark.parametrize("fill", [float("-inf"), -65504.0, -10000.0], ids=["neg_inf", "fp16_lowest", "minus_1e4"])
 @pytest.mark.parametrize("causal", [False, True], ids=["full", "causal"])
 def test_attention_padding_mask_with_fully_masked_key_blocks(lib, fill, causal):

@@ -31,8 +31,8 @@ namespace kb {
 // 4-stage K/V ring), so that TWO CTAs share an SM. A launch that is only one or two waves of
 // two-tile CTAs spends a third of its time in per-CTA fixed costs (set-up, first loads from DRAM,
 // epilogue, exit) with the SM idle; with two independent CTAs per SM one CTA's fixed costs overlap
-// the other's key loop, and the second wave starts per tile, not per pair. Large launches keep
-// TILES = 2, which loads K/V once for two query tiles.
+// the other's key loop, and the second wave starts per tile, not per pair. Measured faster at every
+// launch size, so TILES = 1 is what the dispatcher picks; TILES = 2 loads K/V once for two tiles.
 template <int TILES>
 struct SplitShape {
     static constexpr int kThreads = TILES * 256 + 128;
@@ -682,14 +682,14 @@ static int launch_attention_split_tmt(const kb_attn_params& p, cudaStream_t stre
     return cudaGetLastError() == cudaSuccess ? KB_OK : KB_ERR_LAUNCH;
 }
 
-// One tile per CTA (two CTAs per SM) while the launch is small: fewer than four waves of two-tile CTAs.
+// One tile per CTA, two CTAs per SM, is the shape the dispatcher uses: measured against the two-tile
+// CTA it is 2 % (B8 H12 S4096) to 20 % (B64 H12 S512) faster on launches of many waves as well, not
+// only on small ones — two independent CTAs hide each other's latencies better than two tiles inside
+// one CTA share K/V. The two-tile shape stays selectable (kb_debug_split_tiles) and tested.
 template <typename T, int MODE>
 static int launch_attention_split_tm(const kb_attn_params& p, cudaStream_t stream) {
-    const int64_t tiles = (p.M + kAttnBlock - 1) / kAttnBlock;
-    const int64_t pair_ctas = ((tiles + 1) / 2) * p.B * p.H;
-    if (g_split_tiles == 1 || (g_split_tiles == 0 && pair_ctas < 4 * (int64_t)sm_count()))
-        return launch_attention_split_tmt<T, MODE, 1>(p, stream);
-    return launch_attention_split_tmt<T, MODE, 2>(p, stream);
+    if (g_split_tiles == 2) return launch_attention_split_tmt<T, MODE, 2>(p, stream);
+    return launch_attention_split_tmt<T, MODE, 1>(p, stream);
 }
 
 template <typename T>

@@ -110,7 +110,7 @@ def test_attention_both_kernels(lib, variant, d, dtype, tol, mask_kind, causal, 
                                                   ("pad", False, 1100, 1100)])
 def test_attention_split_rows_both_cta_shapes(lib, tiles, dtype, tol, mask_kind, causal, m, n):
     """The head-dimension-64 kernel in both of its CTA shapes (one query tile per CTA, two CTAs per
-    SM, for small launches; two tiles per CTA otherwise), whatever the launch size would select."""
+    SM — the dispatcher's choice; two tiles per CTA, kept selectable)."""
     try:
         lib.kb_debug_split_tiles(tiles)
         out, expected = _run_attention(2, 3, m, n, 64, dtype, causal, mask_kind, 0.125)

@@ -41,6 +41,11 @@ extern "C" {
 #define KB_ACT_FAST_GELU 3   /* tanh approximation */
 #define KB_ACT_RELU      4
 #define KB_ACT_SILU      5
+/* Gated feed-forward: the rows of W are interleaved in blocks of eight (block 2j = gate rows
+ * 8j..8j+7, block 2j+1 = the matching up rows), N counts all of them (a multiple of 16), and y is
+ * [M, N/2] with y[:, 8j+i] = silu(gate) * up — the silu(w1 x) * (w3 x) of the reference's fused
+ * feed-forward experiment (experimental/llama-v2/kernel/fused_kernel_ff.py:10-114). No act_inputs. */
+#define KB_ACT_SWIGLU    6
 
 /* ---------------------------------------------------------------------------------------
  * LayerNorm / RMSNorm forward.

@@ -15,7 +15,7 @@ LIB_PATH = os.path.join(_HERE, "libkernl_b200.so")
 
 KB_OK = 0
 KB_F16, KB_BF16, KB_F32 = 0, 1, 2
-ACTIVATIONS = {"": 0, None: 0, "tanh": 1, "gelu": 2, "fast_gelu": 3, "relu": 4, "silu": 5}
+ACTIVATIONS = {"": 0, None: 0, "tanh": 1, "gelu": 2, "fast_gelu": 3, "relu": 4, "silu": 5, "swiglu": 6}
 
 EXPORTED_SYMBOLS = [
     "kb_norm_fwd",

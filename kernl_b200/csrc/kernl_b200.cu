@@ -153,7 +153,8 @@ void kb_debug_force_splits(int splits) { g_forced_splits = splits; }
 int kb_linear_fwd(const kb_linear_params* p, void* stream) {
     if (p == nullptr || p->x == nullptr || p->w == nullptr || p->y == nullptr) return KB_ERR_BAD_ARG;
     if (p->M < 0 || p->N <= 0 || p->K <= 0) return KB_ERR_BAD_ARG;
-    if (p->activation < KB_ACT_NONE || p->activation > KB_ACT_SILU) return KB_ERR_BAD_ARG;
+    if (p->activation < KB_ACT_NONE || p->activation > KB_ACT_SWIGLU) return KB_ERR_BAD_ARG;
+    if (p->activation == KB_ACT_SWIGLU && (p->N % 16 != 0 || p->act_inputs != nullptr)) return KB_ERR_BAD_ARG;
     if (p->M == 0) return KB_OK;
     if (p->K % 8 != 0 || p->x_row_stride % 8 != 0) return KB_ERR_UNSUPPORTED;
     if (((uintptr_t)p->x & 15) || ((uintptr_t)p->w & 15)) return KB_ERR_UNSUPPORTED;

@@ -173,6 +173,47 @@ __device__ __forceinline__ void epilogue_chunk(const float (&accv)[32], const T*
     }
 }
 
+// Gated epilogue (KB_ACT_SWIGLU) of one 32-column chunk: the rows of W are interleaved in blocks of
+// eight — block 2j holds gate rows 8j..8j+7, block 2j+1 the matching up rows — so a chunk carries
+// two gate/up block pairs and yields 16 output columns y[col0/2 + i] = silu(gate_i) * up_i, computed
+// from the fp32 accumulators (the [M, 2F] intermediate never exists). N is a multiple of 16, so a
+// chunk holds whole pairs or none.
+template <typename T>
+__device__ __forceinline__ void epilogue_chunk_swiglu(const float (&accv)[32], const T* __restrict__ bias,
+                                                      T* __restrict__ y_row, int col0, int N, bool row_ok) {
+    float z[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) z[j] = accv[j];
+    if (bias != nullptr) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+            if (col0 + j < N) z[j] += Elem<T>::to_f32(__ldg(bias + col0 + j));
+    }
+    if (!row_ok) return;
+    float o[16];
+#pragma unroll
+    for (int blk = 0; blk < 2; ++blk)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[blk * 8 + i] = act_silu(z[blk * 16 + i]) * z[blk * 16 + 8 + i];
+    T* dst = y_row + col0 / 2;
+    const bool aligned = (((uintptr_t)dst) & 15) == 0;
+#pragma unroll
+    for (int blk = 0; blk < 2; ++blk) {
+        if (col0 + blk * 16 >= N) break;
+        if (aligned) {
+            uint4 v;
+            v.x = Elem<T>::pack2(o[blk * 8 + 0], o[blk * 8 + 1]);
+            v.y = Elem<T>::pack2(o[blk * 8 + 2], o[blk * 8 + 3]);
+            v.z = Elem<T>::pack2(o[blk * 8 + 4], o[blk * 8 + 5]);
+            v.w = Elem<T>::pack2(o[blk * 8 + 6], o[blk * 8 + 7]);
+            reinterpret_cast<uint4*>(dst)[blk] = v;
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) dst[blk * 8 + i] = Elem<T>::from_f32(o[blk * 8 + i]);
+        }
+    }
+}
+
 template <typename T, int BN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
@@ -344,7 +385,8 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                 float accv[32];
 #pragma unroll
                 for (int j = 0; j < 32; ++j) accv[j] = __uint_as_float(r[j]);
-                epilogue_chunk<T>(accv, bias, y_row, a_row, col0, N, row < M, activation);
+                if (activation == KB_ACT_SWIGLU) epilogue_chunk_swiglu<T>(accv, bias, y_row, col0, N, row < M);
+                else epilogue_chunk<T>(accv, bias, y_row, a_row, col0, N, row < M, activation);
             }
             tc_fence_before();
             __syncwarp();
@@ -406,6 +448,36 @@ linear_splitk_finish_kernel(float* __restrict__ ws, const T* __restrict__ bias, 
             }
             if (c0 + j < N) y[(int64_t)row * y_row_stride + c0 + j] = Elem<T>::from_f32(v);
         }
+    }
+}
+
+// Second pass of a split-K launch with the gated epilogue (KB_ACT_SWIGLU): four output columns per
+// thread, read from the gate block and the up block eight columns further (see epilogue_chunk_swiglu).
+template <typename T>
+__global__ void __launch_bounds__(256)
+linear_splitk_finish_swiglu_kernel(float* __restrict__ ws, const T* __restrict__ bias, T* __restrict__ y, int M,
+                                   int N, int64_t y_row_stride) {
+    const int nq = N / 8;  // N / 2 output columns, four per thread
+    const int64_t total = (int64_t)M * nq;
+    const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int row = (int)(i / nq), oc0 = (int)(i % nq) * 4;
+        const int gc = (oc0 >> 3) * 16 + (oc0 & 7);  // gate column; the up column is gc + 8
+        float* wp = ws + (int64_t)row * N + gc;
+        const float4 g4 = __ldcg(reinterpret_cast<const float4*>(wp));
+        const float4 u4 = __ldcg(reinterpret_cast<const float4*>(wp + 8));
+        __stcg(reinterpret_cast<float4*>(wp), zero);
+        __stcg(reinterpret_cast<float4*>(wp + 8), zero);
+        float g[4] = {g4.x, g4.y, g4.z, g4.w}, u[4] = {u4.x, u4.y, u4.z, u4.w};
+        if (bias != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                g[j] += Elem<T>::to_f32(bias[gc + j]);
+                u[j] += Elem<T>::to_f32(bias[gc + 8 + j]);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) y[(int64_t)row * y_row_stride + oc0 + j] = Elem<T>::from_f32(act_silu(g[j]) * u[j]);
     }
 }
 
@@ -499,11 +571,16 @@ static int launch_linear_bn(const kb_linear_params& p, cudaStream_t stream, cons
         p.y_row_stride, p.activation, plan.splits, plan.kps, ws);
     if (cudaGetLastError() != cudaSuccess) return KB_ERR_LAUNCH;
     if (plan.splits > 1) {
-        const int64_t total = p.M * ((p.N + 3) / 4);
+        const bool gated = p.activation == KB_ACT_SWIGLU;
+        const int64_t total = gated ? p.M * (p.N / 8) : p.M * ((p.N + 3) / 4);
         int64_t blocks = (total + 255) / 256;
         if (blocks > (int64_t)sm_count() * 8) blocks = (int64_t)sm_count() * 8;
-        linear_splitk_finish_kernel<T><<<(unsigned)blocks, 256, 0, stream>>>(
-            ws, (const T*)p.bias, (T*)p.y, (T*)p.act_inputs, (int)p.M, (int)p.N, p.y_row_stride, p.activation);
+        if (gated)
+            linear_splitk_finish_swiglu_kernel<T><<<(unsigned)blocks, 256, 0, stream>>>(
+                ws, (const T*)p.bias, (T*)p.y, (int)p.M, (int)p.N, p.y_row_stride);
+        else
+            linear_splitk_finish_kernel<T><<<(unsigned)blocks, 256, 0, stream>>>(
+                ws, (const T*)p.bias, (T*)p.y, (T*)p.act_inputs, (int)p.M, (int)p.N, p.y_row_stride, p.activation);
         if (cudaGetLastError() != cudaSuccess) return KB_ERR_LAUNCH;
     }
     return KB_OK;

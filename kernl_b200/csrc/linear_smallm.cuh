@@ -102,6 +102,24 @@ linear_smallm_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* 
     __syncthreads();
     const int m = threadIdx.x >> 4, nn = threadIdx.x & 15;
     const int n = n0 + nn;
+    if (activation == KB_ACT_SWIGLU) {
+        // the CTA's first eight columns are a gate block, the other eight the matching up block
+        // (rows of W interleaved in blocks of eight): eight outputs at columns n0 / 2 ...
+        if (m < M && nn < 8 && n < N) {
+            float zg = 0.f, zu = 0.f;
+#pragma unroll
+            for (int wi = 0; wi < kSmallMThreads / 32; ++wi) {
+                zg += red[wi][m][nn];
+                zu += red[wi][m][nn + 8];
+            }
+            if (bias != nullptr) {
+                zg += Elem<T>::to_f32(bias[n]);
+                zu += Elem<T>::to_f32(bias[n + 8]);
+            }
+            y[(int64_t)m * y_row_stride + (n0 >> 1) + nn] = Elem<T>::from_f32(act_silu(zg) * zu);
+        }
+        return;
+    }
     if (m < M && n < N) {
         float z = 0.f;
 #pragma unroll

@@ -37,8 +37,9 @@ def linear_layer(
     Same contract as the reference's `linear_layer` (linear_layer.py:285-292 →
     LinearLayer.forward :213-282): x is 2-D or 3-D (flattened over its first two dims), weight is
     [N, K] contiguous, bias [N] contiguous or None, activation in {"", "tanh", "gelu",
-    "fast_gelu", "relu"} (plus "silu"); `act_inputs`, if given, receives the pre-activation
-    values. Returns [M, N], or [x.shape[0], -1, N] for 3-D x. fp32 inputs (tf32 in the
+    "fast_gelu", "relu"} (plus "silu", and "swiglu": weight rows interleaved by
+    `interleave_gate_up`, result [M, N/2] = silu(gate) * up); `act_inputs`, if given, receives the
+    pre-activation values. Returns [M, N], or [x.shape[0], -1, N] for 3-D x. fp32 inputs (tf32 in the
     reference) are not supported: fp16/bf16 only. `out` (an extension over the reference's
     signature) lets the caller provide the [M, N] contiguous result buffer, e.g. a peer-mapped one.
     """
@@ -57,6 +58,10 @@ def linear_layer(
 
     M, K = x_.shape
     N = weight.shape[0]
+    gated = activation == "swiglu"
+    if gated:
+        assert N % 16 == 0 and act_inputs is None, "swiglu wants gate/up rows in blocks of eight and no act_inputs"
+    n_out = N // 2 if gated else N
     # The TMA path wants unit K stride and 16-byte aligned rows; anything else is copied once.
     if x_.stride(1) != 1 or x_.stride(0) % 8 != 0 or x_.data_ptr() % 16 != 0:
         x_ = x_.contiguous()
@@ -67,10 +72,10 @@ def linear_layer(
         weight = torch.nn.functional.pad(weight, (0, pad))
         K += pad
     if out is not None:
-        assert out.shape == (M, N) and out.dtype == x.dtype and out.is_contiguous() and out.device == x.device
+        assert out.shape == (M, n_out) and out.dtype == x.dtype and out.is_contiguous() and out.device == x.device
         outputs = out
     else:
-        outputs = torch.empty((M, N), device=x.device, dtype=x.dtype)
+        outputs = torch.empty((M, n_out), device=x.device, dtype=x.dtype)
     if act_inputs is not None:
         assert act_inputs.shape == (M, N) and act_inputs.dtype == x.dtype and act_inputs.is_contiguous()
     if M > 0:
@@ -85,7 +90,19 @@ def linear_layer(
         )
         with torch.cuda.device(x.device):
             _lib.check(_lib.load().kb_linear_fwd(p, _lib.current_stream(x.device)), "linear_layer")
-    return outputs if x.ndim == 2 else outputs.reshape(x.shape[0], -1, N)
+    return outputs if x.ndim == 2 else outputs.reshape(x.shape[0], -1, n_out)
+
+
+def interleave_gate_up(w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.Tensor:
+    """[F, K] gate and up projection weights → the [2F, K] layout that activation="swiglu" reads:
+    blocks of eight gate rows alternate with the matching eight up rows, so that one CTA (whatever
+    its tile width) holds both halves of every output column it produces. F a multiple of 8.
+    Works on biases ([F]) too."""
+    assert w_gate.shape == w_up.shape and w_gate.shape[0] % 8 == 0
+    f = w_gate.shape[0]
+    rest = w_gate.shape[1:]
+    both = torch.stack((w_gate.reshape(f // 8, 8, *rest), w_up.reshape(f // 8, 8, *rest)), dim=1)
+    return both.reshape(2 * f, *rest).contiguous()
 
 
 def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:

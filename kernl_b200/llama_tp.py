@@ -6,8 +6,8 @@ then greedy decode with a KV cache. The reference has no such model in its dispa
 semantics of the pieces follow its experimental Llama kernels
 (experimental/llama-v2/kernel/pytorch_reference.py:6-8,37-80,88-104: RMSNorm, interleaved-pair
 rotary embedding, silu(gate)·up), and every heavy op is one of the library's kernels:
-RMSNorm (kb_norm_fwd), QKV / O / gate-up / down projections (kb_linear_fwd), silu·mul
-(kb_silu_mul), causal prefill attention (kb_attention_fwd), decode attention (kb_attention_decode_fwd).
+RMSNorm (kb_norm_fwd), QKV / O / down projections and the gate-up projection with its silu·mul
+epilogue (kb_linear_fwd), causal prefill attention (kb_attention_fwd), decode attention (kb_attention_decode_fwd).
 
 Partitioning over `world` ranks (one process per GPU): heads are split (q/k/v column-parallel, the
 KV cache is sharded by head, attention is local), `o_proj` and `down_proj` are row-parallel and
@@ -22,6 +22,8 @@ from dataclasses import dataclass
 from typing import Optional
 
 import torch
+
+from kernl_b200.implementations.linear_layer import interleave_gate_up
 
 
 @dataclass
@@ -53,10 +55,12 @@ class CudaOps:
         return linear_layer(x, w, None, out=out)
 
     @staticmethod
-    def silu_mul(gate_up):
-        from kernl_b200.implementations.linear_layer import silu_mul
+    def gated_linear(x, w_gate_up):
+        """silu(x · w_gateᵀ) * (x · w_upᵀ) in one GEMM whose epilogue does the gating; rows of
+        `w_gate_up` as `interleave_gate_up` lays them out."""
+        from kernl_b200.implementations.linear_layer import linear_layer
 
-        return silu_mul(gate_up)
+        return linear_layer(x, w_gate_up, None, activation="swiglu")
 
     @staticmethod
     def add_rms_norm(x, residual, w, eps):
@@ -134,7 +138,7 @@ class LlamaTP:
 
     def __init__(self, cfg: LlamaConfig, rank: int = 0, world: int = 1, device="cuda", dtype=torch.bfloat16,
                  ops=None, comm=None, seed: int = 0, weight_device: Optional[str] = None):
-        assert cfg.n_heads % world == 0 and cfg.ffn % world == 0
+        assert cfg.n_heads % world == 0 and cfg.ffn % (8 * world) == 0
         self.cfg, self.rank, self.world, self.device, self.dtype = cfg, rank, world, torch.device(device), dtype
         self.ops = ops if ops is not None else CudaOps()
         self.comm = comm if comm is not None else DistComm(world)
@@ -162,7 +166,7 @@ class LlamaTP:
             wo = _seeded((H, cfg.n_heads * D), 0.02, s + 4, wd, dtype)[:, r0h:r0h + hl * D].to(self.device).contiguous()
             wg = _seeded((F, H), 0.02, s + 5, wd, dtype)
             wu = _seeded((F, H), 0.02, s + 6, wd, dtype)
-            wgu = torch.cat([shard_rows(wg, r0f, fl), shard_rows(wu, r0f, fl)], dim=0).contiguous()
+            wgu = interleave_gate_up(shard_rows(wg, r0f, fl), shard_rows(wu, r0f, fl))
             del wg, wu
             wdn = _seeded((H, F), 0.02, s + 7, wd, dtype)[:, r0f:r0f + fl].to(self.device).contiguous()
             self.layers.append({
@@ -198,8 +202,7 @@ class LlamaTP:
         return self.comm.reduce_add_norm(partial, residual, next_norm, self.cfg.eps, self.ops)
 
     def _mlp(self, layer, h, residual, next_norm):
-        gu = self.ops.linear(h, layer["wgu"])
-        act = self.ops.silu_mul(gu)
+        act = self.ops.gated_linear(h, layer["wgu"])
         return self._row_parallel(act, layer["wdn"], residual, next_norm)
 
     def _next_norm(self, li):

@@ -25,9 +25,12 @@ class OracleOps:
         return O.linear(x, w).to(x.dtype)
 
     @staticmethod
-    def silu_mul(gu):
-        n = gu.shape[-1] // 2
-        return (torch.nn.functional.silu(gu[..., :n].float()) * gu[..., n:].float()).to(gu.dtype)
+    def gated_linear(x, w_gate_up):
+        # rows come in blocks of eight: gate block, up block, gate block, ...
+        w = w_gate_up.reshape(-1, 2, 8, w_gate_up.shape[-1])
+        gate = O.linear(x, w[:, 0].reshape(-1, w.shape[-1]))
+        up = O.linear(x, w[:, 1].reshape(-1, w.shape[-1]))
+        return (torch.nn.functional.silu(gate.float()) * up.float()).to(x.dtype)
 
     @staticmethod
     def add_rms_norm(x, residual, w, eps):
@@ -57,6 +60,22 @@ class OracleOps:
 
 def _cpu_model(world=1, rank=0, cfg=SMALL):
     return LlamaTP(cfg, rank=rank, world=world, device="cpu", dtype=torch.float32, ops=OracleOps(), seed=0)
+
+
+def test_gate_up_interleave_layout():
+    from kernl_b200.implementations.linear_layer import interleave_gate_up
+
+    wg = torch.arange(16 * 3, dtype=torch.float32).reshape(16, 3)
+    wu = -wg
+    w = interleave_gate_up(wg, wu)
+    assert w.shape == (32, 3)
+    assert torch.equal(w[0:8], wg[0:8]) and torch.equal(w[8:16], wu[0:8])
+    assert torch.equal(w[16:24], wg[8:16]) and torch.equal(w[24:32], wu[8:16])
+    x = torch.randn(5, 3)
+    expected = torch.nn.functional.silu(x @ wg.t()) * (x @ wu.t())
+    assert torch.allclose(OracleOps.gated_linear(x, w), expected, atol=1e-5)
+    b = interleave_gate_up(torch.arange(16.0), torch.arange(16.0) + 100)
+    assert b[:8].tolist() == list(range(8)) and b[8:16].tolist() == [100.0 + i for i in range(8)]
 
 
 def test_rope_is_a_rotation_of_interleaved_pairs():

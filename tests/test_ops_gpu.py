@@ -437,6 +437,62 @@ def test_linear_split_k(lib, shape, splits):
     O.assert_parity(pre, O.linear(x, w, b, ""))
 
 
+def _gated_case(m, k, f, dtype, with_bias, seed=0):
+    from kernl_b200.implementations.linear_layer import interleave_gate_up
+
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn((m, k), generator=g).to(dtype)
+    wg = (torch.randn((f, k), generator=g) * 0.05).to(dtype)
+    wu = (torch.randn((f, k), generator=g) * 0.05).to(dtype)
+    bg = (torch.randn((f,), generator=g) * 0.1).to(dtype) if with_bias else None
+    bu = (torch.randn((f,), generator=g) * 0.1).to(dtype) if with_bias else None
+    expected = torch.nn.functional.silu(O.linear(x, wg, bg)) * O.linear(x, wu, bu)
+    w = interleave_gate_up(wg, wu).cuda()
+    b = interleave_gate_up(bg, bu).cuda() if with_bias else None
+    return x.cuda(), w, b, expected
+
+
+@pytest.mark.parametrize("m", [1, 8, 13, 16, 100, 300, 1100])
+@pytest.mark.parametrize("f", [8, 176, 1376])
+@pytest.mark.parametrize("with_bias", [False, True], ids=["nobias", "bias"])
+def test_linear_gated_epilogue(lib, m, f, with_bias):
+    """activation="swiglu": silu(x·Wgᵀ) * (x·Wuᵀ) out of one GEMM over the interleaved weight, on
+    the few-row kernel (m <= 16), the tensor-core kernel, and its split-K form (chosen by the
+    planner for the middle sizes), against the two projections evaluated separately in fp32."""
+    from kernl_b200.implementations.linear_layer import linear_layer
+
+    x, w, b, expected = _gated_case(m, 264, f, torch.bfloat16, with_bias)
+    for _ in range(2):  # twice: a split-K workspace must come back clean
+        out = linear_layer(x, w, b, activation="swiglu")
+    assert out.shape == (m, f)
+    O.assert_parity(out, expected, max_abs=3e-2)
+
+
+@pytest.mark.parametrize("bn", [32, 64, 128, 256])
+@pytest.mark.parametrize("splits", [1, 3])
+def test_linear_gated_epilogue_every_tile_width(lib, bn, splits):
+    from kernl_b200.implementations.linear_layer import linear_layer
+
+    x, w, b, expected = _gated_case(200, 512, 328, torch.float16, True, seed=1)
+    try:
+        lib.kb_debug_force_bn(bn)
+        lib.kb_debug_force_splits(splits)
+        for _ in range(2):
+            out = linear_layer(x, w, b, activation="swiglu")
+    finally:
+        lib.kb_debug_force_bn(0)
+        lib.kb_debug_force_splits(0)
+    O.assert_parity(out, expected, max_abs=3e-2)
+
+
+def test_linear_gated_epilogue_rejects_bad_shapes(lib):
+    from kernl_b200.implementations.linear_layer import linear_layer
+
+    x = torch.zeros((4, 64), dtype=torch.float16, device="cuda")
+    with pytest.raises(AssertionError):
+        linear_layer(x, torch.zeros((24, 64), dtype=torch.float16, device="cuda"), None, activation="swiglu")
+
+
 def test_silu_mul(lib):
     from kernl_b200.implementations.linear_layer import silu_mul
 

@@ -44,6 +44,14 @@ def test_bad_arguments_are_rejected_before_any_device_call():
     assert lib.kb_linear_fwd(p, None) == -1
     p = _lib.LinearParams(x=16, w=16, y=16, M=4, N=4, K=12, x_row_stride=12, y_row_stride=4)
     assert lib.kb_linear_fwd(p, None) == -2  # K not a multiple of 8
+    gated = _lib.ACTIVATIONS["swiglu"]
+    p = _lib.LinearParams(x=16, w=16, y=16, M=4, N=24, K=16, x_row_stride=16, y_row_stride=12, activation=gated)
+    assert lib.kb_linear_fwd(p, None) == -1  # gate/up rows come in blocks of eight: N a multiple of 16
+    p = _lib.LinearParams(x=16, w=16, y=16, act_inputs=16, M=4, N=32, K=16, x_row_stride=16, y_row_stride=16,
+                          activation=gated)
+    assert lib.kb_linear_fwd(p, None) == -1  # no pre-activation output with the gated epilogue
+    p = _lib.LinearParams(x=16, w=16, y=16, M=4, N=32, K=16, x_row_stride=16, y_row_stride=16, activation=7)
+    assert lib.kb_linear_fwd(p, None) == -1
     assert lib.kb_attention_decode_scratch_bytes(2, 3, 1, 1500, 64) == 2 * 3 * 1 * 12 * 66 * 4
     assert lib.kb_attention_decode_scratch_bytes(1, 1, 1, 128 * 256 + 1, 64) == 129 * 66 * 4
 

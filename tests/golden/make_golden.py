@@ -5,6 +5,12 @@ Run where the reference tree is checked out and point KERNL_REFERENCE_ROOT at it
 stores inputs and outputs. The fixtures are small (a few hundred KB in total) and committed; the
 tests only read the .npz files, never the reference tree.
 
+The Llama pieces (RMSNorm, rotary embedding on interleaved pairs, gated feed-forward) come from the
+reference's experimental eager code, `experimental/llama-v2/kernel/pytorch_reference.py`
+(`rms_norm_pytorch`, `apply_rotary_emb_pytorch`), loaded by file path; the feed-forward is composed
+from `rms_norm_pytorch` exactly as `ff_pytorch` in `fused_kernel_ff.py:130-134` composes it (that
+file runs Triton kernels at import and cannot be loaded on a CPU-only box).
+
 Not covered (and why): the causal branch of `attention_reference` builds its mask on "cuda"
 (src/kernl/implementations/attention.py:57) and cannot run on a CPU-only box; the reference's
 `linear_layer` module does not import under the installed Triton (`triton.ops` is gone), and its
@@ -67,6 +73,32 @@ def main():
         cases[f"n{n}_f_ln"] = torch.nn.functional.layer_norm(x, (n,), w, b, 1e-5).numpy()
         cases[f"n{n}_rms"] = pytorch_naive_rmsnorm(x.clone(), w, 1e-6).numpy()
     np.savez_compressed(os.path.join(HERE, "norm_reference.npz"), **cases)
+
+    # ---- Llama pieces from the reference's experimental eager code
+    import importlib.util
+
+    spec = importlib.util.spec_from_file_location(
+        "kernl_llama_eager", os.path.join(REF_ROOT, "experimental", "llama-v2", "kernel", "pytorch_reference.py"))
+    eager = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(eager)
+    cases = {}
+    B, S, H, D = 2, 7, 3, 16
+    x = torch.randn(B, S, H, D, generator=g)
+    inv = 1.0 / (10000.0 ** (torch.arange(0, D, 2, dtype=torch.float32) / D))
+    ang = (torch.arange(S, dtype=torch.float32) + 5)[:, None] * inv[None, :]  # positions 5 .. 5 + S - 1
+    cos, sin = torch.cos(ang), torch.sin(ang)
+    cases["rope_x"], cases["rope_cos"], cases["rope_sin"] = x.numpy(), cos.numpy(), sin.numpy()
+    cases["rope_out"] = eager.apply_rotary_emb_pytorch(x, cos, sin).numpy()
+    hid, ffn = 48, 40
+    xf = torch.randn(5, hid, generator=g)
+    rms_w = torch.rand(hid, generator=g) + 0.5
+    w1 = torch.randn(ffn, hid, generator=g) * 0.2
+    w3 = torch.randn(ffn, hid, generator=g) * 0.2
+    x_norm = eager.rms_norm_pytorch(xf, rms_w, eps=1e-6)
+    cases["ff_x"], cases["ff_rms_w"], cases["ff_w1"], cases["ff_w3"] = xf.numpy(), rms_w.numpy(), w1.numpy(), w3.numpy()
+    cases["ff_x_norm"] = x_norm.numpy()
+    cases["ff_out"] = (torch.nn.functional.silu(torch.matmul(x_norm, w1.t())) * torch.matmul(x_norm, w3.t())).numpy()
+    np.savez_compressed(os.path.join(HERE, "llama_reference.npz"), **cases)
     print("wrote", os.listdir(HERE))
 
 

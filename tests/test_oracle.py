@@ -95,3 +95,39 @@ def test_kernel_eps_clamp():
     assert O.kernel_eps(1e-12, torch.float16) == 1.6e-5
     assert O.kernel_eps(1e-12, torch.bfloat16) == 1e-12
     assert O.kernel_eps(1e-3, torch.float16) == 1e-3
+
+
+# ------------------------------------------------------------------------------------------------
+# Llama pieces against vectors from the reference's experimental eager code
+# ------------------------------------------------------------------------------------------------
+@pytest.fixture(scope="module")
+def llama_golden():
+    return np.load(os.path.join(GOLDEN, "llama_reference.npz"))
+
+
+def test_rotary_matches_reference_golden(llama_golden):
+    from kernl_b200.llama_tp import apply_rope
+
+    x, cos, sin = (torch.from_numpy(llama_golden[k]) for k in ("rope_x", "rope_cos", "rope_sin"))
+    expected = torch.from_numpy(llama_golden["rope_out"])
+    assert torch.allclose(O.rotary(x, cos, sin), expected, atol=1e-6, rtol=0)
+    # the host-side helper of the decoder (used where no kernel runs) follows the same convention
+    assert torch.allclose(apply_rope(x, cos, sin), expected, atol=1e-6, rtol=0)
+
+
+def test_gated_feed_forward_matches_reference_golden(llama_golden):
+    from kernl_b200.implementations.linear_layer import interleave_gate_up
+
+    x, rms_w, w1, w3 = (torch.from_numpy(llama_golden[k]) for k in ("ff_x", "ff_rms_w", "ff_w1", "ff_w3"))
+    x_norm = O.rms_norm(x, rms_w, 1e-6)
+    assert torch.allclose(x_norm, torch.from_numpy(llama_golden["ff_x_norm"]), atol=1e-6, rtol=0)
+    expected = torch.from_numpy(llama_golden["ff_out"])
+    assert torch.allclose(O.gated_feed_forward(x_norm, w1, w3), expected, atol=1e-5, rtol=0)
+    # the interleaved weight layout the gated GEMM epilogue reads: block 2j = gate rows 8j .. 8j+7,
+    # block 2j+1 = the matching up rows; evaluated block-wise it gives the same numbers
+    w = interleave_gate_up(w1, w3)
+    z = x_norm @ w.t()
+    z = z.reshape(z.shape[0], -1, 2, 8)
+    out = (torch.nn.functional.silu(z[:, :, 0]) * z[:, :, 1]).reshape(z.shape[0], -1)
+    assert torch.allclose(out, expected, atol=1e-5, rtol=0)
+

@@ -437,6 +437,32 @@ def test_linear_split_k(lib, shape, splits):
     O.assert_parity(pre, O.linear(x, w, b, ""))
 
 
+def test_host_attention_pipeline_keeps_calls_apart(lib):
+    """Six calls with different pinned host operands through the two-deep host pipeline: each
+    result buffer must hold its own call's attention (set reuse is ordered by events), equal to
+    the direct call on device tensors bit for bit."""
+    from kernl_b200.host_pipeline import HostAttentionPipeline
+    from kernl_b200.implementations.attention import attention_forward
+
+    g = torch.Generator().manual_seed(3)
+    B, H, S, D = 2, 3, 200, 64
+    pipe = HostAttentionPipeline((B, H, S, D), (B, H, S, D), (B, 1, 1, S), torch.float16, "cuda")
+    calls = []
+    for i in range(6):
+        hq, hk, hv = (torch.randn((B, H, S, D), generator=g).half().pin_memory() for _ in range(3))
+        valid = torch.randint(1, S, (B,), generator=g)
+        hm = torch.where(valid[:, None] > torch.arange(S)[None, :], 0.0, float("-inf")).reshape(B, 1, 1, S).half().pin_memory()
+        hout = torch.full((B, H, S, D), float("nan"), dtype=torch.float16).pin_memory()
+        calls.append((hq, hk, hv, hm, hout))
+        pipe.submit(hq, hk, hv, hm, hout, 0.125)
+    pipe.synchronize()
+    for i, (hq, hk, hv, hm, hout) in enumerate(calls):
+        q, k, v, m = hq.cuda(), hk.cuda(), hv.cuda(), hm.cuda()
+        direct = attention_forward(q, k, v, torch.empty_like(q), 0.125, False, m)
+        assert torch.equal(hout, direct.cpu()), f"call {i}"
+    O.assert_parity(calls[-1][4], O.attention(calls[-1][0], calls[-1][1], calls[-1][2], 0.125, False, calls[-1][3]))
+
+
 def _gated_case(m, k, f, dtype, with_bias, seed=0):
     from kernl_b200.implementations.linear_layer import interleave_gate_up
 

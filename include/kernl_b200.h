@@ -96,7 +96,7 @@ typedef struct {
     const void* x;          /* [M,K]                                                       */
     const void* w;          /* [N,K] contiguous                                            */
     const void* bias;       /* [N] or NULL                                                 */
-    void*       y;          /* [M,N]                                                       */
+    void*       y;          /* [M,N]; [M,N/2] with KB_ACT_SWIGLU                           */
     void*       act_inputs; /* [M,N] or NULL                                               */
     int64_t     M, N, K;
     int64_t     x_row_stride;

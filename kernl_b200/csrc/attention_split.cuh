@@ -223,6 +223,7 @@ attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
                 mbar_init(v_empty(s), ntl);
             }
             fence_mbar_init();
+            pdl_wait();  // q/k/v may be the output of the kernel before this one
             for (int t = 0; t < ntl; ++t) {
                 mbar_arrive_expect_tx(q_full(t), QTILE);
                 tma_load_4d(q_smem + t * QTILE, &tmap_q, q_full(t), 0, mt[t] * kAttnBlock, h, b);
@@ -260,6 +261,10 @@ attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
         tmem_alloc(smem_u32(tmem_slot), kTmemCols);
         tmem_relinquish();
     }
+    // Launched with programmatic dependent launch: everything above (barriers, TMEM, descriptors)
+    // may run while the previous kernel of the stream drains; nothing of global memory is touched
+    // before this point.
+    pdl_wait();
     if (MODE == 1) {
         // every thread stages its share of the mask row: clamped, in the log2 domain, -inf beyond N
         const float mlow = mask_lowest(p.mask_dtype);
@@ -563,6 +568,11 @@ attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
                 __syncwarp();
                 if (lane == 0) mbar_arrive(p_full(t, bf));
             }
+            // The key loop is over: a dependent kernel's CTAs may take the slots that free up from
+            // here on and set themselves up (they read nothing before this grid has completed). The
+            // first caller in a CTA counts; no thread calls it earlier, so a dependent never
+            // competes with CTAs of this launch that have not started yet.
+            pdl_launch_dependents();
             // ---- epilogue: merge the two halves of every row, O / l -> global
             // (m, l) of this half to the partner warp (same rows, other half) through shared memory
             // a half that never saw a finite score (all of its columns beyond N) must not set the scale
@@ -678,7 +688,9 @@ static int launch_attention_split_tmt(const kb_attn_params& p, cudaStream_t stre
     if (grid > 0x7fffffff) return KB_ERR_UNSUPPORTED;
     const int num_n_blocks = (int)((p.N + kBlkN - 1) / kBlkN);
     const size_t smem_bytes = (size_t)Cfg::kSmemBase + (MODE == 1 ? (size_t)num_n_blocks * kBlkN * 4 : 0);
-    attention_split_kernel<T, MODE, TILES><<<(unsigned)grid, Shape::kThreads, smem_bytes, stream>>>(tq, tk, tv, d);
+    if (launch_pdl(attention_split_kernel<T, MODE, TILES>, (unsigned)grid, (unsigned)Shape::kThreads, smem_bytes, stream, tq,
+                   tk, tv, d) != cudaSuccess)
+        return KB_ERR_LAUNCH;
     return cudaGetLastError() == cudaSuccess ? KB_OK : KB_ERR_LAUNCH;
 }
 

@@ -27,75 +27,52 @@ def linear_wrapper_functional(v: torch.Tensor, weight: torch.Tensor, bias: torch
 torch.fx.wrap("linear_wrapper_functional")
 
 
+class _EagerLinear(torch.nn.Module):
+    """What the models contain: an nn.Linear, optionally followed by an activation (a module such
+    as nn.Tanh() or a function such as F.gelu)."""
+
+    def __init__(self, activation_fn=None):
+        super().__init__()
+        self.linear = torch.nn.Linear(1, 1)
+        self.activation = activation_fn
+
+    def forward(self, v):
+        out = self.linear(v)
+        return out if self.activation is None else self.activation(out)
+
+
+class _KernelLinear(torch.nn.Module):
+    """What replaces it: one call of the fused kernel, the activation named by its string."""
+
+    def __init__(self, activation_name=""):
+        super().__init__()
+        self.linear = torch.nn.Linear(1, 1)
+        self.activation_name = activation_name
+
+    def forward(self, v):
+        return linear_wrapper(v, self.linear, activation=self.activation_name)
+
+
 def replace_linear_activation(gm: torch.fx.GraphModule, activation_module: Callable, activation: str):
     """nn.Linear followed by an activation → one fused call (reference: optimizer/linear.py:44-66)."""
-
-    class Pattern(torch.nn.Module):
-        def __init__(self):
-            super().__init__()
-            self.linear = torch.nn.Linear(1, 1)
-            self.activation = activation_module
-
-        def forward(self, v):
-            return self.activation(self.linear(v))
-
-    class Replacement(torch.nn.Module):
-        def __init__(self):
-            super().__init__()
-            self.linear = torch.nn.Linear(1, 1)
-            self.activation = activation_module
-
-        def forward(self, v):
-            return linear_wrapper(v, self.linear, activation=activation)
-
-    replace_pattern(gm, Pattern(), Replacement())
+    replace_pattern(gm, _EagerLinear(activation_module), _KernelLinear(activation))
 
 
 def replace_linear(gm: torch.fx.GraphModule):
     """Bare nn.Linear modules (reference: optimizer/linear.py:69-86)."""
-
-    class Pattern(torch.nn.Module):
-        def __init__(self):
-            super().__init__()
-            self.linear = torch.nn.Linear(1, 1)
-
-        def forward(self, v):
-            return self.linear(v)
-
-    class Replacement(torch.nn.Module):
-        def __init__(self):
-            super().__init__()
-            self.linear = torch.nn.Linear(1, 1)
-
-        def forward(self, v):
-            return linear_wrapper(v, self.linear)
-
-    replace_pattern(gm, Pattern(), Replacement())
+    replace_pattern(gm, _EagerLinear(), _KernelLinear())
 
 
 def replace_linear_fn(gm: torch.fx.GraphModule):
-    """F.linear(v, weight, bias) calls (reference: optimizer/linear.py:89-98)."""
-
-    def pattern(v, weight, bias):
-        return torch.nn.functional.linear(v, weight, bias)
-
-    def replace(v, weight, bias):
-        return linear_wrapper_functional(v, weight, bias)
-
-    replace_pattern(gm, pattern, replace)
+    """F.linear(v, weight, bias) calls (reference: optimizer/linear.py:89-98), and the same call with
+    a literal None for the bias, which has to be part of the pattern to match (:101-110)."""
+    replace_pattern(gm, lambda v, weight, bias: torch.nn.functional.linear(v, weight, bias),
+                    lambda v, weight, bias: linear_wrapper_functional(v, weight, bias))
 
 
 def replace_linear_fn_constant_match(gm: torch.fx.GraphModule):
-    """F.linear(v, weight, None): the literal None has to be part of the pattern
-    (reference: optimizer/linear.py:101-110)."""
-
-    def pattern(v, weight):
-        return torch.nn.functional.linear(v, weight, None)
-
-    def replace(v, weight):
-        return linear_wrapper_functional(v, weight, None)
-
-    replace_pattern(gm, pattern, replace)
+    replace_pattern(gm, lambda v, weight: torch.nn.functional.linear(v, weight, None),
+                    lambda v, weight: linear_wrapper_functional(v, weight, None))
 
 
 class FusedLinear(torch.nn.Linear):

@@ -118,6 +118,8 @@ def _rewritten_ops(model, **inputs):
         for n in gm.graph.nodes:
             if n.op == "call_function":
                 counts[getattr(n.target, "__name__", str(n.target))] += 1
+                if getattr(n.target, "__name__", "") == "linear_wrapper" and n.kwargs.get("activation"):
+                    counts["linear_wrapper:" + n.kwargs["activation"]] += 1
             elif n.op == "call_module":
                 counts["module:" + type(gm.get_submodule(n.target)).__name__] += 1
 
@@ -144,6 +146,7 @@ def test_bert_graph_is_fully_rewritten():
     assert c["layer_norm_residual_wrapper"] == 1 + 2 * 2 and c["layer_norm_wrapper"] == 0  # every LayerNorm follows an add
     assert c["module:Linear"] == 0 and c["module:LayerNorm"] == 0 and c["module:Dropout"] == 0
     assert c["scaled_dot_product_attention"] == 0 and c["gelu"] == 0
+    assert c["linear_wrapper:gelu"] == 2 and c["linear_wrapper:tanh"] == 1  # fused epilogues: ffn up, pooler
 
 
 def test_t5_encoder_graph_is_fully_rewritten():
@@ -156,6 +159,7 @@ def test_t5_encoder_graph_is_fully_rewritten():
     assert c["linear_wrapper"] == 2 * 4  # q, k, v are one stacked linear
     assert c["layer_norm_rms_wrapper"] == 2 * 2 + 1
     assert c["softmax"] == 0 and c["matmul"] == 0 and c["module:Linear"] == 0 and c["rsqrt"] == 0
+    assert c["linear_wrapper:relu"] == 2 and c["module:ReLU"] == 0  # ffn up with its ReLU fused
 
 
 @pytest.mark.gpu

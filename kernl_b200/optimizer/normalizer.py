@@ -5,19 +5,13 @@ import operator
 
 import torch
 
-NORMALIZED_OPERATORS = {
-    operator.iadd: torch.add,
-    operator.iand: torch.bitwise_and,
-    operator.ifloordiv: functools.partial(torch.div, rounding_mode="floor"),
-    operator.imod: torch.remainder,
-    operator.imul: torch.mul,
-    operator.imatmul: torch.matmul,
-    operator.ior: torch.bitwise_or,
-    operator.ipow: torch.pow,
-    operator.isub: torch.sub,
-    operator.itruediv: torch.div,
-    operator.ixor: torch.bitwise_xor,
+# in-place operator `operator.i<name>` -> the out-of-place torch function with the same meaning
+_OUT_OF_PLACE = {
+    "add": torch.add, "sub": torch.sub, "mul": torch.mul, "matmul": torch.matmul, "pow": torch.pow,
+    "truediv": torch.div, "floordiv": functools.partial(torch.div, rounding_mode="floor"), "mod": torch.remainder,
+    "and": torch.bitwise_and, "or": torch.bitwise_or, "xor": torch.bitwise_xor,
 }
+NORMALIZED_OPERATORS = {getattr(operator, "i" + name): fn for name, fn in _OUT_OF_PLACE.items()}
 
 
 def normalize_operators(gm: torch.fx.GraphModule):

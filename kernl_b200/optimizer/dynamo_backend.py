@@ -14,21 +14,22 @@ from kernl_b200.optimizer.linear import fuse_parallel_linears, replace_all_linea
 from kernl_b200.optimizer.normalizer import normalize_operators, replace_scalar_tensor_constants
 
 
+def rewrite_passes(assume_causal: bool):
+    """The passes in the order they run. Operators are normalised and dropout removed before the
+    attention patterns are looked for; linears are fused with their activation before bare linears
+    are replaced, and stacked afterwards; the residual add is folded into a LayerNorm only once the
+    LayerNorm itself has been replaced."""
+    attention = [fuse_attention_pattern_1, fuse_attention_pattern_2, fuse_attention_pattern_3, fuse_attention_sdpa]
+    return (
+        [normalize_operators, replace_scalar_tensor_constants, remove_dropout]
+        + [lambda gm, rewrite=rewrite: rewrite(gm, assume_causal) for rewrite in attention]
+        + [replace_all_linear, fuse_parallel_linears, replace_layer_norm, fuse_add_layer_norm, replace_layer_norm_rms]
+    )
+
+
 def dynamo_backend_ofi(gm: torch.fx.GraphModule, assume_causal=False):
-    """Order matters: operators are normalised and dropout removed before the attention patterns
-    are looked for, and linears are fused with their activation before bare linears are replaced.
-    `assume_causal` sets the causal flag of every attention replacement, on top of whatever
-    additive mask the model passes."""
-    normalize_operators(gm)
-    replace_scalar_tensor_constants(gm)
-    remove_dropout(gm)
-    fuse_attention_pattern_1(gm, assume_causal)
-    fuse_attention_pattern_2(gm, assume_causal)
-    fuse_attention_pattern_3(gm, assume_causal)
-    fuse_attention_sdpa(gm, assume_causal)
-    replace_all_linear(gm)
-    fuse_parallel_linears(gm)
-    replace_layer_norm(gm)
-    fuse_add_layer_norm(gm)
-    replace_layer_norm_rms(gm)
+    """Rewrites one TorchDynamo graph in place and returns it. `assume_causal` sets the causal flag
+    of every attention replacement, on top of whatever additive mask the model passes."""
+    for rewrite in rewrite_passes(assume_causal):
+        rewrite(gm)
     return gm

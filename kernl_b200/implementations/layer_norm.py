@@ -44,7 +44,7 @@ def layer_norm(
     `residual` (an extension for pre-norm decoders): normalise x + residual in the same kernel and
     return the pair (y, x + residual).
     """
-    x, weight, bias = cast_if_autocast(x, weight, bias)
+    x, weight, bias, residual = cast_if_autocast(x, weight, bias, residual)
     assert x.dtype == weight.dtype, f"input and weight bias must have the same dtype: {x.dtype}, {weight.dtype}"
     if bias is not None:
         assert x.dtype == bias.dtype, f"input and bias must have the same dtype: {x.dtype}, {bias.dtype}"

@@ -144,6 +144,100 @@ def fuse_parallel_linears(gm: torch.fx.GraphModule):
     return gm
 
 
+class GatedLinear(torch.nn.Linear):
+    """The gate and up projections of a gated feed-forward as ONE weight whose rows alternate in
+    blocks of eight (eight gate rows, the matching eight up rows, ...): the layout the kernel's
+    "swiglu" epilogue reads. `out_features` counts both halves; the call returns half as many columns."""
+
+    def __init__(self, gate: torch.nn.Linear, up: torch.nn.Linear):
+        from kernl_b200.implementations.linear_layer import interleave_gate_up
+
+        super().__init__(gate.in_features, 2 * gate.out_features, bias=gate.bias is not None,
+                         device=gate.weight.device, dtype=gate.weight.dtype)
+        with torch.no_grad():
+            self.weight.copy_(interleave_gate_up(gate.weight, up.weight))
+            if self.bias is not None:
+                self.bias.copy_(interleave_gate_up(gate.bias, up.bias))
+        self.requires_grad_(False)
+
+
+def _bare_linear(gm: torch.fx.GraphModule, n):
+    """The nn.Linear behind a `linear_wrapper(v, module)` node without a fused activation, else None."""
+    if not isinstance(n, torch.fx.Node) or n.op != "call_function" or n.target is not linear_wrapper:
+        return None
+    if len(n.args) != 2 or n.kwargs.get("activation", ""):
+        return None
+    mod_node = n.args[1]
+    if not isinstance(mod_node, torch.fx.Node) or mod_node.op != "get_attr":
+        return None
+    try:
+        lin = gm.get_submodule(mod_node.target)
+    except AttributeError:
+        return None
+    return lin if type(lin) is torch.nn.Linear else None
+
+
+def _is_silu(gm: torch.fx.GraphModule, n) -> bool:
+    if not isinstance(n, torch.fx.Node) or len(n.args) != 1 or set(n.kwargs) - {"inplace"}:
+        return False
+    if n.op == "call_function":
+        return n.target is torch.nn.functional.silu
+    if n.op == "call_module":
+        return type(gm.get_submodule(n.target)) is torch.nn.SiLU
+    return False
+
+
+def fuse_gated_feed_forward(gm: torch.fx.GraphModule):
+    """silu(gate(x)) * up(x) — the feed-forward of Llama-style decoders — becomes one linear over the
+    interleaved gate/up weight whose epilogue does the gating, so the two [tokens, F] projections
+    are never written out. Not in the reference's dispatched path (its experimental
+    llama-v2/kernel/fused_kernel_ff.py:10-114 fuses the same three ops). Runs after
+    `replace_all_linear` and before `fuse_parallel_linears` (which would otherwise stack gate and
+    up as plain columns). Skipped unless both projections read the same tensor, have the same shape
+    with a multiple of eight outputs, agree on having a bias, and feed nothing else."""
+    import operator
+
+    fused_count = 0
+    for n in list(gm.graph.nodes):
+        if n.op != "call_function" or n.target not in (operator.mul, torch.mul) or len(n.args) != 2 or n.kwargs:
+            continue
+        for act, up in ((n.args[0], n.args[1]), (n.args[1], n.args[0])):
+            if not _is_silu(gm, act):
+                continue
+            gate = act.args[0]
+            gate_lin, up_lin = _bare_linear(gm, gate), _bare_linear(gm, up)
+            if gate_lin is None or up_lin is None or gate is up:
+                continue
+            if gate.args[0] is not up.args[0] or len(act.users) != 1 or len(gate.users) != 1 or len(up.users) != 1:
+                continue
+            if (gate_lin.weight.shape != up_lin.weight.shape or gate_lin.out_features % 8 != 0
+                    or (gate_lin.bias is None) != (up_lin.bias is None)
+                    or gate_lin.weight.dtype != up_lin.weight.dtype or gate_lin.weight.device != up_lin.weight.device):
+                continue
+            name = f"kernl_gated_linear_{fused_count}"
+            while hasattr(gm, name):
+                fused_count += 1
+                name = f"kernl_gated_linear_{fused_count}"
+            fused_count += 1
+            gm.add_submodule(name, GatedLinear(gate_lin, up_lin))
+            with gm.graph.inserting_before(n):
+                mod = gm.graph.get_attr(name)
+                fused = gm.graph.call_function(linear_wrapper, (gate.args[0], mod), {"activation": "swiglu"})
+            n.replace_all_uses_with(fused)
+            gm.graph.erase_node(n)
+            gm.graph.erase_node(act)
+            for lin_node in (gate, up):
+                mod_node = lin_node.args[1]
+                gm.graph.erase_node(lin_node)
+                if len(mod_node.users) == 0:
+                    gm.graph.erase_node(mod_node)
+            break
+    if fused_count:
+        gm.graph.lint()
+        gm.recompile()
+    return gm
+
+
 def replace_all_linear(gm: torch.fx.GraphModule):
     """Fused variants first, then what is left (reference: optimizer/linear.py:113-119). The
     nn.GELU / nn.SiLU module forms are additions for current model code."""

@@ -101,6 +101,162 @@ def test_static_args_helper():
     assert static_args_are_equal(n1, n1) and not static_args_are_equal(n1, n2)
 
 
+class _GatedMLP(torch.nn.Module):
+    def __init__(self, hidden=32, ffn=48, bias=False, functional=False, up_bias=None):
+        super().__init__()
+        self.gate_proj = torch.nn.Linear(hidden, ffn, bias=bias)
+        self.up_proj = torch.nn.Linear(hidden, ffn, bias=bias if up_bias is None else up_bias)
+        self.down_proj = torch.nn.Linear(ffn, hidden, bias=bias)
+        self.act_fn = torch.nn.SiLU()
+        self.functional = functional
+
+    def forward(self, x):
+        g = self.gate_proj(x)
+        g = torch.nn.functional.silu(g) if self.functional else self.act_fn(g)
+        return self.down_proj(g * self.up_proj(x))
+
+
+def _cpu_linear_layer(x, weight, bias, activation="", act_inputs=None, out=None):
+    """Stand-in for the CUDA front-end with the same contract, evaluated by the oracle: lets the
+    graph rewrites be checked numerically without a GPU."""
+    from oracle import kernl_oracle as O
+
+    if activation == "swiglu":
+        w = weight.reshape(-1, 2, 8, weight.shape[-1])
+        wg, wu = w[:, 0].reshape(-1, weight.shape[-1]), w[:, 1].reshape(-1, weight.shape[-1])
+        bg = bu = None
+        if bias is not None:
+            b = bias.reshape(-1, 2, 8)
+            bg, bu = b[:, 0].reshape(-1), b[:, 1].reshape(-1)
+        x2 = x.reshape(-1, x.shape[-1])
+        y = torch.nn.functional.silu(O.linear(x2, wg, bg)) * O.linear(x2, wu, bu)
+    else:
+        y = O.linear(x.reshape(-1, x.shape[-1]), weight, bias, activation)
+    return y.reshape(*x.shape[:-1], y.shape[-1]).to(x.dtype)
+
+
+@pytest.mark.parametrize("functional", [False, True], ids=["nn.SiLU", "F.silu"])
+@pytest.mark.parametrize("bias", [False, True], ids=["nobias", "bias"])
+def test_gated_feed_forward_becomes_one_linear(monkeypatch, functional, bias):
+    from kernl_b200.optimizer import linear as L
+
+    torch.manual_seed(0)
+    model = _GatedMLP(bias=bias, functional=functional).eval()
+    x = torch.randn(3, 5, 32)
+    expected = model(x)
+    gm = torch.fx.symbolic_trace(model)
+    L.replace_all_linear(gm)
+    L.fuse_gated_feed_forward(gm)
+    L.fuse_parallel_linears(gm)
+    calls = [n for n in gm.graph.nodes if n.op == "call_function"]
+    assert [n.kwargs.get("activation", "") for n in calls if n.target is L.linear_wrapper] == ["swiglu", ""]
+    assert all(n.target is L.linear_wrapper for n in calls)  # no mul, no silu left
+    assert not any(n.op == "call_module" for n in gm.graph.nodes)
+    fused = gm.get_submodule("kernl_gated_linear_0")
+    assert fused.weight.shape == (96, 32) and (fused.bias is not None) == bias
+    monkeypatch.setattr(L, "linear_layer", _cpu_linear_layer)
+    assert torch.allclose(gm(x), expected, atol=5e-3)  # weights are rounded to fp16 by the wrapper
+
+
+def test_gated_feed_forward_is_left_alone_when_it_does_not_fit():
+    from kernl_b200.optimizer import linear as L
+
+    def fused_count(model):
+        gm = torch.fx.symbolic_trace(model)
+        L.replace_all_linear(gm)
+        L.fuse_gated_feed_forward(gm)
+        return sum(1 for n in gm.graph.nodes if n.op == "call_function" and n.kwargs.get("activation") == "swiglu")
+
+    assert fused_count(_GatedMLP()) == 1
+    assert fused_count(_GatedMLP(ffn=44)) == 0  # not a multiple of eight outputs
+    assert fused_count(_GatedMLP(bias=False, up_bias=True)) == 0  # only one of the two has a bias
+
+    class GateUsedTwice(_GatedMLP):
+        def forward(self, x):
+            g = self.gate_proj(x)
+            return self.down_proj(self.act_fn(g) * self.up_proj(x)) + g.sum()
+
+    assert fused_count(GateUsedTwice()) == 0
+
+
+class _EagerRMSNorm(torch.nn.Module):
+    """RMSNorm the way Llama-family models spell it."""
+
+    def __init__(self, n, eps):
+        super().__init__()
+        self.weight = torch.nn.Parameter(torch.rand(n) + 0.5)
+        self.variance_epsilon = eps
+
+    def forward(self, hidden_states):
+        hidden_states = hidden_states.to(torch.float32)
+        variance = hidden_states.pow(2).mean(-1, keepdim=True)
+        hidden_states = hidden_states * torch.rsqrt(variance + self.variance_epsilon)
+        return self.weight * hidden_states.to(torch.float32)
+
+
+class _PreNormBlock(torch.nn.Module):
+    def __init__(self, hidden=32, eps=1e-5):
+        super().__init__()
+        self.norm1, self.norm2, self.final = (_EagerRMSNorm(hidden, eps) for _ in range(3))
+        self.proj = torch.nn.Linear(hidden, hidden, bias=False)
+        self.mlp = _GatedMLP(hidden=hidden, ffn=48)
+
+    def forward(self, x):
+        x = x + self.proj(self.norm1(x))
+        x = x + self.mlp(self.norm2(x))
+        return self.final(x)
+
+
+def _cpu_layer_norm(x, weight, bias, eps, implementation=None, use_rms_norm=False, residual=None):
+    """Stand-in for the CUDA norm front-end with the same contract (oracle arithmetic)."""
+    from oracle import kernl_oracle as O
+
+    total = x if residual is None else (x.float() + residual.float()).to(x.dtype)
+    y = O.rms_norm(total, weight, eps) if use_rms_norm else O.layer_norm(total, weight, bias, eps)
+    y = y.to(x.dtype)
+    return y if residual is None else (y, total)
+
+
+def test_rms_norm_with_any_eps_and_its_residual_add_are_rewritten(monkeypatch):
+    from kernl_b200.optimizer import layer_norm as N
+    from kernl_b200.optimizer import linear as L
+
+    torch.manual_seed(0)
+    model = _PreNormBlock().eval()
+    x = torch.randn(2, 5, 32)
+    expected = model(x)
+    gm = torch.fx.symbolic_trace(model)
+    L.replace_all_linear(gm)
+    L.fuse_gated_feed_forward(gm)
+    N.replace_layer_norm_rms(gm)  # T5's literal-eps form: must leave these alone (eps differs)
+    N.replace_rms_norm_any_eps(gm)
+    plain = [n for n in gm.graph.nodes if n.op == "call_function" and n.target is N.layer_norm_rms_wrapper]
+    assert len(plain) == 3 and all(n.args[2] == 1e-5 for n in plain)
+    assert not any(n.op == "call_function" and n.target is torch.rsqrt for n in gm.graph.nodes)
+    N.fuse_add_rms_norm(gm)
+    names = [getattr(n.target, "__name__", str(n.target)) for n in gm.graph.nodes if n.op == "call_function"]
+    assert names.count("layer_norm_rms_wrapper") == 1 and names.count("layer_norm_rms_residual_wrapper") == 2
+    assert names.count("add") == 0  # both residual adds moved into the norm kernel
+    monkeypatch.setattr(L, "linear_layer", _cpu_linear_layer)
+    monkeypatch.setattr(N, "layer_norm", _cpu_layer_norm)
+    assert torch.allclose(gm(x), expected, atol=5e-3)
+
+
+def test_rms_norm_rewrite_needs_the_whole_expression():
+    from kernl_b200.optimizer import layer_norm as N
+
+    class VarianceUsedTwice(_EagerRMSNorm):
+        def forward(self, hidden_states):
+            h = hidden_states.to(torch.float32)
+            variance = h.pow(2).mean(-1, keepdim=True)
+            return self.weight * (h * torch.rsqrt(variance + self.variance_epsilon)).to(torch.float32) + variance
+
+    for module, count in ((_EagerRMSNorm(16, 1e-5), 1), (VarianceUsedTwice(16, 1e-5), 0)):
+        gm = torch.fx.symbolic_trace(module)
+        N.replace_rms_norm_any_eps(gm)
+        assert sum(1 for n in gm.graph.nodes if n.op == "call_function" and n.target is N.layer_norm_rms_wrapper) == count
+
+
 def _rewritten_ops(model, **inputs):
     import torch._dynamo
 
@@ -157,9 +313,27 @@ def test_t5_encoder_graph_is_fully_rewritten():
     c = _rewritten_ops(model, input_ids=torch.randint(0, 1000, (1, 16)))
     assert c["attention_wrapper"] == 2
     assert c["linear_wrapper"] == 2 * 4  # q, k, v are one stacked linear
-    assert c["layer_norm_rms_wrapper"] == 2 * 2 + 1
+    # the first norm reads the embeddings; every other one follows a residual add and takes it along
+    assert c["layer_norm_rms_wrapper"] == 1 and c["layer_norm_rms_residual_wrapper"] == 2 * 2
     assert c["softmax"] == 0 and c["matmul"] == 0 and c["module:Linear"] == 0 and c["rsqrt"] == 0
     assert c["linear_wrapper:relu"] == 2 and c["module:ReLU"] == 0  # ffn up with its ReLU fused
+
+
+def test_llama_graph_rewrites():
+    """A Llama-shaped decoder from current `transformers` (SDPA attention, RMSNorm written out with its
+    own eps, silu-gated feed-forward): attention, every projection, every norm and every residual
+    add in front of a norm end up on the kernels; what is left is the rotary embedding and the mask
+    arithmetic."""
+    from transformers import LlamaConfig, LlamaModel
+
+    cfg = LlamaConfig(hidden_size=256, intermediate_size=512, num_hidden_layers=2, num_attention_heads=4,
+                      num_key_value_heads=4, vocab_size=1000, max_position_embeddings=128, rms_norm_eps=1e-5)
+    c = _rewritten_ops(LlamaModel(cfg).eval(), input_ids=torch.randint(0, 1000, (1, 16)))
+    assert c["attention_wrapper"] == 2 and c["scaled_dot_product_attention"] == 0
+    assert c["linear_wrapper"] == 2 * 4  # stacked q/k/v, o, gate+up (gated epilogue), down
+    assert c["linear_wrapper:swiglu"] == 2 and c["silu"] == 0 and c["module:Linear"] == 0
+    assert c["layer_norm_rms_wrapper"] == 1 and c["layer_norm_rms_residual_wrapper"] == 2 * 2
+    assert c["rsqrt"] == 0 and c["pow"] == 0
 
 
 @pytest.mark.gpu

@@ -239,7 +239,7 @@ def fuse_gated_feed_forward(gm: torch.fx.GraphModule):
 
 
 def replace_all_linear(gm: torch.fx.GraphModule):
-    """Fused variants first, then what is left (reference: optimizer/linear.py:113-119). The
+    """Fused variants first, then what is left (reference: optimizer/linear.py:113-119).
     The nn.GELU module form is an addition for current model code; a SiLU is left alone here because
     it belongs to a gated feed-forward, which `fuse_gated_feed_forward` takes as a whole."""
     replace_linear_activation(gm, torch.nn.Tanh(), "tanh")

@@ -73,12 +73,28 @@ def layer_norm_residual_wrapper(a: torch.Tensor, b: torch.Tensor, layernorm: tor
     return y
 
 
+def layer_norm_residual_sum_wrapper(a: torch.Tensor, b: torch.Tensor, layernorm: torch.nn.LayerNorm):
+    """(LayerNorm(a + b), a + b) from one kernel, for blocks that keep the sum as their residual."""
+    if layernorm.weight.dtype == torch.float32:
+        layernorm.weight.data = layernorm.weight.data.half()
+    if layernorm.bias is not None and layernorm.bias.dtype == torch.float32:
+        layernorm.bias.data = layernorm.bias.data.half()
+    fits = (a.shape == b.shape and a.dtype == b.dtype and a.dtype in (torch.float16, torch.bfloat16)
+            and a.shape[-1] % 8 == 0 and a.shape[-1] <= 6144)
+    if not fits:
+        total = a + b
+        return layer_norm(total, layernorm.weight, layernorm.bias, layernorm.eps), total
+    return layer_norm(a, layernorm.weight, layernorm.bias, layernorm.eps, residual=b)
+
+
 torch.fx.wrap("layer_norm_residual_wrapper")
+torch.fx.wrap("layer_norm_residual_sum_wrapper")
 
 
 def fuse_add_layer_norm(gm: torch.fx.GraphModule):
-    """`layer_norm_wrapper(a + b, ln)` where the sum has no other reader (the post-LayerNorm residual of
-    BERT-style blocks) becomes one call whose kernel adds and normalises. Not in the reference; an
+    """`layer_norm_wrapper(a + b, ln)` becomes one call whose kernel adds and normalises: where the sum
+    has no other reader (the post-LayerNorm residual of BERT-style blocks) it returns the normalised
+    tensor; where it has (pre-LayerNorm blocks: Whisper, GPT-2, ViT) it returns the sum as well. Not in the reference; an
     elementwise add at batch 1 is a 2-3 µs launch, and there are two per block. Runs after
     `replace_layer_norm`."""
     import operator
@@ -88,7 +104,7 @@ def fuse_add_layer_norm(gm: torch.fx.GraphModule):
         if n.op != "call_function" or n.target is not layer_norm_wrapper or len(n.args) != 2:
             continue
         src = n.args[0]
-        if not isinstance(src, torch.fx.Node) or len(src.users) != 1:
+        if not isinstance(src, torch.fx.Node):
             continue
         is_add = (src.op == "call_function" and src.target in (operator.add, torch.add)) or (
             src.op == "call_method" and src.target == "add")
@@ -97,11 +113,27 @@ def fuse_add_layer_norm(gm: torch.fx.GraphModule):
         a, b = src.args
         if not (isinstance(a, torch.fx.Node) and isinstance(b, torch.fx.Node)):
             continue
-        with gm.graph.inserting_before(n):
-            fused = gm.graph.call_function(layer_norm_residual_wrapper, (a, b, n.args[1]))
-        n.replace_all_uses_with(fused)
-        gm.graph.erase_node(n)
-        gm.graph.erase_node(src)
+        if len(src.users) == 1:
+            with gm.graph.inserting_before(n):
+                fused = gm.graph.call_function(layer_norm_residual_wrapper, (a, b, n.args[1]))
+            n.replace_all_uses_with(fused)
+            gm.graph.erase_node(n)
+            gm.graph.erase_node(src)
+        else:
+            # pre-LayerNorm blocks: the sum is also the next residual; the kernel stores it
+            module_node = n.args[1]
+            if not (isinstance(module_node, torch.fx.Node) and module_node.op == "get_attr"):
+                continue
+            src.prepend(module_node)
+            with gm.graph.inserting_after(src):
+                fused = gm.graph.call_function(layer_norm_residual_sum_wrapper, (a, b, module_node))
+            with gm.graph.inserting_after(fused):
+                normed = gm.graph.call_function(operator.getitem, (fused, 0))
+                total = gm.graph.call_function(operator.getitem, (fused, 1))
+            n.replace_all_uses_with(normed)
+            gm.graph.erase_node(n)
+            src.replace_all_uses_with(total)
+            gm.graph.erase_node(src)
         changed = True
     if changed:
         gm.graph.lint()

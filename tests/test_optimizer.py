@@ -242,6 +242,44 @@ def test_rms_norm_with_any_eps_and_its_residual_add_are_rewritten(monkeypatch):
     assert torch.allclose(gm(x), expected, atol=5e-3)
 
 
+class _PreLayerNormBlock(torch.nn.Module):
+    def __init__(self, hidden=32):
+        super().__init__()
+        self.ln1, self.ln2, self.final = (torch.nn.LayerNorm(hidden) for _ in range(3))
+        self.proj = torch.nn.Linear(hidden, hidden)
+        self.fc = torch.nn.Linear(hidden, hidden)
+
+    def forward(self, x):
+        x = x + self.proj(self.ln1(x))
+        x = x + self.fc(self.ln2(x))
+        return self.final(x) + x  # the last sum is read twice as well
+
+
+def test_pre_layer_norm_residual_adds_move_into_the_norm(monkeypatch):
+    from kernl_b200.optimizer import layer_norm as N
+    from kernl_b200.optimizer import linear as L
+
+    torch.manual_seed(0)
+    model = _PreLayerNormBlock().eval()
+    with torch.no_grad():
+        for ln in (model.ln1, model.ln2, model.final):
+            ln.weight.uniform_(0.5, 1.5)
+            ln.bias.normal_(0, 0.1)
+    x = torch.randn(2, 5, 32)
+    expected = model(x)
+    gm = torch.fx.symbolic_trace(model)
+    L.replace_all_linear(gm)
+    N.replace_layer_norm(gm)
+    N.fuse_add_layer_norm(gm)
+    names = [getattr(n.target, "__name__", str(n.target)) for n in gm.graph.nodes if n.op == "call_function"]
+    assert names.count("layer_norm_wrapper") == 1  # ln1 reads the input, no add in front of it
+    assert names.count("layer_norm_residual_sum_wrapper") == 2 and names.count("layer_norm_residual_wrapper") == 0
+    assert names.count("add") == 1  # only the last one, which follows the norm
+    monkeypatch.setattr(L, "linear_layer", _cpu_linear_layer)
+    monkeypatch.setattr(N, "layer_norm", _cpu_layer_norm)
+    assert torch.allclose(gm(x), expected, atol=5e-3)
+
+
 def test_rms_norm_rewrite_needs_the_whole_expression():
     from kernl_b200.optimizer import layer_norm as N
 
@@ -334,6 +372,24 @@ def test_llama_graph_rewrites():
     assert c["linear_wrapper:swiglu"] == 2 and c["silu"] == 0 and c["module:Linear"] == 0
     assert c["layer_norm_rms_wrapper"] == 1 and c["layer_norm_rms_residual_wrapper"] == 2 * 2
     assert c["rsqrt"] == 0 and c["pow"] == 0
+
+
+def test_whisper_encoder_graph_rewrites():
+    """Pre-LayerNorm encoder from current `transformers` (the reference tests Whisper through
+    optimize_model, test/test_torchdynamo.py:131-165): every LayerNorm takes the residual add in
+    front of it along, q/v (bias) are stacked while k (no bias) stays apart."""
+    from transformers import WhisperConfig, WhisperModel
+
+    cfg = WhisperConfig(d_model=384, encoder_layers=2, decoder_layers=2, encoder_attention_heads=6,
+                        decoder_attention_heads=6, encoder_ffn_dim=1536, decoder_ffn_dim=1536, vocab_size=1000,
+                        pad_token_id=0, bos_token_id=1, eos_token_id=2, decoder_start_token_id=1,
+                        max_source_positions=100, max_target_positions=64, num_mel_bins=80)
+    c = _rewritten_ops(WhisperModel(cfg).eval(), input_features=torch.randn(1, 80, 200),
+                       decoder_input_ids=torch.randint(0, 1000, (1, 8)))
+    assert c["attention_wrapper"] == 2 and c["scaled_dot_product_attention"] == 0 and c["softmax"] == 0
+    assert c["linear_wrapper"] == 2 * 5 and c["linear_wrapper:gelu"] == 2 and c["module:Linear"] == 0
+    assert c["layer_norm_residual_sum_wrapper"] == 4 and c["layer_norm_residual_wrapper"] == 1
+    assert c["module:LayerNorm"] == 0 and c["add"] == 0
 
 
 @pytest.mark.gpu

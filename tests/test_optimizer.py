@@ -392,6 +392,63 @@ def test_whisper_encoder_graph_rewrites():
     assert c["module:LayerNorm"] == 0 and c["add"] == 0
 
 
+def _rewritten_ops_of_every_graph(model, **inputs):
+    """Like `_rewritten_ops`, for models whose forward TorchDynamo splits into several graphs
+    (encoder, decoder, head): each graph is copied, the copy rewritten and counted, and the
+    untouched original runs on, so the whole forward is traced on the CPU."""
+    import copy
+
+    import torch._dynamo
+
+    from kernl_b200.optimizer.dynamo_backend import dynamo_backend_ofi
+
+    torch._dynamo.reset()
+    torch._dynamo.config.inline_inbuilt_nn_modules = False
+    counts = collections.Counter()
+
+    def backend(gm, example_inputs):
+        rewritten = dynamo_backend_ofi(copy.deepcopy(gm))
+        counts["graphs"] += 1
+        for n in rewritten.graph.nodes:
+            if n.op == "call_function":
+                counts[getattr(n.target, "__name__", str(n.target))] += 1
+            elif n.op == "call_module":
+                counts["module:" + type(rewritten.get_submodule(n.target)).__name__] += 1
+        return gm.forward
+
+    with torch.no_grad():
+        torch._dynamo.optimize(backend)(model.forward)(**inputs)
+    torch._dynamo.reset()
+    return counts
+
+
+def test_encoder_decoder_models_are_rewritten_in_every_graph():
+    """The two model families the reference runs through optimize_model besides BERT
+    (test/test_torchdynamo.py: T5 generation, Whisper), as current `transformers` writes them,
+    encoder AND decoder: no eager attention, linear or normalisation survives in any graph."""
+    from transformers import T5Config, T5ForConditionalGeneration, WhisperConfig, WhisperModel
+
+    t5 = T5ForConditionalGeneration(T5Config(d_model=256, d_ff=512, num_layers=1, num_decoder_layers=1, num_heads=4,
+                                             d_kv=64, vocab_size=1000, feed_forward_proj="relu")).eval()
+    c = _rewritten_ops_of_every_graph(t5, input_ids=torch.randint(0, 1000, (1, 16)),
+                                      decoder_input_ids=torch.randint(0, 1000, (1, 4)))
+    assert c["attention_wrapper"] == 3  # encoder self, decoder self, decoder cross
+    assert c["layer_norm_rms_wrapper"] + c["layer_norm_rms_residual_wrapper"] == 3 + 4
+    for eager in ("softmax", "matmul", "scaled_dot_product_attention", "rsqrt", "relu", "module:Linear", "module:ReLU"):
+        assert c[eager] == 0, eager
+
+    whisper = WhisperModel(WhisperConfig(
+        d_model=384, encoder_layers=1, decoder_layers=1, encoder_attention_heads=6, decoder_attention_heads=6,
+        encoder_ffn_dim=1536, decoder_ffn_dim=1536, vocab_size=1000, pad_token_id=0, bos_token_id=1, eos_token_id=2,
+        decoder_start_token_id=1, max_source_positions=100, max_target_positions=64, num_mel_bins=80)).eval()
+    c = _rewritten_ops_of_every_graph(whisper, input_features=torch.randn(1, 80, 200),
+                                      decoder_input_ids=torch.randint(0, 1000, (1, 8)))
+    assert c["attention_wrapper"] == 3
+    assert c["layer_norm_wrapper"] + c["layer_norm_residual_wrapper"] + c["layer_norm_residual_sum_wrapper"] == 3 + 4
+    for eager in ("softmax", "matmul", "bmm", "scaled_dot_product_attention", "module:Linear", "module:LayerNorm", "module:GELU"):
+        assert c[eager] == 0, eager
+
+
 @pytest.mark.gpu
 def test_bert_base_end_to_end(lib):
     """Config 1: BERT-base, random init (seed 0), batch 1 x seq 128, fp16 on the GPU through

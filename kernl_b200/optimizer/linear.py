@@ -161,8 +161,9 @@ class GatedLinear(torch.nn.Linear):
         self.requires_grad_(False)
 
 
-def _bare_linear(gm: torch.fx.GraphModule, n):
-    """The nn.Linear behind a `linear_wrapper(v, module)` node without a fused activation, else None."""
+def _bare_linear(gm: torch.fx.GraphModule, n, exact: bool = True):
+    """The nn.Linear behind a `linear_wrapper(v, module)` node without a fused activation, else None.
+    `exact=False` also accepts the subclasses this package builds (stacked, transposed weights)."""
     if not isinstance(n, torch.fx.Node) or n.op != "call_function" or n.target is not linear_wrapper:
         return None
     if len(n.args) != 2 or n.kwargs.get("activation", ""):
@@ -174,7 +175,9 @@ def _bare_linear(gm: torch.fx.GraphModule, n):
         lin = gm.get_submodule(mod_node.target)
     except AttributeError:
         return None
-    return lin if type(lin) is torch.nn.Linear else None
+    if exact:
+        return lin if type(lin) is torch.nn.Linear else None
+    return lin if isinstance(lin, torch.nn.Linear) else None
 
 
 def _is_silu(gm: torch.fx.GraphModule, n) -> bool:
@@ -238,10 +241,152 @@ def fuse_gated_feed_forward(gm: torch.fx.GraphModule):
     return gm
 
 
+class TransposedLinear(torch.nn.Linear):
+    """An nn.Linear built from a [in, out] weight (the layout of `transformers`' Conv1D, which
+    computes addmm(bias, x, weight)): the kernel streams W as [out, in] rows."""
+
+    def __init__(self, weight_in_out: torch.Tensor, bias):
+        super().__init__(weight_in_out.shape[0], weight_in_out.shape[1], bias=bias is not None,
+                         device=weight_in_out.device, dtype=weight_in_out.dtype)
+        with torch.no_grad():
+            self.weight.copy_(weight_in_out.t())
+            if bias is not None:
+                self.bias.copy_(bias)
+        self.requires_grad_(False)
+
+
+def _fetch(gm: torch.fx.GraphModule, node):
+    """The tensor behind a get_attr node, else None."""
+    if not isinstance(node, torch.fx.Node) or node.op != "get_attr":
+        return None
+    obj = gm
+    for part in node.target.split("."):
+        if not hasattr(obj, part):
+            return None
+        obj = getattr(obj, part)
+    return obj if isinstance(obj, torch.Tensor) else None
+
+
+def replace_addmm(gm: torch.fx.GraphModule):
+    """`torch.addmm(bias, x2d, weight)` on parameters — GPT-2's Conv1D — → the fused linear on the
+    transposed weight (transposed once, here). Not in the reference."""
+    count = 0
+    for n in list(gm.graph.nodes):
+        if n.op != "call_function" or n.target is not torch.addmm or len(n.args) != 3 or n.kwargs:
+            continue
+        bias_node, x, weight_node = n.args
+        bias, weight = _fetch(gm, bias_node), _fetch(gm, weight_node)
+        if bias is None or weight is None or weight.dim() != 2 or bias.shape != (weight.shape[1],):
+            continue
+        name = f"kernl_transposed_linear_{count}"
+        while hasattr(gm, name):
+            count += 1
+            name = f"kernl_transposed_linear_{count}"
+        count += 1
+        gm.add_submodule(name, TransposedLinear(weight, bias))
+        with gm.graph.inserting_before(n):
+            mod = gm.graph.get_attr(name)
+            fused = gm.graph.call_function(linear_wrapper, (x, mod), {"activation": ""})
+        n.replace_all_uses_with(fused)
+        gm.graph.erase_node(n)
+        for old in (bias_node, weight_node):
+            if len(old.users) == 0:
+                gm.graph.erase_node(old)
+    if count:
+        gm.graph.lint()
+        gm.recompile()
+    return gm
+
+
+def _const_and_node(n, targets):
+    """For a commutative binary call_function node: (python number, other operand), else None."""
+    if not (isinstance(n, torch.fx.Node) and n.op == "call_function" and n.target in targets and len(n.args) == 2 and not n.kwargs):
+        return None
+    a, b = n.args
+    if isinstance(a, (int, float)) and isinstance(b, torch.fx.Node):
+        return float(a), b
+    if isinstance(b, (int, float)) and isinstance(a, torch.fx.Node):
+        return float(b), a
+    return None
+
+
+def _match_tanh_gelu(root):
+    """0.5 * x * (1 + tanh(sqrt(2/pi) * (x + 0.044715 * x**3))) as `transformers` writes gelu_new.
+    Returns (x, interior nodes) or None."""
+    import operator
+
+    mul, add = (operator.mul, torch.mul), (operator.add, torch.add)
+
+    def close(value, target):
+        return abs(value - target) < 1e-6
+
+    if not (isinstance(root, torch.fx.Node) and root.op == "call_function" and root.target in mul and len(root.args) == 2):
+        return None
+    for half, one_plus in ((root.args[0], root.args[1]), (root.args[1], root.args[0])):
+        h = _const_and_node(half, mul)
+        o = _const_and_node(one_plus, add)
+        if h is None or o is None or not close(h[0], 0.5) or not close(o[0], 1.0):
+            continue
+        x, tanh = h[1], o[1]
+        if not (tanh.op == "call_function" and tanh.target is torch.tanh and len(tanh.args) == 1):
+            continue
+        scaled = _const_and_node(tanh.args[0], mul)
+        if scaled is None or not close(scaled[0], 0.7978845608028654):
+            continue
+        inner = scaled[1]
+        if not (inner.op == "call_function" and inner.target in add and len(inner.args) == 2 and not inner.kwargs):
+            continue
+        for x2, cubic in ((inner.args[0], inner.args[1]), (inner.args[1], inner.args[0])):
+            c = _const_and_node(cubic, mul)
+            if x2 is not x or c is None or not close(c[0], 0.044715):
+                continue
+            pw = c[1]
+            is_pow = (pw.op == "call_function" and pw.target is torch.pow) or (pw.op == "call_method" and pw.target == "pow")
+            if not (is_pow and len(pw.args) == 2 and pw.args[0] is x and pw.args[1] in (3, 3.0)):
+                continue
+            interior = [one_plus, tanh, tanh.args[0], inner, cubic, pw, half]
+            if any(len(node.users) != 1 for node in interior):
+                continue
+            return x, interior
+    return None
+
+
+def fuse_tanh_gelu_into_linear(gm: torch.fx.GraphModule):
+    """A bare fused linear (possibly seen through a view) whose only reader is the tanh form of GELU
+    gets activation="fast_gelu" (reference kernel: activation_func.py:40-43) and the eager expression
+    goes away. Where the expression does not sit behind such a linear it is left as it is."""
+    changed = False
+    for root in list(gm.graph.nodes):
+        m = _match_tanh_gelu(root)
+        if m is None:
+            continue
+        x, interior = m
+        lin = x
+        if lin.op == "call_method" and lin.target in ("view", "reshape") and isinstance(lin.args[0], torch.fx.Node):
+            if len(lin.args[0].users) != 1:
+                continue
+            lin = lin.args[0]
+        if _bare_linear(gm, lin, exact=False) is None or len(x.users) != 3:  # x feeds 0.5*x, x + ..., pow(x, 3)
+            continue
+        kwargs = dict(lin.kwargs)
+        kwargs["activation"] = "fast_gelu"
+        lin.kwargs = kwargs
+        root.replace_all_uses_with(x)
+        gm.graph.erase_node(root)
+        for node in interior:
+            gm.graph.erase_node(node)
+        changed = True
+    if changed:
+        gm.graph.lint()
+        gm.recompile()
+    return gm
+
+
 def replace_all_linear(gm: torch.fx.GraphModule):
     """Fused variants first, then what is left (reference: optimizer/linear.py:113-119).
     The nn.GELU module form is an addition for current model code; a SiLU is left alone here because
-    it belongs to a gated feed-forward, which `fuse_gated_feed_forward` takes as a whole."""
+    it belongs to a gated feed-forward, which `fuse_gated_feed_forward` takes as a whole. The last two
+    passes cover GPT-2: Conv1D's addmm and the tanh form of GELU written out in eager ops."""
     replace_linear_activation(gm, torch.nn.Tanh(), "tanh")
     replace_linear_activation(gm, torch.nn.ReLU(), "relu")
     replace_linear_activation(gm, torch.nn.functional.gelu, "gelu")
@@ -249,3 +394,5 @@ def replace_all_linear(gm: torch.fx.GraphModule):
     replace_linear(gm)
     replace_linear_fn(gm)
     replace_linear_fn_constant_match(gm)
+    replace_addmm(gm)
+    fuse_tanh_gelu_into_linear(gm)

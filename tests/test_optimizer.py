@@ -449,6 +449,139 @@ def test_encoder_decoder_models_are_rewritten_in_every_graph():
         assert c[eager] == 0, eager
 
 
+def _cpu_attention(q, k, v, output, sm_scale, is_causal=False, attention_mask=None):
+    """Stand-in for both attention front-ends (same signature), evaluated by the oracle."""
+    from oracle import kernl_oracle as O
+
+    output.copy_(O.attention(q, k, v, sm_scale, is_causal, attention_mask).to(output.dtype))
+    return output
+
+
+def _flat_tensors(out):
+    if isinstance(out, torch.Tensor):
+        return [out]
+    if isinstance(out, dict):
+        out = list(out.values())
+    if isinstance(out, (tuple, list)):
+        return [t for item in out for t in _flat_tensors(item)]
+    return []
+
+
+def _max_error_of_rewritten_graphs(monkeypatch, model, **inputs):
+    """Traces `model` with TorchDynamo on the CPU; every graph is copied, the copy is rewritten by the
+    full pipeline and RUN with oracle stand-ins in place of the CUDA front-ends, and its outputs are
+    compared with those of the untouched graph on the same inputs. Returns (graphs, kernel calls,
+    largest absolute difference): what the rewrites do to the numbers, apart from the kernels."""
+    import copy
+
+    import torch._dynamo
+
+    from kernl_b200.optimizer import attention as A
+    from kernl_b200.optimizer import layer_norm as N
+    from kernl_b200.optimizer import linear as L
+    from kernl_b200.optimizer.dynamo_backend import dynamo_backend_ofi
+
+    monkeypatch.setattr(L, "linear_layer", _cpu_linear_layer)
+    monkeypatch.setattr(N, "layer_norm", _cpu_layer_norm)
+    monkeypatch.setattr(A, "attention_forward", _cpu_attention)
+    monkeypatch.setattr(A, "skinny_attention_forward", _cpu_attention)
+    wrappers = {"attention_wrapper", "linear_wrapper", "linear_wrapper_functional", "layer_norm_wrapper",
+                "layer_norm_rms_wrapper", "layer_norm_residual_wrapper", "layer_norm_residual_sum_wrapper",
+                "layer_norm_rms_residual_wrapper"}
+    stats = {"graphs": 0, "calls": 0, "max_abs": 0.0}
+    torch._dynamo.reset()
+    torch._dynamo.config.inline_inbuilt_nn_modules = False
+
+    def backend(gm, example_inputs):
+        rewritten = dynamo_backend_ofi(copy.deepcopy(gm))
+        stats["graphs"] += 1
+        stats["calls"] += sum(1 for n in rewritten.graph.nodes
+                              if n.op == "call_function" and getattr(n.target, "__name__", "") in wrappers)
+
+        def run(*args):
+            want = _flat_tensors(gm.forward(*args))
+            got = _flat_tensors(rewritten.forward(*args))
+            assert len(want) == len(got)
+            for w, g in zip(want, got):
+                assert w.shape == g.shape
+                if w.is_floating_point() and w.numel():
+                    stats["max_abs"] = max(stats["max_abs"], float((w.float() - g.float()).abs().max()))
+                else:
+                    assert torch.equal(w, g)
+            return gm.forward(*args)
+
+        return run
+
+    with torch.no_grad():
+        torch._dynamo.optimize(backend)(model.forward)(**inputs)
+    torch._dynamo.reset()
+    return stats["graphs"], stats["calls"], stats["max_abs"]
+
+
+def _small_models():
+    from transformers import (BertConfig, BertModel, GPT2Config, GPT2Model, LlamaConfig, LlamaModel, T5Config,
+                              T5ForConditionalGeneration, WhisperConfig, WhisperModel)
+
+    ids = torch.randint(3, 1000, (2, 16), generator=torch.Generator().manual_seed(0))
+    yield "bert", BertModel(BertConfig(hidden_size=256, num_hidden_layers=2, num_attention_heads=4, intermediate_size=512,
+                                       vocab_size=1000)), dict(input_ids=ids, attention_mask=torch.ones(2, 16, dtype=torch.long)), 7 * 2 + 2
+    yield "t5", T5ForConditionalGeneration(T5Config(d_model=256, d_ff=512, num_layers=2, num_decoder_layers=2, num_heads=4,
+                                                    d_kv=64, vocab_size=1000, feed_forward_proj="relu")), dict(
+        input_ids=ids, decoder_input_ids=ids[:, :4]), 20
+    yield "whisper", WhisperModel(WhisperConfig(
+        d_model=256, encoder_layers=2, decoder_layers=2, encoder_attention_heads=4, decoder_attention_heads=4,
+        encoder_ffn_dim=512, decoder_ffn_dim=512, vocab_size=1000, pad_token_id=0, bos_token_id=1, eos_token_id=2,
+        decoder_start_token_id=1, max_source_positions=100, max_target_positions=64, num_mel_bins=80)), dict(
+        input_features=torch.randn(2, 80, 200, generator=torch.Generator().manual_seed(1)), decoder_input_ids=ids[:, :8]), 20
+    yield "llama", LlamaModel(LlamaConfig(hidden_size=256, intermediate_size=512, num_hidden_layers=2, num_attention_heads=4,
+                                          num_key_value_heads=4, vocab_size=1000, max_position_embeddings=128,
+                                          rms_norm_eps=1e-5)), dict(input_ids=ids), 2 * 7 + 1
+    yield "gpt2", GPT2Model(GPT2Config(n_embd=256, n_layer=2, n_head=4, vocab_size=1000, n_positions=64)), dict(input_ids=ids), 2 * 7 + 1
+
+
+@pytest.mark.parametrize("name", ["bert", "t5", "whisper", "llama", "gpt2"])
+def test_rewritten_graphs_compute_what_the_model_computes(monkeypatch, name):
+    """End to end on the CPU: the rewritten graphs of five model families, run with the oracle in
+    place of the kernels, reproduce the eager graphs (weights are rounded to fp16 by the wrappers,
+    hence the tolerance). Catches a rewrite that drops a residual, swaps q/k/v slices, interleaves
+    gate/up rows wrongly or mis-scales attention — none of which needs a GPU to go wrong."""
+    model, inputs = _sharpened(name)
+    graphs, calls, max_abs = _max_error_of_rewritten_graphs(monkeypatch, model, **inputs)
+    assert graphs >= 1 and calls >= _sharpened.min_calls, (graphs, calls)
+    assert max_abs < 5e-2, max_abs
+
+
+def _sharpened(name):
+    """The named small model with its matrices scaled by four: random-init attention is close to
+    uniform and hides mistakes; with larger weights a 10 % error in the softmax scale moves the
+    outputs by 0.15 - 0.75 while the fp16 rounding of the weights stays below 0.025."""
+    torch.manual_seed(0)
+    for model_name, model, inputs, min_calls in _small_models():
+        if model_name == name:
+            with torch.no_grad():
+                for p in model.parameters():
+                    if p.dim() >= 2:
+                        p.mul_(4.0)
+            _sharpened.min_calls = min_calls
+            return model.eval(), inputs
+    raise KeyError(name)
+
+
+def test_the_cpu_harness_notices_a_wrong_attention_scale(monkeypatch):
+    import sys
+
+    this = sys.modules[__name__]
+    honest = this._cpu_attention
+
+    def scaled_wrongly(q, k, v, output, sm_scale, is_causal=False, attention_mask=None):
+        return honest(q, k, v, output, sm_scale * 0.9, is_causal, attention_mask)
+
+    monkeypatch.setattr(this, "_cpu_attention", scaled_wrongly)
+    model, inputs = _sharpened("bert")
+    _, _, max_abs = _max_error_of_rewritten_graphs(monkeypatch, model, **inputs)
+    assert max_abs > 0.1, max_abs
+
+
 @pytest.mark.gpu
 def test_bert_base_end_to_end(lib):
     """Config 1: BERT-base, random init (seed 0), batch 1 x seq 128, fp16 on the GPU through

@@ -537,11 +537,27 @@ def _small_models():
                                           num_key_value_heads=4, vocab_size=1000, max_position_embeddings=128,
                                           rms_norm_eps=1e-5)), dict(input_ids=ids), 2 * 7 + 1
     yield "gpt2", GPT2Model(GPT2Config(n_embd=256, n_layer=2, n_head=4, vocab_size=1000, n_positions=64)), dict(input_ids=ids), 2 * 7 + 1
+    # families the reference never saw: grouped-query decoders, OPT, ALBERT (shared layers, gelu_new), ViT
+    import transformers as tf
+
+    ones = torch.ones(2, 16, dtype=torch.long)
+    yield "mistral_gqa", tf.MistralModel(tf.MistralConfig(
+        hidden_size=256, intermediate_size=512, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+        vocab_size=1000, max_position_embeddings=128, sliding_window=None)), dict(input_ids=ids), 2 * 7 + 1
+    yield "opt", tf.OPTModel(tf.OPTConfig(hidden_size=256, ffn_dim=512, num_hidden_layers=2, num_attention_heads=4,
+                                          vocab_size=1000, max_position_embeddings=64, word_embed_proj_dim=256)), dict(
+        input_ids=ids, attention_mask=ones), 2 * 7 + 1
+    yield "albert", tf.AlbertModel(tf.AlbertConfig(hidden_size=256, embedding_size=128, intermediate_size=512,
+                                                   num_hidden_layers=2, num_attention_heads=4, vocab_size=1000)), dict(
+        input_ids=ids, attention_mask=ones), 2 * 7 + 2
+    yield "vit", tf.ViTModel(tf.ViTConfig(hidden_size=256, intermediate_size=512, num_hidden_layers=2, num_attention_heads=4,
+                                          image_size=32, patch_size=8)), dict(
+        pixel_values=torch.randn(2, 3, 32, 32, generator=torch.Generator().manual_seed(2))), 2 * 7 + 1
 
 
-@pytest.mark.parametrize("name", ["bert", "t5", "whisper", "llama", "gpt2"])
+@pytest.mark.parametrize("name", ["bert", "t5", "whisper", "llama", "gpt2", "mistral_gqa", "opt", "albert", "vit"])
 def test_rewritten_graphs_compute_what_the_model_computes(monkeypatch, name):
-    """End to end on the CPU: the rewritten graphs of five model families, run with the oracle in
+    """End to end on the CPU: the rewritten graphs of nine model families, run with the oracle in
     place of the kernels, reproduce the eager graphs (weights are rounded to fp16 by the wrappers,
     hence the tolerance). Catches a rewrite that drops a residual, swaps q/k/v slices, interleaves
     gate/up rows wrongly or mis-scales attention — none of which needs a GPU to go wrong."""

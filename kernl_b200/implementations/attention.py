@@ -82,6 +82,21 @@ def make_params(q, k, v, output, sm_scale, is_causal, attention_mask) -> "_lib.A
     return p
 
 
+def _attention_other_head_dim(q, k, v, output, sm_scale, is_causal, attention_mask):
+    """The kernels are built for head dimensions 64 and 128. Any smaller one (the reference's Triton
+    kernel takes the powers of two from 16 up, attention.py:122-135) runs as the next of the two with
+    zero columns appended to q, k and v: zeros add nothing to q·kᵀ, and the extra output columns
+    (zeros) are dropped. Costs one padded copy of the operands; meant for small models, not for speed."""
+    dhead = q.shape[-1]
+    assert dhead < 128, f"head dimension above 128 is not supported, got {dhead}"
+    extra = (64 if dhead < 64 else 128) - dhead
+    qp, kp, vp = (torch.nn.functional.pad(t, (0, extra)) for t in (q, k, v))
+    padded_out = torch.empty(qp.shape, dtype=output.dtype, device=output.device)
+    attention_forward(qp, kp, vp, padded_out, sm_scale, is_causal, attention_mask)
+    output.copy_(padded_out[..., :dhead])
+    return output
+
+
 def attention_forward(
     q: torch.Tensor,
     k: torch.Tensor,
@@ -97,7 +112,7 @@ def attention_forward(
     Attention.forward :438-529): q [B,H,M,D], k/v [B,H,N,D], all fp16 or all bf16;
     attention_mask additive, broadcastable over batch / heads / rows with last size N; -inf mask
     entries behave as the lowest finite value of the mask dtype; `is_causal` keeps col <= row.
-    Head dimension 64 or 128.
+    Head dimension 64 or 128 natively; smaller ones through zero padding.
     """
     q, k, v, output, attention_mask = cast_if_autocast(q, k, v, output, attention_mask)
     assert q.shape[-1] == k.shape[-1]
@@ -108,7 +123,8 @@ def attention_forward(
     assert q.is_cuda, "kernl_b200 ops run on a CUDA (sm_100a) device only"
     batch, heads, m_size, dhead = q.size()
     n_size = k.size(2)
-    assert dhead in (64, 128), f"head dimension must be 64 or 128 on the tcgen05 kernel, got {dhead}"
+    if dhead not in (64, 128):
+        return _attention_other_head_dim(q, k, v, output, sm_scale, is_causal, attention_mask)
     if attention_mask is not None:
         _check_mask(attention_mask, batch, heads, m_size, n_size)
         assert attention_mask.dtype in (torch.float16, torch.bfloat16, torch.float32)

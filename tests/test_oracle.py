@@ -97,6 +97,17 @@ def test_kernel_eps_clamp():
     assert O.kernel_eps(1e-3, torch.float16) == 1e-3
 
 
+def test_zero_padding_the_head_dimension_changes_nothing():
+    """What the attention front-end relies on for head dimensions other than 64 / 128."""
+    g = torch.Generator().manual_seed(5)
+    q, k, v = (torch.randn(2, 3, 17, 32, generator=g) for _ in range(3))
+    mask = torch.rand(2, 1, 1, 17, generator=g)
+    want = O.attention(q, k, v, 0.2, True, mask)
+    pad = lambda t: torch.nn.functional.pad(t, (0, 32))
+    got = O.attention(pad(q), pad(k), pad(v), 0.2, True, mask)
+    assert torch.allclose(got[..., :32], want, atol=1e-6) and float(got[..., 32:].abs().max()) == 0.0
+
+
 # ------------------------------------------------------------------------------------------------
 # Llama pieces against vectors from the reference's experimental eager code
 # ------------------------------------------------------------------------------------------------

@@ -11,20 +11,36 @@ reference's experimental eager code, `experimental/llama-v2/kernel/pytorch_refer
 from `rms_norm_pytorch` exactly as `ff_pytorch` in `fused_kernel_ff.py:130-134` composes it (that
 file runs Triton kernels at import and cannot be loaded on a CPU-only box).
 
-Not covered (and why): the causal branch of `attention_reference` builds its mask on "cuda"
-(src/kernl/implementations/attention.py:57) and cannot run on a CPU-only box; the reference's
-`linear_layer` module does not import under the installed Triton (`triton.ops` is gone), and its
-tests use plain `F.linear` + activation as ground truth anyway.
+The causal branch of `attention_reference` builds its triangular mask with a literal
+`device="cuda"` (src/kernl/implementations/attention.py:57). The function is still run unmodified:
+a `TorchFunctionMode` redirects that one factory call's `device="cuda"` to the CPU, everything else
+(the masking rule `row >= col`, top-left aligned when M != N; the order scale -> mask -> causal ->
+softmax) is the reference's own code. Cases: square, more keys than queries, more queries than
+keys, with an additive bias, with a padding mask, and head dimension 128.
+
+Not covered (and why): the reference's `linear_layer` module does not import under the installed
+Triton (`triton.ops` is gone), and its tests use plain `F.linear` + activation as ground truth anyway.
 """
 import os
 import sys
 
 import numpy as np
 import torch
+from torch.overrides import TorchFunctionMode
 
 REF_ROOT = os.environ.get("KERNL_REFERENCE_ROOT", os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "..", "..", "reference"))
 sys.path.insert(0, os.path.join(REF_ROOT, "src"))
 HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+class _CudaFactoriesOnCpu(TorchFunctionMode):
+    """Runs factory calls that name `device="cuda"` on the CPU (this box has no GPU)."""
+
+    def __torch_function__(self, func, types, args=(), kwargs=None):
+        kwargs = dict(kwargs or {})
+        if kwargs.get("device") == "cuda":
+            kwargs["device"] = "cpu"
+        return func(*args, **kwargs)
 
 
 def main():
@@ -53,6 +69,32 @@ def main():
         elif kind == "rowvec":
             mask = torch.rand(B, H, 1, N, generator=g)
         out = attention_reference(q, k, v, torch.empty_like(q), scale, False, mask)
+        cases[f"{name}_q"], cases[f"{name}_k"], cases[f"{name}_v"] = q.numpy(), k.numpy(), v.numpy()
+        if mask is not None:
+            cases[f"{name}_mask"] = mask.numpy()
+        cases[f"{name}_scale"] = np.float32(scale)
+        cases[f"{name}_out"] = out.numpy()
+    # ---- attention, causal branch (own generator: the arrays above keep their values)
+    gc = torch.Generator().manual_seed(1)
+    for name, (B, H, M, N, D, kind, scale) in {
+        "causal_square": (2, 2, 48, 48, 64, None, 0.125),
+        "causal_morekeys": (1, 3, 20, 45, 64, None, 0.3),
+        "causal_morequeries": (1, 2, 45, 20, 64, None, 0.3),
+        "causal_bias": (1, 2, 33, 33, 64, "bias", 0.125),
+        "causal_pad": (2, 2, 40, 40, 64, "pad", 0.125),
+        "causal_d128": (1, 2, 37, 37, 128, None, 0.0883883),
+    }.items():
+        q = torch.randn(B, H, M, D, generator=gc)
+        k = torch.randn(B, H, N, D, generator=gc)
+        v = torch.randn(B, H, N, D, generator=gc)
+        mask = None
+        if kind == "pad":
+            valid = torch.randint(1, N, (B,), generator=gc)
+            mask = torch.where(valid[:, None] > torch.arange(N)[None, :], 0.0, float("-inf")).reshape(B, 1, 1, N)
+        elif kind == "bias":
+            mask = torch.rand(B, H, M, N, generator=gc)
+        with _CudaFactoriesOnCpu():
+            out = attention_reference(q, k, v, torch.empty_like(q), scale, True, mask)
         cases[f"{name}_q"], cases[f"{name}_k"], cases[f"{name}_v"] = q.numpy(), k.numpy(), v.numpy()
         if mask is not None:
             cases[f"{name}_mask"] = mask.numpy()

@@ -212,6 +212,58 @@ def test_attention_against_reference_golden(lib, name):
     O.assert_parity(out, torch.from_numpy(g[f"{name}_out"]), max_abs=5e-2, cos=0.999)
 
 
+@pytest.mark.parametrize("name", ["causal_square", "causal_morekeys", "causal_morequeries", "causal_bias", "causal_pad", "causal_d128"])
+def test_attention_causal_against_reference_golden(lib, name):
+    """The kernels' causal branch against outputs of the reference's own
+    `attention_reference(is_causal=True)` (src/kernl/implementations/attention.py:29-61)."""
+    from kernl_b200.implementations.attention import attention_forward
+
+    g = np.load(os.path.join(GOLDEN, "attention_reference.npz"))
+    q, k, v = (torch.from_numpy(g[f"{name}_{t}"]).half() for t in "qkv")
+    mask = torch.from_numpy(g[f"{name}_mask"]).half() if f"{name}_mask" in g.files else None
+    expected = O.attention(q, k, v, float(g[f"{name}_scale"]), True, mask)
+    qc, kc, vc, mc = _cuda(q, k, v, mask)
+    out = attention_forward(qc, kc, vc, torch.empty_like(qc), float(g[f"{name}_scale"]), True, mc)
+    O.assert_parity(out, expected)
+    O.assert_parity(out, torch.from_numpy(g[f"{name}_out"]), max_abs=5e-2, cos=0.999)
+
+
+@pytest.mark.parametrize("kind", ["full", "causal", "pad"])
+@pytest.mark.parametrize("seq", [2048, 4096])
+@pytest.mark.parametrize("d,dtype,tol", [(64, torch.float16, 1e-2), (128, torch.bfloat16, 3e-2)], ids=["d64_fp16", "d128_bf16"])
+def test_attention_long_sequences_sampled_rows(lib, d, dtype, tol, seq, kind):
+    """The sizes the benchmark sweep quotes (4096 tokens split into sequences of 2048 / 4096 keys,
+    both head dimensions): 128-row query tiles sampled from the first, a middle and the last part
+    of several (batch, head) pairs against the oracle evaluated on those rows alone (a causal
+    row only needs the keys up to itself, so the oracle gets the row offset through a bias-free
+    slice: queries [r0, r0+128) against keys [0, r0+128) with a top-left mask shifted by r0)."""
+    from kernl_b200.implementations.attention import attention_forward
+
+    g = torch.Generator().manual_seed(seq + d)
+    B, H = 4096 // seq if d == 64 else 2, 12 if d == 64 else 32
+    B = max(B, 2)
+    q, k, v = (torch.randn((B, H, seq, d), generator=g).to(dtype) for _ in range(3))
+    mask = None
+    valid = torch.full((B,), seq)
+    if kind == "pad":
+        valid = torch.randint(64, seq + 1, (B,), generator=g)
+        mask = torch.where(valid[:, None] > torch.arange(seq)[None, :], 0.0, float("-inf")).reshape(B, 1, 1, seq).to(dtype)
+    scale = d ** -0.5
+    qc, kc, vc, mc = _cuda(q, k, v, mask)
+    out = attention_forward(qc, kc, vc, torch.empty_like(qc), scale, kind == "causal", mc).cpu()
+    for b, h, r0 in [(0, 0, 0), (B - 1, H - 1, seq - 128), (B - 1, 3, seq // 2 - 64), (0, H // 2, seq // 2 + 128)]:
+        rows = slice(r0, r0 + 128)
+        qs = q[b:b + 1, h:h + 1, rows]
+        if kind == "causal":
+            # rows r0.. see keys 0..row: evaluate against keys [0, r0+128) with an additive mask
+            n = r0 + 128
+            tri = torch.where(torch.arange(n)[None, :] <= (torch.arange(128) + r0)[:, None], 0.0, float("-inf")).reshape(1, 1, 128, n)
+            exp = O.attention(qs, k[b:b + 1, h:h + 1, :n], v[b:b + 1, h:h + 1, :n], scale, False, tri)
+        else:
+            exp = O.attention(qs, k[b:b + 1, h:h + 1], v[b:b + 1, h:h + 1], scale, False, mask[b:b + 1] if mask is not None else None)
+        O.assert_parity(out[b:b + 1, h:h + 1, rows], exp, max_abs=tol, what=f"b{b} h{h} rows {r0}")
+
+
 def test_attention_full_size_properties(lib):
     """Config-size check ([8,12,512,64], padding mask) through properties that need no CPU
     oracle at that size plus a sampled oracle comparison: rows of softmax sum to one (V = ones

@@ -40,11 +40,28 @@ def test_blockwise_matches_reference_golden(attn_golden, name):
     assert torch.allclose(out, torch.from_numpy(g[f"{name}_out"]), atol=1e-5, rtol=1e-4)
 
 
+CAUSAL_GOLDEN = ["causal_square", "causal_morekeys", "causal_morequeries", "causal_bias", "causal_pad", "causal_d128"]
+
+
+@pytest.mark.parametrize("name", CAUSAL_GOLDEN)
+def test_causal_matches_reference_golden(attn_golden, name):
+    """The causal branch against outputs of the reference's own `attention_reference(is_causal=True)`
+    (fixtures made by tests/golden/make_golden.py): dense restatement and tile loop."""
+    g = attn_golden
+    q, k, v = (torch.from_numpy(g[f"{name}_{t}"]) for t in "qkv")
+    mask = torch.from_numpy(g[f"{name}_mask"]) if f"{name}_mask" in g.files else None
+    want = torch.from_numpy(g[f"{name}_out"])
+    out = O.attention(q, k, v, float(g[f"{name}_scale"]), True, mask)
+    assert torch.allclose(out, want, atol=2e-6, rtol=1e-5)
+    out = O.attention_blockwise(q, k, v, float(g[f"{name}_scale"]), True, mask, block_m=16, block_n=16)
+    assert torch.allclose(out, want, atol=1e-5, rtol=1e-4)
+
+
 @pytest.mark.parametrize("m,n", [(1, 24), (33, 33), (40, 17), (17, 40), (129, 257)])
 @pytest.mark.parametrize("mask_kind", [None, "bias", "pad"])
 def test_causal_oracle_matches_blockwise(m, n, mask_kind):
-    """The causal branch cannot be pinned on the reference on CPU, so two independent
-    restatements (dense and tile loop) must agree."""
+    """Beyond the golden cases: the dense and the tile-loop restatement agree on more causal
+    shapes."""
     torch.manual_seed(0)
     q, k, v = torch.randn(2, 2, m, 64), torch.randn(2, 2, n, 64), torch.randn(2, 2, n, 64)
     mask = None

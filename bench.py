@@ -39,6 +39,9 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 WORKLOAD = {"B": 8, "H": 12, "S": 512, "D": 64}
+WORKLOAD_NAME = ("attention fwd [batch 8, heads 12, seq 512, head_dim 64], per-sequence padding mask, "
+                 "non-causal, sm_scale 1/8 (baseline config 2)")
+TRAFFIC_PROFILE = os.path.join("profiles", "attention_split_d64_config2_padmask.md")
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
@@ -157,7 +160,7 @@ def run_reference(args):
         "metric": "fused attention TFLOP/s", "value": tflops, "unit": "TFLOP/s",
         "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "ms_per_step": sec * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "attention fwd [8,12,512,64], padding mask, non-causal (baseline config 2)",
+        "config": {"workload": WORKLOAD_NAME,
                    "note": "reference's eager attention_reference restated in fp32 PyTorch on the host CPU; "
                            "its Triton path needs an Ampere+ GPU and Triton 2.0 and cannot run here"},
         "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": cores, "kind": "port",
@@ -246,9 +249,19 @@ def graph_time(step_for_set, n_sets, steps, warmup, min_total_ms=0.0, repeats=1)
         steps = n_sets * max(replays + 1, int(1.5 * min_total_ms / max(total, 1e-3) * max(replays, 1)) + 1)
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the headline workload (ncu capture
-# summarised under profiles/): the inputs are read once, the 6.3 MB output is still in L2 at kernel end
-HEADLINE_NCU_TRAFFIC_BYTES = 18942464
+def headline_traffic_bytes():
+    """dram__bytes_read.sum + dram__bytes_write.sum of one launch of the headline workload, as the
+    committed ncu summary of the kernel that ships records it (a line `dram_bytes_per_launch: N`);
+    None when the summary carries no such line."""
+    import re
+
+    try:
+        text = open(os.path.join(ROOT, TRAFFIC_PROFILE)).read()
+    except OSError:
+        return None
+    m = re.search(r"^dram_bytes_per_launch:\s*([0-9]+)", text, flags=re.M)
+    return int(m.group(1)) if m else None
+
 
 
 def run_ours(args):
@@ -373,6 +386,24 @@ def run_ours(args):
     h2d = sum(t.numel() * t.element_size() for t in (hq, hk, hv, hm))
     d2h = hout.numel() * hout.element_size()
 
+    # ---------------- N > 1: the ranks of this job as ONE tensor-parallel group (baseline config 5)
+    tp = None
+    if world > 1 and not args.no_tp:
+        del sets, pipe, flush
+        torch.cuda.empty_cache()
+        tp = {"workload": "Llama-2-7B-shaped decoder, 32 layers, bf16, prefill batch 8 x 2048 causal + 128 greedy decode steps, "
+                          f"tensor parallel over {world} GPUs (strong scaling; baseline config 5)"}
+        for kind in ("peer", "nccl"):
+            try:
+                par = llama_tp_parity(world, rank, dev, dist, kind)
+                r = measure_llama(world, rank, dev, dist, kind, layers=32, decode_steps=128, prefill_reps=2)
+                tp[kind] = {"prefill_ms": round(r["prefill_ms"], 3), "decode_ms_per_step": round(r["decode_ms_per_step"], 4),
+                            "logits_vs_one_rank_2_layers": par}
+            except Exception as exc:  # the headline line must still be printed
+                tp[kind] = {"error": f"{type(exc).__name__}: {exc}"[:300]}
+        tp["all_reduce"] = {"peer": "fused peer-memory all-reduce + residual + RMSNorm kernel for decode messages, NCCL for prefill",
+                            "nccl": "NCCL all-reduce for every message"}
+
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
@@ -397,17 +428,18 @@ def run_ours(args):
             "tflops": round(tf, 1), "frac_of_tensor_peak": round(tf / peaks["bf16_tflops"], 3), "ms": round(t_ms, 4)}
     del xs, ys, w, b
     for cols in (768, 4096):
-        n_norm_sets = 12 if cols == 768 else 3  # > 2 x L2 of inputs + outputs
+        n_norm_sets = 12 if cols == 768 else 3  # 12 x 50 MB / 3 x 268 MB of inputs + outputs: > 2 x L2
         xn = [torch.randn((16384, cols), generator=g).half().to(dev) for _ in range(n_norm_sets)]
+        yn = [torch.empty_like(t) for t in xn]  # outputs rotate with the inputs: no step finds its output lines in L2
         gm = (torch.rand((cols,), generator=g) + 0.5).half().to(dev)
         bt = (torch.randn((cols,), generator=g) * 0.1).half().to(dev)
         for rms in (False, True):
-            t_ms = graph_time(lambda i: layer_norm(xn[i], gm, None if rms else bt, 1e-5, use_rms_norm=rms),
+            t_ms = graph_time(lambda i: layer_norm(xn[i], gm, None if rms else bt, 1e-5, use_rms_norm=rms, out=yn[i]),
                               n_norm_sets, 4 * n_norm_sets, 3, min_total_ms=3.0, repeats=3)
             gbs = (4.0 * 16384 * cols + 4 * cols) / (t_ms * 1e-3) / 1e9
             ops[f"{'rmsnorm' if rms else 'layernorm'}_16384x{cols}"] = {
                 "gbs": round(gbs, 1), "frac_of_hbm_peak": round(gbs / peaks["hbm_gbs"], 3), "ms": round(t_ms, 4)}
-        del xn
+        del xn, yn
     _lib.device_status()
 
     cpu_sec, cores = time_cpu_attention(5, 2)
@@ -419,8 +451,7 @@ def run_ours(args):
         "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": ms,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
         "config": {
-            "workload": "attention fwd fp16 [batch 8, heads 12, seq 512, head_dim 64], per-sequence padding mask, "
-                        "non-causal, sm_scale 1/8 (baseline config 2)",
+            "workload": WORKLOAD_NAME,
             "per_gpu_batch": WORKLOAD["B"], "parallelism": f"replicas x{world} (batch-sharded, no collective)",
             "timing": "one CUDA-event pair around K back-to-back steps (CUDA-graph replays) on the launching stream; "
                       "steps cycle through 10 input sets (252 MB) so inputs are larger than L2, no flush in the timed region",
@@ -431,11 +462,10 @@ def run_ours(args):
         },
         "roofline": {
             "bound": "tensor", "achieved": per_launch_tflops, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-            "frac": per_launch_tflops / peaks["bf16_tflops"], "traffic": HEADLINE_NCU_TRAFFIC_BYTES,
+            "frac": per_launch_tflops / peaks["bf16_tflops"], "traffic": headline_traffic_bytes(),
             "peak_source": f"{peak_kind} cuBLAS bf16 burst (MEASURED_PEAKS.json)" if peak_kind == "measured" else "fallback 1590 TFLOP/s",
             "kernel": "attention_split_kernel<half, row-broadcast mask>",
-            "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one launch of this workload, "
-                              "profiles/attention_split_d64_config2_padmask.md",
+            "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one launch of this workload, " + TRAFFIC_PROFILE,
         },
         "cpu_baseline": {"value": cpu_tflops, "unit": "TFLOP/s", "cores": cores, "kind": "port",
                          "sample": "5 full steps of the workload in fp32 (oracle restatement of the reference's eager attention)"},
@@ -447,6 +477,8 @@ def run_ours(args):
         "clocks": clocks,
         "ops": ops,
     }
+    if tp is not None:
+        line["tp"] = tp
     print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()
@@ -466,7 +498,7 @@ def run_sweep(args):
     from kernl_b200.implementations.linear_layer import linear_layer
 
     build.build()
-    _lib.load().kb_debug_attention_variant(args.attn_variant)
+    _lib.load()
     peaks, _ = load_peaks()
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(0)
@@ -544,7 +576,8 @@ def run_sweep(args):
                     x = torch.randn((M, K), generator=g).half().to(dev)
                     w = (torch.randn((N, K), generator=g) * 0.02).half().to(dev)
                     b = (torch.randn((N,), generator=g) * 0.02).half().to(dev)
-                    return lambda: linear_layer(x, w, b, act)
+                    y = torch.empty((M, N), dtype=torch.float16, device=dev)
+                    return lambda: linear_layer(x, w, b, act, out=y)
 
                 nbytes = 2.0 * (M * K + N * K + M * N) + 2 * N
                 emit(name, timed(make_set, nbytes), flops=2.0 * M * N * K, nbytes=nbytes)
@@ -556,9 +589,10 @@ def run_sweep(args):
 
             def make_set():
                 x = torch.randn((16384, cols), generator=g).half().to(dev)
+                y = torch.empty_like(x)
                 gm = (torch.rand((cols,), generator=g) + 0.5).half().to(dev)
                 bt = (torch.randn((cols,), generator=g) * 0.1).half().to(dev)
-                return lambda: layer_norm(x, gm, None if rms else bt, 1e-5, use_rms_norm=rms)
+                return lambda: layer_norm(x, gm, None if rms else bt, 1e-5, use_rms_norm=rms, out=y)
 
             nbytes = 4.0 * 16384 * cols + 4 * cols
             emit(name, timed(make_set, nbytes), nbytes=nbytes)
@@ -742,40 +776,34 @@ def run_t5(args):
         dist.destroy_process_group()
 
 
-def run_llama(args):
-    """Baseline config 5: Llama-2-7B-shaped decoder, random init bf16, prefill 8 x 2048 then greedy
-    decode with KV cache; tensor parallel over the ranks of this job (NCCL all-reduce after o_proj
-    and down_proj)."""
+def _make_comm(kind, rank, world, dev):
+    import torch
+
+    if world > 1 and kind == "peer":
+        from kernl_b200.comm import PeerAllReduce
+
+        return PeerAllReduce(rank, world, dev, torch.bfloat16)
+    return None  # LlamaTP then uses NCCL (or nothing on one rank)
+
+
+def measure_llama(world, rank, dev, dist, comm_kind, layers=32, decode_steps=256, prefill_reps=3):
+    """Baseline config 5 on the ranks of this job as ONE tensor-parallel group: prefill 8 x 2048
+    (causal), then `decode_steps` greedy steps replayed from one CUDA graph. Device-timed with CUDA
+    events between barriers, max over ranks. Returns {"prefill_ms", "decode_ms_per_step", "tokens_sample"}."""
     import torch
 
     from kernl_b200 import _lib
     from kernl_b200.llama_tp import LlamaConfig, LlamaTP
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local_rank)
-    dist = None
-    if world > 1:
-        import torch.distributed as dist_mod
-
-        dist = dist_mod
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    dev = torch.device("cuda", local_rank)
-    cfg = LlamaConfig(n_layers=args.layers)
-    comm = None
-    if world > 1 and args.comm == "peer":
-        from kernl_b200.comm import PeerAllReduce
-
-        comm = PeerAllReduce(rank, world, dev, torch.bfloat16)
+    cfg = LlamaConfig(n_layers=layers)
+    assert 2048 + decode_steps <= cfg.max_seq, f"prompt 2048 + {decode_steps} decode steps exceed the KV cache ({cfg.max_seq} slots)"
+    comm = _make_comm(comm_kind, rank, world, dev)
     model = LlamaTP(cfg, rank=rank, world=world, device=dev, dtype=torch.bfloat16, seed=0, comm=comm)
     ids = torch.randint(0, cfg.vocab, (8, 2048), generator=torch.Generator().manual_seed(0)).to(dev)
-    decode_steps = args.decode_steps
-    # warm-up: one prefill and a few decode steps
-    model.prefill(ids)
+    model.prefill(ids)  # warm-up
     torch.cuda.synchronize()
     pre = []
-    for _ in range(max(1, min(args.steps, 3))):
+    for _ in range(max(1, prefill_reps)):
         if dist is not None:
             dist.barrier()
         s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -811,23 +839,102 @@ def run_llama(args):
     t = torch.tensor([statistics.mean(pre), dec_ms], device=dev)
     if dist is not None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    result = {"prefill_ms": float(t[0]), "decode_ms_per_step": float(t[1]) / decode_steps,
+              "tokens_sample": toks[0, :8].tolist()}
+    # drop the captured graph (it holds NCCL work with the nccl communicator) before the caller
+    # builds another model or tears NCCL down
+    del replay, static_tok, static_next, model
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    if comm is not None:
+        comm.close()
+    torch.cuda.empty_cache()
+    return result
+
+
+def llama_tp_parity(world, rank, dev, dist, comm_kind, layers=2, prompt=2048, steps=4):
+    """Logits of the tensor-parallel decoder against the same weights on ONE rank: a `layers`-deep
+    slice of the 7B shape, prefill 8 x `prompt` plus `steps` teacher-forced decode steps (the decode
+    steps are what the fused peer-memory kernel serves). Rank 0 evaluates the single-rank model and
+    broadcasts its greedy tokens, every rank runs its shard. Returns max-abs / cosine per phase."""
+    import torch
+
+    from kernl_b200.llama_tp import LlamaConfig, LlamaTP
+
+    cfg = LlamaConfig(n_layers=layers)
+    ids = torch.randint(0, cfg.vocab, (8, prompt), generator=torch.Generator().manual_seed(1)).to(dev)
+    ref_logits = None
+    forced = torch.zeros((steps, 8), dtype=torch.long, device=dev)
     if rank == 0:
-        prefill_ms, dec_ms = float(t[0]), float(t[1])
+        single = LlamaTP(cfg, rank=0, world=1, device=dev, dtype=torch.bfloat16, seed=0)
+        ref_logits = [single.prefill(ids).float()]
+        for t in range(steps):
+            forced[t] = ref_logits[-1].argmax(-1)
+            ref_logits.append(single.decode_step(forced[t]).float())
+        del single
+        torch.cuda.empty_cache()
+    if dist is not None:
+        dist.broadcast(forced, src=0)
+    comm = _make_comm(comm_kind, rank, world, dev)
+    model = LlamaTP(cfg, rank=rank, world=world, device=dev, dtype=torch.bfloat16, seed=0, comm=comm)
+    logits = [model.prefill(ids).float()]
+    for t in range(steps):
+        logits.append(model.decode_step(forced[t]).float())
+    torch.cuda.synchronize()
+    out = None
+    if rank == 0:
+        def cmp(a, b):
+            a, b = torch.stack(a), torch.stack(b)
+            return {"max_abs": float((a - b).abs().max()), "cos": float(torch.nn.functional.cosine_similarity(a.flatten(), b.flatten(), dim=0)),
+                    "argmax_agree": float((a.argmax(-1) == b.argmax(-1)).float().mean())}
+        out = {"prefill": cmp(logits[:1], ref_logits[:1]), "decode": cmp(logits[1:], ref_logits[1:]),
+               "logit_abs_max": float(torch.stack(ref_logits).abs().max())}
+    del model
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    if comm is not None:
+        comm.close()
+    torch.cuda.empty_cache()
+    return out
+
+
+def run_llama(args):
+    """Baseline config 5: Llama-2-7B-shaped decoder, random init bf16, prefill 8 x 2048 then greedy
+    decode with KV cache; tensor parallel over the ranks of this job (all-reduce after o_proj and
+    down_proj: NCCL, or the fused peer-memory kernel for decode-size messages)."""
+    import torch
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    dev = torch.device("cuda", local_rank)
+    kind = args.comm if world > 1 else "none"
+    parity = llama_tp_parity(world, rank, dev, dist, kind) if world > 1 else None
+    r = measure_llama(world, rank, dev, dist, kind, layers=args.layers, decode_steps=args.decode_steps,
+                      prefill_reps=max(1, min(args.steps, 3)))
+    if rank == 0:
         print(json.dumps({
-            "metric": "Llama-7B-shape prefill latency", "value": prefill_ms, "unit": "ms", "n_gpus": world,
-            "steps": len(pre), "warmup": 1, "ms_per_step": prefill_ms, "higher_is_better": False, "scaling": "strong",
+            "metric": "Llama-7B-shape prefill latency", "value": r["prefill_ms"], "unit": "ms", "n_gpus": world,
+            "steps": max(1, min(args.steps, 3)), "warmup": 1, "ms_per_step": r["prefill_ms"], "higher_is_better": False, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": f"Llama-2-7B-shaped decoder ({cfg.n_layers} layers), prefill batch 8 x 2048 causal, then {decode_steps} greedy decode steps (baseline config 5)",
+            "config": {"workload": f"Llama-2-7B-shaped decoder ({args.layers} layers), prefill batch 8 x 2048 causal, then {args.decode_steps} greedy decode steps (baseline config 5)",
                        "parallelism": f"tp{world}", "all_reduce": ("fused peer-memory kernel for messages <= 1 MiB (decode), NCCL above"
-                                                                    if comm is not None else "NCCL" if world > 1 else "none"),
-                       "prefill_tokens_per_s": 8 * 2048 / prefill_ms * 1e3,
-                       "decode_ms_per_step": dec_ms / decode_steps, "decode_tokens_per_s": 8 * decode_steps / dec_ms * 1e3,
-                       "tokens_sample": toks[0, :8].tolist()},
+                                                                    if kind == "peer" else "NCCL" if world > 1 else "none"),
+                       "prefill_tokens_per_s": 8 * 2048 / r["prefill_ms"] * 1e3,
+                       "decode_ms_per_step": r["decode_ms_per_step"], "decode_tokens_per_s": 8 / r["decode_ms_per_step"] * 1e3,
+                       "tokens_sample": r["tokens_sample"],
+                       "logits_vs_one_rank_2_layers": parity},
         }), flush=True)
     if dist is not None:
-        # drop the captured graph (it holds NCCL work when --comm nccl) before tearing NCCL down
-        del replay, static_tok, static_next, model
-        torch.cuda.synchronize()
         dist.barrier()
         dist.destroy_process_group()
 
@@ -841,8 +948,6 @@ def main():
     ap.add_argument("--sweep", choices=["all", "attention", "attention_big", "linear", "norm", "decode"], default=None,
                     help="per-shape kernel timings instead of the headline line")
     ap.add_argument("--case", default=None, help="with --sweep: only cases whose name contains this")
-    ap.add_argument("--attn-variant", type=int, default=0, help="with --sweep: fused-attention kernel, 0 = dispatcher's choice, "
-                    "1 = 128-key blocks, 2 = 64-key blocks")
     ap.add_argument("--workload", choices=["attention", "bert", "llama", "t5"], default="attention",
                     help="attention = headline (default); bert / llama = the model configs")
     ap.add_argument("--no-pdl", action="store_true", help="model workloads: launch the light kernels without programmatic "
@@ -852,6 +957,7 @@ def main():
     ap.add_argument("--comm", choices=["nccl", "peer"], default="peer",
                     help="llama workload, N > 1: all-reduce through NCCL only, or the fused peer-memory kernel for decode-size messages")
     ap.add_argument("--decode-steps", type=int, default=256, help="llama workload: greedy decode steps")
+    ap.add_argument("--no-tp", action="store_true", help="default run with N > 1: skip the tensor-parallel decoder measurement")
     args = ap.parse_args()
     if args.no_pdl:
         from kernl_b200 import _lib as _kb_lib

@@ -136,7 +136,8 @@ int kb_rope_kv_write(const kb_rope_params* p, void* stream);
  * Fused attention forward: O = softmax(sm_scale · Q·Kᵀ + mask [causal]) · V, online softmax.
  * Replaces: src/kernl/implementations/attention.py:438-529 (Attention.forward launching
  * _fwd_kernel, :122-435).
- *   q [B,H,M,D], k/v [B,H,N,D], o [B,H,M,D]; D in {64,128}; unit D stride required for q,k,v,o;
+ *   q [B,H,M,D], k/v [B,H,N,D] ([B,H/kv_group,N,D] with grouped queries), o [B,H,M,D]; D in {64,128};
+ *   unit D stride required for q,k,v,o;
  *   the other q/k/v strides must be multiples of 8 elements.
  *   mask: additive, logical shape [B|1, H|1, M|1, N]; a broadcast dimension is passed with
  *   stride 0. -inf entries are clamped to the lowest finite value of mask_dtype
@@ -155,6 +156,17 @@ typedef struct {
     int32_t is_causal;
     int32_t dtype;           /* KB_F16 / KB_BF16 for q,k,v,o                               */
     int32_t mask_dtype;      /* KB_F16 / KB_BF16 / KB_F32                                  */
+    /* Grouped-query attention: kv_group consecutive query heads share one K/V head, i.e. query
+     * head h reads K/V head h / kv_group, k and v are [B, H / kv_group, N, D] and H % kv_group == 0.
+     * 0 or 1 = one K/V head per query head (the reference's only case). Replaces the eager
+     * `repeat_kv` copy that grouped-query models otherwise make before attention. */
+    int32_t kv_group;
+    /* Decode entry points only (NULL elsewhere): device int64 holding how many of the N keys exist
+     * (a KV cache filled up to that slot); keys beyond it are neither loaded nor scored. The value
+     * is read by the kernel, so a captured CUDA graph follows a growing cache. It plays the part
+     * of `start_position` in the reference's experimental Llama attention
+     * (experimental/llama-v2/kernel/fused_kernel_attention.py:30,63,76). Values above N count as N. */
+    const int64_t* kv_len_dev;
 } kb_attn_params;
 
 int kb_attention_fwd(const kb_attn_params* p, void* stream);

@@ -65,6 +65,7 @@ class AttnParams(Structure):
         ("q_strides", c_int64 * 4), ("k_strides", c_int64 * 4), ("v_strides", c_int64 * 4),
         ("o_strides", c_int64 * 4), ("mask_strides", c_int64 * 4),
         ("sm_scale", c_float), ("is_causal", c_int32), ("dtype", c_int32), ("mask_dtype", c_int32),
+        ("kv_group", c_int32), ("kv_len_dev", c_void_p),
     ]
 
 
@@ -133,10 +134,14 @@ def load() -> ctypes.CDLL:
     lib.kb_status_str.argtypes = [ctypes.c_int]
     lib.kb_status_str.restype = ctypes.c_char_p
     lib.kb_version.restype = ctypes.c_int
-    for hook in ("kb_debug_force_bn", "kb_debug_force_splits", "kb_debug_attention_variant", "kb_debug_pdl", "kb_debug_split_tiles"):
+    # unstable test hooks (include/kernl_b200_debug.h)
+    for hook in ("kb_debug_force_bn", "kb_debug_force_splits", "kb_debug_pdl", "kb_debug_split_tiles", "kb_debug_attention_persistent"):
         if hasattr(lib, hook):
             getattr(lib, hook).argtypes = [ctypes.c_int]
             getattr(lib, hook).restype = None
+    if hasattr(lib, "kb_debug_wait_limit"):
+        lib.kb_debug_wait_limit.argtypes = [c_int64, c_int64]
+        lib.kb_debug_wait_limit.restype = ctypes.c_int
     if os.environ.get("KERNL_B200_PDL", "1") == "0" and hasattr(lib, "kb_debug_pdl"):
         lib.kb_debug_pdl(0)  # launch every kernel with plain stream ordering (A/B measurements)
     _lib = lib
@@ -166,12 +171,25 @@ def current_stream(device: torch.device) -> int:
     return torch.cuda.current_stream(device).cuda_stream
 
 
+_expiry_hooks = []
+
+
+def on_wait_expired(hook) -> None:
+    """Register a callable that `device_status` runs when it finds that a bounded wait expired
+    (front-ends use it to put scratch that a cut-short kernel may have left dirty back in order)."""
+    _expiry_hooks.append(hook)
+
+
 def device_status() -> list:
     """Synchronise the device and return (and clear) the kernels' status word; raises when a
-    bounded device-side wait expired."""
+    bounded device-side wait expired. Kernels launched between the expiry and this call did no
+    work, so call it at every point where results leave the GPU (end of a generation loop, after
+    replaying captured graphs, before closing peer buffers)."""
     out = (c_int32 * 4)()
     st = load().kb_device_status_read(out)
     vals = list(out)
     if st != KB_OK:
+        for hook in _expiry_hooks:
+            hook()
         raise RuntimeError(f"kernl_b200 device status: {status_str(st)}; word = {vals}")
     return vals

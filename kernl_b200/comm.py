@@ -130,6 +130,13 @@ class PeerAllReduce(NcclAllReduce):
         """Unmap the peers' buffers and free this rank's. Call on every rank, between steps, after a
         barrier, with no kernel in flight."""
         torch.cuda.synchronize(self.device)
+        try:
+            with torch.cuda.device(self.device):
+                _lib.device_status()  # a flag wait that expired during this communicator's life shows here
+        finally:
+            self._release()
+
+    def _release(self):
         for ptr in self._opened:
             self._lib.kb_peer_close(ptr)
         self._opened = []

@@ -57,12 +57,12 @@ __device__ __forceinline__ uint4 ld_peer_16B(const void* p) {
     return v;
 }
 
-// Spin until *flag == want, at most about one second. Returns false (and records it) on expiry.
+// Spin until *flag == want, at most a few seconds (peer_wait_limit). Returns false (and records it) on expiry.
 __device__ __forceinline__ bool ar_wait_flag(const uint32_t* flag, uint32_t want, int site) {
     const long long t0 = clock64();
     for (uint32_t spins = 0;; ++spins) {
         if (ld_acquire_sys(flag) == want) return true;
-        if ((spins & 0x3F) == 0x3F && clock64() - t0 > kWaitLimitCycles) {
+        if ((spins & 0x3F) == 0x3F && clock64() - t0 > peer_wait_limit()) {
             if (atomicCAS(&g_device_status[0], 0, KB_DEV_WAIT_EXPIRED) == 0) {
                 g_device_status[1] = site;
                 g_device_status[2] = (int)blockIdx.x;

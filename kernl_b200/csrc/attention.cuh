@@ -30,6 +30,7 @@ namespace kb {
 
 constexpr int kAttnThreads = 384;
 constexpr int kAttnBlock = 128;  // rows per query tile and keys per block
+constexpr int kBlkN = 64;        // keys per block of the head-dimension-64 kernel (attention_split.cuh)
 // Register re-balancing between the warpgroups (setmaxnreg). The CTA is launched with
 // 65536 / 384 -> 168 registers per thread; the third warpgroup shrinks to kAttnRegsLow and the two
 // softmax warpgroups grow to kAttnRegsHigh. The increase waits (without bound) until the CTA's own
@@ -54,6 +55,7 @@ struct AttnDev {
     int mask_vec;   // mask rows can be read with aligned 128-bit loads
     int num_pairs;  // ceil(ceil(M/128)/2)
     int head_group; // heads whose CTAs are interleaved (see attn_work_item)
+    int kv_group;   // query heads per K/V head (grouped-query attention), >= 1
 };
 
 // CTA -> (batch*head, query-tile pair). Heads are taken in groups of p.head_group; inside a group
@@ -251,12 +253,12 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                 mbar_arrive_expect_tx(k_full(s), TILE);
                 for (int c = 0; c < D / 64; ++c)
                     tma_load_4d(k_smem + s * TILE + c * CHUNK, &tmap_k, k_full(s), c * 64,
-                                j * kAttnBlock, h, b);
+                                j * kAttnBlock, h / p.kv_group, b);
                 if (!mbar_wait(v_empty(s), ph ^ 1, abort_flag, 101)) { ok = false; break; }
                 mbar_arrive_expect_tx(v_full(s), TILE);
                 for (int c = 0; c < D / 64; ++c)
                     tma_load_4d(v_smem + s * TILE + c * CHUNK, &tmap_v, v_full(s), c * 64,
-                                j * kAttnBlock, h, b);
+                                j * kAttnBlock, h / p.kv_group, b);
             }
             if (!ok) {
                 for (int i = 0; i < 64; ++i) __nanosleep(2000);
@@ -589,24 +591,26 @@ template <typename T, int D, int MODE>
 static int launch_attention_tdm(const kb_attn_params& p, cudaStream_t stream) {
     using Cfg = AttnCfg<D>;
     CUtensorMap tq, tk, tv;
-    auto enc = [&](CUtensorMap* out, const void* ptr, int64_t rows, const int64_t* st) -> int {
+    const int64_t kv_group = p.kv_group > 1 ? p.kv_group : 1;
+    if (p.H % kv_group != 0) return KB_ERR_BAD_ARG;
+    auto enc = [&](CUtensorMap* out, const void* ptr, int64_t rows, const int64_t* st, int64_t heads) -> int {
         if (st[3] != 1) return KB_ERR_UNSUPPORTED;
-        const uint64_t dims[4] = {(uint64_t)D, (uint64_t)rows, (uint64_t)p.H, (uint64_t)p.B};
+        const uint64_t dims[4] = {(uint64_t)D, (uint64_t)rows, (uint64_t)heads, (uint64_t)p.B};
         // A dimension of extent 1 may carry any stride in the caller's tensor; TMA still wants a
         // multiple of 16 bytes, and the value is never used, so substitute a harmless one.
         auto fix = [](int64_t extent, int64_t stride) -> uint64_t {
             return (extent == 1) ? 16u : (uint64_t)stride * 2u;
         };
-        const uint64_t strides[4] = {0, fix(rows, st[2]), fix(p.H, st[1]), fix(p.B, st[0])};
+        const uint64_t strides[4] = {0, fix(rows, st[2]), fix(heads, st[1]), fix(p.B, st[0])};
         const uint32_t box[4] = {64, (uint32_t)kAttnBlock, 1, 1};
         return encode_tmap_16bit(out, ptr, 4, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B,
                                  CU_TENSOR_MAP_L2_PROMOTION_L2_128B);
     };
-    int st = enc(&tq, p.q, p.M, p.q_strides);
+    int st = enc(&tq, p.q, p.M, p.q_strides, p.H);
     if (st != KB_OK) return st;
-    st = enc(&tk, p.k, p.N, p.k_strides);
+    st = enc(&tk, p.k, p.N, p.k_strides, p.H / kv_group);
     if (st != KB_OK) return st;
-    st = enc(&tv, p.v, p.N, p.v_strides);
+    st = enc(&tv, p.v, p.N, p.v_strides, p.H / kv_group);
     if (st != KB_OK) return st;
 
     AttnDev d;
@@ -628,6 +632,7 @@ static int launch_attention_tdm(const kb_attn_params& p, cudaStream_t stream) {
     const int num_m_tiles = (int)((p.M + kAttnBlock - 1) / kAttnBlock);
     d.num_pairs = (num_m_tiles + 1) / 2;
     d.head_group = attn_head_group(p.B * p.H, p.N, p.D);
+    d.kv_group = (int)kv_group;
 
     static PerDeviceOnce attr_once;
     if (attr_once.first_time()) {
@@ -651,13 +656,9 @@ static int launch_attention_td(const kb_attn_params& p, cudaStream_t stream) {
 static int launch_attention128(const kb_attn_params& p, cudaStream_t stream) {
     if (p.N <= 0) return KB_ERR_UNSUPPORTED;
     if (p.M > 0x7fffffff || p.N > 0x7fffffff || p.B * p.H > 0x7fffffff) return KB_ERR_UNSUPPORTED;
-    if (p.dtype == KB_F16) {
-        if (p.D == 64) return launch_attention_td<__half, 64>(p, stream);
-        if (p.D == 128) return launch_attention_td<__half, 128>(p, stream);
-    } else if (p.dtype == KB_BF16) {
-        if (p.D == 64) return launch_attention_td<__nv_bfloat16, 64>(p, stream);
-        if (p.D == 128) return launch_attention_td<__nv_bfloat16, 128>(p, stream);
-    }
+    if (p.D != 128) return KB_ERR_UNSUPPORTED;  // head dimension 64 is served by attention_split.cuh
+    if (p.dtype == KB_F16) return launch_attention_td<__half, 128>(p, stream);
+    if (p.dtype == KB_BF16) return launch_attention_td<__nv_bfloat16, 128>(p, stream);
     return KB_ERR_UNSUPPORTED;
 }
 

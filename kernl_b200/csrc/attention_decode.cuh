@@ -24,6 +24,8 @@ struct DecDev {
     float scale_log2;
     int is_causal, mask_dtype;
     int num_splits, chunk;  // chunk = keys per split, multiple of 128
+    int kv_group;           // query heads per K/V head, >= 1
+    const long long* kv_len_dev;  // optional: number of keys that exist (device side), else N
     float* scratch;         // [B*H, M, num_splits, D+2]
 };
 
@@ -48,6 +50,13 @@ static int64_t decode_scratch_bytes(int64_t B, int64_t H, int64_t M, int64_t N, 
     return B * H * M * (int64_t)splits * (D + 2) * (int64_t)sizeof(float);
 }
 
+// Keys that exist: all N, or the device-side count of a partly filled cache.
+__device__ __forceinline__ int decode_live_keys(const DecDev& p) {
+    if (p.kv_len_dev == nullptr) return p.N;
+    const long long n = *p.kv_len_dev;
+    return n < 0 ? 0 : (n < (long long)p.N ? (int)n : p.N);
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kDecThreads)
 attn_decode_part1_kernel(const DecDev p) {
@@ -66,8 +75,9 @@ attn_decode_part1_kernel(const DecDev p) {
     for (int d = tid; d < D; d += kDecThreads) q_s[d] = Elem<T>::to_f32(qp[(int64_t)d * p.q_strides[3]]) * p.scale_log2;
     __syncthreads();
 
-    const T* kbase = reinterpret_cast<const T*>(p.k) + (int64_t)b * p.k_strides[0] + (int64_t)h * p.k_strides[1];
-    const T* vbase = reinterpret_cast<const T*>(p.v) + (int64_t)b * p.v_strides[0] + (int64_t)h * p.v_strides[1];
+    const int hk = h / p.kv_group;
+    const T* kbase = reinterpret_cast<const T*>(p.k) + (int64_t)b * p.k_strides[0] + (int64_t)hk * p.k_strides[1];
+    const T* vbase = reinterpret_cast<const T*>(p.v) + (int64_t)b * p.v_strides[0] + (int64_t)hk * p.v_strides[1];
     const bool k_vec = p.k_strides[3] == 1 && (p.k_strides[2] % 8) == 0 && (((uintptr_t)kbase) & 15) == 0 && (D % 8) == 0;
     const float mlow = mask_lowest(p.mask_dtype);
     const int64_t mask_off = p.mask ? (int64_t)b * p.mask_strides[0] + (int64_t)h * p.mask_strides[1] +
@@ -80,7 +90,7 @@ attn_decode_part1_kernel(const DecDev p) {
     for (int i = 0; i < kDecMaxD / kDecThreads; ++i) acc[i] = 0.f;
 
     const int key_begin = split * p.chunk;
-    const int key_end = min(p.N, key_begin + p.chunk);
+    const int key_end = min(decode_live_keys(p), key_begin + p.chunk);  // a chunk beyond the live keys scores nothing: (m, l) = (-inf, 0)
     for (int k0 = key_begin; k0 < key_end; k0 += kDecThreads) {
         // ---- one key per thread: score in the log2 domain
         const int key = k0 + tid;
@@ -201,8 +211,9 @@ attn_decode_part1_vec_kernel(const DecDev p) {
         for (int i = 0; i < D / 32; ++i)
             qf[i] = (g8 == 0) ? __ldg(reinterpret_cast<const uint4*>(qp + 32 * i + 8 * c4)) : make_uint4(0u, 0u, 0u, 0u);
     }
-    const T* kbase0 = reinterpret_cast<const T*>(p.k) + (int64_t)b * p.k_strides[0] + (int64_t)h * p.k_strides[1];
-    const T* vbase0 = reinterpret_cast<const T*>(p.v) + (int64_t)b * p.v_strides[0] + (int64_t)h * p.v_strides[1];
+    const int hk = h / p.kv_group;
+    const T* kbase0 = reinterpret_cast<const T*>(p.k) + (int64_t)b * p.k_strides[0] + (int64_t)hk * p.k_strides[1];
+    const T* vbase0 = reinterpret_cast<const T*>(p.v) + (int64_t)b * p.v_strides[0] + (int64_t)hk * p.v_strides[1];
     auto stage_tile = [&](uint4* tile, const T* base, int64_t row_stride, int k0, int key_end) {
 #pragma unroll 4
         for (int it = 0; it < LPK; ++it) {
@@ -227,7 +238,7 @@ attn_decode_part1_vec_kernel(const DecDev p) {
     for (int i = 0; i < 8; ++i) acc[i] = 0.f;
 
     const int key_begin = split * p.chunk;
-    const int key_end = min(p.N, key_begin + p.chunk);
+    const int key_end = min(decode_live_keys(p), key_begin + p.chunk);  // a chunk beyond the live keys scores nothing: (m, l) = (-inf, 0)
     for (int k0 = key_begin; k0 < key_end; k0 += kDecThreads) {
         stage_tile(k_tile, kbase0, p.k_strides[2], k0, key_end);
         stage_tile(v_tile, vbase0, p.v_strides[2], k0, key_end);
@@ -382,6 +393,9 @@ static int launch_attention_decode(const kb_attn_params& p, void* scratch, int64
     d.is_causal = p.is_causal ? 1 : 0;
     d.mask_dtype = p.mask ? p.mask_dtype : KB_F32;
     decode_split(p.N, p.B * p.H * p.M, &d.num_splits, &d.chunk);
+    d.kv_group = p.kv_group > 1 ? p.kv_group : 1;
+    if (p.H % d.kv_group != 0) return KB_ERR_BAD_ARG;
+    d.kv_len_dev = reinterpret_cast<const long long*>(p.kv_len_dev);
     d.scratch = reinterpret_cast<float*>(scratch);
     const dim3 g1((unsigned)d.num_splits, (unsigned)p.M, (unsigned)(p.B * p.H));
     const dim3 g2((unsigned)p.M, (unsigned)(p.B * p.H));

@@ -1,8 +1,8 @@
 // Fused attention forward for sm_100a, head dimension 64, "split-row" variant.
 //
-// Same tiling as attention_kb64.cuh (two 128-row query tiles per CTA, keys in blocks of 64, K/V
-// through an 8-stage TMA ring, one tcgen05 issuer warp per tile), but SIXTEEN softmax warps instead
-// of eight: every query row is shared by two threads of different warps, one owning key columns
+// Two 128-row query tiles per CTA, keys in blocks of 64, K/V through an 8-stage TMA ring, one
+// tcgen05 issuer warp per tile, and SIXTEEN softmax warps: every query row is shared by two
+// threads of different warps, one owning key columns
 // [0,32) of each block, the other [32,64). The two halves never talk to each other inside the key
 // loop: each keeps its own running maximum and row sum, writes its own half of P, and its P·V goes
 // into its own accumulator in TMEM (O_a from the keys of the first halves, O_b from the second
@@ -22,7 +22,7 @@
 // first half overwrites columns [0,16), P of the second half columns [32,48) of the same slot),
 // O_a at 128, O_b at 192.
 #pragma once
-#include "attention_kb64.cuh"
+#include "attention.cuh"
 
 namespace kb {
 
@@ -44,6 +44,7 @@ struct SplitShape {
     static_assert(kRegsHigh % 8 == 0 && kRegsLow % 8 == 0, "setmaxnreg wants multiples of 8");
 };
 static int g_split_tiles = 0;  // test hook: 0 = by launch size, 1 / 2 = force the number of query tiles per CTA
+static int g_attn_persistent = -1;  // test hook: -1 = dispatcher's choice, 0 = one CTA per tile, 1 = persistent CTAs
 
 // 2^x for a pair of x <= 0 on the FMA pipe (no special-function unit): x = r + f with r = round(x),
 // f in [-0.5, 0.5]; 2^f by a cubic (max relative error 7.5e-5, below the rounding of a 16-bit P);
@@ -188,6 +189,7 @@ attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     int bh, pair;
     attn_work_item(p, BH, bh, pair);
     const int b = bh / p.H, h = bh % p.H;
+    const int hk = h / p.kv_group;  // K/V head of this query head
     const int num_m_tiles = (p.M + kAttnBlock - 1) / kAttnBlock;
     const int num_n_blocks = (p.N + kBlkN - 1) / kBlkN;
     int mt[2], nblk[2];
@@ -229,22 +231,22 @@ attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
                 tma_load_4d(q_smem + t * QTILE, &tmap_q, q_full(t), 0, mt[t] * kAttnBlock, h, b);
                 if (MODE == 1 && t == 0) {
                     for (int j = 0; j < min(KVS, max_blk); ++j) {
-                        tma_prefetch_l2_4d(&tmap_k, 0, j * kBlkN, h, b);
-                        tma_prefetch_l2_4d(&tmap_v, 0, j * kBlkN, h, b);
+                        tma_prefetch_l2_4d(&tmap_k, 0, j * kBlkN, hk, b);
+                        tma_prefetch_l2_4d(&tmap_v, 0, j * kBlkN, hk, b);
                     }
                 }
                 if (t == 0 && first_kv > 0) {  // K_0 right behind the first Q tile: the first Q·Kᵀ needs just these two
                     mbar_arrive_expect_tx(k_full(0), KVB);
-                    tma_load_4d(k_smem, &tmap_k, k_full(0), 0, 0, h, b);
+                    tma_load_4d(k_smem, &tmap_k, k_full(0), 0, 0, hk, b);
                 }
             }
             for (int j = 0; j < first_kv; ++j) {
                 if (j > 0) {
                     mbar_arrive_expect_tx(k_full(j), KVB);
-                    tma_load_4d(k_smem + j * KVB, &tmap_k, k_full(j), 0, j * kBlkN, h, b);
+                    tma_load_4d(k_smem + j * KVB, &tmap_k, k_full(j), 0, j * kBlkN, hk, b);
                 }
                 mbar_arrive_expect_tx(v_full(j), KVB);
-                tma_load_4d(v_smem + j * KVB, &tmap_v, v_full(j), 0, j * kBlkN, h, b);
+                tma_load_4d(v_smem + j * KVB, &tmap_v, v_full(j), 0, j * kBlkN, hk, b);
             }
         }
     } else if (warp == 0) {
@@ -322,10 +324,10 @@ attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
                 const uint32_t ph = (uint32_t)((i / KVS) & 1);
                 if (!mbar_wait(k_empty(s), ph ^ 1, abort_flag, 600)) { ok = false; break; }
                 mbar_arrive_expect_tx(k_full(s), KVB);
-                tma_load_4d(k_smem + s * KVB, &tmap_k, k_full(s), 0, jb * kBlkN, h, b);
+                tma_load_4d(k_smem + s * KVB, &tmap_k, k_full(s), 0, jb * kBlkN, hk, b);
                 if (!mbar_wait(v_empty(s), ph ^ 1, abort_flag, 601)) { ok = false; break; }
                 mbar_arrive_expect_tx(v_full(s), KVB);
-                tma_load_4d(v_smem + s * KVB, &tmap_v, v_full(s), 0, jb * kBlkN, h, b);
+                tma_load_4d(v_smem + s * KVB, &tmap_v, v_full(s), 0, jb * kBlkN, hk, b);
                 jb = next_blk(jb + 1);
             }
             if (!ok) {
@@ -634,20 +636,22 @@ static int launch_attention_split_tmt(const kb_attn_params& p, cudaStream_t stre
     using Shape = SplitShape<TILES>;
     constexpr int D = 64;
     CUtensorMap tq, tk, tv;
-    auto enc = [&](CUtensorMap* out, const void* ptr, int64_t rows, const int64_t* st, uint32_t box_rows) -> int {
+    const int64_t kv_group = p.kv_group > 1 ? p.kv_group : 1;
+    if (p.H % kv_group != 0) return KB_ERR_BAD_ARG;
+    auto enc = [&](CUtensorMap* out, const void* ptr, int64_t rows, const int64_t* st, uint32_t box_rows, int64_t heads) -> int {
         if (st[3] != 1) return KB_ERR_UNSUPPORTED;
-        const uint64_t dims[4] = {(uint64_t)D, (uint64_t)rows, (uint64_t)p.H, (uint64_t)p.B};
+        const uint64_t dims[4] = {(uint64_t)D, (uint64_t)rows, (uint64_t)heads, (uint64_t)p.B};
         auto fix = [](int64_t extent, int64_t stride) -> uint64_t { return (extent == 1) ? 16u : (uint64_t)stride * 2u; };
-        const uint64_t strides[4] = {0, fix(rows, st[2]), fix(p.H, st[1]), fix(p.B, st[0])};
+        const uint64_t strides[4] = {0, fix(rows, st[2]), fix(heads, st[1]), fix(p.B, st[0])};
         const uint32_t box[4] = {64, box_rows, 1, 1};
         return encode_tmap_16bit(out, ptr, 4, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B,
                                  CU_TENSOR_MAP_L2_PROMOTION_L2_128B);
     };
-    int st = enc(&tq, p.q, p.M, p.q_strides, kAttnBlock);
+    int st = enc(&tq, p.q, p.M, p.q_strides, kAttnBlock, p.H);
     if (st != KB_OK) return st;
-    st = enc(&tk, p.k, p.N, p.k_strides, kBlkN);
+    st = enc(&tk, p.k, p.N, p.k_strides, kBlkN, p.H / kv_group);
     if (st != KB_OK) return st;
-    st = enc(&tv, p.v, p.N, p.v_strides, kBlkN);
+    st = enc(&tv, p.v, p.N, p.v_strides, kBlkN, p.H / kv_group);
     if (st != KB_OK) return st;
 
     AttnDev d;
@@ -669,6 +673,7 @@ static int launch_attention_split_tmt(const kb_attn_params& p, cudaStream_t stre
     const int num_m_tiles = (int)((p.M + kAttnBlock - 1) / kAttnBlock);
     d.num_pairs = (num_m_tiles + TILES - 1) / TILES;  // work items per (batch, head): tile pairs, or tiles
     d.head_group = attn_head_group(p.B * p.H, p.N, p.D);
+    d.kv_group = (int)kv_group;
     static int regs_ok = 0;  // 0 = not checked, 1 = usable, -1 = register allocation does not fit
     if (regs_ok == 0) {
         // setmaxnreg.inc blocks until the CTA's pool holds the registers: refuse to launch a build
@@ -716,6 +721,14 @@ static int launch_attention_split(const kb_attn_params& p, cudaStream_t stream) 
     if (p.dtype == KB_F16) return launch_attention_split_t<__half>(p, stream);
     if (p.dtype == KB_BF16) return launch_attention_split_t<__nv_bfloat16>(p, stream);
     return KB_ERR_UNSUPPORTED;
+}
+
+// The fused-attention entry: head dimension 64 -> the split-row kernel above, 128 -> attention.cuh.
+static int launch_attention(const kb_attn_params& p, cudaStream_t stream) {
+    if (p.N <= 0) return KB_ERR_UNSUPPORTED;
+    if (p.M > 0x7fffffff || p.N > 0x7fffffff || p.B * p.H > 0x7fffffff) return KB_ERR_UNSUPPORTED;
+    if (p.D == 64) return launch_attention_split(p, stream);
+    return launch_attention128(p, stream);
 }
 
 }  // namespace kb

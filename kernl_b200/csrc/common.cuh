@@ -24,10 +24,18 @@ enum : int {
     KB_DEV_WAIT_EXPIRED = 1,
 };
 
-// Wait limit in SM clock cycles (clock64 is cheap to read; %globaltimer is not): 2^31 cycles is a
-// little over one second at 1.9 GHz — long enough that a healthy pipeline never reaches it, short
-// enough that a broken one returns control to the host.
+// Wait limits in SM clock cycles (clock64 is cheap to read; %globaltimer is not). They are device
+// variables so that a test can make a wait run out on purpose (kb_debug_wait_limit) and then put
+// the defaults back. 2^31 cycles is a little over one second at 1.9 GHz: long enough that a healthy
+// pipeline inside one kernel never reaches it, short enough that a broken one returns control to
+// the host. Waits on ANOTHER rank's flag get four times that: a peer that is merely late (first-call
+// module load, a graph capture, a busy host) is not a failure.
 constexpr long long kWaitLimitCycles = 1ll << 31;
+constexpr long long kPeerWaitLimitCycles = 1ll << 33;
+__device__ long long g_wait_limit_cycles = kWaitLimitCycles;
+__device__ long long g_peer_wait_limit_cycles = kPeerWaitLimitCycles;
+__device__ __forceinline__ long long wait_limit() { return *reinterpret_cast<volatile long long*>(&g_wait_limit_cycles); }
+__device__ __forceinline__ long long peer_wait_limit() { return *reinterpret_cast<volatile long long*>(&g_peer_wait_limit_cycles); }
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -89,7 +97,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         if (mbar_try_wait(bar, parity)) return true;
         if ((spins & 0xFF) == 0) {
             if (*abort_flag) return false;
-            if (clock64() - t0 > kWaitLimitCycles) {
+            if (clock64() - t0 > wait_limit()) {
                 *abort_flag = 1;
                 if (atomicCAS(&g_device_status[0], 0, KB_DEV_WAIT_EXPIRED) == 0) {
                     g_device_status[1] = site;
@@ -391,7 +399,7 @@ template <> struct Elem<__nv_bfloat16> {
 };
 
 // ---------------------------------------------------------------------------------------------
-// Host helpers (defined in api.cu)
+// Host helpers (defined in kernl_b200.cu)
 // ---------------------------------------------------------------------------------------------
 // Encodes a tiled tensor map for a 16-bit tensor. dims/strides are innermost first; strides[0] is
 // implied (contiguous), strides[i>0] in BYTES. Returns KB_OK or an error status.

@@ -4,12 +4,12 @@
 #include <cstring>
 #include <mutex>
 
+#include "../../include/kernl_b200_debug.h"
 #include "common.cuh"
 #include "norm.cuh"
 #include "linear.cuh"
 #include "linear_smallm.cuh"
 #include "attention.cuh"
-#include "attention_kb64.cuh"
 #include "attention_split.cuh"
 #include "attention_decode.cuh"
 #include "allreduce.cuh"
@@ -60,30 +60,36 @@ int encode_tmap_16bit(CUtensorMap* out, const void* base, int rank, const uint64
     return r == CUDA_SUCCESS ? KB_OK : KB_ERR_UNSUPPORTED;
 }
 
+// Both answers are per device (a process may drive several GPUs), cached per device index.
 int sm_count() {
-    static int n = 0;
-    if (n == 0) {
-        int dev = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess) return 148;
-        int v = 0;
-        if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) return 148;
-        n = v;
-    }
-    return n;
+    static int cached[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+    if (dev >= 0 && dev < 64 && cached[dev] > 0) return cached[dev];
+    int v = 0;
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) return 148;
+    if (dev >= 0 && dev < 64) cached[dev] = v;
+    return v;
 }
 
 static int check_device() {
-    static int state = 0;  // 0 unknown, 1 ok, -1 bad
-    if (state == 0) {
-        int dev = 0, major = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess ||
-            cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) {
+    static int state[64] = {};  // per device: 0 unknown, 1 ok, -1 not an sm_100 device
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) {
+        cudaGetLastError();
+        return KB_ERR_NO_DEVICE;
+    }
+    const bool cacheable = dev >= 0 && dev < 64;
+    if (!cacheable || state[dev] == 0) {
+        int major = 0;
+        if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) {
             cudaGetLastError();
             return KB_ERR_NO_DEVICE;
         }
-        state = (major == 10) ? 1 : -1;
+        if (!cacheable) return major == 10 ? KB_OK : KB_ERR_NO_DEVICE;
+        state[dev] = (major == 10) ? 1 : -1;
     }
-    return state == 1 ? KB_OK : KB_ERR_NO_DEVICE;
+    return state[dev] == 1 ? KB_OK : KB_ERR_NO_DEVICE;
 }
 
 static int g_forced_bn = 0;
@@ -139,16 +145,22 @@ int kb_norm_fwd(const kb_norm_params* p, void* stream) {
     return cudaGetLastError() == cudaSuccess ? KB_OK : KB_ERR_LAUNCH;
 }
 
-// Test hook: force the GEMM column-tile width (0 = heuristic). Not part of the stable ABI.
+// Test and measurement hooks (include/kernl_b200_debug.h; not part of the stable ABI; process-wide).
 void kb_debug_force_bn(int bn) { g_forced_bn = bn; }
-// Test hook: choose the fused-attention kernel (0 = by head dimension, 1 = 128-key blocks, 2 = 64-key blocks).
-void kb_debug_attention_variant(int v) { g_attn_variant = v; }
-// Test hook: query tiles per CTA of the split-row attention kernel (0 = by launch size, 1, 2).
 void kb_debug_split_tiles(int v) { g_split_tiles = v; }
-// Test / measurement hook: 0 launches the light kernels without programmatic dependent launch.
+void kb_debug_attention_persistent(int mode) { g_attn_persistent = mode; }
 void kb_debug_pdl(int on) { g_use_pdl = on ? 1 : 0; }
-// Test hook: force the number of K splits (0 = heuristic; needs a workspace).
 void kb_debug_force_splits(int splits) { g_forced_splits = splits; }
+int kb_debug_wait_limit(int64_t in_kernel_cycles, int64_t peer_cycles) {
+    int st = check_device();
+    if (st != KB_OK) return st;
+    const long long a = in_kernel_cycles > 0 ? (long long)in_kernel_cycles : kWaitLimitCycles;
+    const long long b = peer_cycles > 0 ? (long long)peer_cycles : kPeerWaitLimitCycles;
+    if (cudaDeviceSynchronize() != cudaSuccess) return KB_ERR_LAUNCH;
+    if (cudaMemcpyToSymbol(g_wait_limit_cycles, &a, sizeof(a)) != cudaSuccess) return KB_ERR_LAUNCH;
+    if (cudaMemcpyToSymbol(g_peer_wait_limit_cycles, &b, sizeof(b)) != cudaSuccess) return KB_ERR_LAUNCH;
+    return cudaDeviceSynchronize() == cudaSuccess ? KB_OK : KB_ERR_LAUNCH;
+}
 
 int kb_linear_fwd(const kb_linear_params* p, void* stream) {
     if (p == nullptr || p->x == nullptr || p->w == nullptr || p->y == nullptr) return KB_ERR_BAD_ARG;
@@ -199,12 +211,14 @@ static int check_attn(const kb_attn_params* p) {
     if (p->dtype != KB_F16 && p->dtype != KB_BF16) return KB_ERR_UNSUPPORTED;
     if (p->mask != nullptr && p->mask_dtype != KB_F16 && p->mask_dtype != KB_BF16 && p->mask_dtype != KB_F32)
         return KB_ERR_UNSUPPORTED;
+    if (p->kv_group < 0 || (p->kv_group > 1 && p->H % p->kv_group != 0)) return KB_ERR_BAD_ARG;
     return KB_OK;
 }
 
 int kb_attention_fwd(const kb_attn_params* p, void* stream) {
     int st = check_attn(p);
     if (st != KB_OK) return st;
+    if (p->kv_len_dev != nullptr) return KB_ERR_UNSUPPORTED;  // a device-side key count is a decode-entry feature
     if (p->B == 0 || p->H == 0 || p->M == 0) return KB_OK;
     st = check_device();
     if (st != KB_OK) return st;

@@ -242,10 +242,10 @@ static int launch_norm_t(const kb_norm_params& p, cudaStream_t stream) {
         const unsigned grid4 = (unsigned)p.rows;
 #define KB_NORM_CASE4(C)                                                                         \
     if (chunks4 <= C) {                                                                          \
-        launch_pdl(norm_fwd_rowwarp_kernel<T, C, RMS, 4>, grid4, kWarps * 32, 0, stream,         \
+        return launch_pdl(norm_fwd_rowwarp_kernel<T, C, RMS, 4>, grid4, kWarps * 32, 0, stream,  \
                    x, y, g, b, p.mean, p.rstd, p.rows, (int)p.cols, p.x_row_stride,              \
-                   p.y_row_stride, p.eps, (const T*)p.residual, (T*)p.sum_out);                  \
-        return KB_OK;                                                                            \
+                   p.y_row_stride, p.eps, (const T*)p.residual, (T*)p.sum_out) == cudaSuccess    \
+                   ? KB_OK : KB_ERR_LAUNCH;                                                      \
     }
         KB_NORM_CASE4(1)
         KB_NORM_CASE4(2)
@@ -257,10 +257,10 @@ static int launch_norm_t(const kb_norm_params& p, cudaStream_t stream) {
         const int chunks = (int)((p.cols + 255) / 256);
 #define KB_NORM_CASE(C)                                                                          \
     if (chunks <= C) {                                                                           \
-        launch_pdl(norm_fwd_rowwarp_kernel<T, C, RMS>, grid, kWarps * 32, 0, stream,             \
+        return launch_pdl(norm_fwd_rowwarp_kernel<T, C, RMS>, grid, kWarps * 32, 0, stream,      \
                    x, y, g, b, p.mean, p.rstd, p.rows, (int)p.cols, p.x_row_stride,              \
-                   p.y_row_stride, p.eps, (const T*)p.residual, (T*)p.sum_out);                  \
-        return KB_OK;                                                                            \
+                   p.y_row_stride, p.eps, (const T*)p.residual, (T*)p.sum_out) == cudaSuccess    \
+                   ? KB_OK : KB_ERR_LAUNCH;                                                      \
     }
         KB_NORM_CASE(1)
         KB_NORM_CASE(2)
@@ -274,9 +274,9 @@ static int launch_norm_t(const kb_norm_params& p, cudaStream_t stream) {
 #undef KB_NORM_CASE
     }
     if (p.residual != nullptr) return KB_ERR_UNSUPPORTED;  // the fused add needs the vector layout
-    launch_pdl(norm_fwd_generic_kernel<T, RMS>, grid, kWarps * 32, 0, stream, x, y, g, b, p.mean, p.rstd, p.rows,
-               p.cols, p.x_row_stride, p.x_col_stride, p.y_row_stride, p.y_col_stride, p.eps);
-    return KB_OK;
+    return launch_pdl(norm_fwd_generic_kernel<T, RMS>, grid, kWarps * 32, 0, stream, x, y, g, b, p.mean, p.rstd, p.rows,
+                      p.cols, p.x_row_stride, p.x_col_stride, p.y_row_stride, p.y_col_stride, p.eps) == cudaSuccess
+               ? KB_OK : KB_ERR_LAUNCH;
 }
 
 static int launch_norm(const kb_norm_params& p, cudaStream_t stream) {

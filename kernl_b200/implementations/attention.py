@@ -58,10 +58,21 @@ def _check_mask(attention_mask, batch, heads, m_size, n_size):
     assert attention_mask.size(3) == n_size, "Last size of mask must broadcast on QK^t"
 
 
-def make_params(q, k, v, output, sm_scale, is_causal, attention_mask) -> "_lib.AttnParams":
+def kv_group_of(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> int:
+    """Query heads per K/V head: 1 for ordinary attention; grouped-query models pass k/v with fewer
+    heads (query head h then reads K/V head h // group) instead of repeating them."""
+    heads, kv_heads = q.size(1), k.size(1)
+    assert v.size(1) == kv_heads and k.size(0) == q.size(0) and v.size(0) == q.size(0), "Incompatible q/k/v shapes"
+    assert kv_heads > 0 and heads % kv_heads == 0, f"{heads} query heads cannot share {kv_heads} key/value heads"
+    return heads // kv_heads
+
+
+def make_params(q, k, v, output, sm_scale, is_causal, attention_mask, kv_len=None) -> "_lib.AttnParams":
     batch, heads, m_size, dhead = q.size()
     n_size = k.size(2)
     p = _lib.AttnParams()
+    p.kv_group = kv_group_of(q, k, v)
+    p.kv_len_dev = kv_len.data_ptr() if kv_len is not None else None
     p.q, p.k, p.v, p.o = q.data_ptr(), k.data_ptr(), v.data_ptr(), output.data_ptr()
     p.B, p.H, p.M, p.N, p.D = batch, heads, m_size, n_size, dhead
     for i in range(4):
@@ -112,7 +123,8 @@ def attention_forward(
     Attention.forward :438-529): q [B,H,M,D], k/v [B,H,N,D], all fp16 or all bf16;
     attention_mask additive, broadcastable over batch / heads / rows with last size N; -inf mask
     entries behave as the lowest finite value of the mask dtype; `is_causal` keeps col <= row.
-    Head dimension 64 or 128 natively; smaller ones through zero padding.
+    Head dimension 64 or 128 natively; smaller ones through zero padding. Beyond the reference:
+    k/v may carry fewer heads than q (grouped-query attention, see `kv_group_of`).
     """
     q, k, v, output, attention_mask = cast_if_autocast(q, k, v, output, attention_mask)
     assert q.shape[-1] == k.shape[-1]

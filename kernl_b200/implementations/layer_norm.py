@@ -7,6 +7,12 @@ from kernl_b200 import _lib
 from kernl_b200.implementations._autocast import cast_if_autocast
 
 
+def _aligned(t: torch.Tensor) -> torch.Tensor:
+    """gamma, beta and the residual are read with 16-byte accesses; a tensor that starts on another
+    boundary (e.g. a graph input placed by the 8-byte-aligned CUDA-graph arena) is copied."""
+    return t if t.data_ptr() % 16 == 0 else t.clone(memory_format=torch.contiguous_format)
+
+
 def pytorch_naive_layernorm(a: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, eps: float):
     """Eager LayerNorm used by benchmarks (reference: layer_norm.py:28-38; note the unbiased
     `var` there — kept, since this function only serves as a comparison point)."""
@@ -34,6 +40,7 @@ def layer_norm(
     implementation=None,
     use_rms_norm: bool = False,
     residual: Optional[torch.Tensor] = None,
+    out: Optional[torch.Tensor] = None,
 ):
     """y = LayerNorm(x) or RMSNorm(x) over the last dimension on the sm_100a kernel.
 
@@ -42,7 +49,8 @@ def layer_norm(
     tensor shaped like x is returned. `implementation` selected one of several Triton kernels in
     the reference; there is a single CUDA implementation here, so it is accepted and ignored.
     `residual` (an extension for pre-norm decoders): normalise x + residual in the same kernel and
-    return the pair (y, x + residual).
+    return the pair (y, x + residual). `out` (an extension as well): a caller-provided result tensor
+    shaped like x, written instead of a new one.
     """
     x, weight, bias, residual = cast_if_autocast(x, weight, bias, residual)
     assert x.dtype == weight.dtype, f"input and weight bias must have the same dtype: {x.dtype}, {weight.dtype}"
@@ -54,21 +62,23 @@ def layer_norm(
         eps = max(eps, 1.6e-5)
     n = x.shape[-1]
     assert weight.shape[-1] == n and weight.numel() == n
-    weight = weight.contiguous()
-    bias = bias.contiguous() if bias is not None else None
+    weight = _aligned(weight.contiguous())
+    bias = _aligned(bias.contiguous()) if bias is not None else None
+    if out is not None:
+        assert out.shape == x.shape and out.dtype == x.dtype and out.device == x.device and out.is_contiguous()
     if x.dim() == 2:
-        out = torch.empty_like(x)
+        out = torch.empty_like(x) if out is None else out
         x2, out2 = x, out
     else:
         x2 = x.reshape(-1, n)
-        out = torch.empty(x.shape, dtype=x.dtype, device=x.device)
+        out = torch.empty(x.shape, dtype=x.dtype, device=x.device) if out is None else out
         out2 = out.view(-1, n)
     rows = x2.shape[0]
     sum_out = None
     if residual is not None:
         assert residual.shape == x.shape and residual.dtype == x.dtype
         x2 = x2.contiguous()
-        residual = residual.contiguous()
+        residual = _aligned(residual.contiguous())
         sum_out = torch.empty(x.shape, dtype=x.dtype, device=x.device)
     if rows == 0:
         return out if residual is None else (out, sum_out)

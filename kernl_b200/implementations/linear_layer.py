@@ -9,19 +9,53 @@ from kernl_b200.implementations._autocast import cast_if_autocast
 
 _WORKSPACE_BYTES = 32 * 1024 * 1024
 _workspaces = {}
+_padded_weights = {}
 
 
 def _workspace(device: torch.device) -> torch.Tensor:
-    """One zero-initialised scratch buffer per device for split-K partial sums, allocated on first
-    use and kept (a stable address, so CUDA graphs that captured it stay valid). The kernel leaves
-    it zero after every call. Calls on different streams of one device would share it; the
-    front-end is single-stream like the reference."""
-    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+    """A zero-initialised scratch buffer for split-K partial sums per (device, stream), allocated on
+    first use and kept (a stable address, so CUDA graphs that captured it stay valid). The kernel
+    leaves it zero after every call. Calls on different streams get different buffers, so they may
+    overlap on the GPU; a graph replayed on a stream other than the one it was captured on keeps
+    using the capture stream's buffer."""
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    key = (index, torch.cuda.current_stream(device).cuda_stream)
     ws = _workspaces.get(key)
     if ws is None:
         ws = torch.zeros(_WORKSPACE_BYTES // 4, dtype=torch.float32, device=device)
         _workspaces[key] = ws
     return ws
+
+
+def _rezero_workspaces() -> None:
+    """A GEMM whose wait expired may have left partial sums behind; split-K needs zeros."""
+    for ws in _workspaces.values():
+        ws.zero_()
+
+
+_lib.on_wait_expired(_rezero_workspaces)
+
+
+def _aligned(t: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+    """The kernels read weights and biases with 16-byte accesses. A tensor that starts elsewhere
+    (a graph input that the CUDA-graph arena placed on an 8-byte boundary, a slice) is copied."""
+    if t is None or t.data_ptr() % 16 == 0:
+        return t
+    return t.clone(memory_format=torch.contiguous_format)
+
+
+def _k_padded_weight(weight: torch.Tensor, pad: int) -> torch.Tensor:
+    """Weight with `pad` zero columns appended, built once per weight (and again when the weight
+    is modified in place) rather than on every call."""
+    key = (weight.data_ptr(), tuple(weight.shape), weight.dtype, weight.device)
+    hit = _padded_weights.get(key)
+    if hit is not None and hit[0] == weight._version:
+        return hit[1]
+    if len(_padded_weights) >= 256:
+        _padded_weights.clear()
+    padded = torch.nn.functional.pad(weight, (0, pad))
+    _padded_weights[key] = (weight._version, padded)
+    return padded
 
 
 def linear_layer(
@@ -69,8 +103,9 @@ def linear_layer(
         # K is padded with zeros to the next multiple of 8 (16-byte rows for TMA); zeros add nothing.
         pad = 8 - K % 8
         x_ = torch.nn.functional.pad(x_, (0, pad))
-        weight = torch.nn.functional.pad(weight, (0, pad))
+        weight = _k_padded_weight(weight, pad)
         K += pad
+    weight, bias = _aligned(weight), _aligned(bias)
     if out is not None:
         assert out.shape == (M, n_out) and out.dtype == x.dtype and out.is_contiguous() and out.device == x.device
         outputs = out

@@ -14,15 +14,18 @@ KV cache is sharded by head, attention is local), `o_proj` and `down_proj` are r
 followed by an all-reduce (sum) over NVLink through `torch.distributed` (NCCL), gate/up are
 column-parallel. Embedding and LM head are replicated.
 
-Decode is shape-static so that ONE CUDA graph serves every step: attention always runs over the
-whole cache with an additive length mask kept on the device, and the position / cache slot are
-device tensors.
+Decode is shape-static so that ONE CUDA graph serves every step: the position / cache slot and the
+number of filled slots are device tensors that the rotary and the decode-attention kernels read
+(the `start_position` of experimental/llama-v2/kernel/fused_kernel_attention.py:30,63,76), so a
+step streams only the keys that exist. Ops without that feature (the CPU stand-ins of the tests)
+get an additive length mask instead.
 """
 from dataclasses import dataclass
 from typing import Optional
 
 import torch
 
+from kernl_b200.comm import NcclAllReduce
 from kernl_b200.implementations.linear_layer import interleave_gate_up
 
 
@@ -41,6 +44,8 @@ class LlamaConfig:
 
 class CudaOps:
     """The library's kernels behind the five ops the model needs."""
+
+    needs_len_mask = False  # decode attention reads the number of filled cache slots from the device
 
     @staticmethod
     def rms_norm(x, w, eps):
@@ -82,37 +87,12 @@ class CudaOps:
         return attention_forward(q, k, v, torch.empty_like(q), sm_scale, True, None)
 
     @staticmethod
-    def attention_decode(q, k, v, sm_scale, mask):
+    def attention_decode(q, k, v, sm_scale, mask, kv_len):
+        """One query row against the filled part of the cache: `kv_len` (device int64) keys are
+        streamed, the slots behind them are never touched (no mask needed)."""
         from kernl_b200.implementations.attention_skinny import skinny_attention_forward
 
-        return skinny_attention_forward(q, k, v, torch.empty_like(q), sm_scale, False, mask)
-
-
-class DistComm:
-    """Sum all-reduce over the default process group (NCCL on GPUs, gloo on CPU); a no-op for a
-    single rank. `kernl_b200.comm.PeerAllReduce` offers the same two methods on top of the
-    library's fused peer-memory kernel."""
-
-    def __init__(self, world: int):
-        self.world = world
-
-    def partial_buffer(self, rows, cols, dtype, device):
-        return None
-
-    def all_reduce(self, t: torch.Tensor) -> torch.Tensor:
-        if self.world > 1:
-            import torch.distributed as dist
-
-            dist.all_reduce(t, op=dist.ReduceOp.SUM)
-        return t
-
-    def reduce_add(self, partial: torch.Tensor, residual: torch.Tensor) -> torch.Tensor:
-        return residual + self.all_reduce(partial)
-
-    def reduce_add_norm(self, partial, residual, weight, eps, ops):
-        """x = residual + all_reduce(partial); returns (x, rms_norm(x) * weight)."""
-        h, x = ops.add_rms_norm(self.all_reduce(partial), residual, weight, eps)
-        return x, h
+        return skinny_attention_forward(q, k, v, torch.empty_like(q), sm_scale, False, None, kv_len=kv_len)
 
 
 def _seeded(shape, std, seed, device, dtype):
@@ -141,7 +121,7 @@ class LlamaTP:
         assert cfg.n_heads % world == 0 and cfg.ffn % (8 * world) == 0
         self.cfg, self.rank, self.world, self.device, self.dtype = cfg, rank, world, torch.device(device), dtype
         self.ops = ops if ops is not None else CudaOps()
-        self.comm = comm if comm is not None else DistComm(world)
+        self.comm = comm if comm is not None else NcclAllReduce(world)
         self.heads_local = cfg.n_heads // world
         self.ffn_local = cfg.ffn // world
         wd = weight_device or device
@@ -191,6 +171,9 @@ class LlamaTP:
         # additive length mask for decode: 0 for filled slots, -inf beyond
         self.len_mask = torch.full((1, 1, 1, cfg.max_seq), float("-inf"), dtype=self.dtype, device=self.device)
         self.pos = torch.zeros(1, dtype=torch.long, device=self.device)
+        self.kv_len = torch.zeros(1, dtype=torch.long, device=self.device)  # filled slots seen by decode attention
+        self._slots = torch.arange(cfg.max_seq, device=self.device).reshape(1, 1, 1, cfg.max_seq)
+        self._host_pos = 0  # host-side copy of the position, for the length checks
 
     # ------------------------------------------------------------------ blocks
     def _row_parallel(self, x2d, w, residual, next_norm):
@@ -212,6 +195,7 @@ class LlamaTP:
         """ids [B, S] → logits [B, vocab] of the last position; fills the KV cache."""
         cfg, hl, D = self.cfg, self.heads_local, self.cfg.head_dim
         B, S = ids.shape
+        assert S <= cfg.max_seq, f"prompt of {S} tokens does not fit the cache (max_seq {cfg.max_seq})"
         if self.kcache is None or self.kcache.shape[1] != B:
             self.alloc_cache(B)
         x = self.embed.index_select(0, ids.reshape(-1)).reshape(B * S, cfg.hidden)
@@ -228,6 +212,8 @@ class LlamaTP:
         self.len_mask.fill_(float("-inf"))
         self.len_mask[..., :S] = 0
         self.pos.fill_(S)
+        self.kv_len.fill_(S)
+        self._host_pos = S
         last = h.reshape(B, S, cfg.hidden)[:, -1].contiguous()  # already through the final norm
         return self.ops.linear(last, self.lm_head)
 
@@ -237,13 +223,18 @@ class LlamaTP:
         cfg, hl, D = self.cfg, self.heads_local, self.cfg.head_dim
         B = tokens.shape[0]
         x = self.embed.index_select(0, tokens)
-        self.len_mask.index_fill_(3, self.pos, 0.0)
+        self.kv_len.add_(1)  # this step's token becomes the last of the keys
+        if getattr(self.ops, "needs_len_mask", True):
+            # open the slot of this position in the length mask. Written as a comparison against the
+            # device-side position, so that a position at or beyond max_seq changes nothing instead
+            # of indexing out of range (the callers check the length on the host as well).
+            self.len_mask.masked_fill_(self._slots == self.pos, 0.0)
         h = self.ops.rms_norm(x, self.layers[0]["norm1"], cfg.eps)
         for li, layer in enumerate(self.layers):
             qkv = self.ops.linear(h, layer["wqkv"])
             q = self.ops.rope_kv_write(qkv, self.kcache[li], self.vcache[li], self.cos, self.sin, self.pos, B, 1)
             attn = self.ops.attention_decode(q.transpose(1, 2), self.kcache[li], self.vcache[li],
-                                             self.sm_scale, self.len_mask)  # [B, hl, 1, D]
+                                             self.sm_scale, self.len_mask, self.kv_len)  # [B, hl, 1, D]
             x, h = self._row_parallel(attn.reshape(B, hl * D), layer["wo"], x, layer["norm2"])
             x, h = self._mlp(layer, h, x, self._next_norm(li))
         self.pos.add_(1)
@@ -254,8 +245,9 @@ class LlamaTP:
         static_next): copy the current tokens into `static_tok`, call `replay()`, read the greedy
         next tokens from `static_next`. The warm-up step and the capture advance the position and
         write cache slots; that state is restored here and the real steps overwrite the slots."""
+        assert self._host_pos + 1 <= self.cfg.max_seq, "no free cache slot left for the capture's warm-up step"
         static_tok = tokens.clone()
-        saved = (self.pos.clone(), self.len_mask.clone())
+        saved = (self.pos.clone(), self.len_mask.clone(), self.kv_len.clone())
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
@@ -267,12 +259,15 @@ class LlamaTP:
             static_next = self.decode_step(static_tok).float().argmax(-1)
         self.pos.copy_(saved[0])
         self.len_mask.copy_(saved[1])
+        self.kv_len.copy_(saved[2])
         self._decode_graph = graph  # keep the graph alive
         return graph.replay, static_tok, static_next
 
     def generate(self, ids: torch.Tensor, steps: int, use_cuda_graph: bool = True) -> torch.Tensor:
         """Greedy decoding: prefill, then `steps` tokens. Returns [B, steps] token ids. The argmax
         stays on the device, so no step waits for the host."""
+        assert ids.shape[1] + max(steps - 1, 1) <= self.cfg.max_seq, (
+            f"prompt {ids.shape[1]} + {steps} generated tokens exceed max_seq {self.cfg.max_seq}")
         logits = self.prefill(ids)
         tok = logits.float().argmax(-1)
         out = [tok]
@@ -285,4 +280,13 @@ class LlamaTP:
         else:
             for _ in range(steps - 1):
                 out.append(self.decode_step(out[-1]).float().argmax(-1))
-        return torch.stack(out, dim=1)
+        self._host_pos += steps - 1
+        tokens = torch.stack(out, dim=1)
+        if self.device.type == "cuda":
+            # a bounded device-side wait that expired makes later kernels skip their work: surface
+            # it here rather than return tokens computed from stale buffers
+            from kernl_b200 import _lib
+
+            with torch.cuda.device(self.device):
+                _lib.device_status()
+        return tokens

@@ -2,8 +2,9 @@
 
 `attention_wrapper` is the call site of the fused kernels: the rewrites replace eager attention
 sub-graphs by a call to it. Patterns 1-3 are the reference's (BERT-style `/ 8.0`, T5-style fp32
-softmax, bmm-style 3-D tensors); two further rewrites cover what current `transformers` emits:
-a direct `scaled_dot_product_attention` call and the `* scaling` form.
+softmax, bmm-style 3-D tensors); a further rewrite covers what current `transformers` emits:
+a direct `scaled_dot_product_attention` call (with its `scale=` literal or the default
+head_dim ** -0.5, and grouped-query K/V when `enable_gqa` is set).
 """
 from typing import Optional
 
@@ -35,10 +36,12 @@ def attention_wrapper(
     if attention_mask is not None and attention_mask.dtype == torch.bool:
         # boolean keep-masks (scaled_dot_product_attention convention) become additive 0 / -inf
         attention_mask = torch.zeros_like(attention_mask, dtype=q.dtype).masked_fill_(~attention_mask, float("-inf"))
+    # The front-ends return the tensor the kernel wrote: under torch.autocast that is an fp16 copy
+    # of a non-fp16 `output`, not `output` itself, so the return value is what goes on.
     if q.size(-2) == 1 and k.size(-2) > 50:
-        skinny_attention_forward(q, k, v, output, sm_scale, is_causal=is_causal, attention_mask=attention_mask)
+        output = skinny_attention_forward(q, k, v, output, sm_scale, is_causal=is_causal, attention_mask=attention_mask)
     else:
-        attention_forward(q, k, v, output, sm_scale, is_causal=is_causal, attention_mask=attention_mask)
+        output = attention_forward(q, k, v, output, sm_scale, is_causal=is_causal, attention_mask=attention_mask)
     if extend_head:
         output = output.squeeze(1)
     return output
@@ -115,7 +118,8 @@ def fuse_attention_sdpa(gm: torch.fx.GraphModule, is_causal: bool):
         dropout_p = args[4] if len(args) > 4 else kwargs.get("dropout_p", 0.0)
         causal = args[5] if len(args) > 5 else kwargs.get("is_causal", False)
         scale = kwargs.get("scale")
-        if dropout_p not in (0, 0.0) or kwargs.get("enable_gqa", False) or isinstance(causal, torch.fx.Node):
+        # enable_gqa needs nothing special: the kernels take k/v with fewer heads than q as they are
+        if dropout_p not in (0, 0.0) or isinstance(causal, torch.fx.Node):
             continue
         if isinstance(scale, torch.fx.Node):
             continue
@@ -129,5 +133,51 @@ def fuse_attention_sdpa(gm: torch.fx.GraphModule, is_causal: bool):
         gm.graph.erase_node(node)
         changed = True
     if changed:
+        gm.graph.lint()
+        gm.recompile()
+
+
+def _repeated_kv_source(node):
+    """If `node` is `x[:, :, None, :, :].expand(B, Hkv, rep, S, D).reshape(B, Hkv * rep, S, D)` — how
+    grouped-query models repeat their K/V heads before an ordinary attention — return x."""
+    if not (isinstance(node, torch.fx.Node) and node.op == "call_method" and node.target == "reshape"):
+        return None
+    expand = node.args[0]
+    if not (isinstance(expand, torch.fx.Node) and expand.op == "call_method" and expand.target == "expand"):
+        return None
+    index = expand.args[0]
+    import operator
+
+    if not (isinstance(index, torch.fx.Node) and index.op == "call_function" and index.target is operator.getitem):
+        return None
+    source, key = index.args
+    full = slice(None, None, None)
+    if not (isinstance(key, tuple) and len(key) == 5 and key[2] is None and all(k == full for i, k in enumerate(key) if i != 2)):
+        return None
+    exp_shape = expand.args[1:] if len(expand.args) > 2 else tuple(expand.args[1])
+    new_shape = node.args[1:] if len(node.args) > 2 else tuple(node.args[1])
+    if len(exp_shape) != 5 or len(new_shape) != 4:
+        return None
+    return source
+
+
+def fuse_repeat_kv(gm: torch.fx.GraphModule):
+    """Grouped-query models (Mistral, Llama 2 70B / 3 families) expand K and V to the number of
+    query heads with a copy before attention (`repeat_kv`). The kernels index the shared K/V head
+    themselves, so the fused call takes the un-repeated tensors and the copies disappear. Has no
+    counterpart in the reference."""
+    changed = False
+    for node in gm.graph.nodes:
+        if node.op != "call_function" or node.target is not attention_wrapper:
+            continue
+        k_src, v_src = _repeated_kv_source(node.args[1]), _repeated_kv_source(node.args[2])
+        if k_src is None or v_src is None:
+            continue
+        args = list(node.args)
+        args[1], args[2] = k_src, v_src
+        node.args = tuple(args)
+        changed = True
+    if changed:
+        gm.graph.eliminate_dead_code()
         gm.graph.lint()
         gm.recompile()

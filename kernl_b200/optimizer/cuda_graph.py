@@ -34,18 +34,21 @@ def argsort(iterable: Iterable, key: Callable) -> list:
     return [i for i, _ in sorted(enumerate(iterable), key=lambda pair: key(pair[1]))]
 
 
-def prepare_inputs(inputs: list, pools: list) -> list:
+def prepare_inputs(inputs: list, pools: list, static_input_idxs: Iterable[int] = ()) -> list:
     """Copy `inputs` into the pools and return the copies, in input order.
 
     Deterministic, so that the same shapes always land on the same addresses: pools are reset and
     sorted by size ascending, inputs are visited by storage size ascending, each goes into the
     first pool with room; the leftovers share one new pool (reference: cuda_graph.py:57-100).
+    Inputs named by `static_input_idxs` are passed through untouched: they take no room in the
+    pools and are not copied (see `cuda_graphs_wrapper`).
     """
     for p in pools:
         p.reset()
     pools.sort(key=lambda p: p.size)
-    order = argsort(inputs, key=lambda t: t.untyped_storage().size())
-    copies: list = [None] * len(inputs)
+    static = set(static_input_idxs)
+    order = [i for i in argsort(inputs, key=lambda t: t.untyped_storage().size()) if i not in static]
+    copies: list = [inputs[i] if i in static else None for i in range(len(inputs))]
     leftovers = []
     for idx in order:
         t = inputs[idx]
@@ -57,7 +60,7 @@ def prepare_inputs(inputs: list, pools: list) -> list:
             leftovers.append(idx)
     if leftovers:
         new_pool = CudaGraphPool(
-            get_pool_size([inputs[i] for i in leftovers], existing_pools=pools), device=inputs[0].device
+            get_pool_size([inputs[i] for i in leftovers], existing_pools=pools), device=inputs[leftovers[0]].device
         )
         pools.append(new_pool)
         for idx in leftovers:
@@ -90,30 +93,62 @@ def _capture(model: Callable, static_inputs: list) -> Callable:
     return replay
 
 
-def cuda_graphs_wrapper(model: Callable, inputs: Union[list, tuple]) -> Callable:
+def _static_idxs(inputs, static_input_idxs) -> tuple:
+    """Inputs that keep their address from call to call: those the caller names, and every
+    `torch.nn.Parameter` (weights that TorchDynamo lifts into graph inputs)."""
+    named = set(static_input_idxs or ())
+    assert all(0 <= i < len(inputs) for i in named), f"static_input_idxs out of range: {sorted(named)}"
+    params = {i for i, t in enumerate(inputs) if isinstance(t, torch.nn.Parameter)}
+    return tuple(sorted(named | params))
+
+
+def _check_static(args, static, addresses) -> None:
+    for i in static:
+        assert args[i].data_ptr() == addresses[i], (
+            f"input {i} was declared static (captured by address) but arrived at another address")
+
+
+def cuda_graphs_wrapper(model: Callable, inputs: Union[list, tuple], static_input_idxs: Optional[Iterable[int]] = None) -> Callable:
     """Run `model` through a CUDA graph (reference: cuda_graph.py:103-138).
 
     With real example inputs the graph is captured now (after one extra eager call, because
     kernels may mutate their inputs during warm-up); with FakeTensor inputs everything is deferred
     to the first real call, with the RNG state preserved around warm-up and capture.
+
+    The reference copies every input into the arena on every call (cuda_graph.py:115-119), which
+    for a decoder means copying its whole KV cache per generated token. Here the inputs listed in
+    `static_input_idxs` — large tensors whose address does not change between calls, such as a KV
+    cache updated in place — and all `torch.nn.Parameter` inputs are captured by address instead:
+    no arena space, no per-call copy. Passing a different tensor at such a position later raises
+    an AssertionError (the graph would silently read the old one).
     """
     assert isinstance(inputs, (list, tuple))
     if not any(isinstance(inp, FakeTensor) for inp in inputs):
-        static_inputs = prepare_inputs(inputs=list(inputs), pools=static_inputs_pool)
+        static = _static_idxs(inputs, static_input_idxs)
+        addresses = {i: inputs[i].data_ptr() for i in static}
+        static_inputs = prepare_inputs(inputs=list(inputs), pools=static_inputs_pool, static_input_idxs=static)
         model(*static_inputs)
         replay = _capture(model, static_inputs)
 
         def run_now(*args):
-            prepare_inputs(inputs=list(args), pools=static_inputs_pool)
+            _check_static(args, static, addresses)
+            prepare_inputs(inputs=list(args), pools=static_inputs_pool, static_input_idxs=static)
             return replay()
 
         return run_now
 
     replay: Optional[Callable] = None
+    static: tuple = ()
+    addresses: dict = {}
 
     def run(*new_inputs):
-        nonlocal replay
-        static_inputs = prepare_inputs(inputs=list(new_inputs), pools=static_inputs_pool)
+        nonlocal replay, static, addresses
+        if replay is None:
+            static = _static_idxs(new_inputs, static_input_idxs)
+            addresses = {i: new_inputs[i].data_ptr() for i in static}
+        else:
+            _check_static(new_inputs, static, addresses)
+        static_inputs = prepare_inputs(inputs=list(new_inputs), pools=static_inputs_pool, static_input_idxs=static)
         if replay is None:
             cpu_state = torch.get_rng_state()
             cuda_state = torch.cuda.get_rng_state()

@@ -7,6 +7,7 @@ from kernl_b200.optimizer.attention import (
     fuse_attention_pattern_2,
     fuse_attention_pattern_3,
     fuse_attention_sdpa,
+    fuse_repeat_kv,
 )
 from kernl_b200.optimizer.dropout import remove_dropout
 from kernl_b200.optimizer.layer_norm import (
@@ -29,6 +30,7 @@ def rewrite_passes(assume_causal: bool):
     return (
         [normalize_operators, replace_scalar_tensor_constants, remove_dropout]
         + [lambda gm, rewrite=rewrite: rewrite(gm, assume_causal) for rewrite in attention]
+        + [fuse_repeat_kv]
         + [replace_all_linear, fuse_gated_feed_forward, fuse_parallel_linears]
         + [replace_layer_norm, fuse_add_layer_norm, replace_layer_norm_rms, replace_rms_norm_any_eps, fuse_add_rms_norm]
     )

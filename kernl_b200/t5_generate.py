@@ -126,6 +126,7 @@ class T5Kernl:
         self.vcache = torch.zeros((nl, B, H, self.max_len, Dh), dtype=dt, device=d)
         self.len_mask = torch.full((1, 1, 1, self.max_len), float("-inf"), dtype=dt, device=d)
         self.pos = torch.zeros(1, dtype=torch.long, device=d)
+        self._slots = torch.arange(self.max_len, device=d).reshape(1, 1, 1, self.max_len)
         self.cross_k, self.cross_v = [], []
         for L in self.dec_layers:
             kv = linear_layer(e2, L["cross"]["kv"], None).reshape(B, S, 2, H, Dh)
@@ -138,7 +139,8 @@ class T5Kernl:
         B = tokens.shape[0]
         H, Dh = self.H, self.Dh
         x = self.embed.index_select(0, tokens)
-        self.len_mask.index_fill_(3, self.pos, 0.0)
+        # open this position's slot; a comparison, so that no position can index out of range
+        self.len_mask.masked_fill_(self._slots == self.pos, 0.0)
         # bias row of the current query position + the length mask: [1, H, 1, L]
         self_mask = (self.dec_bias.index_select(0, self.pos).reshape(1, H, 1, self.max_len) + self.len_mask).contiguous()
         # The residual stream is carried as (x, h): every "x + sublayer" and the norm that follows it
@@ -197,4 +199,12 @@ class T5Kernl:
             for _ in range(steps):
                 tok = self.decode_step(tok).float().argmax(-1)
                 out.append(tok)
-        return torch.stack(out, dim=1)
+        tokens = torch.stack(out, dim=1)
+        if self.device.type == "cuda":
+            # kernels skip their work after a bounded device-side wait has expired: report that
+            # here rather than hand back tokens computed from stale buffers
+            from kernl_b200 import _lib
+
+            with torch.cuda.device(self.device):
+                _lib.device_status()
+        return tokens

@@ -18,6 +18,8 @@ from typing import Callable, Dict, List, Union
 import torch
 from torch.fx import Graph, GraphModule, Node, symbolic_trace
 
+from kernl_b200.utils.fx import literals_are_equal
+
 
 @dataclass
 class Match:
@@ -30,18 +32,6 @@ def _trace(obj: Union[Callable, GraphModule, Graph]) -> GraphModule:
     if isinstance(obj, GraphModule):
         return obj
     return symbolic_trace(obj)
-
-
-def _same_literal(a, b) -> bool:
-    if isinstance(a, Node) or isinstance(b, Node):
-        return False
-    if type(a) != type(b):  # noqa: E721  (1 and 1.0, or True and 1, are different literals)
-        return False
-    if isinstance(a, (tuple, list)):
-        return len(a) == len(b) and all(_same_literal(x, y) for x, y in zip(a, b))
-    if isinstance(a, slice):
-        return (a.start, a.stop, a.step) == (b.start, b.stop, b.step)
-    return a == b
 
 
 class _Matcher:
@@ -80,7 +70,7 @@ class _Matcher:
             if not isinstance(ga, dict) or pa.keys() != ga.keys():
                 return False
             return all(self._match_arg(pa[k], ga[k], m) for k in pa)
-        return _same_literal(pa, ga)
+        return literals_are_equal(pa, ga)
 
     @staticmethod
     def _kwargs(node: Node) -> dict:

@@ -73,6 +73,44 @@ def test_zero_stride_inputs_are_materialised():
     assert torch.equal(copy, t)
 
 
+def test_static_inputs_take_no_room_and_are_not_copied():
+    pools = [CudaGraphPool(64, device="cpu")]
+    cache = torch.zeros(1 << 20)  # 4 MiB: would not fit any pool here
+    ids = torch.tensor([1, 2, 3])
+    out = prepare_inputs(inputs=[cache, ids], pools=pools, static_input_idxs=(0,))
+    assert out[0] is cache
+    assert out[1].data_ptr() != ids.data_ptr() and torch.equal(out[1], ids)
+    assert len(pools) == 1 and pools[0].offset == get_aligned_size(ids)
+
+
+@pytest.mark.gpu
+def test_static_inputs_of_the_wrapper_are_captured_by_address(lib):
+    """A large address-stable input (a KV cache updated in place) declared static is not copied
+    per call, and weights that arrive as `nn.Parameter` inputs are treated the same way; the
+    reference copies every input on every call (src/kernl/optimizer/cuda_graph.py:115-119)."""
+    from kernl_b200.optimizer import cuda_graph
+
+    cuda_graph.static_inputs_pool.clear()
+    cache = torch.zeros((64, 1024, 1024), dtype=torch.float16, device="cuda")  # 128 MiB
+    weight = torch.nn.Parameter(torch.full((1024,), 2.0, dtype=torch.float16, device="cuda"), requires_grad=False)
+    seen = []
+
+    def model(x, kv, w):
+        seen.append((kv.data_ptr(), w.data_ptr()))
+        return (kv[0, 0] * w + x,)
+
+    x = torch.ones(1024, dtype=torch.float16, device="cuda")
+    run = cuda_graph.cuda_graphs_wrapper(model, [x, cache, weight], static_input_idxs=[1])
+    assert all(ptrs == (cache.data_ptr(), weight.data_ptr()) for ptrs in seen)
+    assert sum(p.size for p in cuda_graph.static_inputs_pool) < (1 << 20)  # only x lives in the arena
+    cache[0, 0] = 3.0  # in-place update is visible to the next replay without any copy
+    out = run(x * 5, cache, weight)[0]
+    assert torch.equal(out, torch.full_like(out, 11.0))
+    with pytest.raises(AssertionError):
+        run(x, cache.clone(), weight)
+    cuda_graph.static_inputs_pool.clear()
+
+
 @pytest.mark.gpu
 def test_pool_rejects_other_device_and_exact_fit():
     c = CudaGraphPool(8, device="cpu")

@@ -54,7 +54,7 @@ class OracleOps:
         return O.attention(q, k, v, sm_scale, True, None).to(q.dtype)
 
     @staticmethod
-    def attention_decode(q, k, v, sm_scale, mask):
+    def attention_decode(q, k, v, sm_scale, mask, kv_len):
         return O.attention(q, k, v, sm_scale, False, mask).to(q.dtype)
 
 

@@ -84,23 +84,39 @@ def test_attention_head_dim_128(lib, dtype, tol, causal):
     O.assert_parity(out, expected, max_abs=tol, what="attention d=128")
 
 
-@pytest.mark.parametrize("variant", [1, 2, 3], ids=["blocks128", "blocks64", "split_rows"])
 @pytest.mark.parametrize("d,dtype,tol", [(64, torch.float16, 1e-2), (64, torch.bfloat16, 3e-2), (128, torch.float16, 1e-2), (128, torch.bfloat16, 3e-2)],
                          ids=["d64_fp16", "d64_bf16", "d128_fp16", "d128_bf16"])
 @pytest.mark.parametrize("mask_kind,causal,m,n", [("none", False, 512, 512), ("pad", False, 300, 300), ("bias", True, 257, 257),
                                                   ("none", True, 640, 640), ("bias", False, 100, 700), ("none", False, 1, 24)])
-def test_attention_both_kernels(lib, variant, d, dtype, tol, mask_kind, causal, m, n):
-    """Every fused kernel (128-key blocks; 64-key blocks with double-buffered scores; 64-key blocks
-    with two threads per query row, head dimension 64 only) on every head dimension and dtype it
-    supports, whatever the dispatcher would pick."""
-    if variant == 3 and d != 64:
-        pytest.skip("the split-row kernel serves head dimension 64 only")
-    try:
-        lib.kb_debug_attention_variant(variant)
-        out, expected = _run_attention(2, 3, m, n, d, dtype, causal, mask_kind, d ** -0.5)
-    finally:
-        lib.kb_debug_attention_variant(0)
-    O.assert_parity(out, expected, max_abs=tol, what=f"variant {variant} d={d}")
+def test_attention_both_head_dims(lib, d, dtype, tol, mask_kind, causal, m, n):
+    """Both fused kernels (head dimension 64: 64-key blocks, two threads per query row; head
+    dimension 128: 128-key blocks) on every dtype, mask form and shape class."""
+    out, expected = _run_attention(2, 3, m, n, d, dtype, causal, mask_kind, d ** -0.5)
+    O.assert_parity(out, expected, max_abs=tol, what=f"d={d}")
+
+
+@pytest.mark.parametrize("d,dtype,tol", [(64, torch.float16, 1e-2), (128, torch.bfloat16, 3e-2)], ids=["d64_fp16", "d128_bf16"])
+@pytest.mark.parametrize("group", [2, 4, 8])
+@pytest.mark.parametrize("m,n,causal,mask_kind", [(300, 300, True, "none"), (130, 520, False, "pad"), (1, 700, False, "none")])
+def test_attention_grouped_query(lib, d, dtype, tol, group, m, n, causal, mask_kind):
+    """k/v with H / group heads: query head h reads K/V head h // group — in the fused kernels and,
+    for one query row, in the decode kernel — against the oracle on explicitly repeated K/V."""
+    from kernl_b200.implementations.attention import attention_forward
+    from kernl_b200.implementations.attention_skinny import skinny_attention_forward
+
+    g = torch.Generator().manual_seed(group)
+    B, H = 2, 8
+    q = torch.randn((B, H, m, d), generator=g).to(dtype)
+    k = torch.randn((B, H // group, n, d), generator=g).to(dtype)
+    v = torch.randn((B, H // group, n, d), generator=g).to(dtype)
+    mask = _mask(mask_kind, B, H, m, n, dtype, g)
+    scale = d ** -0.5
+    expected = O.attention(q, k.repeat_interleave(group, 1), v.repeat_interleave(group, 1), scale, causal, mask)
+    qc, kc, vc, mc = _cuda(q, k, v, mask)
+    fn = skinny_attention_forward if m == 1 else attention_forward
+    out = fn(qc, kc, vc, torch.empty_like(qc), scale, causal, mc)
+    O.assert_parity(out, expected, max_abs=tol, what=f"group {group}")
+    O.assert_parity(out, O.attention(q, k, v, scale, causal, mask), max_abs=tol, what="oracle's own head expansion")
 
 
 @pytest.mark.parametrize("tiles", [1, 2], ids=["one_tile_per_cta", "two_tiles_per_cta"])
@@ -311,6 +327,31 @@ def test_skinny_attention_shapes(lib, m, n, d, dtype):
 
     out, expected = _run_attention(2, 3, m, n, d, dtype, False, "pad", 0.3, fn=skinny_attention_forward)
     O.assert_parity(out, expected, max_abs=1e-2 if dtype == torch.float16 else 3e-2)
+
+
+@pytest.mark.parametrize("d,dtype,tol", [(64, torch.float16, 1e-2), (128, torch.bfloat16, 3e-2)], ids=["d64_fp16", "d128_bf16"])
+@pytest.mark.parametrize("live", [1, 127, 128, 129, 1000, 2304])
+def test_skinny_attention_device_side_key_count(lib, d, dtype, tol, live):
+    """A KV cache of 2304 slots of which `live` are filled (the count lives on the device): the
+    result equals attention over the first `live` keys, whatever the other slots hold, and the
+    same captured call follows the count when it changes."""
+    from kernl_b200.implementations.attention_skinny import skinny_attention_forward
+
+    g = torch.Generator().manual_seed(live)
+    B, H, N = 2, 4, 2304
+    q = torch.randn((B, H, 1, d), generator=g).to(dtype)
+    k = torch.randn((B, H, N, d), generator=g).to(dtype)
+    v = torch.randn((B, H, N, d), generator=g).to(dtype)
+    k[:, :, live:] = 50.0   # stale slots must not matter
+    v[:, :, live:] = -70.0
+    qc, kc, vc = _cuda(q, k, v)
+    count = torch.tensor([live], dtype=torch.int64, device="cuda")
+    out = skinny_attention_forward(qc, kc, vc, torch.empty_like(qc), d ** -0.5, False, None, kv_len=count)
+    O.assert_parity(out, O.attention(q, k[:, :, :live], v[:, :, :live], d ** -0.5), max_abs=tol, what=f"{live} live keys")
+    if live > 1:
+        count.fill_(live - 1)
+        out = skinny_attention_forward(qc, kc, vc, torch.empty_like(qc), d ** -0.5, False, None, kv_len=count)
+        O.assert_parity(out, O.attention(q, k[:, :, :live - 1], v[:, :, :live - 1], d ** -0.5), max_abs=tol)
 
 
 @pytest.mark.parametrize("d,dtype,tol", [(64, torch.float16, 1e-2), (128, torch.bfloat16, 3e-2)], ids=["d64_fp16", "d128_bf16"])

@@ -191,8 +191,10 @@ class LlamaTP:
     def _next_norm(self, li):
         return self.layers[li + 1]["norm1"] if li + 1 < len(self.layers) else self.final_norm
 
-    def prefill(self, ids: torch.Tensor) -> torch.Tensor:
-        """ids [B, S] → logits [B, vocab] of the last position; fills the KV cache."""
+    def prefill(self, ids: torch.Tensor, return_hidden: bool = False) -> torch.Tensor:
+        """ids [B, S] → logits [B, vocab] of the last position; fills the KV cache. With
+        `return_hidden` the final-norm hidden states of ALL positions, [B, S, hidden], are returned
+        instead (what a parity check of inner positions needs)."""
         cfg, hl, D = self.cfg, self.heads_local, self.cfg.head_dim
         B, S = ids.shape
         assert S <= cfg.max_seq, f"prompt of {S} tokens does not fit the cache (max_seq {cfg.max_seq})"
@@ -214,6 +216,8 @@ class LlamaTP:
         self.pos.fill_(S)
         self.kv_len.fill_(S)
         self._host_pos = S
+        if return_hidden:
+            return h.reshape(B, S, cfg.hidden)
         last = h.reshape(B, S, cfg.hidden)[:, -1].contiguous()  # already through the final norm
         return self.ops.linear(last, self.lm_head)
 

@@ -184,3 +184,36 @@ def test_llama_kernels_against_oracle_model(lib, use_graph):
         # teacher-force the GPU's token so that one near-tie cannot derail the rest of the check
         logits = cpu2.decode_step(toks[:, t]) if t < 5 else logits
     assert agree >= 5, f"greedy tokens agree on {agree}/6 steps"
+
+
+@pytest.mark.gpu
+def test_llama_full_width_layer_sampled_rows(lib):
+    """Baseline config 5 at full width: ONE layer of the 7B shape (hidden 4096, 32 heads of 128,
+    SwiGLU 11008), batch 8 x 2048, causal, bf16 — the shapes every kernel of the prefill sees — with
+    the final hidden state of sampled (batch, position) pairs compared with the oracle's ops in fp32
+    on the same bf16 weights. A position's output needs the keys/values of its own sequence up to
+    itself and nothing else, so the oracle evaluates just that."""
+    cfg = LlamaConfig(n_layers=1, max_seq=2048)
+    B, S = 8, 2048
+    ids = torch.randint(0, cfg.vocab, (B, S), generator=torch.Generator().manual_seed(0))
+    gpu = LlamaTP(cfg, device="cuda", dtype=torch.bfloat16, seed=0)
+    hidden = gpu.prefill(ids.cuda(), return_hidden=True).float().cpu()  # [B, S, 4096]
+    L = {k: v.float().cpu() for k, v in gpu.layers[0].items()}
+    embed, final_norm = gpu.embed.float().cpu(), gpu.final_norm.float().cpu()
+    cos, sin = gpu.cos.cpu(), gpu.sin.cpu()
+    H, D = cfg.n_heads, cfg.head_dim
+    ops = OracleOps()
+    for b, s_pos in [(0, 0), (0, S - 1), (7, 1000), (3, 129), (5, 2047)]:
+        n = s_pos + 1
+        x = embed[ids[b, :n]]                                           # [n, 4096]
+        h = ops.rms_norm(x, L["norm1"], cfg.eps)
+        qkv = ops.linear(h, L["wqkv"]).reshape(1, n, 3, H, D)
+        q = apply_rope(qkv[:, n - 1:, 0], cos[n - 1:n], sin[n - 1:n])   # the sampled position only
+        k = apply_rope(qkv[:, :, 1], cos[:n], sin[:n])
+        attn = O.attention(q.transpose(1, 2), k.transpose(1, 2), qkv[:, :, 2].transpose(1, 2), D ** -0.5)  # [1, H, 1, D]
+        x1 = x[n - 1:] + ops.linear(attn.transpose(1, 2).reshape(1, H * D), L["wo"])
+        h2 = ops.rms_norm(x1, L["norm2"], cfg.eps)
+        x2 = x1 + ops.linear(ops.gated_linear(h2, L["wgu"]), L["wdn"])
+        want = ops.rms_norm(x2, final_norm, cfg.eps)[0]
+        # final-norm outputs are O(1) (unit RMS); bf16 carries 8 mantissa bits: |x| up to ~4 has ulp 3e-2
+        O.assert_parity(hidden[b, s_pos], want, max_abs=4e-2, cos=0.9995, what=f"batch {b} position {s_pos}")

@@ -68,3 +68,44 @@ def test_t5_generate_reuses_its_graph_across_requests(lib):
     assert torch.equal(first, again)
     eager = T5Kernl(model, device="cuda", dtype=torch.float16, max_new_tokens=12).generate(ids_b, 12, use_cuda_graph=False)
     assert (second == eager).float().mean().item() >= 0.9
+
+
+def test_t5_base_full_size_teacher_forced(lib):
+    """Baseline config 4 at full size: T5-base shape (12 + 12 layers, d_model 768, 12 heads, d_ff 3072
+    ReLU, 32 buckets, vocab 32128), random init, batch 1, encoder input 512 ids — encoder output and the
+    logits of the first 8 decode steps, teacher-forced along the reference's greedy path, against the
+    Hugging Face model in fp32 on the CPU."""
+    from transformers import T5Config, T5ForConditionalGeneration
+
+    from kernl_b200.t5_generate import T5Kernl
+    from oracle import kernl_oracle as O
+
+    torch.manual_seed(0)
+    cfg = T5Config(d_model=768, d_ff=3072, num_layers=12, num_decoder_layers=12, num_heads=12, d_kv=64, vocab_size=32128,
+                   feed_forward_proj="relu", relative_attention_num_buckets=32, decoder_start_token_id=0, pad_token_id=0,
+                   eos_token_id=1)
+    model = T5ForConditionalGeneration(cfg).eval()
+    ids = torch.randint(2, 32128, (1, 512), generator=torch.Generator().manual_seed(0))
+    steps = 8
+    with torch.inference_mode():
+        enc_ref = model.encoder(input_ids=ids).last_hidden_state
+        dec_in = torch.zeros((1, 1), dtype=torch.long)
+        ref_logits, ref_tokens = [], []
+        for _ in range(steps):
+            logits = model(encoder_outputs=(enc_ref,), decoder_input_ids=dec_in).logits[:, -1]
+            ref_logits.append(logits)
+            ref_tokens.append(logits.argmax(-1))
+            dec_in = torch.cat([dec_in, ref_tokens[-1][:, None]], dim=1)
+    runner = T5Kernl(model, device="cuda", dtype=torch.float16, max_new_tokens=steps)
+    enc = runner.encode(ids.cuda())
+    print(f"T5-base encoder vs fp32 CPU: {O.parity(enc, enc_ref)}")
+    O.assert_parity(enc, enc_ref, max_abs=1e-2, cos=0.9995, what="T5-base encoder output")
+    runner.start(enc)
+    tok = torch.zeros(1, dtype=torch.long, device="cuda")
+    scale = float(torch.stack(ref_logits).abs().max())
+    for t in range(steps):
+        logits = runner.decode_step(tok)
+        print(f"T5-base decode step {t}: {O.parity(logits, ref_logits[t])} (largest reference logit {scale:.2f})")
+        # logits reach a few units (fp16 ulp 4e-3 there) after 24 fp16 layers and a 768-term dot product
+        O.assert_parity(logits, ref_logits[t], max_abs=3e-2, cos=0.9995, what=f"T5-base decoder logits step {t}")
+        tok = ref_tokens[t].cuda()

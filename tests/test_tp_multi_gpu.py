@@ -1,6 +1,7 @@
-"""Tensor parallelism on real GPUs (needs at least two): the Llama-shaped decoder sharded over two
-ranks — with NCCL all-reduce and with the library's fused peer-memory all-reduce + residual kernel —
-must reproduce the single-GPU logits, and the fused kernel must match NCCL on raw buffers."""
+"""Tensor parallelism on real GPUs (needs at least two; uses 2, 4 or 8 of what the box has): the
+Llama-shaped decoder sharded over the ranks — with NCCL all-reduce and with the library's fused
+peer-memory all-reduce + residual kernel — must reproduce the single-GPU LOGITS (a token sample
+cannot tell a rounding near-tie from an error), and the fused kernel must match NCCL on raw buffers."""
 import os
 import socket
 
@@ -67,8 +68,8 @@ def _worker(rank, world, port, out_path):
     results["fused_norm_sums_equal"] = sums_equal
     results["fused_norm_max_abs"] = worst_norm
     assert peer.partial_buffer(1024, 4096, torch.bfloat16, dev) is None  # too large for the one-shot kernel
-    # ---- model: TP=2 with both communicators vs the same model on one GPU
-    cfg = LlamaConfig(n_layers=2, hidden=512, n_heads=4, head_dim=128, ffn=1408, vocab=1000, max_seq=208)
+    # ---- model: tensor parallel over all ranks with both communicators vs the same model on one GPU
+    cfg = LlamaConfig(n_layers=2, hidden=1024, n_heads=8, head_dim=128, ffn=2816, vocab=1000, max_seq=208)
     ids = torch.randint(0, cfg.vocab, (2, 200), generator=torch.Generator().manual_seed(0)).to(dev)
     outs = {}
     for name, comm in (("nccl", NcclAllReduce(world)), ("peer", peer)):
@@ -98,21 +99,24 @@ def _worker(rank, world, port, out_path):
     dist.destroy_process_group()
 
 
-def test_two_gpu_tensor_parallel(lib, tmp_path):
+def test_multi_gpu_tensor_parallel(lib, tmp_path):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
 
     from oracle import kernl_oracle as O
 
-    out_path = str(tmp_path / "tp2.pt")
-    mp.spawn(_worker, args=(2, _free_port(), out_path), nprocs=2, join=True)
+    world = 8 if torch.cuda.device_count() >= 8 else 4 if torch.cuda.device_count() >= 4 else 2
+    out_path = str(tmp_path / "tp.pt")
+    mp.spawn(_worker, args=(world, _free_port(), out_path), nprocs=world, join=True)
     r = torch.load(out_path)
+    print(f"world {world}: fused vs NCCL {O.parity(r['peer'], r['nccl'])}, fused vs one GPU {O.parity(r['peer'], r['single'])}, "
+          f"NCCL vs one GPU {O.parity(r['nccl'], r['single'])}")
     # same additions in another order (per-rank partial sums rounded to bf16 before the reduction)
-    assert r["fused_vs_nccl_max_abs"] < 0.13, r["fused_vs_nccl_max_abs"]
+    assert r["fused_vs_nccl_max_abs"] < 0.13 * (world / 2) ** 0.5, r["fused_vs_nccl_max_abs"]
     assert r["fused_norm_sums_equal"]
     assert r["fused_norm_max_abs"] < 4e-2, r["fused_norm_max_abs"]  # bf16 rounding of values up to ~8
-    O.assert_parity(r["nccl"], r["single"], max_abs=6e-2, cos=0.999, what="TP2 (NCCL) vs single GPU")
-    O.assert_parity(r["peer"], r["single"], max_abs=6e-2, cos=0.999, what="TP2 (fused kernel) vs single GPU")
+    O.assert_parity(r["nccl"], r["single"], max_abs=6e-2, cos=0.999, what=f"TP{world} (NCCL) vs single GPU")
+    O.assert_parity(r["peer"], r["single"], max_abs=6e-2, cos=0.999, what=f"TP{world} (fused kernel) vs single GPU")
     O.assert_parity(r["peer"], r["nccl"], max_abs=6e-2, cos=0.999, what="fused kernel vs NCCL")
     assert (r["peer_tokens"] == r["nccl_tokens"]).float().mean() >= 0.8

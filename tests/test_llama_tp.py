@@ -215,5 +215,7 @@ def test_llama_full_width_layer_sampled_rows(lib):
         h2 = ops.rms_norm(x1, L["norm2"], cfg.eps)
         x2 = x1 + ops.linear(ops.gated_linear(h2, L["wgu"]), L["wdn"])
         want = ops.rms_norm(x2, final_norm, cfg.eps)[0]
-        # final-norm outputs are O(1) (unit RMS); bf16 carries 8 mantissa bits: |x| up to ~4 has ulp 3e-2
-        O.assert_parity(hidden[b, s_pos], want, max_abs=4e-2, cos=0.9995, what=f"batch {b} position {s_pos}")
+        # final-norm outputs have unit RMS over 4096 values, so the largest reach 4-5, where bf16 (8
+        # mantissa bits) has an ulp of 3.1e-2; seven bf16 roundings lie between the embedding and the output
+        print(f"batch {b} position {s_pos}: {O.parity(hidden[b, s_pos], want)}")
+        O.assert_parity(hidden[b, s_pos], want, max_abs=6e-2, cos=0.9995, what=f"batch {b} position {s_pos}")

@@ -39,6 +39,17 @@ def _models():
     }
 
 
+def _clamp_eps_like_the_kernel_path(model):
+    """The reference's norm kernel raises eps to 1.6e-5 whenever its input is fp16
+    (src/kernl/implementations/layer_norm.py:295-296), and so does this library. With freshly
+    initialised embeddings (variance ~4e-4) that is a visible change of the model's arithmetic, so
+    the fp32 expectation is computed with the same eps."""
+    for m in model.modules():
+        for attr in ("eps", "variance_epsilon"):
+            if isinstance(getattr(m, attr, None), float) and "norm" in type(m).__name__.lower():
+                setattr(m, attr, max(getattr(m, attr), 1.6e-5))
+
+
 def _main_output(out):
     return out.logits if hasattr(out, "logits") else out.last_hidden_state
 
@@ -56,10 +67,11 @@ def test_small_model_through_optimize_model(lib, name, mode):
     torch.manual_seed(0)
     build, inputs = _models()[name]
     model = build().eval()
+    gpu_model = copy.deepcopy(model)
+    _clamp_eps_like_the_kernel_path(model)
     with torch.inference_mode():
         expected = _main_output(model(**inputs)).float()
     gpu_inputs = {k: v.cuda() for k, v in inputs.items()}
-    gpu_model = copy.deepcopy(model)
     gpu_model = gpu_model.half().cuda() if mode == "half" else gpu_model.cuda()
 
     def call(m):

@@ -709,10 +709,22 @@ static int launch_attention_split_tm(const kb_attn_params& p, cudaStream_t strea
     return launch_attention_split_tmt<T, MODE, 1>(p, stream);
 }
 
+// The persistent form of this kernel (attention_persist.cuh) takes the launches it is made for.
+static bool attention_persist_applicable(const kb_attn_params& p, int mode);
+template <typename T, int MODE>
+static int launch_attention_persist_tm(const kb_attn_params& p, cudaStream_t stream);
+
 template <typename T>
 static int launch_attention_split_t(const kb_attn_params& p, cudaStream_t stream) {
-    if (p.mask == nullptr && p.sm_scale > 0.f) return launch_attention_split_tm<T, 0>(p, stream);
-    if (p.mask != nullptr && p.mask_strides[2] == 0 && p.N <= AttnSplitCfg::kMaskMaxN) return launch_attention_split_tm<T, 1>(p, stream);
+    const int mode = (p.mask == nullptr && p.sm_scale > 0.f) ? 0
+                     : (p.mask != nullptr && p.mask_strides[2] == 0 && p.N <= AttnSplitCfg::kMaskMaxN) ? 1 : 2;
+    if (g_split_tiles == 0 && attention_persist_applicable(p, mode)) {
+        if (mode == 0) return launch_attention_persist_tm<T, 0>(p, stream);
+        if (mode == 1) return launch_attention_persist_tm<T, 1>(p, stream);
+        return launch_attention_persist_tm<T, 2>(p, stream);
+    }
+    if (mode == 0) return launch_attention_split_tm<T, 0>(p, stream);
+    if (mode == 1) return launch_attention_split_tm<T, 1>(p, stream);
     return launch_attention_split_tm<T, 2>(p, stream);
 }
 

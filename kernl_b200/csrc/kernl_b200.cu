@@ -1,5 +1,6 @@
 // C ABI of the kernl_b200 kernels (declared in include/kernl_b200.h) and the host helpers they
 // share. All kernels live in this single translation unit so that they share one device status word.
+#include <atomic>
 #include <cstdio>
 #include <cstring>
 #include <mutex>
@@ -11,6 +12,7 @@
 #include "linear_smallm.cuh"
 #include "attention.cuh"
 #include "attention_split.cuh"
+#include "attention_persist.cuh"
 #include "attention_decode.cuh"
 #include "allreduce.cuh"
 #include "rope.cuh"

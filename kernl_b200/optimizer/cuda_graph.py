@@ -112,8 +112,9 @@ def cuda_graphs_wrapper(model: Callable, inputs: Union[list, tuple], static_inpu
     """Run `model` through a CUDA graph (reference: cuda_graph.py:103-138).
 
     With real example inputs the graph is captured now (after one extra eager call, because
-    kernels may mutate their inputs during warm-up); with FakeTensor inputs everything is deferred
-    to the first real call, with the RNG state preserved around warm-up and capture.
+    kernels may mutate their inputs during warm-up); with FakeTensor inputs (how TorchDynamo calls
+    a backend) the first real call runs eagerly and the second one captures, with the RNG state
+    preserved around warm-up and capture.
 
     The reference copies every input into the arena on every call (cuda_graph.py:115-119), which
     for a decoder means copying its whole KV cache per generated token. Here the inputs listed in
@@ -140,9 +141,19 @@ def cuda_graphs_wrapper(model: Callable, inputs: Union[list, tuple], static_inpu
     replay: Optional[Callable] = None
     static: tuple = ()
     addresses: dict = {}
+    calls = 0
 
     def run(*new_inputs):
-        nonlocal replay, static, addresses
+        nonlocal replay, static, addresses, calls
+        calls += 1
+        if calls == 1:
+            # The first call runs eagerly and captures nothing. A model is usually cut into several
+            # graphs, and the wrappers convert fp32 parameters to fp16 in place the first time they
+            # run (optimizer/linear.py, optimizer/layer_norm.py): a graph captured during the first
+            # forward would keep the address of a parameter that a LATER graph of the same forward
+            # replaces (tied embedding / output weights), and read freed memory on replay. After
+            # one whole forward every parameter has its final storage.
+            return model(*new_inputs)
         if replay is None:
             static = _static_idxs(new_inputs, static_input_idxs)
             addresses = {i: new_inputs[i].data_ptr() for i in static}

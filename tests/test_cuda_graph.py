@@ -150,14 +150,16 @@ def test_cuda_graphs_wrapper_replays_kernels(lib, fake):
         run = cuda_graph.cuda_graphs_wrapper(model, example)
     else:
         run = cuda_graph.cuda_graphs_wrapper(model, [x0.cuda()])
-    ptrs = set()
-    for seed in range(3):
+    ptrs = []
+    for seed in range(4):
         x = torch.randn((64, 128), generator=torch.Generator().manual_seed(seed)).half()
         out = run(x.cuda())[0]
-        ptrs.add(out.data_ptr())
+        ptrs.append(out.data_ptr())
         expected = O.layer_norm(O.linear(x, w, b, "gelu").half(), gamma, beta, 1.6e-5)
         O.assert_parity(out, expected, max_abs=2e-2)
-    assert len(ptrs) == 1
+    # static outputs: every replay writes the same tensor (in deferred mode the first call runs
+    # eagerly, before anything is captured, and returns an ordinary tensor)
+    assert len(set(ptrs[1:] if fake else ptrs)) == 1
     cuda_graph.static_inputs_pool.clear()
 
 

@@ -135,6 +135,65 @@ def test_attention_split_rows_both_cta_shapes(lib, tiles, dtype, tol, mask_kind,
     O.assert_parity(out, expected, max_abs=tol, what=f"split rows, {tiles} tile(s) per CTA")
 
 
+@pytest.mark.parametrize("dtype,tol", [(torch.float16, 1e-2), (torch.bfloat16, 3e-2)], ids=["fp16", "bf16"])
+@pytest.mark.parametrize("mask_kind,causal,m,n", [("none", False, 512, 512), ("pad", False, 300, 300), ("bias", True, 257, 257),
+                                                  ("none", True, 640, 640), ("bias", False, 100, 700), ("none", False, 1, 24),
+                                                  ("pad", False, 1100, 1100), ("pad", True, 384, 384)])
+def test_attention_persistent_scheduling_small_launches(lib, dtype, tol, mask_kind, causal, m, n):
+    """The head-dimension-64 kernel with persistent CTAs drawing query tiles from the device-side
+    queue, forced on launches of a few tiles (every CTA draws one tile and then finds the queue
+    empty) up to a few tiles per CTA."""
+    try:
+        lib.kb_debug_attention_persistent(1)
+        out, expected = _run_attention(2, 3, m, n, 64, dtype, causal, mask_kind, 0.125)
+    finally:
+        lib.kb_debug_attention_persistent(-1)
+    O.assert_parity(out, expected, max_abs=tol, what="persistent CTAs")
+
+
+@pytest.mark.parametrize("kind", ["none", "pad", "causal", "bias", "pad_causal"])
+@pytest.mark.parametrize("shape", [(16, 12, 512), (40, 12, 128), (3, 16, 4096), (8, 12, 512)], ids=str)
+def test_attention_persistent_scheduling_equals_one_cta_per_tile(lib, shape, kind):
+    """Launches of more query tiles than CTA slots (what the dispatcher gives to the persistent
+    kernel): every tile goes through the same arithmetic in both forms of the kernel, so the outputs
+    must be bit-identical whatever CTA computed a tile and in whatever order; sampled (batch, head)
+    slices are checked against the oracle as well. Repeated, because the tile-to-CTA assignment
+    depends on timing."""
+    from kernl_b200.implementations.attention import attention_forward
+
+    B, H, S = shape
+    g = torch.Generator().manual_seed(B * 1000 + S)
+    q, k, v = (torch.randn((B, H, S, 64), generator=g).half() for _ in range(3))
+    mask = None
+    if kind.startswith("pad"):
+        valid = torch.randint(min(64, S), S + 1, (B,), generator=g)
+        valid[0] = S // 3
+        mask = torch.where(valid[:, None] > torch.arange(S)[None, :], 0.0, float("-inf")).reshape(B, 1, 1, S).half()
+    elif kind == "bias":
+        if B * H * S * S * 2 > (1 << 31):
+            pytest.skip("bias mask of this shape is larger than needed here")
+        mask = torch.rand((B, H, S, S), generator=g).half()
+    causal = kind.endswith("causal")
+    qc, kc, vc, mc = _cuda(q, k, v, mask)
+    outs = {}
+    for mode in (0, 1, 1, 1):
+        try:
+            lib.kb_debug_attention_persistent(mode)
+            out = attention_forward(qc, kc, vc, torch.empty_like(qc), 0.125, causal, mc)
+        finally:
+            lib.kb_debug_attention_persistent(-1)
+        if mode in outs:
+            assert torch.equal(out, outs[mode]), "two runs of the persistent kernel differ"
+        outs[mode] = out
+    assert torch.equal(outs[0], outs[1]), "persistent CTAs and one CTA per tile disagree"
+    default = attention_forward(qc, kc, vc, torch.empty_like(qc), 0.125, causal, mc)
+    assert torch.equal(default, outs[1])
+    for b, h in [(0, 0), (B - 1, H - 1), (B // 2, 5)]:
+        exp = O.attention(q[b:b + 1, h:h + 1], k[b:b + 1, h:h + 1], v[b:b + 1, h:h + 1], 0.125, causal,
+                          None if mask is None else mask[b:b + 1, (h if mask.shape[1] > 1 else 0):(h if mask.shape[1] > 1 else 0) + 1])
+        O.assert_parity(outs[1][b:b + 1, h:h + 1], exp, what=f"batch {b} head {h}")
+
+
 @pytest.mark.parametrize("fill", [float("-inf"), -65504.0, -10000.0], ids=["neg_inf", "fp16_lowest", "minus_1e4"])
 @pytest.mark.parametrize("causal", [False, True], ids=["full", "causal"])
 def test_attention_padding_mask_with_fully_masked_key_blocks(lib, fill, causal):

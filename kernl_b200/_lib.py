@@ -135,7 +135,7 @@ def load() -> ctypes.CDLL:
     lib.kb_status_str.restype = ctypes.c_char_p
     lib.kb_version.restype = ctypes.c_int
     # unstable test hooks (include/kernl_b200_debug.h)
-    for hook in ("kb_debug_force_bn", "kb_debug_force_splits", "kb_debug_pdl", "kb_debug_split_tiles", "kb_debug_attention_persistent"):
+    for hook in ("kb_debug_force_bn", "kb_debug_force_splits", "kb_debug_pdl", "kb_debug_split_tiles", "kb_debug_attention_persistent", "kb_debug_linear_pair"):
         if hasattr(lib, hook):
             getattr(lib, hook).argtypes = [ctypes.c_int]
             getattr(lib, hook).restype = None

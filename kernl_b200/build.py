@@ -12,7 +12,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_PATH = os.path.join(HERE, "libkernl_b200.so")
 SOURCES = ["kernl_b200.cu"]
-HEADERS = ["common.cuh", "norm.cuh", "linear.cuh", "linear_smallm.cuh", "attention.cuh", "attention_split.cuh", "attention_persist.cuh", "attention_decode.cuh", "allreduce.cuh", "rope.cuh"]
+HEADERS = ["common.cuh", "norm.cuh", "linear.cuh", "linear_pair.cuh", "linear_smallm.cuh", "attention.cuh", "attention_split.cuh", "attention_persist.cuh", "attention_decode.cuh", "allreduce.cuh", "rope.cuh"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-lineinfo", "-O3", "-std=c++17", "--shared",

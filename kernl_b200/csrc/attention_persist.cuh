@@ -34,6 +34,26 @@ namespace kb {
 constexpr int kAttnQueueSlots = 1024;
 __device__ unsigned int g_attn_queue[kAttnQueueSlots][2];
 
+// Optional time stamps for tuning (compiled in with -DKB_ATTN_TRACE only): per CTA and tile, when the
+// tile was published, when the softmax warps began it, when its first scores were ready, when its key
+// loop and its epilogue ended (%globaltimer, ns); slot 15 of a CTA holds start, end, SM id and tiles.
+#ifdef KB_ATTN_TRACE
+constexpr int kTraceTiles = 15, kTraceEvents = 8;
+__device__ unsigned long long g_attn_trace[296 * (kTraceTiles + 1) * kTraceEvents];
+__device__ __forceinline__ unsigned long long trace_now() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+#define KB_TRACE(tile, ev, val)                                                                         \
+    do {                                                                                                \
+        if (blockIdx.x < 296 && (tile) <= kTraceTiles)                                                  \
+            g_attn_trace[((size_t)blockIdx.x * (kTraceTiles + 1) + (tile)) * kTraceEvents + (ev)] = (val); \
+    } while (0)
+#else
+#define KB_TRACE(tile, ev, val) do { } while (0)
+#endif
+
 struct AttnItem {   // one slot of the CTA's two-deep tile pipeline (shared memory)
     int bh;         // batch * H + head, or -1: no more tiles
     int mt;         // query tile
@@ -59,11 +79,82 @@ struct AttnPersistCfg {
     static_assert(2 * kRegsHigh + kRegsLow <= 3 * kRegsLaunch, "setmaxnreg totals exceed the CTA's register pool");
 };
 
+// Stages one mask row for MODE 1: clamped, in the log2 domain, -inf beyond N (see attention_split.cuh).
+// The calling warps cover the columns [first, mask_cols) in steps of `step` (both multiples of 32, so a
+// warp always holds half a key block); `bits` collects, warp-uniformly, the key blocks in which this
+// warp saw a value above kSkipBelow. Eight loads are in flight per thread before the first is used.
+__device__ __forceinline__ void stage_mask_row(const AttnDev& p, int b, int h, float* dst, int mask_cols, int first, int step,
+                                               uint32_t (&bits)[4]) {
+    const float mlow = mask_lowest(p.mask_dtype);
+    const int64_t moff = (int64_t)b * p.mask_strides[0] + (int64_t)h * p.mask_strides[1];
+    const int lane = threadIdx.x & 31;
+    if (first == 0 && step == 32 && p.mask_vec && p.mask_dtype != KB_F32 && (p.N & 7) == 0 && mask_cols <= 1536) {
+        // One warp, 16-bit contiguous 16-byte-aligned row: 256 values per 128-bit load of the warp,
+        // all loads (at most six) in flight at once.
+        const uint16_t* row = reinterpret_cast<const uint16_t*>(p.mask) + moff;
+        uint4 raw[6];
+#pragma unroll
+        for (int e = 0; e < 6; ++e) {
+            const int col = e * 256 + lane * 8;
+            raw[e] = make_uint4(0xfc00fc00u, 0xfc00fc00u, 0xfc00fc00u, 0xfc00fc00u);
+            if (col < p.N) raw[e] = __ldg(reinterpret_cast<const uint4*>(row + col));
+        }
+#pragma unroll
+        for (int e = 0; e < 6; ++e) {
+            const int col = e * 256 + lane * 8;
+            if (e * 256 < mask_cols) {
+                const uint32_t w4[4] = {raw[e].x, raw[e].y, raw[e].z, raw[e].w};
+                float v[8];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float2 f = (p.mask_dtype == KB_F16) ? Elem<__half>::unpack2(w4[i]) : Elem<__nv_bfloat16>::unpack2(w4[i]);
+                    v[2 * i] = f.x;
+                    v[2 * i + 1] = f.y;
+                }
+                bool mine = false;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    v[i] = (col + i < p.N) ? fmaxf(v[i], mlow) * kLog2e : -INFINITY;
+                    mine = mine || v[i] > kSkipBelow;
+                }
+                if (col < mask_cols) {
+                    *reinterpret_cast<float4*>(dst + col) = make_float4(v[0], v[1], v[2], v[3]);
+                    *reinterpret_cast<float4*>(dst + col + 4) = make_float4(v[4], v[5], v[6], v[7]);
+                }
+                const uint32_t ballot = __ballot_sync(0xffffffffu, mine);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const int blk = e * 4 + k;
+                    if ((ballot >> (8 * k)) & 0xffu) bits[blk >> 5] |= 1u << (blk & 31);
+                }
+            }
+        }
+        return;
+    }
+    for (int c0 = first; c0 < mask_cols; c0 += 8 * step) {
+        float vals[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const int col = c0 + e * step + lane;
+            vals[e] = (col < p.N) ? mask_load(p.mask, moff + (int64_t)col * p.mask_strides[3], p.mask_dtype) : -INFINITY;
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const int col = c0 + e * step + lane;
+            const float v = (col < p.N) ? fmaxf(vals[e], mlow) * kLog2e : -INFINITY;
+            if (col < mask_cols) dst[col] = v;
+            const bool live = __any_sync(0xffffffffu, col < p.N && v > kSkipBelow);
+            const int blk = (c0 + e * step) >> 6;
+            if (live && blk < 128) bits[blk >> 5] |= 1u << (blk & 31);
+        }
+    }
+}
+
 template <typename T, int MODE>
 __global__ void __launch_bounds__(AttnPersistCfg::kThreads, 2)
 attention_persist_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                          const __grid_constant__ CUtensorMap tmap_v, const AttnDev p, const int num_items,
-                         const int mask_cols, unsigned int* const queue) {
+                         const int mask_cols, unsigned int* const queue, const int sort_batches) {
     using Cfg = AttnPersistCfg;
     constexpr int D = 64;
     constexpr int KVS = Cfg::kKvStages;
@@ -94,19 +185,35 @@ attention_persist_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
     auto k_empty = [&](int s) { return bar_base + 8u * (kKvBar + KVS + s); };
     auto v_full = [&](int s) { return bar_base + 8u * (kKvBar + 2 * KVS + s); };
     auto v_empty = [&](int s) { return bar_base + 8u * (kKvBar + 3 * KVS + s); };
-    constexpr int kNumBars = kKvBar + 4 * KVS;
+    const uint32_t near_end = bar_base + 8u * (kKvBar + 4 * KVS);  // the issuer has issued a tile's last Q·Kᵀ
+    constexpr int kNumBars = kKvBar + 4 * KVS + 1;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBars);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     AttnItem* items = reinterpret_cast<AttnItem*>(tmem_slot + 4);  // two slots
-    static_assert(kNumBars * 8 + 16 + 2 * sizeof(AttnItem) <= Cfg::kBarBytes, "barrier area too small");
+    uint32_t* warp_bits = reinterpret_cast<uint32_t*>(items + 2);  // [12 warps][4]: live blocks of the first tile, per staging warp
+    int* batch_order = reinterpret_cast<int*>(warp_bits + 12 * 4);  // [32]: batches, longest first (sort_batches)
+    int* setup_issued = batch_order + 32;  // K/V blocks of the first tile that the set-up has requested already
+    static_assert(kNumBars * 8 + 16 + 2 * sizeof(AttnItem) + 12 * 16 + 32 * 4 + 4 <= Cfg::kBarBytes, "barrier area too small");
     float2* xch = reinterpret_cast<float2*>(smem + Cfg::kTilesBytes + Cfg::kBarBytes);
     float* mask_smem = reinterpret_cast<float*>(smem + Cfg::kTilesBytes + Cfg::kBarBytes + Cfg::kXchBytes);  // [2][mask_cols]
+    // sort_batches: [12 warps][32 batches] live-block words, in the (not yet used) second mask row
+    uint32_t* warp_live = reinterpret_cast<uint32_t*>(mask_smem + mask_cols);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#ifdef KB_ATTN_TRACE
+    if (threadIdx.x == 0) {
+        unsigned smid;
+        asm volatile("mov.u32 %0, %smid;" : "=r"(smid));
+        KB_TRACE(kTraceTiles, 0, trace_now());
+        KB_TRACE(kTraceTiles, 2, (unsigned long long)smid);
+    }
+#endif
+    // A wait that expired in an earlier launch leaves the status word set: such a launch does no
+    // work. The word is read here and looked at after the set-up barrier, so that its latency
+    // overlaps the set-up instead of preceding it.
     __shared__ int s_skip;
-    if (threadIdx.x == 0) s_skip = *reinterpret_cast<volatile int*>(&g_device_status[0]);
-    __syncthreads();
-    const bool skip = s_skip != 0;
+    int status_early = 0;
+    if (threadIdx.x == 0 || threadIdx.x == 8 * 32) status_early = *reinterpret_cast<volatile int*>(&g_device_status[0]);
 
     const int BH = p.B * p.H;
     const int num_n_blocks = (p.N + kBlkN - 1) / kBlkN;
@@ -120,8 +227,34 @@ attention_persist_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
         mt = p.num_pairs - 1 - rem / gsz;
         bh = first + rem % gsz;
     };
+    // With sort_batches the batch part of a tile number counts batches from the longest (most live
+    // key blocks behind its padding mask) to the shortest, so the tiles that CTAs start with are the
+    // long ones and those drawn from the queue later are the short ones: the launch ends with
+    // little work left per CTA instead of a long tile that somebody started late.
+    auto locate_sorted = [&](int idx, int& bh, int& mt) {
+        if (!sort_batches) {
+            locate(idx, bh, mt);
+            return;
+        }
+        // batch-major: all tiles of the longest batch, then of the next one, ...; inside a batch
+        // the heads of one query tile are neighbours (they share no K/V, but a batch's K/V of all
+        // heads is small next to L2)
+        const int per_batch = p.H * p.num_pairs;
+        const int r = idx / per_batch, rem = idx % per_batch;
+        mt = p.num_pairs - 1 - rem / p.H;
+        bh = batch_order[r] * p.H + rem % p.H;
+    };
+    // The CTA's first tile is its block index: known without the queue, so its operands are
+    // requested during set-up and its mask row is staged by all threads at once.
+    int bh0, mt0;
+    locate((int)blockIdx.x, bh0, mt0);
+    const int nblk0 = p.is_causal ? min(num_n_blocks, (mt0 + 1) * (kAttnBlock / kBlkN)) : num_n_blocks;
+    // MODE 1 does not know which key blocks it will visit before the mask has been looked at: it
+    // only pulls the first ring of K/V blocks into L2 during set-up
+    const int first_kv = (MODE == 1) ? 0 : min(KVS, nblk0);
+    const bool early_q = !(MODE == 1 && sort_batches);  // sorted: the first tile is known after the scan only (requested there)
 
-    if (!skip) {
+    {
         if (warp == 8) {
             if (lane == 0) {
                 tma_prefetch_desc(&tmap_q);
@@ -138,7 +271,26 @@ attention_persist_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
                     mbar_init(v_full(s), 1);
                     mbar_init(v_empty(s), 1);
                 }
+                mbar_init(near_end, 1);
                 fence_mbar_init();
+                pdl_wait();  // q/k/v may be the output of the kernel before this one
+              if (status_early == 0 && early_q) {
+                const int b0 = bh0 / p.H, h0 = bh0 % p.H, hk0 = h0 / p.kv_group;
+                mbar_arrive_expect_tx(q_full(0), QTILE);
+                tma_load_4d(q_smem, &tmap_q, q_full(0), 0, mt0 * kAttnBlock, h0, b0);
+                if (MODE == 1) {
+                    for (int j = 0; j < min(KVS, nblk0); ++j) {
+                        tma_prefetch_l2_4d(&tmap_k, 0, j * kBlkN, hk0, b0);
+                        tma_prefetch_l2_4d(&tmap_v, 0, j * kBlkN, hk0, b0);
+                    }
+                }
+                for (int j = 0; j < first_kv; ++j) {
+                    mbar_arrive_expect_tx(k_full(j), KVB);
+                    tma_load_4d(k_smem + j * KVB, &tmap_k, k_full(j), 0, j * kBlkN, hk0, b0);
+                    mbar_arrive_expect_tx(v_full(j), KVB);
+                    tma_load_4d(v_smem + j * KVB, &tmap_v, v_full(j), 0, j * kBlkN, hk0, b0);
+                }
+              }
             }
         } else if (warp == 0) {
             if (lane < 2) {
@@ -149,7 +301,10 @@ attention_persist_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
             if (lane == 2) mbar_init(o_final, 1);
             if (lane == 3) mbar_init(o_free, 8);
             if (lane >= 4 && lane < 8) mbar_init(ep_bar(lane - 4), 2);
-            if (lane == 0) *abort_flag = 0;
+            if (lane == 0) {
+                *abort_flag = 0;
+                s_skip = status_early;
+            }
             fence_mbar_init();
         } else if (warp == 9) {
             tmem_alloc(smem_u32(tmem_slot), kTmemCols);
@@ -157,12 +312,134 @@ attention_persist_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
         }
     }
     // Launched with programmatic dependent launch: everything above may run while the previous
-    // kernel of the stream drains; nothing of global memory is touched before this point.
+    // kernel of the stream drains; nothing of global memory is touched before this point (the TMA
+    // thread has made the same wait before its loads).
     pdl_wait();
+#ifdef KB_ATTN_TRACE
+    if (threadIdx.x == 0) KB_TRACE(kTraceTiles, 3, trace_now());
+#endif
+    if (MODE == 1 && !sort_batches) {
+        // every warp stages its share of the first tile's mask row and leaves the key blocks it
+        // found live in its own slot; the scheduler combines the slots after the barrier
+        uint32_t bits[4] = {0u, 0u, 0u, 0u};
+        stage_mask_row(p, bh0 / p.H, bh0 % p.H, mask_smem, mask_cols, warp * 32, Cfg::kThreads, bits);
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+            if (lane == i) warp_bits[warp * 4 + i] = bits[i];
+    }
+    if (MODE == 1 && sort_batches) {
+        // All batches' mask rows (the mask is the same for every head and query row): which key
+        // blocks of each are live. The rows are 16-bit, contiguous and 16-byte aligned (checked by
+        // the host), so a warp reads 256 values — four key blocks of one batch — per 128-bit load;
+        // warp w takes the 256-value pieces w, w + 12, ... and keeps what it saw in its own row of
+        // warp_live (at most 32 batches of at most 32 key blocks).
+        warp_live[warp * 32 + lane] = 0u;
+        __syncwarp();
+        const float mlow_s = mask_lowest(p.mask_dtype);
+        constexpr int kW = Cfg::kThreads / 32;
+        constexpr int kRounds = 4;  // 12 warps x 4 rounds x 256 values = 12288 >= B x mask_cols
+        const int pieces_per_row = (mask_cols + 255) >> 8;
+        const int pieces = p.B * pieces_per_row;
+        uint4 vals[kRounds];
+#pragma unroll
+        for (int r = 0; r < kRounds; ++r) {
+            const int pc = warp + r * kW;
+            const int bb = pc / pieces_per_row, col = (pc % pieces_per_row) * 256 + lane * 8;
+            vals[r] = make_uint4(0xfc00fc00u, 0xfc00fc00u, 0xfc00fc00u, 0xfc00fc00u);  // -inf in fp16; very negative in bf16
+            if (pc < pieces && col < p.N)
+                vals[r] = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.mask) + (int64_t)bb * p.mask_strides[0] + col));
+        }
+#pragma unroll
+        for (int r = 0; r < kRounds; ++r) {
+            const int pc = warp + r * kW;
+            const int bb = pc / pieces_per_row, blk0 = (pc % pieces_per_row) * 4;
+            const uint32_t w4[4] = {vals[r].x, vals[r].y, vals[r].z, vals[r].w};
+            bool mine = false;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 f = (p.mask_dtype == KB_F16) ? Elem<__half>::unpack2(w4[i]) : Elem<__nv_bfloat16>::unpack2(w4[i]);
+                mine = mine || f.x * kLog2e > kSkipBelow || f.y * kLog2e > kSkipBelow;
+            }
+            const uint32_t ballot = __ballot_sync(0xffffffffu, mine);
+            if (lane == 0 && pc < pieces) {
+                uint32_t bits = 0u;
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                    if ((ballot >> (8 * k)) & 0xffu) bits |= 1u << (blk0 + k);
+                warp_live[warp * 32 + bb] |= bits;
+            }
+        }
+        // Every warp now ranks the batches (longest first, ties by number) for itself, which tells
+        // it the batch of this CTA's first tile; the threads that hold that batch's mask values put
+        // them into mask slot 0, and the TMA thread requests the tile's Q and first K/V blocks —
+        // nobody reads the mask from memory a second time or waits for the scheduler warp.
+        __syncthreads();
+        uint32_t w = 0u;
+#pragma unroll
+        for (int ww = 0; ww < kW; ++ww) w |= warp_live[ww * 32 + lane];
+        const int len = (lane < p.B) ? (w != 0u ? __popc(w) : num_n_blocks) : -1;
+        int rank = 0;
+        for (int o = 0; o < 32; ++o) {
+            const int other = __shfl_sync(0xffffffffu, len, o);
+            rank += (other > len || (other == len && o < lane)) ? 1 : 0;
+        }
+        if (warp == 10 && lane < p.B) batch_order[rank] = lane;  // the scheduler warp keeps the table for the later tiles
+        const int per_batch = p.H * p.num_pairs;
+        const int r0 = (int)blockIdx.x / per_batch, rem0 = (int)blockIdx.x % per_batch;
+        const int b0 = __ffs((int)__ballot_sync(0xffffffffu, lane < p.B && rank == r0)) - 1;
+        const uint32_t live0 = __shfl_sync(0xffffffffu, w, b0);
+#pragma unroll
+        for (int r = 0; r < kRounds; ++r) {
+            const int pc = warp + r * kW;
+            const int bb = pc / pieces_per_row, col = (pc % pieces_per_row) * 256 + lane * 8;
+            if (pc < pieces && bb == b0 && col < mask_cols) {
+                const uint32_t w4[4] = {vals[r].x, vals[r].y, vals[r].z, vals[r].w};
+                float v[8];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float2 f = (p.mask_dtype == KB_F16) ? Elem<__half>::unpack2(w4[i]) : Elem<__nv_bfloat16>::unpack2(w4[i]);
+                    v[2 * i] = f.x;
+                    v[2 * i + 1] = f.y;
+                }
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] = (col + i < p.N) ? fmaxf(v[i], mlow_s) * kLog2e : -INFINITY;
+                *reinterpret_cast<float4*>(mask_smem + col) = make_float4(v[0], v[1], v[2], v[3]);
+                *reinterpret_cast<float4*>(mask_smem + col + 4) = make_float4(v[4], v[5], v[6], v[7]);
+            }
+        }
+        if (warp == 8 && lane == 0) {
+            int issued = 0;
+            if (status_early == 0) {
+                const int mt_s = p.num_pairs - 1 - rem0 / p.H, h_s = rem0 % p.H, hk_s = h_s / p.kv_group;
+                const uint32_t act_s[4] = {live0 != 0u ? live0 : 0xffffffffu, live0 != 0u ? 0u : 0xffffffffu,
+                                           live0 != 0u ? 0u : 0xffffffffu, live0 != 0u ? 0u : 0xffffffffu};
+                const int nb_s = bits_count_below(act_s, num_n_blocks);
+                mbar_arrive_expect_tx(q_full(0), QTILE);
+                tma_load_4d(q_smem, &tmap_q, q_full(0), 0, mt_s * kAttnBlock, h_s, b0);
+                int jb = bits_next(act_s, 0);
+                for (; issued < min(KVS, nb_s); ++issued) {
+                    mbar_arrive_expect_tx(k_full(issued), KVB);
+                    tma_load_4d(k_smem + issued * KVB, &tmap_k, k_full(issued), 0, jb * kBlkN, hk_s, b0);
+                    mbar_arrive_expect_tx(v_full(issued), KVB);
+                    tma_load_4d(v_smem + issued * KVB, &tmap_v, v_full(issued), 0, jb * kBlkN, hk_s, b0);
+                    jb = bits_next(act_s, jb + 1);
+                }
+            }
+            *setup_issued = issued;
+        }
+    }
+    if (!(MODE == 1 && sort_batches) && warp == 8 && lane == 0) *setup_issued = first_kv;
+#ifdef KB_ATTN_TRACE
+    if (threadIdx.x == 0) KB_TRACE(kTraceTiles, 4, trace_now());
+#endif
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+#ifdef KB_ATTN_TRACE
+    if (threadIdx.x == 0) KB_TRACE(kTraceTiles, 5, trace_now());
+#endif
 
+    const bool skip = s_skip != 0;
     if (!skip) {
       const uint32_t tmem_base = *tmem_slot;
       if (warp >= 8) {
@@ -170,8 +447,18 @@ attention_persist_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
         if (warp == 10) {
             // -------------------------------------------------------------- scheduler (whole warp)
             bool ok = true;
+#ifdef KB_ATTN_TRACE
+            if (lane == 0) KB_TRACE(kTraceTiles, 6, trace_now());
+#endif
             for (int it = 0; ok; ++it) {
                 const int slot = it & 1;
+                // The next tile is drawn only once the current one is two key blocks from its end (its
+                // last Q·Kᵀ has been issued; scores run two blocks ahead of the softmax): a CTA that is
+                // busy with a long tile must not reserve another one that an idle CTA could have started
+                // at once. Two blocks and the epilogue are enough to stage the next tile behind them.
+                if (it >= 1) {
+                    if (!mbar_wait(near_end, (uint32_t)((it - 1) & 1), abort_flag, 701)) { ok = false; break; }
+                }
                 int idx = 0;
                 if (lane == 0) idx = (it == 0) ? (int)blockIdx.x : (int)gridDim.x + (int)atomicAdd(&queue[0], 1u);
                 idx = __shfl_sync(0xffffffffu, idx, 0);
@@ -180,6 +467,7 @@ attention_persist_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
                 }
                 AttnItem* item = &items[slot];
                 if (idx >= num_items) {
+                    __syncwarp();
                     if (lane == 0) {
                         item->bh = -1;
                         mbar_arrive(item_full(slot));
@@ -188,34 +476,21 @@ attention_persist_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
                     break;
                 }
                 int bh, mt;
-                locate(idx, bh, mt);
+                locate_sorted(idx, bh, mt);
                 const int nblk = p.is_causal ? min(num_n_blocks, (mt + 1) * (kAttnBlock / kBlkN)) : num_n_blocks;
                 uint32_t act[4] = {0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu};
                 int nb = nblk;
                 if (MODE == 1) {
-                    // this tile's mask row: clamped, in the log2 domain, -inf beyond N; a key block is
-                    // live if one of its values is above kSkipBelow (see attention_split.cuh)
-                    const int b = bh / p.H, h = bh % p.H;
-                    const float mlow = mask_lowest(p.mask_dtype);
-                    const int64_t moff = (int64_t)b * p.mask_strides[0] + (int64_t)h * p.mask_strides[1];
-                    float* dst = mask_smem + slot * mask_cols;
                     uint32_t bits[4] = {0u, 0u, 0u, 0u};
-                    for (int c0 = 0; c0 < mask_cols; c0 += 128) {
-                        float vals[4];
+                    if (it == 0 && !sort_batches) {  // staged by the whole CTA during set-up
+                        for (int w = 0; w < Cfg::kThreads / 32; ++w) {
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const int col = c0 + e * 32 + lane;
-                            vals[e] = (col < p.N) ? mask_load(p.mask, moff + (int64_t)col * p.mask_strides[3], p.mask_dtype) : -INFINITY;
+                            for (int i = 0; i < 4; ++i) bits[i] |= warp_bits[w * 4 + i];
                         }
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const int col = c0 + e * 32 + lane;
-                            const float v = (col < p.N) ? fmaxf(vals[e], mlow) * kLog2e : -INFINITY;
-                            if (col < mask_cols) dst[col] = v;
-                            const bool live = __any_sync(0xffffffffu, col < p.N && v > kSkipBelow);
-                            const int blk = (c0 + e * 32) >> 6;
-                            if (live && blk < 128) bits[blk >> 5] |= 1u << (blk & 31);
-                        }
+                    } else if (it == 0) {  // sorted: staged from the scan's registers; live blocks from the scan
+                        for (int w = 0; w < Cfg::kThreads / 32; ++w) bits[0] |= warp_live[w * 32 + bh / p.H];
+                    } else {
+                        stage_mask_row(p, bh / p.H, bh % p.H, mask_smem + slot * mask_cols, mask_cols, 0, 32, bits);
                     }
                     // Nothing is skipped when the whole row is masked (the reference then returns a
                     // plain softmax), nor for causal calls (a row's prefix may hold masked keys only).
@@ -226,6 +501,9 @@ attention_persist_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
                     nb = bits_count_below(act, nblk);
                 }
                 __syncwarp();
+#ifdef KB_ATTN_TRACE
+                if (lane == 0 && it == 0) KB_TRACE(kTraceTiles, 7, trace_now());
+#endif
                 if (lane == 0) {
                     item->bh = bh;
                     item->mt = mt;
@@ -234,6 +512,11 @@ attention_persist_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
 #pragma unroll
                     for (int i = 0; i < 4; ++i) item->act[i] = act[i];
                     mbar_arrive(item_full(slot));  // release: the mask row and the item are visible to who waits
+#ifdef KB_ATTN_TRACE
+                    KB_TRACE(it, 0, trace_now());
+                    KB_TRACE(it, 5, (unsigned long long)nb);
+                    KB_TRACE(it, 6, (unsigned long long)idx);
+#endif
                 }
             }
         } else if (warp == 8) {
@@ -241,30 +524,25 @@ attention_persist_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
             if (elect_one()) {
                 bool ok = true;
                 int kv_i = 0;  // K/V ring position, running over the CTA's life
-                {   // pull the first tile's operands towards L2 while the scheduler stages its mask
-                    int bh0, mt0;
-                    locate((int)blockIdx.x, bh0, mt0);
-                    const int b0 = bh0 / p.H, h0 = bh0 % p.H, hk0 = h0 / p.kv_group;
-                    tma_prefetch_l2_4d(&tmap_q, 0, mt0 * kAttnBlock, h0, b0);
-                    for (int j = 0; j < min(KVS, num_n_blocks); ++j) {
-                        tma_prefetch_l2_4d(&tmap_k, 0, j * kBlkN, hk0, b0);
-                        tma_prefetch_l2_4d(&tmap_v, 0, j * kBlkN, hk0, b0);
-                    }
-                }
                 for (int it = 0; ok; ++it) {
                     const int slot = it & 1;
                     if (!mbar_wait(item_full(slot), (uint32_t)((it >> 1) & 1), abort_flag, 710)) { ok = false; break; }
                     const AttnItem item = items[slot];
-                    if (item.bh < 0) {
-                        mbar_arrive(q_full(slot));  // pass the end of the queue on to the consumers
-                        break;
-                    }
+                    if (item.bh < 0) break;
                     const int b = item.bh / p.H, h = item.bh % p.H, hk = h / p.kv_group;
-                    // the scheduler has waited for slot_free: Q buffer `slot` is no longer read
-                    mbar_arrive_expect_tx(q_full(slot), QTILE);
-                    tma_load_4d(q_smem + slot * QTILE, &tmap_q, q_full(slot), 0, item.mt * kAttnBlock, h, b);
+                    int i = 0;
                     int jb = (MODE == 1) ? bits_next(item.act, 0) : 0;
-                    for (int i = 0; i < item.nb; ++i, ++kv_i) {
+                    if (it == 0) {
+                        // Q and the first blocks of the first tile were requested during set-up
+                        const int done = *setup_issued;
+                        for (; i < done; ++i) jb = (MODE == 1) ? bits_next(item.act, jb + 1) : jb + 1;
+                        kv_i = done;
+                    } else {
+                        // the scheduler has waited for slot_free: Q buffer `slot` is no longer read
+                        mbar_arrive_expect_tx(q_full(slot), QTILE);
+                        tma_load_4d(q_smem + slot * QTILE, &tmap_q, q_full(slot), 0, item.mt * kAttnBlock, h, b);
+                    }
+                    for (; i < item.nb; ++i, ++kv_i) {
                         const int s = kv_i % KVS;
                         const uint32_t ph = (uint32_t)((kv_i / KVS) & 1);
                         if (!mbar_wait(k_empty(s), ph ^ 1, abort_flag, 711)) { ok = false; break; }
@@ -294,9 +572,10 @@ attention_persist_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
                 int kv_i = 0;  // K/V ring position of the current tile's first block
                 for (int it = 0; ok; ++it) {
                     const int slot = it & 1;
-                    if (!mbar_wait(q_full(slot), (uint32_t)((it >> 1) & 1), abort_flag, 720)) { ok = false; break; }
+                    if (!mbar_wait(item_full(slot), (uint32_t)((it >> 1) & 1), abort_flag, 719)) { ok = false; break; }
                     const int nb = items[slot].nb;
                     if (items[slot].bh < 0) break;
+                    if (!mbar_wait(q_full(slot), (uint32_t)((it >> 1) & 1), abort_flag, 720)) { ok = false; break; }
                     const uint32_t q_lo = ((q_smem + slot * QTILE) & 0x3FFFF) >> 4;
                     auto issue_qk = [&](int j) {  // S[(g + j) & 1] = Q · K_jᵀ
                         const uint32_t b_lo = k_lo + (uint32_t)(((kv_i + j) % KVS) * (KVB >> 4));
@@ -307,7 +586,10 @@ attention_persist_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
                                       ks > 0 ? 1u : 0u);
                         tc_commit(s_full((g + j) & 1));
                         tc_commit(k_empty((kv_i + j) % KVS));
-                        if (j + 1 == nb) tc_commit(slot_free(slot));  // the tile's last read of its Q buffer
+                        if (j + 1 == nb) {
+                            tc_commit(slot_free(slot));  // the tile's last read of its Q buffer
+                            mbar_arrive(near_end);
+                        }
                     };
                     auto issue_pv = [&](int j) {  // O_a += P_j[:, 0:32] · V_j[0:32, :],  O_b += P_j[:, 32:64] · V_j[32:64, :]
                         const uint32_t b_lo = v_lo + (uint32_t)(((kv_i + j) % KVS) * (KVB >> 4));
@@ -367,9 +649,12 @@ attention_persist_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
         int g = 0;  // key blocks seen so far
         for (int it = 0; ok; ++it) {
             const int slot = it & 1;
-            if (!mbar_wait(q_full(slot), (uint32_t)((it >> 1) & 1), abort_flag, 730)) { ok = false; break; }
+            if (!mbar_wait(item_full(slot), (uint32_t)((it >> 1) & 1), abort_flag, 730)) { ok = false; break; }
             const int bh = items[slot].bh;
             if (bh < 0) break;
+#ifdef KB_ATTN_TRACE
+            if (threadIdx.x == 0) KB_TRACE(it, 1, trace_now());
+#endif
             const int mt = items[slot].mt, nb = items[slot].nb;
             uint32_t act[4];
 #pragma unroll
@@ -390,6 +675,10 @@ attention_persist_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
                 const uint32_t ph = (uint32_t)((gj >> 1) & 1);
                 const uint32_t s_addr = lane_addr + (uint32_t)(bf * kBlkN + hf * 32);
                 if (!mbar_wait(s_full(bf), ph, abort_flag, 731)) { ok = false; break; }
+#ifdef KB_ATTN_TRACE
+                if (threadIdx.x == 0 && j == 0) KB_TRACE(it, 2, trace_now());
+                if (threadIdx.x == 0 && it == 0 && j < 8) KB_TRACE(kTraceTiles - 1, j, trace_now());  // row 14: scores of block j of the first tile ready
+#endif
                 tc_fence_after();
                 uint32_t sr[32];
                 tmem_ld_32x32(s_addr, sr);
@@ -516,6 +805,9 @@ attention_persist_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
             }
             if (!ok) break;
             g += nb;
+#ifdef KB_ATTN_TRACE
+            if (threadIdx.x == 0) KB_TRACE(it, 3, trace_now());
+#endif
             // the key loop is over: this warp no longer reads the slot's mask row or item
             __syncwarp();
             if (lane == 0) mbar_arrive(slot_free(slot));
@@ -566,6 +858,9 @@ attention_persist_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
                             Elem<T>::from_f32(fmaf(__uint_as_float(oa[i]), wa, __uint_as_float(ob[i]) * wb));
                 }
             }
+#ifdef KB_ATTN_TRACE
+            if (threadIdx.x == 0) KB_TRACE(it, 4, trace_now());
+#endif
         }
       }
     }
@@ -576,6 +871,9 @@ attention_persist_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
         __syncwarp();
         tmem_dealloc(*tmem_slot, kTmemCols);
     }
+#ifdef KB_ATTN_TRACE
+    if (threadIdx.x == 0) KB_TRACE(kTraceTiles, 1, trace_now());
+#endif
     // every CTA reports in, also one that did no work; the last one leaves the queue slot clean
     if (threadIdx.x == 0) {
         __threadfence();
@@ -603,6 +901,8 @@ static bool attention_persist_applicable(const kb_attn_params& p, int mode) {
     if (g_attn_persistent == 1) return true;
     return tiles > 2 * (int64_t)sm_count();
 }
+
+static int g_attn_sort_batches = 1;  // test hook (kb_debug_attention_persistent: bit 1 of the mode switches it off)
 
 // The next queue slot on the current device. g_attn_queue is a host-side handle; its device address
 // is looked up once per device (with that device current) and kept.
@@ -693,8 +993,16 @@ static int launch_attention_persist_tm(const kb_attn_params& p, cudaStream_t str
     const int64_t grid = tiles < 2 * (int64_t)sm_count() ? tiles : 2 * (int64_t)sm_count();
     unsigned int* queue = attention_queue_slot();
     if (queue == nullptr) return KB_ERR_LAUNCH;
+    // Longest-first order of the batches: for padding masks (one row per batch, shared by heads and
+    // query rows) of a size that every CTA can scan during its set-up.
+    const int sort_batches = (MODE == 1 && g_attn_sort_batches && !p.is_causal && p.mask_strides[1] == 0 && p.mask_strides[0] != 0 &&
+                              p.B > 1 && p.B <= 32 && mask_cols >= 384 && mask_cols <= 2048 &&
+                              p.B * (int64_t)((mask_cols + 255) / 256) <= 48 &&  // what twelve warps scan in four loads each
+                              (p.mask_dtype == KB_F16 || p.mask_dtype == KB_BF16) && p.mask_strides[3] == 1 && p.N % 8 == 0 &&
+                              p.mask_strides[0] % 8 == 0 && (((uintptr_t)p.mask) & 15) == 0)
+                                 ? 1 : 0;
     if (launch_pdl(attention_persist_kernel<T, MODE>, (unsigned)grid, (unsigned)Cfg::kThreads, smem_bytes, stream, tq, tk, tv, d,
-                   (int)tiles, mask_cols, queue) != cudaSuccess)
+                   (int)tiles, mask_cols, queue, sort_batches) != cudaSuccess)
         return KB_ERR_LAUNCH;
     return cudaGetLastError() == cudaSuccess ? KB_OK : KB_ERR_LAUNCH;
 }

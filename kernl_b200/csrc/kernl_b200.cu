@@ -9,6 +9,7 @@
 #include "common.cuh"
 #include "norm.cuh"
 #include "linear.cuh"
+#include "linear_pair.cuh"
 #include "linear_smallm.cuh"
 #include "attention.cuh"
 #include "attention_split.cuh"
@@ -150,9 +151,22 @@ int kb_norm_fwd(const kb_norm_params* p, void* stream) {
 // Test and measurement hooks (include/kernl_b200_debug.h; not part of the stable ABI; process-wide).
 void kb_debug_force_bn(int bn) { g_forced_bn = bn; }
 void kb_debug_split_tiles(int v) { g_split_tiles = v; }
-void kb_debug_attention_persistent(int mode) { g_attn_persistent = mode; }
+void kb_debug_attention_persistent(int mode) {
+    g_attn_persistent = mode == 2 ? 1 : mode;
+    g_attn_sort_batches = mode == 2 ? 0 : 1;
+}
 void kb_debug_pdl(int on) { g_use_pdl = on ? 1 : 0; }
+void kb_debug_linear_pair(int on) { g_linear_pair = on ? 1 : 0; }
 void kb_debug_force_splits(int splits) { g_forced_splits = splits; }
+#ifdef KB_ATTN_TRACE
+// Tuning builds only: copies the persistent attention kernel's time stamps to the host.
+int kb_debug_attention_trace_read(void* host_buf, int64_t bytes) {
+    if (cudaDeviceSynchronize() != cudaSuccess) return KB_ERR_LAUNCH;
+    const size_t n = sizeof(unsigned long long) * 296 * (kTraceTiles + 1) * kTraceEvents;
+    if (bytes < (int64_t)n) return KB_ERR_BAD_ARG;
+    return cudaMemcpyFromSymbol(host_buf, g_attn_trace, n) == cudaSuccess ? KB_OK : KB_ERR_LAUNCH;
+}
+#endif
 int kb_debug_wait_limit(int64_t in_kernel_cycles, int64_t peer_cycles) {
     int st = check_device();
     if (st != KB_OK) return st;

@@ -173,6 +173,56 @@ __device__ __forceinline__ void epilogue_chunk(const float (&accv)[32], const T*
     }
 }
 
+// The arithmetic of epilogue_chunk without its stores: z = act(acc + bias) for one 32-column chunk.
+template <typename T>
+__device__ __forceinline__ void epilogue_values(const float (&accv)[32], const T* __restrict__ bias, int col0, int N,
+                                                int activation, float (&z)[32]) {
+    if (bias != nullptr) {
+        if (col0 + 32 <= N && (((uintptr_t)(bias + col0)) & 15) == 0) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+                const uint4 bw = __ldg(reinterpret_cast<const uint4*>(bias + col0) + v);
+                const uint32_t w[4] = {bw.x, bw.y, bw.z, bw.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float2 bf = Elem<T>::unpack2(w[i]);
+                    z[v * 8 + 2 * i] = accv[v * 8 + 2 * i] + bf.x;
+                    z[v * 8 + 2 * i + 1] = accv[v * 8 + 2 * i + 1] + bf.y;
+                }
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) z[j] = accv[j] + ((col0 + j < N) ? Elem<T>::to_f32(bias[col0 + j]) : 0.f);
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) z[j] = accv[j];
+    }
+    switch (activation) {
+        case KB_ACT_TANH:
+#pragma unroll
+            for (int j = 0; j < 32; ++j) z[j] = act_tanh(z[j]);
+            break;
+        case KB_ACT_GELU:
+#pragma unroll
+            for (int j = 0; j < 32; ++j) z[j] = act_gelu(z[j]);
+            break;
+        case KB_ACT_FAST_GELU:
+#pragma unroll
+            for (int j = 0; j < 32; ++j) z[j] = act_fast_gelu(z[j]);
+            break;
+        case KB_ACT_RELU:
+#pragma unroll
+            for (int j = 0; j < 32; ++j) z[j] = fmaxf(z[j], 0.0f);
+            break;
+        case KB_ACT_SILU:
+#pragma unroll
+            for (int j = 0; j < 32; ++j) z[j] = act_silu(z[j]);
+            break;
+        default: break;
+    }
+}
+
 // Gated epilogue (KB_ACT_SWIGLU) of one 32-column chunk: the rows of W are interleaved in blocks of
 // eight — block 2j holds gate rows 8j..8j+7, block 2j+1 the matching up rows — so a chunk carries
 // two gate/up block pairs and yields 16 output columns y[col0/2 + i] = silu(gate_i) * up_i, computed
@@ -586,8 +636,14 @@ static int launch_linear_bn(const kb_linear_params& p, cudaStream_t stream, cons
     return KB_OK;
 }
 
+// Large problems go to CTA pairs on 256 x 256 tiles (linear_pair.cuh).
+static bool linear_pair_applicable(const kb_linear_params& p);
+template <typename T>
+static int launch_linear_pair_t(const kb_linear_params& p, cudaStream_t stream);
+
 template <typename T>
 static int launch_linear_t(const kb_linear_params& p, cudaStream_t stream, int forced_bn, int forced_splits) {
+    if (forced_bn == 0 && forced_splits == 0 && linear_pair_applicable(p)) return launch_linear_pair_t<T>(p, stream);
     const bool has_ws = p.workspace != nullptr && p.workspace_bytes >= splitk_workspace_bytes(p.M, p.N) &&
                         (((uintptr_t)p.workspace) & 15) == 0 && (splitk_allowed(p.M, p.N) || forced_splits > 1);
     const LinearPlan plan = plan_linear(p.M, p.N, p.K, has_ws, forced_bn, forced_splits);

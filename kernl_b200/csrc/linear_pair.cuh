@@ -1,0 +1,380 @@
+// Fused linear layer y = act(x · Wᵀ + bias) for sm_100a, large problems: CTA PAIRS on 256 x 256 tiles.
+//
+// linear.cuh gives every SM its own 128 x 256 tile: per 64-wide k-block an SM pulls 16 KB of x and
+// 32 KB of W through shared memory for 512 tensor-core cycles, and neighbouring SMs load the same W
+// tile again from L2 (ncu on [8192,4096]x[11008,4096]: 2.7x the algorithmic DRAM bytes, tensor pipe
+// 79 % busy). Here two CTAs of a cluster (two neighbouring SMs) share one 256 x 256 output tile and
+// issue `tcgen05.mma.cta_group::2`: each CTA stages its own 128 rows of x and only HALF of the W tile
+// (128 of its 256 rows), the tensor cores of both SMs read both halves, and each CTA ends up with its
+// 128 rows of the result in its own tensor memory. Per SM and k-block that is 32 KB through shared
+// memory instead of 48 KB, and every W byte is fetched once per pair instead of once per SM.
+//
+// Roles per CTA (320 threads, as in linear.cuh): warp 0 TMA producer, warp 1 tcgen05 issuer (only the
+// pair's leader — cluster rank 0 — issues; the other CTA's warp 1 only allocates tensor memory),
+// warps 2..9 epilogue. Barriers:
+//   full[s]    in the LEADER's shared memory: the leader's producer arrives with the byte count of all
+//              four copies of a stage; both CTAs' TMA copies complete on it (the second CTA addresses
+//              it through the cluster's shared window);
+//   empty[s]   in each CTA: `tcgen05.commit` of the leader, multicast to both CTAs;
+//   tfull[a]   in each CTA: accumulator a complete (multicast commit);
+//   tempty[a]  in the leader: all sixteen epilogue warps of the pair have read accumulator a.
+// Accumulators are double-buffered (2 x 256 columns = all of tensor memory), the ring has six stages.
+// Every bulk copy has one destination CTA: the pair's sharing happens inside the tensor-core instruction.
+#pragma once
+#include "linear.cuh"
+
+namespace kb {
+
+constexpr int kPairBN = 256;          // columns of the pair's tile
+constexpr int kPairHalfN = 128;       // W rows staged by each CTA
+constexpr int kPairStages = 6;
+constexpr int kPairABytes = kGemmBM * kGemmBK * 2;     // 16 KB: this CTA's 128 rows of x
+constexpr int kPairBBytes = kPairHalfN * kGemmBK * 2;  // 16 KB: this CTA's half of the W tile
+constexpr int kPairStageBytes = kPairABytes + kPairBBytes;
+// Output staging of the epilogue: per epilogue warp 32 rows x 64 columns (128 bytes per row, eight
+// 16-byte pieces; piece c of row r sits at r * 128 + ((c ^ (r & 7)) * 16), which keeps both the
+// row-wise writes and the piece-wise reads free of bank conflicts).
+constexpr int kPairOutWarpBytes = 32 * 128;
+constexpr int kPairOutBytes = kGemmEpilogueWarps * kPairOutWarpBytes;
+constexpr int kPairSmemBytes = kPairStages * kPairStageBytes + 256 + kPairOutBytes + 1024;
+constexpr uint32_t kPairTmemCols = 512;
+// The address, in the cluster's shared window, of the leader's (rank 0) copy of one of this CTA's own
+// shared-memory locations: both CTAs lay out their shared memory identically.
+__device__ __forceinline__ uint32_t in_leader(uint32_t own_smem_addr) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(own_smem_addr), "r"(0u));
+    return r;
+}
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA tile load whose completion is counted on a barrier that may live in the pair's other CTA.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(x), "r"(y)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t smem_dst, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// D[tmem of both CTAs] (+)= A[smem of both CTAs] * B[smem of both CTAs]: M = 256 (128 rows per CTA)
+__device__ __forceinline__ void tc_mma_ss_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+        "}\n" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Arrive (once all MMAs issued so far have completed) on the barrier at this offset in BOTH CTAs.
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+                 "h"((uint16_t)3)
+                 : "memory");
+}
+
+template <typename T>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+linear_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
+                   const T* __restrict__ bias, T* __restrict__ y, T* __restrict__ act_inputs, int M, int N, int K,
+                   int64_t y_row_stride, int activation) {
+    constexpr int STAGES = kPairStages;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * kPairStageBytes);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    uint8_t* out_stage = smem + STAGES * kPairStageBytes + 256;
+
+    const uint32_t smem_base = smem_u32(smem);
+    const uint32_t bar_base = smem_u32(bars);
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+    auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
+    auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();  // 0 = the pair's leader
+    const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+
+    // A wait that expired earlier leaves the status word set: such a launch does no work. Both CTAs
+    // of a pair must take the same decision (they allocate tensor memory together), so the leader's
+    // reading counts for both: it is exchanged through the cluster barrier below.
+    __shared__ int s_skip;
+    if (threadIdx.x == 0) {
+        s_skip = *reinterpret_cast<volatile int*>(&g_device_status[0]);
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(tfull_bar(a), 1);
+            mbar_init(tempty_bar(a), 2 * kGemmEpilogueWarps);  // the epilogue warps of both CTAs
+        }
+        *abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == 0 && lane == 0) {
+        tma_prefetch_desc(&tmap_x);
+        tma_prefetch_desc(&tmap_w);
+    }
+    __syncthreads();
+    cluster_sync_all();  // both CTAs' barriers exist before anybody signals across the pair
+    // the leader's decision, read from its shared memory through the cluster window
+    int skip;
+    {
+        const uint32_t leader_skip = in_leader(smem_u32(&s_skip));
+        asm volatile("ld.shared::cluster.s32 %0, [%1];" : "=r"(skip) : "r"(leader_skip) : "memory");
+    }
+    if (skip == 0) {
+        if (warp == 1) {
+            tmem_alloc_pair(smem_u32(tmem_slot), kPairTmemCols);
+            tmem_relinquish_pair();
+        }
+        tc_fence_before();
+        __syncthreads();
+        tc_fence_after();
+    }
+    const uint32_t tmem_base = (skip == 0) ? *tmem_slot : 0u;
+
+    const int num_m = (M + 2 * kGemmBM - 1) / (2 * kGemmBM);  // 256-row tiles
+    const int num_n = (N + kPairBN - 1) / kPairBN;
+    const int num_tiles = num_m * num_n;
+    const int num_k = (K + kGemmBK - 1) / kGemmBK;
+
+    if (skip == 0 && warp == 0) {
+        // ------------------------------------------------------------------ TMA producer (both CTAs)
+        if (elect_one()) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int t = pair; t < num_tiles && ok; t += num_pairs) {
+                int m_idx, n_idx;
+                tile_coords(t, num_m, num_n, m_idx, n_idx);
+                const int row0 = m_idx * 2 * kGemmBM + (int)rank * kGemmBM;    // this CTA's rows of x
+                const int wrow0 = n_idx * kPairBN + (int)rank * kPairHalfN;    // this CTA's rows of W
+                for (int kb = 0; kb < num_k; ++kb) {
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1, abort_flag, 110)) { ok = false; break; }
+                    // the leader's barrier counts the bytes of both CTAs' copies of this stage
+                    if (rank == 0) mbar_arrive_expect_tx(full_bar(stage), 2 * kPairStageBytes);
+                    const uint32_t a_dst = smem_base + stage * kPairStageBytes;
+                    const uint32_t leader_full = in_leader(full_bar(stage));
+                    tma_load_2d_pair(a_dst, &tmap_x, leader_full, kb * kGemmBK, row0);
+                    tma_load_2d_pair(a_dst + kPairABytes, &tmap_w, leader_full, kb * kGemmBK, wrow0);
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+            if (!ok) {
+                for (int i = 0; i < 64; ++i) __nanosleep(2000);  // let copies in flight land
+            }
+        }
+    } else if (skip == 0 && warp == 1) {
+        // ------------------------------------------------------------------ tcgen05 issuer (leader only)
+        if (rank == 0 && elect_one()) {
+            constexpr uint32_t idesc = make_idesc_f16(Elem<T>::kIsBf16, 2 * kGemmBM, kPairBN, 0, 0);
+            int stage = 0;
+            uint32_t phase = 0;
+            int acc = 0;
+            uint32_t acc_phase = 0;
+            bool ok = true;
+            for (int t = pair; t < num_tiles && ok; t += num_pairs) {
+                if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1, abort_flag, 210)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * kPairBN);
+                for (int kb = 0; kb < num_k; ++kb) {
+                    if (!mbar_wait(full_bar(stage), phase, abort_flag, 211)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_base + stage * kPairStageBytes;
+                    const uint64_t a_desc = make_smem_desc_sw128(a_addr, 16, 1024);
+                    const uint64_t b_desc = make_smem_desc_sw128(a_addr + kPairABytes, 16, 1024);
+#pragma unroll
+                    for (int k = 0; k < kGemmBK / 16; ++k)
+                        tc_mma_ss_pair(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    tc_commit_pair(empty_bar(stage));  // frees this stage in both CTAs
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+                if (!ok) break;
+                tc_commit_pair(tfull_bar(acc));  // both CTAs' epilogues may read accumulator `acc`
+                acc ^= 1;
+                if (acc == 0) acc_phase ^= 1;
+            }
+        }
+    } else if (skip == 0) {
+        // ------------------------------------------------------------------ epilogue (both CTAs)
+        const int q = warp & 3;                // TMEM lane quadrant this warp may access
+        const int col_half = (warp - 2) >> 2;  // which half of the tile's columns this warp handles
+        const int c_begin = col_half * (kPairBN / 2), c_end = c_begin + kPairBN / 2;
+        const uint32_t leader_tempty[2] = {in_leader(tempty_bar(0)), in_leader(tempty_bar(1))};
+        // whole 16-byte pieces of y: plain activations, no pre-activation output, aligned rows
+        const bool staged = activation != KB_ACT_SWIGLU && act_inputs == nullptr && (N & 7) == 0 && (y_row_stride & 7) == 0 &&
+                            (((uintptr_t)y) & 15) == 0;
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        bool ok = true;
+        for (int t = pair; t < num_tiles && ok; t += num_pairs) {
+            int m_idx, n_idx;
+            tile_coords(t, num_m, num_n, m_idx, n_idx);
+            if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, 310)) { ok = false; break; }
+            tc_fence_after();
+            const int row = m_idx * 2 * kGemmBM + (int)rank * kGemmBM + q * 32 + lane;
+            const int n0 = n_idx * kPairBN;
+            T* y_row = y + (int64_t)row * y_row_stride;
+            T* a_row = act_inputs ? act_inputs + (int64_t)row * y_row_stride : nullptr;
+            if (staged) {
+                // Results go through shared memory so that the warp writes whole 128-byte row
+                // segments (four rows per store instruction) instead of 32 rows x 16 bytes: a
+                // thread-per-row store touches 32 cache lines per instruction.
+                uint8_t* mine = out_stage + (warp - 2) * kPairOutWarpBytes;
+                const int row_base = m_idx * 2 * kGemmBM + (int)rank * kGemmBM + q * 32;
+#pragma unroll 1
+                for (int c0 = c_begin; c0 < c_end; c0 += 64) {
+                    if (n0 + c0 >= N) break;
+                    // both 32-column halves are requested before the wait: one tensor-memory round trip per 64 columns
+                    uint32_t r2[2][32];
+                    tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * kPairBN + c0), r2[0]);
+                    tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * kPairBN + c0 + 32), r2[1]);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int hc = 0; hc < 2; ++hc) {
+                        float accv[32], z[32];
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) accv[j] = __uint_as_float(r2[hc][j]);
+                        epilogue_values<T>(accv, bias, n0 + c0 + hc * 32, N, activation, z);
+#pragma unroll
+                        for (int v = 0; v < 4; ++v) {
+                            uint4 o;
+                            o.x = Elem<T>::pack2(z[v * 8 + 0], z[v * 8 + 1]);
+                            o.y = Elem<T>::pack2(z[v * 8 + 2], z[v * 8 + 3]);
+                            o.z = Elem<T>::pack2(z[v * 8 + 4], z[v * 8 + 5]);
+                            o.w = Elem<T>::pack2(z[v * 8 + 6], z[v * 8 + 7]);
+                            const int pc = hc * 4 + v;
+                            *reinterpret_cast<uint4*>(mine + lane * 128 + ((pc ^ (lane & 7)) * 16)) = o;
+                        }
+                    }
+                    __syncwarp();
+#pragma unroll
+                    for (int it = 0; it < 8; ++it) {
+                        const int rr = it * 4 + (lane >> 3), pc = lane & 7;
+                        const uint4 o = *reinterpret_cast<const uint4*>(mine + rr * 128 + ((pc ^ (rr & 7)) * 16));
+                        const int grow = row_base + rr, gcol = n0 + c0 + pc * 8;
+                        if (grow < M && gcol < N) *reinterpret_cast<uint4*>(y + (int64_t)grow * y_row_stride + gcol) = o;
+                    }
+                    __syncwarp();
+                }
+            } else {
+#pragma unroll 1
+            for (int c0 = c_begin; c0 < c_end; c0 += 32) {
+                if (n0 + c0 >= N) break;
+                uint32_t r[32];
+                tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * kPairBN + c0), r);
+                tmem_ld_wait();
+                float accv[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) accv[j] = __uint_as_float(r[j]);
+                if (activation == KB_ACT_SWIGLU) epilogue_chunk_swiglu<T>(accv, bias, y_row, n0 + c0, N, row < M);
+                else epilogue_chunk<T>(accv, bias, y_row, a_row, n0 + c0, N, row < M, activation);
+            }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(leader_tempty[acc]);  // counted in the leader, whose issuer reuses the accumulator
+            acc ^= 1;
+            if (acc == 0) acc_phase ^= 1;
+        }
+    }
+
+    // Teardown: every role of both CTAs falls through to here, also after an abandoned wait. Neither
+    // CTA may retire while the other can still signal its barriers or use its tensor memory.
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();
+    if (skip == 0 && warp == 1) {
+        __syncwarp();
+        tmem_dealloc_pair(tmem_base, kPairTmemCols);
+    }
+}
+
+static int g_linear_pair = 1;  // test hook (kb_debug_linear_pair): 0 = never use the pair kernel
+
+// The pair kernel serves problems with at least one 256 x 256 tile per pair of SMs and no split-K.
+static bool linear_pair_applicable(const kb_linear_params& p) {
+    if (g_linear_pair == 0) return false;
+    const int64_t tiles = ((p.M + 255) / 256) * ((p.N + kPairBN - 1) / kPairBN);
+    return p.M >= 512 && p.N >= 256 && p.K >= 256 && tiles >= sm_count() / 2;
+}
+
+template <typename T>
+static int launch_linear_pair_t(const kb_linear_params& p, cudaStream_t stream) {
+    CUtensorMap tmap_x, tmap_w;
+    {
+        const uint64_t dims[2] = {(uint64_t)p.K, (uint64_t)p.M};
+        const uint64_t strides[2] = {0, (uint64_t)p.x_row_stride * 2};
+        const uint32_t box[2] = {kGemmBK, kGemmBM};
+        int st = encode_tmap_16bit(&tmap_x, p.x, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B,
+                                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B);
+        if (st != KB_OK) return st;
+    }
+    {
+        const uint64_t dims[2] = {(uint64_t)p.K, (uint64_t)p.N};
+        const uint64_t strides[2] = {0, (uint64_t)p.K * 2};
+        const uint32_t box[2] = {kGemmBK, kPairHalfN};
+        int st = encode_tmap_16bit(&tmap_w, p.w, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B,
+                                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
+        if (st != KB_OK) return st;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.blockDim = dim3(kGemmThreads);
+    cfg.dynamicSmemBytes = kPairSmemBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    // pairs that can be resident at once, per device (the grid is persistent: one pair per slot)
+    static int max_pairs[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return KB_ERR_LAUNCH;
+    if (max_pairs[dev] == 0) {
+        if (cudaFuncSetAttribute(linear_pair_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBytes) != cudaSuccess)
+            return KB_ERR_LAUNCH;
+        cfg.gridDim = dim3(2 * (unsigned)(sm_count() / 2));
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, linear_pair_kernel<T>, &cfg) != cudaSuccess || n <= 0) {
+            cudaGetLastError();
+            return KB_ERR_LAUNCH;
+        }
+        max_pairs[dev] = n < sm_count() / 2 ? n : sm_count() / 2;
+    }
+    const int64_t tiles = ((p.M + 255) / 256) * ((p.N + kPairBN - 1) / kPairBN);
+    const int pairs = (int)(tiles < max_pairs[dev] ? tiles : max_pairs[dev]);
+    cfg.gridDim = dim3(2 * (unsigned)pairs);
+    if (cudaLaunchKernelEx(&cfg, linear_pair_kernel<T>, tmap_x, tmap_w, (const T*)p.bias, (T*)p.y, (T*)p.act_inputs, (int)p.M,
+                           (int)p.N, (int)p.K, p.y_row_stride, p.activation) != cudaSuccess)
+        return KB_ERR_LAUNCH;
+    return cudaGetLastError() == cudaSuccess ? KB_OK : KB_ERR_LAUNCH;
+}
+
+}  // namespace kb

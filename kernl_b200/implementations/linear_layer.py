@@ -22,7 +22,8 @@ def _workspace(device: torch.device) -> torch.Tensor:
     key = (index, torch.cuda.current_stream(device).cuda_stream)
     ws = _workspaces.get(key)
     if ws is None:
-        ws = torch.zeros(_WORKSPACE_BYTES // 4, dtype=torch.float32, device=device)
+        with torch.inference_mode(False):  # an ordinary tensor: it is zeroed in place again after an expired wait
+            ws = torch.zeros(_WORKSPACE_BYTES // 4, dtype=torch.float32, device=device)
         _workspaces[key] = ws
     return ws
 

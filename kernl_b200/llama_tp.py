@@ -161,6 +161,9 @@ class LlamaTP:
         self.kcache = None
         self.vcache = None
         self.sm_scale = D ** -0.5
+        self.overlap_prefill = True  # two half-batches on two streams when tensor parallel (see prefill)
+        self._streams = None
+        self._prefill_out = {}
 
     # ------------------------------------------------------------------ cache / state
     def alloc_cache(self, batch: int):
@@ -200,17 +203,39 @@ class LlamaTP:
         assert S <= cfg.max_seq, f"prompt of {S} tokens does not fit the cache (max_seq {cfg.max_seq})"
         if self.kcache is None or self.kcache.shape[1] != B:
             self.alloc_cache(B)
-        x = self.embed.index_select(0, ids.reshape(-1)).reshape(B * S, cfg.hidden)
-        h = self.ops.rms_norm(x, self.layers[0]["norm1"], cfg.eps)
-        for li, layer in enumerate(self.layers):
-            qkv = self.ops.linear(h, layer["wqkv"])
-            # rotate q and k, write k and v into the cache at positions 0..S-1: one kernel
-            q = self.ops.rope_kv_write(qkv, self.kcache[li], self.vcache[li], self.cos, self.sin, 0, B, S)
-            attn = self.ops.attention_prefill(q.transpose(1, 2), self.kcache[li, :, :, :S], self.vcache[li, :, :, :S],
-                                              self.sm_scale)  # [B, hl, S, D]
-            attn2d = attn.transpose(1, 2).reshape(B * S, hl * D)
-            x, h = self._row_parallel(attn2d, layer["wo"], x, layer["norm2"])
-            x, h = self._mlp(layer, h, x, self._next_norm(li))
+        # Tensor parallel on GPUs: the batch is cut into two halves that run on two streams, so that
+        # the all-reduce of one half (64 of them per prefill, 67 MB each at the 7B shape) travels
+        # while the other half computes. Every rank enqueues the same sequence of collectives.
+        # (only for messages far above what the one-shot peer-memory kernel takes: its single buffer
+        # cannot serve two streams at once, and small messages gain nothing from the overlap)
+        halves = 2 if (self.world > 1 and self.device.type == "cuda" and B % 2 == 0 and not return_hidden
+                       and self.overlap_prefill and (B // 2) * S * cfg.hidden * 2 >= (8 << 20)) else 1
+        if halves == 1:
+            gen = self._prefill_rows(ids, 0, return_hidden)
+            for _ in gen:
+                pass
+            h = self._prefill_out[0]
+        else:
+            main = torch.cuda.current_stream(self.device)
+            if self._streams is None:
+                self._streams = [torch.cuda.Stream(self.device) for _ in range(halves)]
+            nb = B // halves
+            gens = [self._prefill_rows(ids[i * nb:(i + 1) * nb], i * nb, False) for i in range(halves)]
+            for st in self._streams:
+                st.wait_stream(main)
+            live = list(range(halves))
+            while live:
+                for i in list(live):
+                    with torch.cuda.stream(self._streams[i]):
+                        try:
+                            next(gens[i])
+                        except StopIteration:
+                            live.remove(i)
+            for i, st in enumerate(self._streams):
+                main.wait_stream(st)
+                self._prefill_out[i * nb].record_stream(main)
+            h = torch.cat([self._prefill_out[i * nb] for i in range(halves)], dim=0)
+        self._prefill_out = {}
         self.len_mask.fill_(float("-inf"))
         self.len_mask[..., :S] = 0
         self.pos.fill_(S)
@@ -218,8 +243,33 @@ class LlamaTP:
         self._host_pos = S
         if return_hidden:
             return h.reshape(B, S, cfg.hidden)
-        last = h.reshape(B, S, cfg.hidden)[:, -1].contiguous()  # already through the final norm
-        return self.ops.linear(last, self.lm_head)
+        return self.ops.linear(h, self.lm_head)  # h: final-norm hidden state of the last position of every sequence
+
+    def _prefill_rows(self, ids: torch.Tensor, b0: int, return_hidden: bool):
+        """The layer loop of the prefill for the sequences [b0, b0 + len(ids)) of the batch, written as
+        a generator that yields after every collective, so that two parts of a batch can take turns.
+        Leaves the final-norm hidden states (all positions, or the last one per sequence) in
+        `self._prefill_out[b0]`."""
+        cfg, hl, D = self.cfg, self.heads_local, self.cfg.head_dim
+        B, S = ids.shape
+        rows = slice(b0, b0 + B)
+        x = self.embed.index_select(0, ids.reshape(-1)).reshape(B * S, cfg.hidden)
+        h = self.ops.rms_norm(x, self.layers[0]["norm1"], cfg.eps)
+        for li, layer in enumerate(self.layers):
+            qkv = self.ops.linear(h, layer["wqkv"])
+            # rotate q and k, write k and v into the cache at positions 0..S-1: one kernel
+            q = self.ops.rope_kv_write(qkv, self.kcache[li, rows], self.vcache[li, rows], self.cos, self.sin, 0, B, S)
+            attn = self.ops.attention_prefill(q.transpose(1, 2), self.kcache[li, rows, :, :S], self.vcache[li, rows, :, :S],
+                                              self.sm_scale)  # [B, hl, S, D]
+            attn2d = attn.transpose(1, 2).reshape(B * S, hl * D)
+            x, h = self._row_parallel(attn2d, layer["wo"], x, layer["norm2"])
+            yield
+            x, h = self._mlp(layer, h, x, self._next_norm(li))
+            yield
+        if return_hidden:
+            self._prefill_out[b0] = h
+        else:
+            self._prefill_out[b0] = h.reshape(B, S, cfg.hidden)[:, -1].contiguous()  # already through the final norm
 
     def decode_step(self, tokens: torch.Tensor) -> torch.Tensor:
         """tokens [B] → logits [B, vocab]; appends one position to the cache. Every shape is static

@@ -11,7 +11,10 @@ from kernl_b200.optimizer.dynamo_backend import dynamo_backend_ofi
 # this backend, e.g. the encoder and the decoder of one model (reference: model_optimization.py:25-29).
 def _compiler(gm: torch.fx.GraphModule, example_inputs: List[torch.Tensor]):
     dynamo_backend_ofi(gm)
-    return cuda_graphs_wrapper(gm, example_inputs)
+    # Capture is put off to the second call: a model is cut into several graphs, and a graph
+    # captured while the first forward is still under way could hold the address of a parameter that
+    # a later graph of that forward converts to fp16 in place (tied embedding / output weights).
+    return cuda_graphs_wrapper(gm, example_inputs, defer_capture=True)
 
 
 def optimize_model(model) -> None:

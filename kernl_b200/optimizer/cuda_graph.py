@@ -90,6 +90,12 @@ def _capture(model: Callable, static_inputs: list) -> Callable:
         graph.replay()
         return static_outputs
 
+    # The captured graph holds device ADDRESSES, not references: everything it reads must outlive
+    # it. The rewritten GraphModule owns tensors that exist nowhere else (stacked / transposed /
+    # interleaved weights built by the rewrites), and nothing else may be holding it once the
+    # backend has returned — without this reference a garbage collection frees those weights and
+    # later replays read whatever was allocated in their place.
+    replay.keep_alive = (model, static_inputs)
     return replay
 
 
@@ -108,13 +114,15 @@ def _check_static(args, static, addresses) -> None:
             f"input {i} was declared static (captured by address) but arrived at another address")
 
 
-def cuda_graphs_wrapper(model: Callable, inputs: Union[list, tuple], static_input_idxs: Optional[Iterable[int]] = None) -> Callable:
+def cuda_graphs_wrapper(model: Callable, inputs: Union[list, tuple], static_input_idxs: Optional[Iterable[int]] = None,
+                        defer_capture: Optional[bool] = None) -> Callable:
     """Run `model` through a CUDA graph (reference: cuda_graph.py:103-138).
 
     With real example inputs the graph is captured now (after one extra eager call, because
-    kernels may mutate their inputs during warm-up); with FakeTensor inputs (how TorchDynamo calls
-    a backend) the first real call runs eagerly and the second one captures, with the RNG state
-    preserved around warm-up and capture.
+    kernels may mutate their inputs during warm-up). With FakeTensor inputs, or when the caller
+    asks for it (`defer_capture=True`: `optimize_model` does, whatever kind of example inputs
+    TorchDynamo hands over), the first real call runs eagerly and the second one captures, with the
+    RNG state preserved around warm-up and capture.
 
     The reference copies every input into the arena on every call (cuda_graph.py:115-119), which
     for a decoder means copying its whole KV cache per generated token. Here the inputs listed in
@@ -124,7 +132,10 @@ def cuda_graphs_wrapper(model: Callable, inputs: Union[list, tuple], static_inpu
     an AssertionError (the graph would silently read the old one).
     """
     assert isinstance(inputs, (list, tuple))
-    if not any(isinstance(inp, FakeTensor) for inp in inputs):
+    if defer_capture is None:
+        defer_capture = any(isinstance(inp, FakeTensor) for inp in inputs)
+    assert defer_capture or not any(isinstance(inp, FakeTensor) for inp in inputs), "FakeTensor inputs cannot be captured now"
+    if not defer_capture:
         static = _static_idxs(inputs, static_input_idxs)
         addresses = {i: inputs[i].data_ptr() for i in static}
         static_inputs = prepare_inputs(inputs=list(inputs), pools=static_inputs_pool, static_input_idxs=static)

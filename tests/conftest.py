@@ -29,3 +29,4 @@ def _device_status_clean(request):
         from kernl_b200 import _lib
 
         _lib.device_status()
+

@@ -92,3 +92,40 @@ def test_small_model_through_optimize_model(lib, name, mode):
     finally:
         cuda_graph.static_inputs_pool.clear()
         torch._dynamo.reset()
+
+
+def test_weights_built_by_the_rewrites_outlive_the_backend_call(lib):
+    """The rewrites build weights that exist nowhere else (stacked q/k/v, transposed Conv1D, gate/up
+    interleaved) and the captured graphs know them by address only. They must survive garbage
+    collection and the reuse of freed memory: collect, fill the allocator's free blocks with junk,
+    replay, compare."""
+    import gc
+
+    import torch._dynamo
+
+    from kernl_b200.model_optimization import optimize_model
+    from kernl_b200.optimizer import cuda_graph
+    from oracle import kernl_oracle as O
+
+    torch._dynamo.reset()
+    torch.manual_seed(0)
+    build, inputs = _models()["t5"]
+    model = build().eval()
+    with torch.inference_mode():
+        expected = _main_output(model(**inputs)).float()
+    gpu_inputs = {k: v.cuda() for k, v in inputs.items()}
+    gpu_model = model.half().cuda()
+    try:
+        optimize_model(gpu_model)
+        with torch.inference_mode():
+            for _ in range(2):  # eager pass, then capture
+                _main_output(gpu_model(**gpu_inputs))
+            for _ in range(3):
+                gc.collect()
+                junk = [torch.full((n,), 123.0, dtype=torch.float16, device="cuda") for n in (1 << 14, 1 << 16, 1 << 18, 1 << 20, 1 << 22)] * 4
+                del junk
+                out = _main_output(gpu_model(**gpu_inputs))
+                O.assert_parity(out, expected, max_abs=1e-2, cos=0.9995, what="T5 after garbage collection")
+    finally:
+        cuda_graph.static_inputs_pool.clear()
+        torch._dynamo.reset()

@@ -542,6 +542,46 @@ def test_linear_every_tile_width(lib):
         lib.kb_debug_force_bn(0)
 
 
+@pytest.mark.parametrize("dtype,tol", [(torch.float16, 1e-2), (torch.bfloat16, 6e-2)], ids=["fp16", "bf16"])
+@pytest.mark.parametrize("activation", ["", "gelu", "swiglu"])
+@pytest.mark.parametrize("shape", [(2048, 512, 2560), (2000, 264, 2512), (513, 1024, 9488), (4096, 256, 1280)], ids=str)
+def test_linear_cta_pairs(lib, shape, activation, dtype, tol):
+    """Problems large enough for the CTA-pair kernel (256 x 256 tiles, `tcgen05.mma.cta_group::2`), with
+    ragged edges in every dimension, against the oracle and against the one-CTA-per-tile kernel."""
+    from kernl_b200.implementations.linear_layer import linear_layer
+
+    M, K, N = shape
+    g = torch.Generator().manual_seed(M + N)
+    x = torch.randn((M, K), generator=g).to(dtype)
+    w = (torch.randn((N, K), generator=g) * 0.05).to(dtype)
+    b = (torch.randn((N,), generator=g) * 0.1).to(dtype)
+    xc, wc, bc = _cuda(x, w, b)
+    pre = torch.empty((M, N), dtype=dtype, device="cuda") if activation == "gelu" else None
+    out = linear_layer(xc, wc, bc, activation, act_inputs=pre)
+    try:
+        lib.kb_debug_linear_pair(0)
+        single = linear_layer(xc, wc, bc, activation)
+    finally:
+        lib.kb_debug_linear_pair(1)
+    if activation == "swiglu":
+        z = O.linear(x, w, b, "").reshape(M, N // 16, 2, 8)
+        expected = (torch.nn.functional.silu(z[:, :, 0]) * z[:, :, 1]).reshape(M, N // 2)
+    else:
+        expected = O.linear(x, w, b, activation)
+    if dtype == torch.bfloat16:  # 8 mantissa bits: one ulp of the largest result
+        tol = max(tol, float(expected.abs().max()) * 2.0 ** -7)
+    O.assert_parity(out, expected, max_abs=tol, what="pair kernel vs oracle")
+    # the two kernels add the same products in the same k order: they may differ by a rounding of the
+    # 16-bit result here and there, not more (compared in double precision: the fp32 cosine of
+    # several million values is itself only good to ~1e-4)
+    diff = out.double().cpu() - single.double().cpu()
+    rel_rms = float(diff.norm() / single.double().cpu().norm())
+    print(f"pair vs one CTA per tile: relative rms difference {rel_rms:.3e}, max abs {float(diff.abs().max()):.3e}")
+    assert rel_rms < (5e-4 if dtype == torch.float16 else 4e-3), rel_rms
+    if pre is not None:
+        O.assert_parity(pre, O.linear(x, w, b, ""), max_abs=tol, what="pre-activation output")
+
+
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16], ids=["fp16", "bf16"])
 @pytest.mark.parametrize("shape", [(1, 4096, 4096), (5, 520, 1000), (8, 11008, 4096), (9, 264, 17), (16, 8, 40), (13, 4096, 12288)], ids=str)
 def test_linear_few_rows(lib, shape, dtype):

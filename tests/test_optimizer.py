@@ -679,7 +679,7 @@ def test_bert_base_end_to_end(lib):
     half_ulp = float(torch.finfo(torch.float16).eps * 2.0 ** torch.floor(torch.log2(expected.abs().max())) / 2)
     print(f"half an fp16 ulp at the largest output ({float(expected.abs().max()):.2f}): {half_ulp:.2e}; mean abs error {float(err.mean()):.2e}")
     O.assert_parity(out.last_hidden_state, expected, max_abs=1e-2 + half_ulp, cos=0.9995, what="BERT-base last_hidden_state")
-    assert float(err.mean()) < 1e-3 and float((err > 1e-2).float().mean()) < 1e-4, "errors beyond 1e-2 must be isolated values"
+    assert float(err.mean()) < 2e-3 and float((err > 1e-2).float().mean()) < 1e-4, "errors beyond 1e-2 must be isolated values"
     torch._dynamo.reset()
 
 

@@ -427,6 +427,19 @@ attention_persist_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
             }
             *setup_issued = issued;
         }
+        if (warp == 10 && lane == 0) {
+            // the first tile is complete as far as the scheduler is concerned: publish it here, so
+            // that nobody waits for the scheduler warp to get going after the barrier
+            const bool any_live = live0 != 0u;
+            AttnItem* item = &items[0];
+            item->bh = b0 * p.H + rem0 % p.H;
+            item->mt = p.num_pairs - 1 - rem0 / p.H;
+            item->act[0] = any_live ? live0 : 0xffffffffu;
+            item->act[1] = item->act[2] = item->act[3] = any_live ? 0u : 0xffffffffu;
+            item->nblk = num_n_blocks;
+            item->nb = any_live ? __popc(live0) : num_n_blocks;
+            mbar_arrive(item_full(0));
+        }
     }
     if (!(MODE == 1 && sort_batches) && warp == 8 && lane == 0) *setup_issued = first_kv;
 #ifdef KB_ATTN_TRACE
@@ -450,7 +463,7 @@ attention_persist_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
 #ifdef KB_ATTN_TRACE
             if (lane == 0) KB_TRACE(kTraceTiles, 6, trace_now());
 #endif
-            for (int it = 0; ok; ++it) {
+            for (int it = (MODE == 1 && sort_batches) ? 1 : 0; ok; ++it) {  // (sorted: the first tile was published during set-up)
                 const int slot = it & 1;
                 // The next tile is drawn only once the current one is two key blocks from its end (its
                 // last Q·Kᵀ has been issued; scores run two blocks ahead of the softmax): a CTA that is
@@ -487,8 +500,6 @@ attention_persist_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
 #pragma unroll
                             for (int i = 0; i < 4; ++i) bits[i] |= warp_bits[w * 4 + i];
                         }
-                    } else if (it == 0) {  // sorted: staged from the scan's registers; live blocks from the scan
-                        for (int w = 0; w < Cfg::kThreads / 32; ++w) bits[0] |= warp_live[w * 32 + bh / p.H];
                     } else {
                         stage_mask_row(p, bh / p.H, bh % p.H, mask_smem + slot * mask_cols, mask_cols, 0, 32, bits);
                     }

@@ -41,7 +41,7 @@ sys.path.insert(0, ROOT)
 WORKLOAD = {"B": 8, "H": 12, "S": 512, "D": 64}
 WORKLOAD_NAME = ("attention fwd [batch 8, heads 12, seq 512, head_dim 64], per-sequence padding mask, "
                  "non-causal, sm_scale 1/8 (baseline config 2)")
-TRAFFIC_PROFILE = os.path.join("profiles", "attention_split_d64_config2_padmask.md")
+TRAFFIC_PROFILE = os.path.join("profiles", "attention_persist_d64_config2_padmask.md")
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
@@ -464,7 +464,7 @@ def run_ours(args):
             "bound": "tensor", "achieved": per_launch_tflops, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
             "frac": per_launch_tflops / peaks["bf16_tflops"], "traffic": headline_traffic_bytes(),
             "peak_source": f"{peak_kind} cuBLAS bf16 burst (MEASURED_PEAKS.json)" if peak_kind == "measured" else "fallback 1590 TFLOP/s",
-            "kernel": "attention_split_kernel<half, row-broadcast mask>",
+            "kernel": "attention_persist_kernel<half, row-broadcast mask>",
             "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one launch of this workload, " + TRAFFIC_PROFILE,
         },
         "cpu_baseline": {"value": cpu_tflops, "unit": "TFLOP/s", "cores": cores, "kind": "port",

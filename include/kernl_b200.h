@@ -136,7 +136,9 @@ int kb_rope_kv_write(const kb_rope_params* p, void* stream);
  * Fused attention forward: O = softmax(sm_scale · Q·Kᵀ + mask [causal]) · V, online softmax.
  * Replaces: src/kernl/implementations/attention.py:438-529 (Attention.forward launching
  * _fwd_kernel, :122-435).
- *   q [B,H,M,D], k/v [B,H,N,D] ([B,H/kv_group,N,D] with grouped queries), o [B,H,M,D]; D in {64,128};
+ *   q [B,H,M,D], k/v [B,H,N,D] ([B,H/kv_group,N,D] with grouped queries), o [B,H,M,D]; D a multiple
+ *   of 8 up to 128 (the reference takes the powers of two from 16, attention.py:521; the kernels
+ *   compute on 64 or 128 columns and TMA fills the missing ones with zeros);
  *   unit D stride required for q,k,v,o;
  *   the other q/k/v strides must be multiples of 8 elements.
  *   mask: additive, logical shape [B|1, H|1, M|1, N]; a broadcast dimension is passed with
@@ -248,6 +250,14 @@ int kb_attention_decode_fwd_static(const kb_attn_params* p, void* stream);
  * Kernels with bounded waits record a non-zero code here instead of trapping or hanging.
  * kb_device_status_read synchronises the current device, returns the word and clears it. */
 int kb_device_status_read(int32_t* status_out);
+
+/* ---- SMs for the persistent GEMM kernels ------------------------------------------------
+ * The fused-linear kernels for large problems are persistent: one CTA (or CTA pair) per SM for the
+ * whole launch, so a collective that should run AT THE SAME TIME (the all-reduce of one half of a
+ * batch while the other half computes) finds no SM until the GEMM ends. kb_gemm_sm_limit(n) makes
+ * later launches use at most n SMs (0 = all, the default); the setting is process-wide and read
+ * when a launch is enqueued. Nothing in the reference corresponds to it (it has no multi-GPU path). */
+int kb_gemm_sm_limit(int sms);
 
 const char* kb_status_str(int status);
 int kb_version(void);

@@ -31,6 +31,7 @@ EXPORTED_SYMBOLS = [
     "kb_attention_decode_static_max_bytes",
     "kb_attention_decode_fwd_static",
     "kb_device_status_read",
+    "kb_gemm_sm_limit",
     "kb_status_str",
     "kb_version",
 ]
@@ -129,6 +130,8 @@ def load() -> ctypes.CDLL:
     lib.kb_peer_close.argtypes = [c_void_p]
     for name in ("kb_peer_alloc", "kb_peer_export", "kb_peer_open", "kb_peer_free", "kb_peer_close"):
         getattr(lib, name).restype = ctypes.c_int
+    lib.kb_gemm_sm_limit.argtypes = [ctypes.c_int]
+    lib.kb_gemm_sm_limit.restype = ctypes.c_int
     lib.kb_device_status_read.argtypes = [POINTER(c_int32)]
     lib.kb_device_status_read.restype = ctypes.c_int
     lib.kb_status_str.argtypes = [ctypes.c_int]

@@ -56,7 +56,37 @@ struct AttnDev {
     int num_pairs;  // ceil(ceil(M/128)/2)
     int head_group; // heads whose CTAs are interleaved (see attn_work_item)
     int kv_group;   // query heads per K/V head (grouped-query attention), >= 1
+    int d_out;      // head dimension of the caller's tensors (a multiple of 8, at most the kernel's D): the
+                    // tensor maps end there — TMA fills the columns beyond with zeros, which add nothing to
+                    // q·kᵀ — and only these output columns are stored
 };
+
+// Stores 32 output columns [col0, col0 + 32) of one row. GUARD: the caller's head dimension ends
+// inside or before the chunk (d_out < col0 + 32), so only whole 8-column pieces below d_out are
+// written; the unguarded form is the hot path and carries no per-store condition (a guard inside the
+// store loop of the head-dimension-64 kernel cost 2.7 µs of a 21 µs launch).
+template <typename T, bool GUARD>
+__device__ __forceinline__ void attn_store_32(T* __restrict__ o_row, int col0, int64_t col_stride, bool vec,
+                                              const float (&val)[32], int d_out) {
+    if (vec) {
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+            if (GUARD && col0 + v * 8 >= d_out) continue;
+            uint4 w;
+            w.x = Elem<T>::pack2(val[v * 8 + 0], val[v * 8 + 1]);
+            w.y = Elem<T>::pack2(val[v * 8 + 2], val[v * 8 + 3]);
+            w.z = Elem<T>::pack2(val[v * 8 + 4], val[v * 8 + 5]);
+            w.w = Elem<T>::pack2(val[v * 8 + 6], val[v * 8 + 7]);
+            reinterpret_cast<uint4*>(o_row + col0)[v] = w;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {  // (fully unrolled: val stays in registers)
+            if (GUARD && col0 + i >= d_out) continue;
+            o_row[(int64_t)(col0 + i) * col_stride] = Elem<T>::from_f32(val[i]);
+        }
+    }
+}
 
 // CTA -> (batch*head, query-tile pair). Heads are taken in groups of p.head_group; inside a group
 // the order is pair-major with the late (causally heavier) pairs first, so the tail of a causal
@@ -558,21 +588,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                     tmem_ld_32x32(o_addr + dch * 32, orr);
                     tmem_ld_wait();
                     if (row < p.M) {
-                        if (vec) {
+                        float val[32];
 #pragma unroll
-                            for (int v = 0; v < 4; ++v) {
-                                uint4 w;
-                                w.x = Elem<T>::pack2(__uint_as_float(orr[v * 8 + 0]) * inv_l, __uint_as_float(orr[v * 8 + 1]) * inv_l);
-                                w.y = Elem<T>::pack2(__uint_as_float(orr[v * 8 + 2]) * inv_l, __uint_as_float(orr[v * 8 + 3]) * inv_l);
-                                w.z = Elem<T>::pack2(__uint_as_float(orr[v * 8 + 4]) * inv_l, __uint_as_float(orr[v * 8 + 5]) * inv_l);
-                                w.w = Elem<T>::pack2(__uint_as_float(orr[v * 8 + 6]) * inv_l, __uint_as_float(orr[v * 8 + 7]) * inv_l);
-                                reinterpret_cast<uint4*>(o_row + dch * 32)[v] = w;
-                            }
-                        } else {
-                            for (int i = 0; i < 32; ++i)
-                                o_row[(int64_t)(dch * 32 + i) * p.o_strides[3]] =
-                                    Elem<T>::from_f32(__uint_as_float(orr[i]) * inv_l);
-                        }
+                        for (int i = 0; i < 32; ++i) val[i] = __uint_as_float(orr[i]) * inv_l;
+                        if (dch * 32 + 32 <= p.d_out) attn_store_32<T, false>(o_row, dch * 32, p.o_strides[3], vec, val, p.d_out);
+                        else attn_store_32<T, true>(o_row, dch * 32, p.o_strides[3], vec, val, p.d_out);
                     }
                 }
             }
@@ -595,7 +615,7 @@ static int launch_attention_tdm(const kb_attn_params& p, cudaStream_t stream) {
     if (p.H % kv_group != 0) return KB_ERR_BAD_ARG;
     auto enc = [&](CUtensorMap* out, const void* ptr, int64_t rows, const int64_t* st, int64_t heads) -> int {
         if (st[3] != 1) return KB_ERR_UNSUPPORTED;
-        const uint64_t dims[4] = {(uint64_t)D, (uint64_t)rows, (uint64_t)heads, (uint64_t)p.B};
+        const uint64_t dims[4] = {(uint64_t)p.D, (uint64_t)rows, (uint64_t)heads, (uint64_t)p.B};  // boxes reach to D: zero fill
         // A dimension of extent 1 may carry any stride in the caller's tensor; TMA still wants a
         // multiple of 16 bytes, and the value is never used, so substitute a harmless one.
         auto fix = [](int64_t extent, int64_t stride) -> uint64_t {
@@ -633,6 +653,7 @@ static int launch_attention_tdm(const kb_attn_params& p, cudaStream_t stream) {
     d.num_pairs = (num_m_tiles + 1) / 2;
     d.head_group = attn_head_group(p.B * p.H, p.N, p.D);
     d.kv_group = (int)kv_group;
+    d.d_out = (int)p.D;
 
     static PerDeviceOnce attr_once;
     if (attr_once.first_time()) {
@@ -656,7 +677,8 @@ static int launch_attention_td(const kb_attn_params& p, cudaStream_t stream) {
 static int launch_attention128(const kb_attn_params& p, cudaStream_t stream) {
     if (p.N <= 0) return KB_ERR_UNSUPPORTED;
     if (p.M > 0x7fffffff || p.N > 0x7fffffff || p.B * p.H > 0x7fffffff) return KB_ERR_UNSUPPORTED;
-    if (p.D != 128) return KB_ERR_UNSUPPORTED;  // head dimension 64 is served by attention_split.cuh
+    // head dimensions up to 64 are served by attention_split.cuh; 72 ... 128 run here on the D = 128 kernel
+    if (p.D <= 64 || p.D > 128 || p.D % 8 != 0) return KB_ERR_UNSUPPORTED;
     if (p.dtype == KB_F16) return launch_attention_td<__half, 128>(p, stream);
     if (p.dtype == KB_BF16) return launch_attention_td<__nv_bfloat16, 128>(p, stream);
     return KB_ERR_UNSUPPORTED;

@@ -851,23 +851,11 @@ attention_persist_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
                        (int64_t)row * p.o_strides[2];
             const bool vec = p.o_strides[3] == 1 && ((((uintptr_t)o_row) & 15) == 0);
             if (row < p.M) {
-                if (vec) {
+                float val[32];
 #pragma unroll
-                    for (int v = 0; v < 4; ++v) {
-                        uint32_t w4[4];
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            const int e = v * 8 + 2 * i;
-                            w4[i] = Elem<T>::pack2(fmaf(__uint_as_float(oa[e]), wa, __uint_as_float(ob[e]) * wb),
-                                                   fmaf(__uint_as_float(oa[e + 1]), wa, __uint_as_float(ob[e + 1]) * wb));
-                        }
-                        reinterpret_cast<uint4*>(o_row + hf * 32)[v] = make_uint4(w4[0], w4[1], w4[2], w4[3]);
-                    }
-                } else {
-                    for (int i = 0; i < 32; ++i)
-                        o_row[(int64_t)(hf * 32 + i) * p.o_strides[3]] =
-                            Elem<T>::from_f32(fmaf(__uint_as_float(oa[i]), wa, __uint_as_float(ob[i]) * wb));
-                }
+                for (int i = 0; i < 32; ++i) val[i] = fmaf(__uint_as_float(oa[i]), wa, __uint_as_float(ob[i]) * wb);
+                if (hf * 32 + 32 <= p.d_out) attn_store_32<T, false>(o_row, hf * 32, p.o_strides[3], vec, val, p.d_out);
+                else attn_store_32<T, true>(o_row, hf * 32, p.o_strides[3], vec, val, p.d_out);
             }
 #ifdef KB_ATTN_TRACE
             if (threadIdx.x == 0) KB_TRACE(it, 4, trace_now());
@@ -946,7 +934,7 @@ static int launch_attention_persist_tm(const kb_attn_params& p, cudaStream_t str
     if (p.H % kv_group != 0) return KB_ERR_BAD_ARG;
     auto enc = [&](CUtensorMap* out, const void* ptr, int64_t rows, const int64_t* st, uint32_t box_rows, int64_t heads) -> int {
         if (st[3] != 1) return KB_ERR_UNSUPPORTED;
-        const uint64_t dims[4] = {(uint64_t)D, (uint64_t)rows, (uint64_t)heads, (uint64_t)p.B};
+        const uint64_t dims[4] = {(uint64_t)p.D, (uint64_t)rows, (uint64_t)heads, (uint64_t)p.B};  // the box reaches to 64: zero fill
         auto fix = [](int64_t extent, int64_t stride) -> uint64_t { return (extent == 1) ? 16u : (uint64_t)stride * 2u; };
         const uint64_t strides[4] = {0, fix(rows, st[2]), fix(heads, st[1]), fix(p.B, st[0])};
         const uint32_t box[4] = {64, box_rows, 1, 1};
@@ -979,6 +967,7 @@ static int launch_attention_persist_tm(const kb_attn_params& p, cudaStream_t str
     d.num_pairs = (int)((p.M + kAttnBlock - 1) / kAttnBlock);  // query tiles per (batch, head)
     d.head_group = attn_head_group(p.B * p.H, p.N, p.D);
     d.kv_group = (int)kv_group;
+    d.d_out = (int)p.D;
     static int regs_ok = 0;  // 0 = not checked, 1 = usable, -1 = register allocation does not fit
     if (regs_ok == 0) {
         // setmaxnreg.inc blocks until the CTA's pool holds the registers: refuse to launch a build

@@ -600,23 +600,11 @@ attention_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
                            (int64_t)row * p.o_strides[2];
                 const bool vec = p.o_strides[3] == 1 && ((((uintptr_t)o_row) & 15) == 0);
                 if (row < p.M) {
-                    if (vec) {
+                    float val[32];
 #pragma unroll
-                        for (int v = 0; v < 4; ++v) {
-                            uint32_t w4[4];
-#pragma unroll
-                            for (int i = 0; i < 4; ++i) {
-                                const int e = v * 8 + 2 * i;
-                                w4[i] = Elem<T>::pack2(fmaf(__uint_as_float(oa[e]), wa, __uint_as_float(ob[e]) * wb),
-                                                       fmaf(__uint_as_float(oa[e + 1]), wa, __uint_as_float(ob[e + 1]) * wb));
-                            }
-                            reinterpret_cast<uint4*>(o_row + hf * 32)[v] = make_uint4(w4[0], w4[1], w4[2], w4[3]);
-                        }
-                    } else {
-                        for (int i = 0; i < 32; ++i)
-                            o_row[(int64_t)(hf * 32 + i) * p.o_strides[3]] =
-                                Elem<T>::from_f32(fmaf(__uint_as_float(oa[i]), wa, __uint_as_float(ob[i]) * wb));
-                    }
+                    for (int i = 0; i < 32; ++i) val[i] = fmaf(__uint_as_float(oa[i]), wa, __uint_as_float(ob[i]) * wb);
+                    if (hf * 32 + 32 <= p.d_out) attn_store_32<T, false>(o_row, hf * 32, p.o_strides[3], vec, val, p.d_out);
+                    else attn_store_32<T, true>(o_row, hf * 32, p.o_strides[3], vec, val, p.d_out);
                 }
             }
         }
@@ -640,7 +628,7 @@ static int launch_attention_split_tmt(const kb_attn_params& p, cudaStream_t stre
     if (p.H % kv_group != 0) return KB_ERR_BAD_ARG;
     auto enc = [&](CUtensorMap* out, const void* ptr, int64_t rows, const int64_t* st, uint32_t box_rows, int64_t heads) -> int {
         if (st[3] != 1) return KB_ERR_UNSUPPORTED;
-        const uint64_t dims[4] = {(uint64_t)D, (uint64_t)rows, (uint64_t)heads, (uint64_t)p.B};
+        const uint64_t dims[4] = {(uint64_t)p.D, (uint64_t)rows, (uint64_t)heads, (uint64_t)p.B};  // the box reaches to 64: zero fill
         auto fix = [](int64_t extent, int64_t stride) -> uint64_t { return (extent == 1) ? 16u : (uint64_t)stride * 2u; };
         const uint64_t strides[4] = {0, fix(rows, st[2]), fix(heads, st[1]), fix(p.B, st[0])};
         const uint32_t box[4] = {64, box_rows, 1, 1};
@@ -674,6 +662,7 @@ static int launch_attention_split_tmt(const kb_attn_params& p, cudaStream_t stre
     d.num_pairs = (num_m_tiles + TILES - 1) / TILES;  // work items per (batch, head): tile pairs, or tiles
     d.head_group = attn_head_group(p.B * p.H, p.N, p.D);
     d.kv_group = (int)kv_group;
+    d.d_out = (int)p.D;
     static int regs_ok = 0;  // 0 = not checked, 1 = usable, -1 = register allocation does not fit
     if (regs_ok == 0) {
         // setmaxnreg.inc blocks until the CTA's pool holds the registers: refuse to launch a build
@@ -729,17 +718,19 @@ static int launch_attention_split_t(const kb_attn_params& p, cudaStream_t stream
 }
 
 static int launch_attention_split(const kb_attn_params& p, cudaStream_t stream) {
-    if (p.D != 64) return KB_ERR_UNSUPPORTED;
+    if (p.D > 64 || p.D % 8 != 0) return KB_ERR_UNSUPPORTED;
     if (p.dtype == KB_F16) return launch_attention_split_t<__half>(p, stream);
     if (p.dtype == KB_BF16) return launch_attention_split_t<__nv_bfloat16>(p, stream);
     return KB_ERR_UNSUPPORTED;
 }
 
-// The fused-attention entry: head dimension 64 -> the split-row kernel above, 128 -> attention.cuh.
+// The fused-attention entry: head dimensions up to 64 -> the split-row kernels above, up to 128 ->
+// attention.cuh (multiples of 8; the kernels compute on 64 / 128 columns, the missing ones are zeros).
 static int launch_attention(const kb_attn_params& p, cudaStream_t stream) {
     if (p.N <= 0) return KB_ERR_UNSUPPORTED;
     if (p.M > 0x7fffffff || p.N > 0x7fffffff || p.B * p.H > 0x7fffffff) return KB_ERR_UNSUPPORTED;
-    if (p.D == 64) return launch_attention_split(p, stream);
+    if (p.D % 8 != 0 || p.D > 128) return KB_ERR_UNSUPPORTED;
+    if (p.D <= 64) return launch_attention_split(p, stream);
     return launch_attention128(p, stream);
 }
 

@@ -407,5 +407,8 @@ int encode_tmap_16bit(CUtensorMap* out, const void* base, int rank, const uint64
                       const uint64_t* strides_bytes, const uint32_t* box, CUtensorMapSwizzle swz,
                       CUtensorMapL2promotion l2);
 int sm_count();
+// SMs the persistent GEMM kernels may occupy: sm_count(), or less while the caller has set a limit
+// (kb_gemm_sm_limit) to leave SMs to a collective that runs at the same time.
+int gemm_sms();
 
 }  // namespace kb

@@ -75,6 +75,12 @@ int sm_count() {
     return v;
 }
 
+static std::atomic<int> g_gemm_sm_limit{0};  // 0 = no limit
+int gemm_sms() {
+    const int all = sm_count(), lim = g_gemm_sm_limit.load(std::memory_order_relaxed);
+    return (lim > 0 && lim < all) ? lim : all;
+}
+
 static int check_device() {
     static int state[64] = {};  // per device: 0 unknown, 1 ok, -1 not an sm_100 device
     int dev = 0;
@@ -105,6 +111,12 @@ using namespace kb;
 extern "C" {
 
 int kb_version(void) { return 100; }
+
+int kb_gemm_sm_limit(int sms) {
+    if (sms < 0) return KB_ERR_BAD_ARG;
+    g_gemm_sm_limit.store(sms, std::memory_order_relaxed);
+    return KB_OK;
+}
 
 const char* kb_status_str(int status) {
     switch (status) {
@@ -165,6 +177,15 @@ int kb_debug_attention_trace_read(void* host_buf, int64_t bytes) {
     const size_t n = sizeof(unsigned long long) * 296 * (kTraceTiles + 1) * kTraceEvents;
     if (bytes < (int64_t)n) return KB_ERR_BAD_ARG;
     return cudaMemcpyFromSymbol(host_buf, g_attn_trace, n) == cudaSuccess ? KB_OK : KB_ERR_LAUNCH;
+}
+#endif
+#ifdef KB_GEMM_TRACE
+// Tuning builds only: copies the CTA-pair GEMM's clock stamps to the host.
+int kb_debug_gemm_trace_read(void* host_buf, int64_t bytes) {
+    if (cudaDeviceSynchronize() != cudaSuccess) return KB_ERR_LAUNCH;
+    const size_t n = sizeof(long long) * 148 * 8 * 16;
+    if (bytes < (int64_t)n) return KB_ERR_BAD_ARG;
+    return cudaMemcpyFromSymbol(host_buf, g_gemm_trace, n) == cudaSuccess ? KB_OK : KB_ERR_LAUNCH;
 }
 #endif
 int kb_debug_wait_limit(int64_t in_kernel_cycles, int64_t peer_cycles) {

@@ -40,29 +40,47 @@ struct GemmCfg {
 
 // Activations of the epilogue, evaluated on the fp32 accumulator (+bias).
 // tanh uses the hardware tanh.approx (relative error about 2^-11, far below the rounding of the
-// 16-bit output). erf uses the rational approximation 7.1.26 of Abramowitz & Stegun,
-// erf(x) = 1 - (a1 t + ... + a5 t^5) exp(-x^2) with t = 1/(1 + p x), absolute error <= 1.5e-7 in
-// exact arithmetic (about 1e-6 in fp32): the libdevice erff costs several times more instructions
-// than the GEMM main loop leaves room for in the epilogue warps.
+// 16-bit output); GELU (the erf form of the reference, activation_func.py) is described below.
 __device__ __forceinline__ float act_tanh(float z) {
     float y;
     asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(z));
     return y;
 }
-__device__ __forceinline__ float act_erf(float x) {
-    const float ax = fabsf(x);
-    const float t = __fdividef(1.0f, fmaf(0.3275911f, ax, 1.0f));
-    float poly = fmaf(1.061405429f, t, -1.453152027f);
-    poly = fmaf(poly, t, 1.421413741f);
-    poly = fmaf(poly, t, -0.284496736f);
-    poly = fmaf(poly, t, 0.254829592f);
-    poly *= t;
-    const float e = __expf(-ax * ax);
-    const float r = fmaf(-poly, e, 1.0f);
-    return copysignf(r, x);
+// GELU(z) = z·Φ(z) written as relu(z) − |z|·Φ(−|z|), with Φ(−a) = ½·erfc(a/√2) = 2^P(a): P is a
+// degree-6 fit of log2(½·erfc(a/√2)) on [0, 5.5] (weighted for the error that reaches the output),
+// |z| is clamped to 5.5 (beyond it |z|·Φ(−|z|) < 1.1e-7). Maximum absolute error against the
+// erf form in double precision: 1.1e-7 over [−8, 8], at one
+// special-function instruction and eight arithmetic ones per value; the f32x2 form evaluates two
+// values per instruction. (The erf form cost more issue slots than a short main loop leaves to the
+// epilogue warps.)
+constexpr float kGeluP0 = -0.999993085861206f, kGeluP1 = -1.1512017250061035f, kGeluP2 = -0.4587709605693817f,
+                kGeluP3 = -0.053412117063999176f, kGeluP4 = 0.008080724626779556f, kGeluP5 = -0.0007692216895520687f,
+                kGeluP6 = 3.3092990634031594e-05f;
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
 }
 __device__ __forceinline__ float act_gelu(float z) {
-    return z * 0.5f * (1.0f + act_erf(z * 0.70710678118654752440f));
+    const float a = fminf(fabsf(z), 5.5f);
+    float pl = fmaf(kGeluP6, a, kGeluP5);
+    pl = fmaf(pl, a, kGeluP4);
+    pl = fmaf(pl, a, kGeluP3);
+    pl = fmaf(pl, a, kGeluP2);
+    pl = fmaf(pl, a, kGeluP1);
+    pl = fmaf(pl, a, kGeluP0);
+    return fmaf(-a, ex2_approx(pl), fmaxf(z, 0.0f));
+}
+__device__ __forceinline__ float2 act_gelu2(float2 z) {
+    const float2 a = make_float2(fminf(fabsf(z.x), 5.5f), fminf(fabsf(z.y), 5.5f));
+    float2 pl = __ffma2_rn(make_float2(kGeluP6, kGeluP6), a, make_float2(kGeluP5, kGeluP5));
+    pl = __ffma2_rn(pl, a, make_float2(kGeluP4, kGeluP4));
+    pl = __ffma2_rn(pl, a, make_float2(kGeluP3, kGeluP3));
+    pl = __ffma2_rn(pl, a, make_float2(kGeluP2, kGeluP2));
+    pl = __ffma2_rn(pl, a, make_float2(kGeluP1, kGeluP1));
+    pl = __ffma2_rn(pl, a, make_float2(kGeluP0, kGeluP0));
+    const float2 g = make_float2(ex2_approx(pl.x), ex2_approx(pl.y));
+    return __ffma2_rn(make_float2(-a.x, -a.y), g, make_float2(fmaxf(z.x, 0.0f), fmaxf(z.y, 0.0f)));
 }
 __device__ __forceinline__ float act_fast_gelu(float z) {
     return 0.5f * z * (1.0f + act_tanh(0.79788456080286535588f * (z + 0.044715f * z * z * z)));
@@ -205,7 +223,11 @@ __device__ __forceinline__ void epilogue_values(const float (&accv)[32], const T
             break;
         case KB_ACT_GELU:
 #pragma unroll
-            for (int j = 0; j < 32; ++j) z[j] = act_gelu(z[j]);
+            for (int j = 0; j < 32; j += 2) {
+                const float2 g = act_gelu2(make_float2(z[j], z[j + 1]));
+                z[j] = g.x;
+                z[j + 1] = g.y;
+            }
             break;
         case KB_ACT_FAST_GELU:
 #pragma unroll
@@ -549,7 +571,7 @@ struct LinearPlan {
 // SMs when there are few tiles (few rows: the op is then bound by streaming W from HBM once, and
 // what counts is how many SMs pull on it and how many bytes each keeps in flight).
 static LinearPlan plan_linear(int64_t M, int64_t N, int64_t K, bool has_ws, int forced_bn, int forced_splits) {
-    const int sms = sm_count();
+    const int sms = gemm_sms();
     const int64_t num_m = (M + kGemmBM - 1) / kGemmBM;
     const int num_k = (int)((K + kGemmBK - 1) / kGemmBK);
     LinearPlan best{32, 1, num_k};
@@ -614,7 +636,7 @@ static int launch_linear_bn(const kb_linear_params& p, cudaStream_t stream, cons
     }
     const int64_t num_tiles = ((p.M + kGemmBM - 1) / kGemmBM) * ((p.N + BN - 1) / BN);
     const int64_t items = num_tiles * plan.splits;
-    const int grid = (int)(items < sm_count() ? items : sm_count());
+    const int grid = (int)(items < gemm_sms() ? items : gemm_sms());
     float* ws = reinterpret_cast<float*>(p.workspace);
     linear_tc_kernel<T, BN><<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(
         tmap_x, tmap_w, (const T*)p.bias, (T*)p.y, (T*)p.act_inputs, (int)p.M, (int)p.N, (int)p.K,

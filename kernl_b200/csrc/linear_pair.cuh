@@ -9,15 +9,20 @@
 // 128 rows of the result in its own tensor memory. Per SM and k-block that is 32 KB through shared
 // memory instead of 48 KB, and every W byte is fetched once per pair instead of once per SM.
 //
-// Roles per CTA (320 threads, as in linear.cuh): warp 0 TMA producer, warp 1 tcgen05 issuer (only the
-// pair's leader — cluster rank 0 — issues; the other CTA's warp 1 only allocates tensor memory),
-// warps 2..9 epilogue. Barriers:
+// Roles per CTA (576 threads): warp 0 TMA producer, warp 1 tcgen05 issuer (only the pair's leader —
+// cluster rank 0 — issues; the other CTA's warp 1 only allocates tensor memory), warps 2..17
+// epilogue: warp w reads the tensor-memory lanes of quadrant w % 4 (its 32 rows) and the 64 columns
+// (w - 2) / 4 of the CTA's 128 x 256 accumulator. Sixteen warps, because with a short K loop the
+// epilogue is the longer of the two pipelines: clock stamps at K = 768 showed eight warps needing
+// 7500-9000 cycles per tile (tensor-memory reads, conversion and stores each saturate their unit in
+// turn, all warps in the same phase) against 6144 tensor-pipe cycles of the main loop. Barriers:
 //   full[s]    in the LEADER's shared memory: the leader's producer arrives with the byte count of all
 //              four copies of a stage; both CTAs' TMA copies complete on it (the second CTA addresses
 //              it through the cluster's shared window);
 //   empty[s]   in each CTA: `tcgen05.commit` of the leader, multicast to both CTAs;
 //   tfull[a]   in each CTA: accumulator a complete (multicast commit);
-//   tempty[a]  in the leader: all sixteen epilogue warps of the pair have read accumulator a.
+//   tempty[a]  in the leader: all 32 epilogue warps of the pair have read accumulator a (a warp
+//              arrives as soon as its 64 columns are in registers, before it converts and stores them).
 // Accumulators are double-buffered (2 x 256 columns = all of tensor memory), the ring has six stages.
 // Every bulk copy has one destination CTA: the pair's sharing happens inside the tensor-core instruction.
 #pragma once
@@ -27,16 +32,33 @@ namespace kb {
 
 constexpr int kPairBN = 256;          // columns of the pair's tile
 constexpr int kPairHalfN = 128;       // W rows staged by each CTA
-constexpr int kPairStages = 6;
+#ifndef KB_PAIR_STAGES
+#define KB_PAIR_STAGES 6
+#endif
+constexpr int kPairStages = KB_PAIR_STAGES;
 constexpr int kPairABytes = kGemmBM * kGemmBK * 2;     // 16 KB: this CTA's 128 rows of x
 constexpr int kPairBBytes = kPairHalfN * kGemmBK * 2;  // 16 KB: this CTA's half of the W tile
 constexpr int kPairStageBytes = kPairABytes + kPairBBytes;
-// Output staging of the epilogue: per epilogue warp 32 rows x 64 columns (128 bytes per row, eight
-// 16-byte pieces; piece c of row r sits at r * 128 + ((c ^ (r & 7)) * 16), which keeps both the
-// row-wise writes and the piece-wise reads free of bank conflicts).
-constexpr int kPairOutWarpBytes = 32 * 128;
-constexpr int kPairOutBytes = kGemmEpilogueWarps * kPairOutWarpBytes;
+constexpr int kPairEpilogueWarps = 16;
+constexpr int kPairThreads = (2 + kPairEpilogueWarps) * 32;
+// Output staging of the epilogue: per epilogue warp 32 rows x kPairPassCols columns of 16-bit
+// results, in 16-byte pieces; piece c of row r sits at r * row_bytes + (c ^ f(r)) * 16 with f chosen so
+// that the row-wise writes and the piece-wise reads are both free of bank conflicts (64-byte rows:
+// f = (r >> 1) & 3; 32-byte rows: f = (r >> 2) & 1). Behind it the warp's 64 bias values as fp32.
+#ifndef KB_PAIR_PASS_COLS
+#define KB_PAIR_PASS_COLS 16
+#endif
+constexpr int kPairPassCols = KB_PAIR_PASS_COLS;
+static_assert(kPairPassCols == 16 || kPairPassCols == 32, "columns per staging pass");
+constexpr int kPairRowBytes = kPairPassCols * 2;
+constexpr int kPairOutWarpBytes = 32 * kPairRowBytes;
+constexpr int kPairBiasWarpBytes = 64 * 4;
+constexpr int kPairOutBytes = kPairEpilogueWarps * (kPairOutWarpBytes + kPairBiasWarpBytes);
 constexpr int kPairSmemBytes = kPairStages * kPairStageBytes + 256 + kPairOutBytes + 1024;
+__device__ __forceinline__ int pair_stage_offset(int r, int piece) {
+    return kPairPassCols == 32 ? r * 64 + ((piece ^ ((r >> 1) & 3)) * 16) : r * 32 + ((piece ^ ((r >> 2) & 1)) * 16);
+}
+static_assert(kPairSmemBytes <= 227 * 1024, "shared memory of the pair kernel");
 constexpr uint32_t kPairTmemCols = 512;
 // The address, in the cluster's shared window, of the leader's (rank 0) copy of one of this CTA's own
 // shared-memory locations: both CTAs lay out their shared memory identically.
@@ -93,8 +115,23 @@ __device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
                  : "memory");
 }
 
+// Optional clock stamps for tuning (compiled in with -DKB_GEMM_TRACE only): per CTA and for its first
+// eight tiles, clock64 of: 0 issuer starts waiting for the accumulator, 1 has it, 2 has issued the
+// tile's last MMA; 3 epilogue warp 2 starts waiting for the accumulator, 4 has it, 5 is done with it;
+// 6 the same warp's first 64 columns are stored (8 / 9 / 10: its first tensor-memory load has
+// landed / values are in shared memory / the warp has synchronised). Event 7 of tile 0 is the CTA's start.
+#ifdef KB_GEMM_TRACE
+__device__ long long g_gemm_trace[148 * 8 * 16];
+#define KB_GTRACE(tile, ev)                                                                   \
+    do {                                                                                      \
+        if (blockIdx.x < 148 && (tile) < 8) g_gemm_trace[(blockIdx.x * 8 + (tile)) * 16 + (ev)] = clock64(); \
+    } while (0)
+#else
+#define KB_GTRACE(tile, ev) do { } while (0)
+#endif
+
 template <typename T>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
 linear_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
                    const T* __restrict__ bias, T* __restrict__ y, T* __restrict__ act_inputs, int M, int N, int K,
                    int64_t y_row_stride, int activation) {
@@ -122,6 +159,7 @@ linear_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
     // reading counts for both: it is exchanged through the cluster barrier below.
     __shared__ int s_skip;
     if (threadIdx.x == 0) {
+        KB_GTRACE(0, 7);
         s_skip = *reinterpret_cast<volatile int*>(&g_device_status[0]);
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(full_bar(s), 1);
@@ -129,7 +167,7 @@ linear_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(tfull_bar(a), 1);
-            mbar_init(tempty_bar(a), 2 * kGemmEpilogueWarps);  // the epilogue warps of both CTAs
+            mbar_init(tempty_bar(a), 2 * kPairEpilogueWarps);  // the epilogue warps of both CTAs
         }
         *abort_flag = 0;
         fence_mbar_init();
@@ -197,8 +235,11 @@ linear_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
             int acc = 0;
             uint32_t acc_phase = 0;
             bool ok = true;
-            for (int t = pair; t < num_tiles && ok; t += num_pairs) {
+            int ti = 0;
+            for (int t = pair; t < num_tiles && ok; t += num_pairs, ++ti) {
+                KB_GTRACE(ti, 0);
                 if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1, abort_flag, 210)) { ok = false; break; }
+                KB_GTRACE(ti, 1);
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * kPairBN);
                 for (int kb = 0; kb < num_k; ++kb) {
@@ -215,89 +256,129 @@ linear_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
                 }
                 if (!ok) break;
                 tc_commit_pair(tfull_bar(acc));  // both CTAs' epilogues may read accumulator `acc`
+                KB_GTRACE(ti, 2);
                 acc ^= 1;
                 if (acc == 0) acc_phase ^= 1;
             }
         }
     } else if (skip == 0) {
         // ------------------------------------------------------------------ epilogue (both CTAs)
-        const int q = warp & 3;                // TMEM lane quadrant this warp may access
-        const int col_half = (warp - 2) >> 2;  // which half of the tile's columns this warp handles
-        const int c_begin = col_half * (kPairBN / 2), c_end = c_begin + kPairBN / 2;
+        const int q = warp & 3;                 // TMEM lane quadrant this warp may access
+        const int c_begin = ((warp - 2) >> 2) * 64;  // the warp's 64 columns of the tile
         const uint32_t leader_tempty[2] = {in_leader(tempty_bar(0)), in_leader(tempty_bar(1))};
         // whole 16-byte pieces of y: plain activations, no pre-activation output, aligned rows
         const bool staged = activation != KB_ACT_SWIGLU && act_inputs == nullptr && (N & 7) == 0 && (y_row_stride & 7) == 0 &&
                             (((uintptr_t)y) & 15) == 0;
+        uint8_t* mine = out_stage + (warp - 2) * (kPairOutWarpBytes + kPairBiasWarpBytes);
+        float* bias_s = reinterpret_cast<float*>(mine + kPairOutWarpBytes);
         int acc = 0;
         uint32_t acc_phase = 0;
         bool ok = true;
-        for (int t = pair; t < num_tiles && ok; t += num_pairs) {
+        int ti = 0;
+        // the warp's bias values of a tile (lane l: columns 2l, 2l + 1 of the warp's 64)
+        auto load_bias = [&](int tile) -> float2 {
+            float2 b2 = make_float2(0.f, 0.f);
+            if (bias != nullptr && tile < num_tiles) {
+                int m_i, n_i;
+                tile_coords(tile, num_m, num_n, m_i, n_i);
+                const int c = n_i * kPairBN + c_begin + 2 * lane;
+                if (c < N) b2.x = Elem<T>::to_f32(bias[c]);
+                if (c + 1 < N) b2.y = Elem<T>::to_f32(bias[c + 1]);
+            }
+            return b2;
+        };
+        if (staged) reinterpret_cast<float2*>(bias_s)[lane] = load_bias(pair);
+        for (int t = pair; t < num_tiles && ok; t += num_pairs, ++ti) {
             int m_idx, n_idx;
             tile_coords(t, num_m, num_n, m_idx, n_idx);
+            const int n0 = n_idx * kPairBN;
+            // the next tile's bias is requested now and put into shared memory when this tile is done
+            float2 bias_next = make_float2(0.f, 0.f);
+            if (staged) bias_next = load_bias(t + num_pairs);
+            if (warp == 2 && lane == 0) KB_GTRACE(ti, 3);
             if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, 310)) { ok = false; break; }
+            if (warp == 2 && lane == 0) KB_GTRACE(ti, 4);
             tc_fence_after();
             const int row = m_idx * 2 * kGemmBM + (int)rank * kGemmBM + q * 32 + lane;
-            const int n0 = n_idx * kPairBN;
             T* y_row = y + (int64_t)row * y_row_stride;
             T* a_row = act_inputs ? act_inputs + (int64_t)row * y_row_stride : nullptr;
             if (staged) {
-                // Results go through shared memory so that the warp writes whole 128-byte row
-                // segments (four rows per store instruction) instead of 32 rows x 16 bytes: a
+                // Results go through shared memory so that the warp writes whole row segments (eight
+                // rows x 64 bytes per store instruction) instead of 32 rows x 16 bytes: a
                 // thread-per-row store touches 32 cache lines per instruction.
-                uint8_t* mine = out_stage + (warp - 2) * kPairOutWarpBytes;
                 const int row_base = m_idx * 2 * kGemmBM + (int)rank * kGemmBM + q * 32;
-#pragma unroll 1
-                for (int c0 = c_begin; c0 < c_end; c0 += 64) {
-                    if (n0 + c0 >= N) break;
-                    // both 32-column halves are requested before the wait: one tensor-memory round trip per 64 columns
-                    uint32_t r2[2][32];
-                    tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * kPairBN + c0), r2[0]);
-                    tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * kPairBN + c0 + 32), r2[1]);
-                    tmem_ld_wait();
+                // all 64 columns in one tensor-memory round trip; with them in registers the
+                // accumulator goes back to the issuer at once. (Fetching the second half while the
+                // first is converted and stored was slower: the accumulator came back later.)
+                uint32_t r2[2][32];
+                tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * kPairBN + c_begin), r2[0]);
+                tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * kPairBN + c_begin + 32), r2[1]);
+                tmem_ld_wait();
+                tc_fence_before();
+                __syncwarp();  // (also: every lane's bias values are in bias_s)
+                if (lane == 0) mbar_arrive_cluster(leader_tempty[acc]);
+                if (warp == 2 && lane == 0) KB_GTRACE(ti, 8);
 #pragma unroll
-                    for (int hc = 0; hc < 2; ++hc) {
-                        float accv[32], z[32];
+                for (int hc = 0; hc < 2; ++hc) {
+                    if (n0 + c_begin + hc * 32 >= N) break;
+                    float z[32];
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) accv[j] = __uint_as_float(r2[hc][j]);
-                        epilogue_values<T>(accv, bias, n0 + c0 + hc * 32, N, activation, z);
+                    for (int v = 0; v < 8; ++v) {
+                        const float4 b4 = reinterpret_cast<const float4*>(bias_s)[hc * 8 + v];
+                        z[v * 4 + 0] = __uint_as_float(r2[hc][v * 4 + 0]) + b4.x;
+                        z[v * 4 + 1] = __uint_as_float(r2[hc][v * 4 + 1]) + b4.y;
+                        z[v * 4 + 2] = __uint_as_float(r2[hc][v * 4 + 2]) + b4.z;
+                        z[v * 4 + 3] = __uint_as_float(r2[hc][v * 4 + 3]) + b4.w;
+                    }
+                    epilogue_values<T>(z, nullptr, 0, N, activation, z);
+                    constexpr int kPieces = kPairPassCols / 8;     // 16-byte pieces per staged row
+                    constexpr int kRowsPerStore = 32 / kPieces;  // rows one store instruction covers
 #pragma unroll
-                        for (int v = 0; v < 4; ++v) {
+                    for (int ps = 0; ps < 32 / kPairPassCols; ++ps) {
+#pragma unroll
+                        for (int v = 0; v < kPieces; ++v) {
+                            const int e = ps * kPairPassCols + v * 8;
                             uint4 o;
-                            o.x = Elem<T>::pack2(z[v * 8 + 0], z[v * 8 + 1]);
-                            o.y = Elem<T>::pack2(z[v * 8 + 2], z[v * 8 + 3]);
-                            o.z = Elem<T>::pack2(z[v * 8 + 4], z[v * 8 + 5]);
-                            o.w = Elem<T>::pack2(z[v * 8 + 6], z[v * 8 + 7]);
-                            const int pc = hc * 4 + v;
-                            *reinterpret_cast<uint4*>(mine + lane * 128 + ((pc ^ (lane & 7)) * 16)) = o;
+                            o.x = Elem<T>::pack2(z[e + 0], z[e + 1]);
+                            o.y = Elem<T>::pack2(z[e + 2], z[e + 3]);
+                            o.z = Elem<T>::pack2(z[e + 4], z[e + 5]);
+                            o.w = Elem<T>::pack2(z[e + 6], z[e + 7]);
+                            *reinterpret_cast<uint4*>(mine + pair_stage_offset(lane, v)) = o;
                         }
-                    }
-                    __syncwarp();
+                        if (warp == 2 && lane == 0 && hc == 0 && ps == 0) KB_GTRACE(ti, 9);
+                        __syncwarp();
+                        if (warp == 2 && lane == 0 && hc == 0 && ps == 0) KB_GTRACE(ti, 10);
 #pragma unroll
-                    for (int it = 0; it < 8; ++it) {
-                        const int rr = it * 4 + (lane >> 3), pc = lane & 7;
-                        const uint4 o = *reinterpret_cast<const uint4*>(mine + rr * 128 + ((pc ^ (rr & 7)) * 16));
-                        const int grow = row_base + rr, gcol = n0 + c0 + pc * 8;
-                        if (grow < M && gcol < N) *reinterpret_cast<uint4*>(y + (int64_t)grow * y_row_stride + gcol) = o;
+                        for (int it = 0; it < 32 / kRowsPerStore; ++it) {
+                            const int rr = it * kRowsPerStore + lane / kPieces, pc = lane % kPieces;
+                            const uint4 o = *reinterpret_cast<const uint4*>(mine + pair_stage_offset(rr, pc));
+                            const int grow = row_base + rr, gcol = n0 + c_begin + hc * 32 + ps * kPairPassCols + pc * 8;
+                            if (grow < M && gcol < N) *reinterpret_cast<uint4*>(y + (int64_t)grow * y_row_stride + gcol) = o;
+                        }
+                        if (ps + 1 < 32 / kPairPassCols) __syncwarp();
                     }
+                    if (warp == 2 && lane == 0 && hc == 0) KB_GTRACE(ti, 6);
                     __syncwarp();
                 }
+                reinterpret_cast<float2*>(bias_s)[lane] = bias_next;  // (all reads of this tile's values are behind the last __syncwarp)
             } else {
 #pragma unroll 1
-            for (int c0 = c_begin; c0 < c_end; c0 += 32) {
-                if (n0 + c0 >= N) break;
-                uint32_t r[32];
-                tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * kPairBN + c0), r);
-                tmem_ld_wait();
-                float accv[32];
+                for (int c0 = c_begin; c0 < c_begin + 64; c0 += 32) {
+                    if (n0 + c0 >= N) break;
+                    uint32_t r[32];
+                    tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * kPairBN + c0), r);
+                    tmem_ld_wait();
+                    float accv[32];
 #pragma unroll
-                for (int j = 0; j < 32; ++j) accv[j] = __uint_as_float(r[j]);
-                if (activation == KB_ACT_SWIGLU) epilogue_chunk_swiglu<T>(accv, bias, y_row, n0 + c0, N, row < M);
-                else epilogue_chunk<T>(accv, bias, y_row, a_row, n0 + c0, N, row < M, activation);
+                    for (int j = 0; j < 32; ++j) accv[j] = __uint_as_float(r[j]);
+                    if (activation == KB_ACT_SWIGLU) epilogue_chunk_swiglu<T>(accv, bias, y_row, n0 + c0, N, row < M);
+                    else epilogue_chunk<T>(accv, bias, y_row, a_row, n0 + c0, N, row < M, activation);
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(leader_tempty[acc]);  // counted in the leader, whose issuer reuses the accumulator
             }
-            }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(leader_tempty[acc]);  // counted in the leader, whose issuer reuses the accumulator
+            if (warp == 2 && lane == 0) KB_GTRACE(ti, 5);
             acc ^= 1;
             if (acc == 0) acc_phase ^= 1;
         }
@@ -320,7 +401,7 @@ static int g_linear_pair = 1;  // test hook (kb_debug_linear_pair): 0 = never us
 static bool linear_pair_applicable(const kb_linear_params& p) {
     if (g_linear_pair == 0) return false;
     const int64_t tiles = ((p.M + 255) / 256) * ((p.N + kPairBN - 1) / kPairBN);
-    return p.M >= 512 && p.N >= 256 && p.K >= 256 && tiles >= sm_count() / 2;
+    return p.M >= 512 && p.N >= 256 && p.K >= 256 && tiles >= gemm_sms() / 2;
 }
 
 template <typename T>
@@ -343,7 +424,7 @@ static int launch_linear_pair_t(const kb_linear_params& p, cudaStream_t stream) 
         if (st != KB_OK) return st;
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.blockDim = dim3(kGemmThreads);
+    cfg.blockDim = dim3(kPairThreads);
     cfg.dynamicSmemBytes = kPairSmemBytes;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
@@ -369,7 +450,8 @@ static int launch_linear_pair_t(const kb_linear_params& p, cudaStream_t stream) 
         max_pairs[dev] = n < sm_count() / 2 ? n : sm_count() / 2;
     }
     const int64_t tiles = ((p.M + 255) / 256) * ((p.N + kPairBN - 1) / kPairBN);
-    const int pairs = (int)(tiles < max_pairs[dev] ? tiles : max_pairs[dev]);
+    int pairs = (int)(tiles < max_pairs[dev] ? tiles : max_pairs[dev]);
+    if (pairs > gemm_sms() / 2) pairs = gemm_sms() / 2;  // a caller-set limit leaves SMs to a concurrent collective
     cfg.gridDim = dim3(2 * (unsigned)pairs);
     if (cudaLaunchKernelEx(&cfg, linear_pair_kernel<T>, tmap_x, tmap_w, (const T*)p.bias, (T*)p.y, (T*)p.act_inputs, (int)p.M,
                            (int)p.N, (int)p.K, p.y_row_stride, p.activation) != cudaSuccess)

@@ -94,13 +94,14 @@ def make_params(q, k, v, output, sm_scale, is_causal, attention_mask, kv_len=Non
 
 
 def _attention_other_head_dim(q, k, v, output, sm_scale, is_causal, attention_mask):
-    """The kernels are built for head dimensions 64 and 128. Any smaller one (the reference's Triton
-    kernel takes the powers of two from 16 up, attention.py:122-135) runs as the next of the two with
-    zero columns appended to q, k and v: zeros add nothing to q·kᵀ, and the extra output columns
-    (zeros) are dropped. Costs one padded copy of the operands; meant for small models, not for speed."""
+    """Head dimensions that are not a multiple of 8 (their rows cannot be addressed by a tensor map:
+    TMA wants 16-byte strides) run as the next multiple of 8 with zero columns appended to q, k and v:
+    zeros add nothing to q·kᵀ, and the extra output columns (zeros) are dropped. Costs one padded copy
+    of the operands; the reference's kernel takes powers of two from 16 (attention.py:122-135), all of
+    which run natively."""
     dhead = q.shape[-1]
     assert dhead < 128, f"head dimension above 128 is not supported, got {dhead}"
-    extra = (64 if dhead < 64 else 128) - dhead
+    extra = (-dhead) % 8
     qp, kp, vp = (torch.nn.functional.pad(t, (0, extra)) for t in (q, k, v))
     padded_out = torch.empty(qp.shape, dtype=output.dtype, device=output.device)
     attention_forward(qp, kp, vp, padded_out, sm_scale, is_causal, attention_mask)
@@ -123,7 +124,8 @@ def attention_forward(
     Attention.forward :438-529): q [B,H,M,D], k/v [B,H,N,D], all fp16 or all bf16;
     attention_mask additive, broadcastable over batch / heads / rows with last size N; -inf mask
     entries behave as the lowest finite value of the mask dtype; `is_causal` keeps col <= row.
-    Head dimension 64 or 128 natively; smaller ones through zero padding. Beyond the reference:
+    Head dimensions that are multiples of 8 up to 128 run natively (the kernels compute on 64 or 128
+    columns; the tensor maps end at the real head dimension and TMA fills the rest with zeros). Beyond the reference:
     k/v may carry fewer heads than q (grouped-query attention, see `kv_group_of`).
     """
     q, k, v, output, attention_mask = cast_if_autocast(q, k, v, output, attention_mask)
@@ -135,7 +137,7 @@ def attention_forward(
     assert q.is_cuda, "kernl_b200 ops run on a CUDA (sm_100a) device only"
     batch, heads, m_size, dhead = q.size()
     n_size = k.size(2)
-    if dhead not in (64, 128):
+    if dhead % 8 != 0 or dhead > 128:
         return _attention_other_head_dim(q, k, v, output, sm_scale, is_causal, attention_mask)
     if attention_mask is not None:
         _check_mask(attention_mask, batch, heads, m_size, n_size)

@@ -20,6 +20,7 @@ number of filled slots are device tensors that the rotary and the decode-attenti
 step streams only the keys that exist. Ops without that feature (the CPU stand-ins of the tests)
 get an additive length mask instead.
 """
+import os
 from dataclasses import dataclass
 from typing import Optional
 
@@ -162,6 +163,10 @@ class LlamaTP:
         self.vcache = None
         self.sm_scale = D ** -0.5
         self.overlap_prefill = True  # two half-batches on two streams when tensor parallel (see prefill)
+        # SMs left free for the collective while the two halves overlap: the GEMMs of the prefill are
+        # persistent (one CTA per SM for the whole launch), so without this an all-reduce that is ready
+        # to run finds no SM until the other half's GEMM has ended
+        self.overlap_reserved_sms = int(os.environ.get("KERNL_B200_TP_RESERVED_SMS", "16"))
         self._streams = None
         self._prefill_out = {}
 
@@ -224,13 +229,24 @@ class LlamaTP:
             for st in self._streams:
                 st.wait_stream(main)
             live = list(range(halves))
-            while live:
-                for i in list(live):
-                    with torch.cuda.stream(self._streams[i]):
-                        try:
-                            next(gens[i])
-                        except StopIteration:
-                            live.remove(i)
+            lib = None
+            if self.overlap_reserved_sms > 0:
+                from kernl_b200 import _lib
+
+                lib = _lib.load()
+                sms = torch.cuda.get_device_properties(self.device).multi_processor_count
+                lib.kb_gemm_sm_limit(max(2, sms - self.overlap_reserved_sms))
+            try:
+                while live:
+                    for i in list(live):
+                        with torch.cuda.stream(self._streams[i]):
+                            try:
+                                next(gens[i])
+                            except StopIteration:
+                                live.remove(i)
+            finally:
+                if lib is not None:
+                    lib.kb_gemm_sm_limit(0)
             for i, st in enumerate(self._streams):
                 main.wait_stream(st)
                 self._prefill_out[i * nb].record_stream(main)

@@ -95,6 +95,33 @@ def test_attention_both_head_dims(lib, d, dtype, tol, mask_kind, causal, m, n):
     O.assert_parity(out, expected, max_abs=tol, what=f"d={d}")
 
 
+@pytest.mark.parametrize("d", [16, 32, 40, 96, 20])
+@pytest.mark.parametrize("mask_kind,causal,m,n", [("none", False, 300, 300), ("pad", False, 130, 520), ("bias", True, 257, 257), ("none", False, 1, 24)])
+def test_attention_other_head_dims(lib, d, mask_kind, causal, m, n):
+    """Head dimensions other than 64 / 128 (the reference takes powers of two from 16): multiples of 8
+    run natively — tensor maps that end at the real head dimension under a 64-column box, output
+    columns beyond it never written — and anything else (20) through the front-end's zero padding."""
+    out, expected = _run_attention(2, 3, m, n, d, torch.float16, causal, mask_kind, d ** -0.5)
+    assert out.shape[-1] == d
+    O.assert_parity(out, expected, what=f"d={d}")
+
+
+def test_attention_small_head_dim_leaves_neighbours_alone(lib):
+    """The output of a head-dimension-16 call is a [.., 16] view into a wider buffer: the columns next
+    to it must keep their contents (the kernel computes 64 columns and may store only 16)."""
+    from kernl_b200.implementations.attention import attention_forward
+
+    g = torch.Generator().manual_seed(3)
+    q, k, v = (torch.randn((1, 2, 200, 16), generator=g).half().cuda() for _ in range(3))
+    wide = torch.full((1, 2, 200, 64), 7.0, dtype=torch.float16, device="cuda")
+    out = wide[..., 8:24]
+    attention_forward(q, k, v, out, 0.25)
+    torch.cuda.synchronize()
+    assert torch.all(wide[..., :8] == 7.0) and torch.all(wide[..., 24:] == 7.0)
+    expected = O.attention(q.cpu(), k.cpu(), v.cpu(), 0.25)
+    O.assert_parity(out.cpu(), expected, what="d=16 into a strided view")
+
+
 @pytest.mark.parametrize("d,dtype,tol", [(64, torch.float16, 1e-2), (128, torch.bfloat16, 3e-2)], ids=["d64_fp16", "d128_bf16"])
 @pytest.mark.parametrize("group", [2, 4, 8])
 @pytest.mark.parametrize("m,n,causal,mask_kind", [(300, 300, True, "none"), (130, 520, False, "pad"), (1, 700, False, "none")])

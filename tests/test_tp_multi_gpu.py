@@ -71,27 +71,28 @@ def _worker(rank, world, port, out_path):
     # ---- model: tensor parallel over all ranks with both communicators vs the same model on one GPU
     cfg = LlamaConfig(n_layers=2, hidden=1024, n_heads=8, head_dim=128, ffn=2816, vocab=1000, max_seq=208)
     ids = torch.randint(0, cfg.vocab, (2, 200), generator=torch.Generator().manual_seed(0)).to(dev)
+    # the decode steps are teacher-forced with fixed tokens: with greedy feedback a rounding near-tie
+    # of these random-init logits makes two arms continue with different tokens, and their later
+    # logits then answer different questions
+    forced = torch.randint(0, cfg.vocab, (2, 3), generator=torch.Generator().manual_seed(5)).to(dev)
     outs = {}
     for name, comm in (("nccl", NcclAllReduce(world)), ("peer", peer)):
         m = LlamaTP(cfg, rank=rank, world=world, device=dev, dtype=torch.bfloat16, seed=0, comm=comm)
         logits = [m.prefill(ids)]
-        tok = logits[0].float().argmax(-1)
-        for _ in range(3):
-            logits.append(m.decode_step(tok))
-            tok = logits[-1].float().argmax(-1)
+        for t in range(3):
+            logits.append(m.decode_step(forced[:, t]))
         outs[name] = torch.stack(logits).float().cpu()
         # greedy generation under one CUDA graph, fused all-reduce inside the graph
         outs[name + "_tokens"] = m.generate(ids, 6, use_cuda_graph=True).cpu()
+        outs[name + "_tokens_eager"] = m.generate(ids, 6, use_cuda_graph=False).cpu()
     _lib.device_status()
     dist.barrier()
     peer.close()
     if rank == 0:
         single = LlamaTP(cfg, rank=0, world=1, device=dev, dtype=torch.bfloat16, seed=0)
         logits = [single.prefill(ids)]
-        tok = logits[0].float().argmax(-1)
-        for _ in range(3):
-            logits.append(single.decode_step(tok))
-            tok = logits[-1].float().argmax(-1)
+        for t in range(3):
+            logits.append(single.decode_step(forced[:, t]))
         outs["single"] = torch.stack(logits).float().cpu()
         results.update({k: v for k, v in outs.items()})
         torch.save(results, out_path)
@@ -119,4 +120,7 @@ def test_multi_gpu_tensor_parallel(lib, tmp_path):
     O.assert_parity(r["nccl"], r["single"], max_abs=6e-2, cos=0.999, what=f"TP{world} (NCCL) vs single GPU")
     O.assert_parity(r["peer"], r["single"], max_abs=6e-2, cos=0.999, what=f"TP{world} (fused kernel) vs single GPU")
     O.assert_parity(r["peer"], r["nccl"], max_abs=6e-2, cos=0.999, what="fused kernel vs NCCL")
-    assert (r["peer_tokens"] == r["nccl_tokens"]).float().mean() >= 0.8
+    # replaying the captured decode step gives the tokens of the same arm's eager steps (same kernels,
+    # same order of additions); tokens of different arms may part at a near-tie and are not compared
+    assert torch.equal(r["peer_tokens"], r["peer_tokens_eager"])
+    assert torch.equal(r["nccl_tokens"], r["nccl_tokens_eager"])

@@ -39,6 +39,12 @@ def optimize_model(model) -> None:
     # The rewrites match `call_module` nodes by module type; recent TorchDynamo inlines built-in
     # modules (parameters become graph inputs) unless told otherwise.
     torch._dynamo.config.inline_inbuilt_nn_modules = False
+    # One CUDA graph per input shape, as in the reference: every new shape is a new static trace
+    # (symbolic sizes would reach the graph wrapper as integer inputs that a captured graph cannot
+    # follow), and a generation loop meets one shape per decoded token — far more than TorchDynamo's
+    # default of 8 variants per frame (the reference raises the same limit: conftest.py:37-39, tutorial/t5 e2e.ipynb).
+    torch._dynamo.config.automatic_dynamic_shapes = False
+    torch._dynamo.config.cache_size_limit = max(torch._dynamo.config.cache_size_limit, 512)
     model.forward_original = model.forward
 
     @torch._dynamo.optimize(_compiler)

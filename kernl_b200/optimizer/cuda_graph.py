@@ -132,6 +132,11 @@ def cuda_graphs_wrapper(model: Callable, inputs: Union[list, tuple], static_inpu
     an AssertionError (the graph would silently read the old one).
     """
     assert isinstance(inputs, (list, tuple))
+    if any(not isinstance(inp, torch.Tensor) for inp in inputs):
+        # A graph traced with symbolic sizes takes integers as inputs: one capture cannot serve the
+        # shapes it stands for. Such a graph runs as it is (`optimize_model` asks TorchDynamo for
+        # static shapes, so this is a safety net, not the normal path).
+        return model
     if defer_capture is None:
         defer_capture = any(isinstance(inp, FakeTensor) for inp in inputs)
     assert defer_capture or not any(isinstance(inp, FakeTensor) for inp in inputs), "FakeTensor inputs cannot be captured now"

@@ -391,6 +391,7 @@ def replace_all_linear(gm: torch.fx.GraphModule):
     replace_linear_activation(gm, torch.nn.ReLU(), "relu")
     replace_linear_activation(gm, torch.nn.functional.gelu, "gelu")
     replace_linear_activation(gm, torch.nn.GELU(), "gelu")
+    replace_linear_activation(gm, torch.nn.GELU(approximate="tanh"), "fast_gelu")
     replace_linear(gm)
     replace_linear_fn(gm)
     replace_linear_fn_constant_match(gm)

@@ -48,6 +48,9 @@ class _Matcher:
             pm, tm = self.pattern_modules.get(pn.target), self.target_modules.get(gn.target)
             if pm is None or tm is None or type(pm) is not type(tm):
                 return False
+            # same type, different function: nn.GELU() is the erf form, nn.GELU(approximate="tanh") is not
+            if isinstance(pm, torch.nn.GELU) and pm.approximate != tm.approximate:
+                return False
             known = m.modules_map.get(pn.target)
             if known is not None and known != gn.target:
                 return False

@@ -129,3 +129,52 @@ def test_weights_built_by_the_rewrites_outlive_the_backend_call(lib):
     finally:
         cuda_graph.static_inputs_pool.clear()
         torch._dynamo.reset()
+
+
+def test_t5_generate_through_optimize_model(lib):
+    """The reference's T5 path: HF `generate` over the TorchDynamo graphs of an optimized model
+    (test/test_torchdynamo.py:103-131, tutorial/t5 e2e.ipynb) — a new graph (and CUDA graph) per
+    decoded length, the KV cache as graph inputs. A random-init model has near-ties among its logits,
+    so the check is teacher-forced: every token the optimized fp16 model chose must be, for the fp32
+    eager model fed the same prefix, the arg-max or within the fp16 error of it. A second and third
+    call (capture, then replay of every per-length graph) must return the same tokens."""
+    import transformers as tf
+
+    from kernl_b200.model_optimization import optimize_model
+
+    torch.manual_seed(0)
+    cfg = tf.T5Config(d_model=256, d_ff=512, num_layers=2, num_decoder_layers=2, num_heads=4, d_kv=64, vocab_size=1000,
+                      feed_forward_proj="relu", decoder_start_token_id=0, eos_token_id=1, pad_token_id=0,
+                      tie_word_embeddings=False)
+    ref = tf.T5ForConditionalGeneration(cfg).eval().cuda()
+    _clamp_eps_like_the_kernel_path(ref)
+    with torch.no_grad():
+        ref.lm_head.weight.normal_(0.0, 0.5)  # logits of O(10): distinct tokens instead of one dominant id
+    opt = copy.deepcopy(ref).half()
+    optimize_model(opt)
+    ids = torch.randint(3, 1000, (2, 24), generator=torch.Generator().manual_seed(0)).cuda()
+    steps = 6
+    runs = []
+    # no token twice (and never the start token or the end token): a random-init model would otherwise
+    # repeat one id for ever. The processors act on the scores, outside the model's graphs.
+    kwargs = dict(max_new_tokens=steps, min_new_tokens=steps, do_sample=False, no_repeat_ngram_size=1, suppress_tokens=[0])
+    for _ in range(3):
+        with torch.inference_mode():
+            runs.append(opt.generate(ids, **kwargs))
+        torch.cuda.synchronize()
+    toks = runs[0]
+    assert toks.shape == (2, steps + 1)
+    assert torch.equal(runs[1], toks) and torch.equal(runs[2], toks)
+    assert len(set(toks[:, 1:].flatten().tolist())) > 2, "degenerate generation: the test would prove nothing"
+    with torch.inference_mode():
+        logits = ref(input_ids=ids, decoder_input_ids=toks[:, :-1]).logits.float()
+    logits = logits.clone()  # (a tensor made in inference mode cannot be written outside it)
+    for b in range(toks.shape[0]):  # what the processors forbid at step t: ids 0 and 1 and everything generated so far
+        for t in range(steps):
+            banned = [0, 1] + toks[b, 1:t + 1].tolist()
+            logits[b, t, banned] = float("-inf")
+    chosen = logits.gather(-1, toks[:, 1:].unsqueeze(-1)).squeeze(-1)
+    gap = logits.max(-1).values - chosen
+    scale = float(logits[torch.isfinite(logits)].abs().max())
+    print(f"tokens {toks.tolist()}, gap to the fp32 arg-max per step {gap.tolist()}, logit scale {scale:.1f}")
+    assert float(gap.max()) <= 1e-2 * max(scale, 1.0), (gap, scale)

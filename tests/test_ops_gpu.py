@@ -609,6 +609,30 @@ def test_linear_cta_pairs(lib, shape, activation, dtype, tol):
         O.assert_parity(pre, O.linear(x, w, b, ""), max_abs=tol, what="pre-activation output")
 
 
+@pytest.mark.parametrize("limit", [100, 32, 3])
+@pytest.mark.parametrize("shape", [(4096, 512, 5120), (2048, 768, 768)], ids=str)  # (more than 1024 rows: no split-K, whose atomics add in no fixed order)
+def test_linear_with_an_sm_limit(lib, shape, limit):
+    """`kb_gemm_sm_limit(n)`: the persistent GEMMs run on at most n SMs (what the two-stream prefill of
+    the tensor-parallel decoder sets while a collective shares the GPU) and give the same bits."""
+    from kernl_b200.implementations.linear_layer import linear_layer
+
+    M, K, N = shape
+    g = torch.Generator().manual_seed(limit)
+    x, w, b = (torch.randn((M, K), generator=g).half(), (torch.randn((N, K), generator=g) * 0.05).half(),
+               torch.randn((N,), generator=g).half())
+    xc, wc, bc = _cuda(x, w, b)
+    full = linear_layer(xc, wc, bc, "relu")
+    try:
+        assert lib.kb_gemm_sm_limit(limit) == 0
+        limited = linear_layer(xc, wc, bc, "relu")
+    finally:
+        lib.kb_gemm_sm_limit(0)
+    assert lib.kb_gemm_sm_limit(-1) != 0
+    torch.cuda.synchronize()
+    assert torch.equal(full, limited)
+    O.assert_parity(limited, O.linear(x, w, b, "relu"), what=f"linear on {limit} SMs")
+
+
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16], ids=["fp16", "bf16"])
 @pytest.mark.parametrize("shape", [(1, 4096, 4096), (5, 520, 1000), (8, 11008, 4096), (9, 264, 17), (16, 8, 40), (13, 4096, 12288)], ids=str)
 def test_linear_few_rows(lib, shape, dtype):

@@ -63,6 +63,27 @@ def test_module_type_matching_and_remapping():
     assert [n.target for n in gm.graph.nodes if n.op == "call_module"] == ["fc2", "norm"]
 
 
+def test_gelu_modules_match_by_their_form():
+    """nn.GELU() is the erf form and nn.GELU(approximate="tanh") the tanh form: same module type,
+    different function, so each is fused into the linear with its own epilogue."""
+    from kernl_b200.optimizer import linear as L
+
+    class Two(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.a, self.b = torch.nn.Linear(8, 8), torch.nn.Linear(8, 8)
+            self.erf_form, self.tanh_form = torch.nn.GELU(), torch.nn.GELU(approximate="tanh")
+
+        def forward(self, x):
+            return self.tanh_form(self.b(self.erf_form(self.a(x))))
+
+    gm = torch.fx.symbolic_trace(Two())
+    L.replace_all_linear(gm)
+    calls = [(n.args[1].target, n.kwargs.get("activation")) for n in gm.graph.nodes
+             if n.op == "call_function" and n.target is L.linear_wrapper]
+    assert calls == [("a", "gelu"), ("b", "fast_gelu")], calls
+
+
 def test_literals_must_be_equal():
     gm = torch.fx.symbolic_trace(TwoLayer())
     assert len(replace_pattern(gm, lambda a: a / 4.0, lambda a: a * 0.25)) == 0

@@ -23,8 +23,9 @@ void kb_debug_split_tiles(int tiles);
  * tiles from a device-side queue, 2 = the same without the longest-batch-first tile order,
  * 0 = one CTA per query tile, -1 = dispatcher's choice. */
 void kb_debug_attention_persistent(int mode);
-/* 0 = large GEMMs stay on the one-CTA-per-tile kernel instead of CTA pairs on 256 x 256 tiles. */
-void kb_debug_linear_pair(int on);
+/* 0 = large GEMMs stay on the one-CTA-per-tile kernel instead of CTA pairs on 256-row tiles;
+ * 192 / 256 = CTA pairs with that tile width whatever the cost model says; 1 = dispatcher's choice. */
+void kb_debug_linear_pair(int mode);
 /* 0 = launch every kernel with plain stream ordering instead of programmatic dependent launch. */
 void kb_debug_pdl(int on);
 /* Limits (SM clock cycles) of the bounded device-side waits on the CURRENT device: waits inside one

@@ -168,7 +168,7 @@ void kb_debug_attention_persistent(int mode) {
     g_attn_sort_batches = mode == 2 ? 0 : 1;
 }
 void kb_debug_pdl(int on) { g_use_pdl = on ? 1 : 0; }
-void kb_debug_linear_pair(int on) { g_linear_pair = on ? 1 : 0; }
+void kb_debug_linear_pair(int mode) { g_linear_pair = (mode == 192 || mode == 256) ? mode : (mode ? 1 : 0); }
 void kb_debug_force_splits(int splits) { g_forced_splits = splits; }
 #ifdef KB_ATTN_TRACE
 // Tuning builds only: copies the persistent attention kernel's time stamps to the host.

@@ -191,39 +191,17 @@ __device__ __forceinline__ void epilogue_chunk(const float (&accv)[32], const T*
     }
 }
 
-// The arithmetic of epilogue_chunk without its stores: z = act(acc + bias) for one 32-column chunk.
-template <typename T>
-__device__ __forceinline__ void epilogue_values(const float (&accv)[32], const T* __restrict__ bias, int col0, int N,
-                                                int activation, float (&z)[32]) {
-    if (bias != nullptr) {
-        if (col0 + 32 <= N && (((uintptr_t)(bias + col0)) & 15) == 0) {
-#pragma unroll
-            for (int v = 0; v < 4; ++v) {
-                const uint4 bw = __ldg(reinterpret_cast<const uint4*>(bias + col0) + v);
-                const uint32_t w[4] = {bw.x, bw.y, bw.z, bw.w};
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const float2 bf = Elem<T>::unpack2(w[i]);
-                    z[v * 8 + 2 * i] = accv[v * 8 + 2 * i] + bf.x;
-                    z[v * 8 + 2 * i + 1] = accv[v * 8 + 2 * i + 1] + bf.y;
-                }
-            }
-        } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) z[j] = accv[j] + ((col0 + j < N) ? Elem<T>::to_f32(bias[col0 + j]) : 0.f);
-        }
-    } else {
-#pragma unroll
-        for (int j = 0; j < 32; ++j) z[j] = accv[j];
-    }
+// z = act(z) in place for NV values (an even count) of one output row.
+template <int NV>
+__device__ __forceinline__ void apply_activation(float (&z)[NV], int activation) {
     switch (activation) {
         case KB_ACT_TANH:
 #pragma unroll
-            for (int j = 0; j < 32; ++j) z[j] = act_tanh(z[j]);
+            for (int j = 0; j < NV; ++j) z[j] = act_tanh(z[j]);
             break;
         case KB_ACT_GELU:
 #pragma unroll
-            for (int j = 0; j < 32; j += 2) {
+            for (int j = 0; j < NV; j += 2) {
                 const float2 g = act_gelu2(make_float2(z[j], z[j + 1]));
                 z[j] = g.x;
                 z[j + 1] = g.y;
@@ -231,15 +209,15 @@ __device__ __forceinline__ void epilogue_values(const float (&accv)[32], const T
             break;
         case KB_ACT_FAST_GELU:
 #pragma unroll
-            for (int j = 0; j < 32; ++j) z[j] = act_fast_gelu(z[j]);
+            for (int j = 0; j < NV; ++j) z[j] = act_fast_gelu(z[j]);
             break;
         case KB_ACT_RELU:
 #pragma unroll
-            for (int j = 0; j < 32; ++j) z[j] = fmaxf(z[j], 0.0f);
+            for (int j = 0; j < NV; ++j) z[j] = fmaxf(z[j], 0.0f);
             break;
         case KB_ACT_SILU:
 #pragma unroll
-            for (int j = 0; j < 32; ++j) z[j] = act_silu(z[j]);
+            for (int j = 0; j < NV; ++j) z[j] = act_silu(z[j]);
             break;
         default: break;
     }

@@ -30,8 +30,8 @@
 
 namespace kb {
 
-constexpr int kPairBN = 256;          // columns of the pair's tile
-constexpr int kPairHalfN = 128;       // W rows staged by each CTA
+constexpr int kPairBN = 256;          // columns of the pair's widest tile (the kernel is also built for 192)
+constexpr int kPairHalfN = 128;       // W rows staged by each CTA at that width
 #ifndef KB_PAIR_STAGES
 #define KB_PAIR_STAGES 6
 #endif
@@ -77,8 +77,12 @@ __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
+// Arrive on a barrier of the pair's other CTA. CTA-scope release (the default): what the arrival
+// orders are this warp's tensor-memory reads, which tcgen05.wait::ld and the tcgen05 fence before it
+// have completed — no global data is handed over. A cluster-scope release also waits for the warp's
+// earlier global stores to be acknowledged, which showed as 3.3 stall cycles per issued instruction.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 // TMA tile load whose completion is counted on a barrier that may live in the pair's other CTA.
 __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int x, int y) {
@@ -130,12 +134,20 @@ __device__ long long g_gemm_trace[148 * 8 * 16];
 #define KB_GTRACE(tile, ev) do { } while (0)
 #endif
 
-template <typename T>
+// BN: columns of the pair's tile, 256 or 192. Each CTA stages BN / 2 rows of W per stage (the stage
+// keeps its 32 KB stride), the accumulators sit at tensor-memory columns 0 and 256 whatever BN, and an
+// epilogue warp owns BN / 4 columns. The narrower tile exists for problems of a few rounds: 384 tiles
+// of 256 columns on 74 pairs run 5.2 rounds as 6, 512 tiles of 192 columns run 6.9 rounds as 7.
+template <typename T, int BN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
 linear_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
                    const T* __restrict__ bias, T* __restrict__ y, T* __restrict__ act_inputs, int M, int N, int K,
                    int64_t y_row_stride, int activation) {
     constexpr int STAGES = kPairStages;
+    static_assert(BN == 256 || BN == 192, "tile width of the pair kernel");
+    constexpr int kHalfN = BN / 2;                     // W rows this CTA stages
+    constexpr int kStageTx = kPairABytes + kHalfN * kGemmBK * 2;  // bytes one CTA's copies put into a stage
+    constexpr int CW = BN / 4;                         // columns per epilogue warp
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * kPairStageBytes);
@@ -196,7 +208,7 @@ linear_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
     const uint32_t tmem_base = (skip == 0) ? *tmem_slot : 0u;
 
     const int num_m = (M + 2 * kGemmBM - 1) / (2 * kGemmBM);  // 256-row tiles
-    const int num_n = (N + kPairBN - 1) / kPairBN;
+    const int num_n = (N + BN - 1) / BN;
     const int num_tiles = num_m * num_n;
     const int num_k = (K + kGemmBK - 1) / kGemmBK;
 
@@ -210,11 +222,11 @@ linear_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
                 int m_idx, n_idx;
                 tile_coords(t, num_m, num_n, m_idx, n_idx);
                 const int row0 = m_idx * 2 * kGemmBM + (int)rank * kGemmBM;    // this CTA's rows of x
-                const int wrow0 = n_idx * kPairBN + (int)rank * kPairHalfN;    // this CTA's rows of W
+                const int wrow0 = n_idx * BN + (int)rank * kHalfN;    // this CTA's rows of W
                 for (int kb = 0; kb < num_k; ++kb) {
                     if (!mbar_wait(empty_bar(stage), phase ^ 1, abort_flag, 110)) { ok = false; break; }
                     // the leader's barrier counts the bytes of both CTAs' copies of this stage
-                    if (rank == 0) mbar_arrive_expect_tx(full_bar(stage), 2 * kPairStageBytes);
+                    if (rank == 0) mbar_arrive_expect_tx(full_bar(stage), 2 * kStageTx);
                     const uint32_t a_dst = smem_base + stage * kPairStageBytes;
                     const uint32_t leader_full = in_leader(full_bar(stage));
                     tma_load_2d_pair(a_dst, &tmap_x, leader_full, kb * kGemmBK, row0);
@@ -229,7 +241,7 @@ linear_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
     } else if (skip == 0 && warp == 1) {
         // ------------------------------------------------------------------ tcgen05 issuer (leader only)
         if (rank == 0 && elect_one()) {
-            constexpr uint32_t idesc = make_idesc_f16(Elem<T>::kIsBf16, 2 * kGemmBM, kPairBN, 0, 0);
+            constexpr uint32_t idesc = make_idesc_f16(Elem<T>::kIsBf16, 2 * kGemmBM, BN, 0, 0);
             int stage = 0;
             uint32_t phase = 0;
             int acc = 0;
@@ -264,7 +276,7 @@ linear_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
     } else if (skip == 0) {
         // ------------------------------------------------------------------ epilogue (both CTAs)
         const int q = warp & 3;                 // TMEM lane quadrant this warp may access
-        const int c_begin = ((warp - 2) >> 2) * 64;  // the warp's 64 columns of the tile
+        const int c_begin = ((warp - 2) >> 2) * CW;  // the warp's CW columns of the tile
         const uint32_t leader_tempty[2] = {in_leader(tempty_bar(0)), in_leader(tempty_bar(1))};
         // whole 16-byte pieces of y: plain activations, no pre-activation output, aligned rows
         const bool staged = activation != KB_ACT_SWIGLU && act_inputs == nullptr && (N & 7) == 0 && (y_row_stride & 7) == 0 &&
@@ -281,9 +293,9 @@ linear_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
             if (bias != nullptr && tile < num_tiles) {
                 int m_i, n_i;
                 tile_coords(tile, num_m, num_n, m_i, n_i);
-                const int c = n_i * kPairBN + c_begin + 2 * lane;
-                if (c < N) b2.x = Elem<T>::to_f32(bias[c]);
-                if (c + 1 < N) b2.y = Elem<T>::to_f32(bias[c + 1]);
+                const int c = n_i * BN + c_begin + 2 * lane;
+                if (2 * lane < CW && c < N) b2.x = Elem<T>::to_f32(bias[c]);
+                if (2 * lane < CW && c + 1 < N) b2.y = Elem<T>::to_f32(bias[c + 1]);
             }
             return b2;
         };
@@ -291,7 +303,7 @@ linear_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
         for (int t = pair; t < num_tiles && ok; t += num_pairs, ++ti) {
             int m_idx, n_idx;
             tile_coords(t, num_m, num_n, m_idx, n_idx);
-            const int n0 = n_idx * kPairBN;
+            const int n0 = n_idx * BN;
             // the next tile's bias is requested now and put into shared memory when this tile is done
             float2 bias_next = make_float2(0.f, 0.f);
             if (staged) bias_next = load_bias(t + num_pairs);
@@ -307,64 +319,75 @@ linear_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
                 // rows x 64 bytes per store instruction) instead of 32 rows x 16 bytes: a
                 // thread-per-row store touches 32 cache lines per instruction.
                 const int row_base = m_idx * 2 * kGemmBM + (int)rank * kGemmBM + q * 32;
-                // all 64 columns in one tensor-memory round trip; with them in registers the
+                // all CW columns in one tensor-memory round trip; with them in registers the
                 // accumulator goes back to the issuer at once. (Fetching the second half while the
                 // first is converted and stored was slower: the accumulator came back later.)
-                uint32_t r2[2][32];
-                tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * kPairBN + c_begin), r2[0]);
-                tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * kPairBN + c_begin + 32), r2[1]);
+                uint32_t r2[CW];
+                const uint32_t t_addr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * kPairBN + c_begin);
+                {
+                    uint32_t (&lo)[32] = *reinterpret_cast<uint32_t(*)[32]>(&r2[0]);
+                    tmem_ld_32x32(t_addr, lo);
+                    if (CW == 64) {
+                        uint32_t (&hi)[32] = *reinterpret_cast<uint32_t(*)[32]>(&r2[CW - 32]);
+                        tmem_ld_32x32(t_addr + 32, hi);
+                    } else {
+                        uint32_t (&hi)[16] = *reinterpret_cast<uint32_t(*)[16]>(&r2[CW - 16]);
+                        tmem_ld_32x16(t_addr + 32, hi);
+                    }
+                }
                 tmem_ld_wait();
                 tc_fence_before();
                 __syncwarp();  // (also: every lane's bias values are in bias_s)
                 if (lane == 0) mbar_arrive_cluster(leader_tempty[acc]);
                 if (warp == 2 && lane == 0) KB_GTRACE(ti, 8);
+                constexpr int kPieces = kPairPassCols / 8;     // 16-byte pieces per staged row
+                constexpr int kRowsPerStore = 32 / kPieces;  // rows one store instruction covers
 #pragma unroll
-                for (int hc = 0; hc < 2; ++hc) {
-                    if (n0 + c_begin + hc * 32 >= N) break;
-                    float z[32];
+                for (int ps = 0; ps < CW / kPairPassCols; ++ps) {
+                    const int pc0 = c_begin + ps * kPairPassCols;  // first column of the pass, inside the tile
+                    if (n0 + pc0 >= N) break;
+                    float z[kPairPassCols];
 #pragma unroll
-                    for (int v = 0; v < 8; ++v) {
-                        const float4 b4 = reinterpret_cast<const float4*>(bias_s)[hc * 8 + v];
-                        z[v * 4 + 0] = __uint_as_float(r2[hc][v * 4 + 0]) + b4.x;
-                        z[v * 4 + 1] = __uint_as_float(r2[hc][v * 4 + 1]) + b4.y;
-                        z[v * 4 + 2] = __uint_as_float(r2[hc][v * 4 + 2]) + b4.z;
-                        z[v * 4 + 3] = __uint_as_float(r2[hc][v * 4 + 3]) + b4.w;
+                    for (int v = 0; v < kPairPassCols / 4; ++v) {
+                        const float4 b4 = reinterpret_cast<const float4*>(bias_s)[ps * (kPairPassCols / 4) + v];
+                        z[v * 4 + 0] = __uint_as_float(r2[ps * kPairPassCols + v * 4 + 0]) + b4.x;
+                        z[v * 4 + 1] = __uint_as_float(r2[ps * kPairPassCols + v * 4 + 1]) + b4.y;
+                        z[v * 4 + 2] = __uint_as_float(r2[ps * kPairPassCols + v * 4 + 2]) + b4.z;
+                        z[v * 4 + 3] = __uint_as_float(r2[ps * kPairPassCols + v * 4 + 3]) + b4.w;
                     }
-                    epilogue_values<T>(z, nullptr, 0, N, activation, z);
-                    constexpr int kPieces = kPairPassCols / 8;     // 16-byte pieces per staged row
-                    constexpr int kRowsPerStore = 32 / kPieces;  // rows one store instruction covers
+                    apply_activation<kPairPassCols>(z, activation);
 #pragma unroll
-                    for (int ps = 0; ps < 32 / kPairPassCols; ++ps) {
-#pragma unroll
-                        for (int v = 0; v < kPieces; ++v) {
-                            const int e = ps * kPairPassCols + v * 8;
-                            uint4 o;
-                            o.x = Elem<T>::pack2(z[e + 0], z[e + 1]);
-                            o.y = Elem<T>::pack2(z[e + 2], z[e + 3]);
-                            o.z = Elem<T>::pack2(z[e + 4], z[e + 5]);
-                            o.w = Elem<T>::pack2(z[e + 6], z[e + 7]);
-                            *reinterpret_cast<uint4*>(mine + pair_stage_offset(lane, v)) = o;
-                        }
-                        if (warp == 2 && lane == 0 && hc == 0 && ps == 0) KB_GTRACE(ti, 9);
-                        __syncwarp();
-                        if (warp == 2 && lane == 0 && hc == 0 && ps == 0) KB_GTRACE(ti, 10);
-#pragma unroll
-                        for (int it = 0; it < 32 / kRowsPerStore; ++it) {
-                            const int rr = it * kRowsPerStore + lane / kPieces, pc = lane % kPieces;
-                            const uint4 o = *reinterpret_cast<const uint4*>(mine + pair_stage_offset(rr, pc));
-                            const int grow = row_base + rr, gcol = n0 + c_begin + hc * 32 + ps * kPairPassCols + pc * 8;
-                            if (grow < M && gcol < N) *reinterpret_cast<uint4*>(y + (int64_t)grow * y_row_stride + gcol) = o;
-                        }
-                        if (ps + 1 < 32 / kPairPassCols) __syncwarp();
+                    for (int v = 0; v < kPieces; ++v) {
+                        uint4 o;
+                        o.x = Elem<T>::pack2(z[v * 8 + 0], z[v * 8 + 1]);
+                        o.y = Elem<T>::pack2(z[v * 8 + 2], z[v * 8 + 3]);
+                        o.z = Elem<T>::pack2(z[v * 8 + 4], z[v * 8 + 5]);
+                        o.w = Elem<T>::pack2(z[v * 8 + 6], z[v * 8 + 7]);
+                        *reinterpret_cast<uint4*>(mine + pair_stage_offset(lane, v)) = o;
                     }
-                    if (warp == 2 && lane == 0 && hc == 0) KB_GTRACE(ti, 6);
+                    if (warp == 2 && lane == 0 && ps == 0) KB_GTRACE(ti, 9);
+                    __syncwarp();
+                    if (warp == 2 && lane == 0 && ps == 0) KB_GTRACE(ti, 10);
+#pragma unroll
+                    for (int it = 0; it < 32 / kRowsPerStore; ++it) {
+                        const int rr = it * kRowsPerStore + lane / kPieces, pc = lane % kPieces;
+                        const uint4 o = *reinterpret_cast<const uint4*>(mine + pair_stage_offset(rr, pc));
+                        const int grow = row_base + rr, gcol = n0 + pc0 + pc * 8;
+                        if (grow < M && gcol < N) *reinterpret_cast<uint4*>(y + (int64_t)grow * y_row_stride + gcol) = o;
+                    }
+                    if (warp == 2 && lane == 0 && ps == 0) KB_GTRACE(ti, 6);
                     __syncwarp();
                 }
                 reinterpret_cast<float2*>(bias_s)[lane] = bias_next;  // (all reads of this tile's values are behind the last __syncwarp)
             } else {
 #pragma unroll 1
-                for (int c0 = c_begin; c0 < c_begin + 64; c0 += 32) {
+                // (a 32-column chunk at a time: with 48 columns per warp, warps pair up on chunks — the
+                // even warp of a pair of column groups takes the chunk that straddles them)
+                for (int c0 = (c_begin / 32) * 32; c0 < c_begin + CW; c0 += 32) {
                     if (n0 + c0 >= N) break;
+                    if (c0 < c_begin || c0 + 32 > c_begin + CW) {
+                        if ((((warp - 2) >> 2) & 1) != 0) continue;  // the straddling chunk belongs to the even group
+                    }
                     uint32_t r[32];
                     tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * kPairBN + c0), r);
                     tmem_ld_wait();
@@ -395,7 +418,7 @@ linear_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
     }
 }
 
-static int g_linear_pair = 1;  // test hook (kb_debug_linear_pair): 0 = never use the pair kernel
+static int g_linear_pair = 1;  // test hook (kb_debug_linear_pair): 0 = never use the pair kernel, 192 / 256 = force that tile width
 
 // The pair kernel serves problems with at least one 256 x 256 tile per pair of SMs and no split-K.
 static bool linear_pair_applicable(const kb_linear_params& p) {
@@ -404,8 +427,23 @@ static bool linear_pair_applicable(const kb_linear_params& p) {
     return p.M >= 512 && p.N >= 256 && p.K >= 256 && tiles >= gemm_sms() / 2;
 }
 
-template <typename T>
-static int launch_linear_pair_t(const kb_linear_params& p, cudaStream_t stream) {
+// Tile width: rounds of tiles on the pairs x (columns of a tile + a fixed cost per tile, in columns).
+// 192 columns only where that is clearly cheaper (a launch of a few rounds whose last one is nearly
+// empty) and the epilogue can take its staged path (whole 16-byte pieces, no gated or pre-activation output).
+static int linear_pair_tile_width(const kb_linear_params& p, int pairs) {
+    if (g_linear_pair == 192 || g_linear_pair == 256) return g_linear_pair;
+    const bool staged = p.activation != KB_ACT_SWIGLU && p.act_inputs == nullptr && (p.N & 7) == 0 && (p.y_row_stride & 7) == 0 &&
+                        (((uintptr_t)p.y) & 15) == 0;
+    if (!staged) return 256;
+    auto cost = [&](int bn) {
+        const int64_t tiles = ((p.M + 255) / 256) * ((p.N + bn - 1) / bn);
+        return (double)((tiles + pairs - 1) / pairs) * (bn + 24);
+    };
+    return cost(192) < 0.95 * cost(256) ? 192 : 256;
+}
+
+template <typename T, int BN>
+static int launch_linear_pair_tb(const kb_linear_params& p, cudaStream_t stream) {
     CUtensorMap tmap_x, tmap_w;
     {
         const uint64_t dims[2] = {(uint64_t)p.K, (uint64_t)p.M};
@@ -418,7 +456,7 @@ static int launch_linear_pair_t(const kb_linear_params& p, cudaStream_t stream) 
     {
         const uint64_t dims[2] = {(uint64_t)p.K, (uint64_t)p.N};
         const uint64_t strides[2] = {0, (uint64_t)p.K * 2};
-        const uint32_t box[2] = {kGemmBK, kPairHalfN};
+        const uint32_t box[2] = {kGemmBK, BN / 2};
         int st = encode_tmap_16bit(&tmap_w, p.w, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B,
                                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
         if (st != KB_OK) return st;
@@ -439,24 +477,31 @@ static int launch_linear_pair_t(const kb_linear_params& p, cudaStream_t stream) 
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return KB_ERR_LAUNCH;
     if (max_pairs[dev] == 0) {
-        if (cudaFuncSetAttribute(linear_pair_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBytes) != cudaSuccess)
+        if (cudaFuncSetAttribute(linear_pair_kernel<T, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBytes) != cudaSuccess)
             return KB_ERR_LAUNCH;
         cfg.gridDim = dim3(2 * (unsigned)(sm_count() / 2));
         int n = 0;
-        if (cudaOccupancyMaxActiveClusters(&n, linear_pair_kernel<T>, &cfg) != cudaSuccess || n <= 0) {
+        if (cudaOccupancyMaxActiveClusters(&n, linear_pair_kernel<T, BN>, &cfg) != cudaSuccess || n <= 0) {
             cudaGetLastError();
             return KB_ERR_LAUNCH;
         }
         max_pairs[dev] = n < sm_count() / 2 ? n : sm_count() / 2;
     }
-    const int64_t tiles = ((p.M + 255) / 256) * ((p.N + kPairBN - 1) / kPairBN);
+    const int64_t tiles = ((p.M + 255) / 256) * ((p.N + BN - 1) / BN);
     int pairs = (int)(tiles < max_pairs[dev] ? tiles : max_pairs[dev]);
     if (pairs > gemm_sms() / 2) pairs = gemm_sms() / 2;  // a caller-set limit leaves SMs to a concurrent collective
     cfg.gridDim = dim3(2 * (unsigned)pairs);
-    if (cudaLaunchKernelEx(&cfg, linear_pair_kernel<T>, tmap_x, tmap_w, (const T*)p.bias, (T*)p.y, (T*)p.act_inputs, (int)p.M,
+    if (cudaLaunchKernelEx(&cfg, linear_pair_kernel<T, BN>, tmap_x, tmap_w, (const T*)p.bias, (T*)p.y, (T*)p.act_inputs, (int)p.M,
                            (int)p.N, (int)p.K, p.y_row_stride, p.activation) != cudaSuccess)
         return KB_ERR_LAUNCH;
     return cudaGetLastError() == cudaSuccess ? KB_OK : KB_ERR_LAUNCH;
+}
+
+template <typename T>
+static int launch_linear_pair_t(const kb_linear_params& p, cudaStream_t stream) {
+    const int pairs = gemm_sms() / 2;
+    if (linear_pair_tile_width(p, pairs > 0 ? pairs : 1) == 192) return launch_linear_pair_tb<T, 192>(p, stream);
+    return launch_linear_pair_tb<T, 256>(p, stream);
 }
 
 }  // namespace kb

@@ -76,7 +76,8 @@ def linear_layer(
     `interleave_gate_up`, result [M, N/2] = silu(gate) * up); `act_inputs`, if given, receives the
     pre-activation values. Returns [M, N], or [x.shape[0], -1, N] for 3-D x. fp32 inputs (tf32 in the
     reference) are not supported: fp16/bf16 only. `out` (an extension over the reference's
-    signature) lets the caller provide the [M, N] contiguous result buffer, e.g. a peer-mapped one.
+    signature) lets the caller provide the [M, N] result buffer (unit column stride, any row stride),
+    e.g. a peer-mapped one or a column slice of a wider tensor.
     """
     x, weight, bias = cast_if_autocast(x, weight, bias)
     x_ = x if x.ndim == 2 else x.flatten(0, 1)
@@ -108,7 +109,7 @@ def linear_layer(
         K += pad
     weight, bias = _aligned(weight), _aligned(bias)
     if out is not None:
-        assert out.shape == (M, n_out) and out.dtype == x.dtype and out.is_contiguous() and out.device == x.device
+        assert out.shape == (M, n_out) and out.dtype == x.dtype and out.stride(1) == 1 and out.device == x.device
         outputs = out
     else:
         outputs = torch.empty((M, n_out), device=x.device, dtype=x.dtype)

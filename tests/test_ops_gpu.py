@@ -572,9 +572,12 @@ def test_linear_every_tile_width(lib):
 @pytest.mark.parametrize("dtype,tol", [(torch.float16, 1e-2), (torch.bfloat16, 6e-2)], ids=["fp16", "bf16"])
 @pytest.mark.parametrize("activation", ["", "gelu", "swiglu"])
 @pytest.mark.parametrize("shape", [(2048, 512, 2560), (2000, 264, 2512), (513, 1024, 9488), (4096, 256, 1280)], ids=str)
-def test_linear_cta_pairs(lib, shape, activation, dtype, tol):
-    """Problems large enough for the CTA-pair kernel (256 x 256 tiles, `tcgen05.mma.cta_group::2`), with
-    ragged edges in every dimension, against the oracle and against the one-CTA-per-tile kernel."""
+@pytest.mark.parametrize("width", [256, 192])
+def test_linear_cta_pairs(lib, shape, activation, dtype, tol, width):
+    """Problems large enough for the CTA-pair kernel (256-row tiles of 256 or 192 columns,
+    `tcgen05.mma.cta_group::2`), with ragged edges in every dimension, against the oracle and against
+    the one-CTA-per-tile kernel. Gelu runs once with a pre-activation output (the epilogue's
+    thread-per-row path) and, in `test_linear_cta_pairs_staged_gelu`, once without."""
     from kernl_b200.implementations.linear_layer import linear_layer
 
     M, K, N = shape
@@ -584,8 +587,9 @@ def test_linear_cta_pairs(lib, shape, activation, dtype, tol):
     b = (torch.randn((N,), generator=g) * 0.1).to(dtype)
     xc, wc, bc = _cuda(x, w, b)
     pre = torch.empty((M, N), dtype=dtype, device="cuda") if activation == "gelu" else None
-    out = linear_layer(xc, wc, bc, activation, act_inputs=pre)
     try:
+        lib.kb_debug_linear_pair(width)
+        out = linear_layer(xc, wc, bc, activation, act_inputs=pre)
         lib.kb_debug_linear_pair(0)
         single = linear_layer(xc, wc, bc, activation)
     finally:
@@ -607,6 +611,30 @@ def test_linear_cta_pairs(lib, shape, activation, dtype, tol):
     assert rel_rms < (5e-4 if dtype == torch.float16 else 4e-3), rel_rms
     if pre is not None:
         O.assert_parity(pre, O.linear(x, w, b, ""), max_abs=tol, what="pre-activation output")
+
+
+@pytest.mark.parametrize("width", [256, 192, 1])
+@pytest.mark.parametrize("activation", ["gelu", "fast_gelu", "tanh", "silu"])
+@pytest.mark.parametrize("shape", [(8192, 768, 3072), (1000, 520, 1400)], ids=str)
+def test_linear_cta_pairs_staged_epilogue(lib, shape, activation, width):
+    """The pair kernel's staged epilogue (results through shared memory, sixteen warps) with every
+    activation and both tile widths (1 = the dispatcher's own choice), without bias as well."""
+    from kernl_b200.implementations.linear_layer import linear_layer
+
+    M, K, N = shape
+    g = torch.Generator().manual_seed(N)
+    x = torch.randn((M, K), generator=g).half()
+    w = (torch.randn((N, K), generator=g) * 0.05).half()
+    b = (torch.randn((N,), generator=g) * 0.5).half()
+    xc, wc, bc = _cuda(x, w, b)
+    try:
+        lib.kb_debug_linear_pair(width)
+        with_bias = linear_layer(xc, wc, bc, activation)
+        without = linear_layer(xc, wc, None, activation)
+    finally:
+        lib.kb_debug_linear_pair(1)
+    O.assert_parity(with_bias, O.linear(x, w, b, activation), what=f"{activation} with bias, width {width}")
+    O.assert_parity(without, O.linear(x, w, None, activation), what=f"{activation} without bias, width {width}")
 
 
 @pytest.mark.parametrize("limit", [100, 32, 3])

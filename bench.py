@@ -278,6 +278,10 @@ def run_ours(args):
         import torch.distributed as dist_mod
 
         dist = dist_mod
+        # The tensor-parallel prefill overlaps its all-reduces with the other half-batch's GEMMs,
+        # which leave 24 SMs free for them (LlamaTP.overlap_reserved_sms): the collective is told to
+        # stay within that many CTAs. Has to be set before the communicator exists.
+        os.environ.setdefault("NCCL_MAX_CTAS", "24")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
     from kernl_b200 import _lib, build
@@ -633,6 +637,10 @@ def run_bert(args):
         import torch.distributed as dist_mod
 
         dist = dist_mod
+        # The tensor-parallel prefill overlaps its all-reduces with the other half-batch's GEMMs,
+        # which leave 24 SMs free for them (LlamaTP.overlap_reserved_sms): the collective is told to
+        # stay within that many CTAs. Has to be set before the communicator exists.
+        os.environ.setdefault("NCCL_MAX_CTAS", "24")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     dev = torch.device("cuda", local_rank)
     torch.manual_seed(0)
@@ -732,6 +740,10 @@ def run_t5(args):
         import torch.distributed as dist_mod
 
         dist = dist_mod
+        # The tensor-parallel prefill overlaps its all-reduces with the other half-batch's GEMMs,
+        # which leave 24 SMs free for them (LlamaTP.overlap_reserved_sms): the collective is told to
+        # stay within that many CTAs. Has to be set before the communicator exists.
+        os.environ.setdefault("NCCL_MAX_CTAS", "24")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     dev = torch.device("cuda", local_rank)
     torch.manual_seed(0)
@@ -915,6 +927,10 @@ def run_llama(args):
         import torch.distributed as dist_mod
 
         dist = dist_mod
+        # The tensor-parallel prefill overlaps its all-reduces with the other half-batch's GEMMs,
+        # which leave 24 SMs free for them (LlamaTP.overlap_reserved_sms): the collective is told to
+        # stay within that many CTAs. Has to be set before the communicator exists.
+        os.environ.setdefault("NCCL_MAX_CTAS", "24")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     dev = torch.device("cuda", local_rank)
     kind = args.comm if world > 1 else "none"

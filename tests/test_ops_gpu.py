@@ -869,6 +869,31 @@ def test_norm_full_size_properties(lib):
     O.assert_parity(y[rows.cuda()], O.layer_norm(x[rows.cuda()].cpu(), one.cpu(), zero.cpu(), 1.6e-5))
 
 
+@pytest.mark.parametrize("rows,cols", [(16384, 768), (9001, 768), (40000, 256), (8200, 1000), (5000, 1024)])
+@pytest.mark.parametrize("rms", [False, True], ids=["layernorm", "rmsnorm"])
+@pytest.mark.parametrize("with_residual", [False, True], ids=["plain", "residual"])
+def test_norm_many_short_rows(lib, rows, cols, rms, with_residual):
+    """Many rows of at most 1024 columns (one warp per row, four rows per CTA): every row against the
+    oracle, ragged row counts included, with and without the fused residual add."""
+    from kernl_b200.implementations.layer_norm import layer_norm
+
+    g = torch.Generator().manual_seed(rows)
+    x = (1.5 * torch.randn((rows, cols), generator=g) + 0.3).half()
+    res = torch.randn((rows, cols), generator=g).half() if with_residual else None
+    w = (torch.rand((cols,), generator=g) + 0.5).half()
+    b = (torch.randn((cols,), generator=g) * 0.1).half()
+    xc, wc, bc = _cuda(x, w, b)
+    if with_residual:
+        y, s = layer_norm(xc, wc, None if rms else bc, 1e-5, use_rms_norm=rms, residual=res.cuda())
+        base = (x.float() + res.float()).half()
+        assert torch.equal(s.cpu(), base)
+    else:
+        y = layer_norm(xc, wc, None if rms else bc, 1e-5, use_rms_norm=rms)
+        base = x
+    expected = O.rms_norm(base, w, 1.6e-5) if rms else O.layer_norm(base, w, b, 1.6e-5)
+    O.assert_parity(y, expected, what=f"{rows} x {cols}")
+
+
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("shape", [(8, 4096), (3, 7, 768), (1, 8), (513, 6144)])
 @pytest.mark.parametrize("rms", [False, True])

@@ -264,6 +264,38 @@ def headline_traffic_bytes():
 
 
 
+def bind_to_gpu_numa_node(local_rank):
+    """Run this process on the CPUs next to its GPU, so that the pinned host buffers allocated
+    afterwards (first touch) and the copy threads sit on the GPU's own NUMA node. Returns what it
+    found: {"nodes": NUMA nodes of the host, "gpu_node": the GPU's node or -1, "bound": whether the
+    affinity was changed}. A host with one node (or without the sysfs entries) is left alone."""
+    info = {"nodes": 1, "gpu_node": -1, "bound": False}
+    try:
+        nodes = [d for d in os.listdir("/sys/devices/system/node") if d.startswith("node") and d[4:].isdigit()]
+        info["nodes"] = max(1, len(nodes))
+        import pynvml
+
+        pynvml.nvmlInit()
+        handle = pynvml.nvmlDeviceGetHandleByIndex(local_rank)
+        bus = pynvml.nvmlDeviceGetPciInfo(handle).busId
+        bus = bus.decode() if isinstance(bus, bytes) else bus
+        dev_dir = os.path.join("/sys/bus/pci/devices", bus[-12:].lower())  # 0000:1b:00.0
+        node = int(open(os.path.join(dev_dir, "numa_node")).read().strip())
+        info["gpu_node"] = node
+        if info["nodes"] > 1 and node >= 0:
+            cpus = set()
+            for part in open(os.path.join(dev_dir, "local_cpulist")).read().strip().split(","):
+                lo, _, hi = part.partition("-")
+                cpus.update(range(int(lo), int(hi or lo) + 1))
+            allowed = cpus & os.sched_getaffinity(0)
+            if allowed:
+                os.sched_setaffinity(0, allowed)
+                info["bound"] = True
+    except Exception:
+        pass
+    return info
+
+
 def run_ours(args):
     import torch
 
@@ -344,6 +376,7 @@ def run_ours(args):
     executed_fraction = visited / (len(sets) * WORKLOAD["B"] * WORKLOAD["S"])
 
     # ---------------- end to end through the public API with host buffers
+    numa = bind_to_gpu_numa_node(local_rank)
     hq, hk, hv, hm = (t.half().pin_memory() for t in (q32, k32, v32, mask32))
     hout = torch.empty(q.shape, dtype=torch.float16).pin_memory()
     dq, dk, dv, dm, do = (torch.empty_like(t, device=dev) for t in (hq, hk, hv, hm, hq))
@@ -476,6 +509,7 @@ def run_ours(args):
         "e2e": {"value": world * flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
                 "latency_ms": e2e_latency_ms,
+                "host_gbs_per_rank": (h2d + d2h) / (e2e_ms * 1e-3) / 1e9, "numa": numa,
                 "api": "kernl_b200.host_pipeline.HostAttentionPipeline (two-deep: copies in both directions overlap)"},
         "gpu_launches": steps,
         "clocks": clocks,

@@ -385,7 +385,15 @@ attention_persist_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
         }
         if (warp == 10 && lane < p.B) batch_order[rank] = lane;  // the scheduler warp keeps the table for the later tiles
         const int per_batch = p.H * p.num_pairs;
-        const int r0 = (int)blockIdx.x / per_batch, rem0 = (int)blockIdx.x % per_batch;
+        // A grid of two CTAs per SM: CTA c and CTA c + grid/2 usually share an SM (the block scheduler
+        // fills every SM once before it doubles up), so the second half takes its tiles in reverse —
+        // the SM that runs the longest tile also gets the shortest of the statically assigned ones,
+        // and the work per SM is even (8 + 3, 7 + 4, ... key blocks instead of 8 + 5, ..., 5 + 3).
+        // Only a heuristic for balance: any placement computes every tile exactly once.
+        const int half = (int)gridDim.x >> 1;
+        const int first_idx = ((gridDim.x & 1) == 0 && (int)blockIdx.x >= half) ? (int)gridDim.x - 1 - ((int)blockIdx.x - half)
+                                                                              : (int)blockIdx.x;
+        const int r0 = first_idx / per_batch, rem0 = first_idx % per_batch;
         const int b0 = __ffs((int)__ballot_sync(0xffffffffu, lane < p.B && rank == r0)) - 1;
         const uint32_t live0 = __shfl_sync(0xffffffffu, w, b0);
 #pragma unroll

@@ -287,15 +287,9 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-    // A wait that expired in an earlier CTA or launch leaves the status word set: do no work until
-    // the host has read (and cleared) it, so that one failure cannot cost a second per CTA.
-    {
-        __shared__ int s_skip;
-        if (threadIdx.x == 0) s_skip = *reinterpret_cast<volatile int*>(&g_device_status[0]);
-        __syncthreads();
-        if (s_skip != 0) return;
-    }
-
+    // Launched with programmatic dependent launch: the barriers and the descriptor prefetch touch no
+    // global memory and may run while the previous kernel of the stream drains (a few-row GEMM of a
+    // latency-bound graph is itself only a few microseconds long).
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(full_bar(s), 1);
@@ -308,13 +302,22 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
         *abort_flag = 0;
         fence_mbar_init();
     }
-    if (warp == 1) {
-        tmem_alloc(smem_u32(tmem_slot), Cfg::kTmemCols);
-        tmem_relinquish();
-    }
     if (warp == 0 && lane == 0) {
         tma_prefetch_desc(&tmap_x);
         tma_prefetch_desc(&tmap_w);
+    }
+    pdl_wait();
+    // A wait that expired in an earlier CTA or launch leaves the status word set: do no work until
+    // the host has read (and cleared) it, so that one failure cannot cost a second per CTA.
+    {
+        __shared__ int s_skip;
+        if (threadIdx.x == 0) s_skip = *reinterpret_cast<volatile int*>(&g_device_status[0]);
+        __syncthreads();
+        if (s_skip != 0) return;
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(tmem_slot), Cfg::kTmemCols);
+        tmem_relinquish();
     }
     tc_fence_before();
     __syncthreads();
@@ -446,7 +449,9 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
         }
     }
 
-    // Teardown: every role falls through to here, also after an abandoned wait.
+    // Teardown: every role falls through to here, also after an abandoned wait. This CTA takes no
+    // more work: a dependent launch may have the slots that free up.
+    pdl_launch_dependents();
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
@@ -461,6 +466,9 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 linear_splitk_finish_kernel(float* __restrict__ ws, const T* __restrict__ bias, T* __restrict__ y,
                             T* __restrict__ act_inputs, int M, int N, int64_t y_row_stride, int activation) {
+    // (no early trigger: what follows is often another GEMM, whose CTAs would sit on the SMs with all
+    // their registers and shared memory while this kernel's CTAs still look for room)
+    pdl_wait();
     const int nq = (N + 3) / 4;
     const int64_t total = (int64_t)M * nq;
     const bool vec4 = (N % 4) == 0;
@@ -507,6 +515,7 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 linear_splitk_finish_swiglu_kernel(float* __restrict__ ws, const T* __restrict__ bias, T* __restrict__ y, int M,
                                    int N, int64_t y_row_stride) {
+    pdl_wait();
     const int nq = N / 8;  // N / 2 output columns, four per thread
     const int64_t total = (int64_t)M * nq;
     const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -616,9 +625,21 @@ static int launch_linear_bn(const kb_linear_params& p, cudaStream_t stream, cons
     const int64_t items = num_tiles * plan.splits;
     const int grid = (int)(items < gemm_sms() ? items : gemm_sms());
     float* ws = reinterpret_cast<float*>(p.workspace);
-    linear_tc_kernel<T, BN><<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(
-        tmap_x, tmap_w, (const T*)p.bias, (T*)p.y, (T*)p.act_inputs, (int)p.M, (int)p.N, (int)p.K,
-        p.y_row_stride, p.activation, plan.splits, plan.kps, ws);
+    // Programmatic launch for the few-row problems of latency-bound graphs only: there the kernel
+    // before is small as well. Behind a kernel of thousands of CTAs, 148 early-resident GEMM CTAs
+    // (all of an SM's shared memory, most of its registers) would take the room its later waves need.
+    cudaError_t le;
+    if (p.M <= 1024)
+        le = launch_pdl(linear_tc_kernel<T, BN>, dim3((unsigned)grid), dim3(kGemmThreads), (size_t)Cfg::kSmemBytes, stream, tmap_x,
+                        tmap_w, (const T*)p.bias, (T*)p.y, (T*)p.act_inputs, (int)p.M, (int)p.N, (int)p.K, p.y_row_stride,
+                        p.activation, plan.splits, plan.kps, ws);
+    else {
+        linear_tc_kernel<T, BN><<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(
+            tmap_x, tmap_w, (const T*)p.bias, (T*)p.y, (T*)p.act_inputs, (int)p.M, (int)p.N, (int)p.K, p.y_row_stride,
+            p.activation, plan.splits, plan.kps, ws);
+        le = cudaSuccess;
+    }
+    if (le != cudaSuccess) return KB_ERR_LAUNCH;
     if (cudaGetLastError() != cudaSuccess) return KB_ERR_LAUNCH;
     if (plan.splits > 1) {
         const bool gated = p.activation == KB_ACT_SWIGLU;
@@ -626,11 +647,11 @@ static int launch_linear_bn(const kb_linear_params& p, cudaStream_t stream, cons
         int64_t blocks = (total + 255) / 256;
         if (blocks > (int64_t)sm_count() * 8) blocks = (int64_t)sm_count() * 8;
         if (gated)
-            linear_splitk_finish_swiglu_kernel<T><<<(unsigned)blocks, 256, 0, stream>>>(
-                ws, (const T*)p.bias, (T*)p.y, (int)p.M, (int)p.N, p.y_row_stride);
+            launch_pdl(linear_splitk_finish_swiglu_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, stream, ws, (const T*)p.bias,
+                       (T*)p.y, (int)p.M, (int)p.N, p.y_row_stride);
         else
-            linear_splitk_finish_kernel<T><<<(unsigned)blocks, 256, 0, stream>>>(
-                ws, (const T*)p.bias, (T*)p.y, (T*)p.act_inputs, (int)p.M, (int)p.N, p.y_row_stride, p.activation);
+            launch_pdl(linear_splitk_finish_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, stream, ws, (const T*)p.bias, (T*)p.y,
+                       (T*)p.act_inputs, (int)p.M, (int)p.N, p.y_row_stride, p.activation);
         if (cudaGetLastError() != cudaSuccess) return KB_ERR_LAUNCH;
     }
     return KB_OK;

@@ -50,6 +50,27 @@ def attention_wrapper(
 torch.fx.wrap("attention_wrapper")
 
 
+def additive_mask(attention_mask: Optional[torch.Tensor], like: torch.Tensor) -> Optional[torch.Tensor]:
+    """A boolean keep-mask (scaled_dot_product_attention convention) as an additive 0 / -inf mask of
+    `like`'s dtype; any other mask unchanged. A graph node of its own, so that the layers of a model —
+    which all receive the same mask — share ONE conversion instead of three small kernels each."""
+    if attention_mask is not None and attention_mask.dtype == torch.bool:
+        # Broadcast dimensions (stride 0: the usual [B, 1, M, N] expansion of a [B, N] padding mask)
+        # stay broadcast: only one copy of them is converted, and the kernel then sees a per-sequence
+        # row mask (staged once per tile, padded key blocks skipped) instead of a dense [M, N] mask.
+        shape = attention_mask.shape
+        core = attention_mask
+        for dim in range(core.dim()):
+            if core.stride(dim) == 0 and core.size(dim) > 1:
+                core = core.narrow(dim, 0, 1)
+        additive = torch.zeros(core.shape, dtype=like.dtype, device=core.device).masked_fill_(~core, float("-inf"))
+        return additive.expand(shape)
+    return attention_mask
+
+
+torch.fx.wrap("additive_mask")
+
+
 def fuse_attention_pattern_1(gm: torch.fx.GraphModule, is_causal: bool):
     """softmax(q·kᵀ / 8.0 + mask)·v (reference: optimizer/attention.py:61-76)."""
 
@@ -108,6 +129,7 @@ def fuse_attention_sdpa(gm: torch.fx.GraphModule, is_causal: bool):
     target stack predates the op); literals (scale, is_causal) are read from the node."""
     targets = (torch.nn.functional.scaled_dot_product_attention, torch._C._nn.scaled_dot_product_attention)
     changed = False
+    converted = {}  # mask node -> its additive form, built before the first attention that uses it
     for node in list(gm.graph.nodes):
         if node.op != "call_function" or node.target not in targets:
             continue
@@ -124,6 +146,10 @@ def fuse_attention_sdpa(gm: torch.fx.GraphModule, is_causal: bool):
         if isinstance(scale, torch.fx.Node):
             continue
         with gm.graph.inserting_before(node):
+            if isinstance(mask, torch.fx.Node):
+                if mask not in converted:
+                    converted[mask] = gm.graph.call_function(additive_mask, (mask, q))
+                mask = converted[mask]
             out = gm.graph.call_function(torch.empty_like, (q,))
             if scale is None:
                 head_dim = gm.graph.call_method("size", (q, -1))

@@ -357,6 +357,7 @@ def test_bert_graph_is_fully_rewritten():
     model = BertModel(BertConfig(num_hidden_layers=2)).eval()
     c = _rewritten_ops(model, input_ids=torch.randint(0, 1000, (1, 16)), attention_mask=torch.ones(1, 16, dtype=torch.long))
     assert c["attention_wrapper"] == 2
+    assert c["additive_mask"] == 1  # both layers read ONE converted mask
     assert c["linear_wrapper"] == 2 * 4 + 1  # qkv (one stacked linear), o, ffn up (+GELU), ffn down per layer; pooler (+tanh)
     assert c["layer_norm_residual_wrapper"] == 1 + 2 * 2 and c["layer_norm_wrapper"] == 0  # every LayerNorm follows an add
     assert c["module:Linear"] == 0 and c["module:LayerNorm"] == 0 and c["module:Dropout"] == 0

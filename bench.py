@@ -312,8 +312,10 @@ def run_ours(args):
         dist = dist_mod
         # The tensor-parallel prefill overlaps its all-reduces with the other half-batch's GEMMs,
         # which leave 24 SMs free for them (LlamaTP.overlap_reserved_sms): the collective is told to
-        # stay within that many CTAs. Has to be set before the communicator exists.
-        os.environ.setdefault("NCCL_MAX_CTAS", "24")
+        # stay within that many CTAs (from four ranks on; two ranks measured better uncapped). Has to be
+        # set before the communicator exists.
+        if world >= 4:
+            os.environ.setdefault("NCCL_MAX_CTAS", "24")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
     from kernl_b200 import _lib, build
@@ -673,8 +675,10 @@ def run_bert(args):
         dist = dist_mod
         # The tensor-parallel prefill overlaps its all-reduces with the other half-batch's GEMMs,
         # which leave 24 SMs free for them (LlamaTP.overlap_reserved_sms): the collective is told to
-        # stay within that many CTAs. Has to be set before the communicator exists.
-        os.environ.setdefault("NCCL_MAX_CTAS", "24")
+        # stay within that many CTAs (from four ranks on; two ranks measured better uncapped). Has to be
+        # set before the communicator exists.
+        if world >= 4:
+            os.environ.setdefault("NCCL_MAX_CTAS", "24")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     dev = torch.device("cuda", local_rank)
     torch.manual_seed(0)
@@ -776,8 +780,10 @@ def run_t5(args):
         dist = dist_mod
         # The tensor-parallel prefill overlaps its all-reduces with the other half-batch's GEMMs,
         # which leave 24 SMs free for them (LlamaTP.overlap_reserved_sms): the collective is told to
-        # stay within that many CTAs. Has to be set before the communicator exists.
-        os.environ.setdefault("NCCL_MAX_CTAS", "24")
+        # stay within that many CTAs (from four ranks on; two ranks measured better uncapped). Has to be
+        # set before the communicator exists.
+        if world >= 4:
+            os.environ.setdefault("NCCL_MAX_CTAS", "24")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     dev = torch.device("cuda", local_rank)
     torch.manual_seed(0)
@@ -963,8 +969,10 @@ def run_llama(args):
         dist = dist_mod
         # The tensor-parallel prefill overlaps its all-reduces with the other half-batch's GEMMs,
         # which leave 24 SMs free for them (LlamaTP.overlap_reserved_sms): the collective is told to
-        # stay within that many CTAs. Has to be set before the communicator exists.
-        os.environ.setdefault("NCCL_MAX_CTAS", "24")
+        # stay within that many CTAs (from four ranks on; two ranks measured better uncapped). Has to be
+        # set before the communicator exists.
+        if world >= 4:
+            os.environ.setdefault("NCCL_MAX_CTAS", "24")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     dev = torch.device("cuda", local_rank)
     kind = args.comm if world > 1 else "none"

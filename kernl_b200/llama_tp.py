@@ -168,7 +168,7 @@ class LlamaTP:
         # to run finds no SM until the other half's GEMM has ended. 24 goes with a collective limited to
         # 24 CTAs (NCCL_MAX_CTAS=24, set by the caller before the process group exists); measured at
         # TP = 4, prefill 8 x 2048: 66.7 ms with nothing reserved, 61.5 ms with 24 / 24. Two ranks exchange
-        # less and do better with 16 SMs and an uncapped collective (101.7 against 106.0 ms)
+        # less; there the setting did not move the result (101.7-106.0 ms with 16 or 24 SMs)
         self.overlap_reserved_sms = int(os.environ.get("KERNL_B200_TP_RESERVED_SMS", "16" if world <= 2 else "24"))
         self._streams = None
         self._prefill_out = {}

@@ -27,14 +27,31 @@ def _nvcc() -> str:
     return exe
 
 
-def is_stale() -> bool:
-    if not os.path.exists(LIB_PATH):
-        return True
-    built = os.path.getmtime(LIB_PATH)
+HASH_PATH = LIB_PATH + ".srchash"
+
+
+def _source_hash() -> str:
+    """Hash of everything the library is built from (sources, headers, flags)."""
+    import hashlib
+
+    h = hashlib.sha256(" ".join(NVCC_FLAGS).encode())
     deps = [os.path.join(CSRC, f) for f in SOURCES + HEADERS]
-    deps.append(os.path.join(HERE, "..", "include", "kernl_b200.h"))
-    deps.append(os.path.join(HERE, "..", "include", "kernl_b200_debug.h"))
-    return any(os.path.getmtime(d) > built for d in deps)
+    deps += [os.path.join(HERE, "..", "include", "kernl_b200.h"), os.path.join(HERE, "..", "include", "kernl_b200_debug.h")]
+    for d in deps:
+        with open(d, "rb") as f:
+            h.update(f.read())
+    return h.hexdigest()
+
+
+def is_stale() -> bool:
+    """The library is rebuilt when it is missing or was built from other sources. By content, not by
+    modification time: a copy of the tree to another machine keeps the contents, not the times."""
+    if not os.path.exists(LIB_PATH) or not os.path.exists(HASH_PATH):
+        return True
+    try:
+        return open(HASH_PATH).read().strip() != _source_hash()
+    except OSError:
+        return True
 
 
 def build(force: bool = False, verbose: bool = False) -> str:
@@ -50,6 +67,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
         raise RuntimeError("nvcc failed:\n" + proc.stdout + proc.stderr)
     if verbose:
         print(proc.stderr)
+    with open(HASH_PATH, "w") as f:
+        f.write(_source_hash() + "\n")
     return LIB_PATH
 
 
